@@ -1,0 +1,52 @@
+"""Shared test configuration: the ``gpu`` marker, import paths and helpers."""
+
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+GOLDEN_DIR = os.path.join(ROOT, "tests", "golden")
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (B200)")
+
+
+def pytest_collection_modifyitems(config, items):
+    if torch.cuda.is_available():
+        return
+    skip = pytest.mark.skip(reason="no CUDA device")
+    for item in items:
+        if "gpu" in item.keywords:
+            item.add_marker(skip)
+
+
+def load_golden(name: str) -> dict:
+    with np.load(os.path.join(GOLDEN_DIR, name + ".npz")) as z:
+        return {k: torch.from_numpy(z[k].copy()) for k in z.files}
+
+
+def rel_rms(actual: torch.Tensor, expected: torch.Tensor) -> float:
+    a, e = actual.detach().double().cpu(), expected.detach().double().cpu()
+    return float((a - e).square().mean().sqrt() / (e.square().mean().sqrt() + 1e-30))
+
+
+def assert_close(actual, expected, rtol, name=""):
+    """``|a-e| <= rtol * (|e| + rms(e))``: the stated relative tolerance, with
+    the tensor's RMS as the floor for entries near zero."""
+    a, e = actual.detach().double().cpu(), expected.detach().double().cpu()
+    assert a.shape == e.shape, f"{name}: shape {tuple(a.shape)} vs {tuple(e.shape)}"
+    assert torch.isfinite(a).all(), f"{name}: non-finite values"
+    rms = e.square().mean().sqrt()
+    bad = (a - e).abs() > rtol * (e.abs() + rms) + 1e-30
+    if bad.any():
+        worst = ((a - e).abs() / (e.abs() + rms + 1e-30)).max()
+        raise AssertionError(
+            f"{name}: {int(bad.sum())}/{a.numel()} entries beyond rtol={rtol}; "
+            f"worst {float(worst):.3e}; rel-rms {rel_rms(a, e):.3e}")

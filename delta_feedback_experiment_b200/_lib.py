@@ -1,0 +1,153 @@
+"""ctypes binding of ``libpkda_b200.so`` (declared in ``include/pkda_b200.h``).
+
+The library is the product; this module only loads it, mirrors its argument
+structs and turns status codes into ``RuntimeError``.  There is no fallback: if
+the shared library is missing or does not load, every operator raises.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Optional
+
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libpkda_b200.so")
+
+PKDA_BF16, PKDA_F32 = 0, 1
+ABI_VERSION = 1
+CHUNK = 64
+
+
+class Problem(C.Structure):
+    _fields_ = [
+        ("n_seqs", C.c_int32), ("seq_len", C.c_int32), ("total_tokens", C.c_int32),
+        ("heads", C.c_int32), ("head_dim", C.c_int32), ("dtype", C.c_int32),
+        ("scale", C.c_float), ("squash_x", C.c_float), ("squash_eps", C.c_float),
+        ("reserved0", C.c_int32),
+        ("cu_seqlens", C.c_void_p),
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("g", C.c_void_p),
+        ("g_atk", C.c_void_p), ("beta_atk", C.c_void_p), ("beta", C.c_void_p),
+        ("A_log", C.c_void_p), ("dt_bias", C.c_void_p), ("log_atk_scale", C.c_void_p),
+        ("initial_state", C.c_void_p), ("initial_A_state", C.c_void_p),
+    ]
+
+
+class RecurrentArgs(C.Structure):
+    _fields_ = [("p", Problem), ("o", C.c_void_p), ("final_state", C.c_void_p),
+                ("final_A_state", C.c_void_p)]
+
+
+class ChunkFwdArgs(C.Structure):
+    _fields_ = [
+        ("p", Problem), ("o", C.c_void_p), ("final_state", C.c_void_p),
+        ("final_A_state", C.c_void_p),
+        ("Aqk", C.c_void_p), ("Akk", C.c_void_p), ("k_precond", C.c_void_p),
+        ("ac_atk", C.c_void_p), ("a_atk", C.c_void_p), ("sa_atk", C.c_void_p),
+        ("w", C.c_void_p), ("kg", C.c_void_p), ("v_new", C.c_void_p), ("h", C.c_void_p),
+        ("qg", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
+
+
+class ChunkBwdArgs(C.Structure):
+    _fields_ = [
+        ("p", Problem), ("d_o", C.c_void_p), ("d_final_state", C.c_void_p),
+        ("recompute", C.c_int32), ("reserved1", C.c_int32),
+        ("Aqk", C.c_void_p), ("Akk", C.c_void_p), ("k_precond", C.c_void_p),
+        ("ac_atk", C.c_void_p), ("a_atk", C.c_void_p), ("sa_atk", C.c_void_p),
+        ("w", C.c_void_p), ("kg", C.c_void_p), ("v_new", C.c_void_p), ("h", C.c_void_p),
+        ("qg", C.c_void_p),
+        ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p), ("dg", C.c_void_p),
+        ("dg_atk", C.c_void_p), ("dbeta_atk", C.c_void_p), ("dbeta", C.c_void_p),
+        ("dA_log", C.c_void_p), ("ddt_bias", C.c_void_p), ("dlog_atk_scale", C.c_void_p),
+        ("d_initial_state", C.c_void_p), ("d_initial_A_state", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
+
+
+EXPORTS = (
+    "pkda_recurrent_fwd", "pkda_chunk_fwd_workspace_bytes", "pkda_chunk_fwd",
+    "pkda_chunk_bwd_workspace_bytes", "pkda_chunk_bwd", "pkda_abi_version",
+    "pkda_status_string", "pkda_sizeof_problem", "pkda_sizeof_recurrent_args",
+    "pkda_sizeof_chunk_fwd_args", "pkda_sizeof_chunk_bwd_args", "pkda_last_launch_count",
+)
+
+_lib: Optional[C.CDLL] = None
+_load_error: Optional[str] = None
+
+
+def _configure(lib: C.CDLL) -> None:
+    lib.pkda_recurrent_fwd.argtypes = [C.POINTER(RecurrentArgs), C.c_void_p]
+    lib.pkda_recurrent_fwd.restype = C.c_int
+    lib.pkda_chunk_fwd.argtypes = [C.POINTER(ChunkFwdArgs), C.c_void_p]
+    lib.pkda_chunk_fwd.restype = C.c_int
+    lib.pkda_chunk_bwd.argtypes = [C.POINTER(ChunkBwdArgs), C.c_void_p]
+    lib.pkda_chunk_bwd.restype = C.c_int
+    for name in ("pkda_chunk_fwd_workspace_bytes", "pkda_chunk_bwd_workspace_bytes"):
+        getattr(lib, name).argtypes = [C.POINTER(Problem)]
+        getattr(lib, name).restype = C.c_size_t
+    lib.pkda_abi_version.restype = C.c_int
+    lib.pkda_status_string.argtypes = [C.c_int]
+    lib.pkda_status_string.restype = C.c_char_p
+    for name in ("pkda_sizeof_problem", "pkda_sizeof_recurrent_args",
+                 "pkda_sizeof_chunk_fwd_args", "pkda_sizeof_chunk_bwd_args"):
+        getattr(lib, name).restype = C.c_size_t
+    lib.pkda_last_launch_count.restype = C.c_int
+
+
+def load() -> C.CDLL:
+    """Loads the shared library once; raises ``RuntimeError`` if that fails."""
+    global _lib, _load_error
+    if _lib is not None:
+        return _lib
+    if _load_error is not None:
+        raise RuntimeError(_load_error)
+    try:
+        if not os.path.exists(LIB_PATH):
+            raise OSError(f"{LIB_PATH} has not been built "
+                          "(python -m delta_feedback_experiment_b200.build)")
+        lib = C.CDLL(LIB_PATH)
+        _configure(lib)
+        if lib.pkda_abi_version() != ABI_VERSION:
+            raise OSError("libpkda_b200.so ABI version mismatch")
+        sizes = ((lib.pkda_sizeof_problem(), Problem),
+                 (lib.pkda_sizeof_recurrent_args(), RecurrentArgs),
+                 (lib.pkda_sizeof_chunk_fwd_args(), ChunkFwdArgs),
+                 (lib.pkda_sizeof_chunk_bwd_args(), ChunkBwdArgs))
+        for size, struct in sizes:
+            if size != C.sizeof(struct):
+                raise OSError(f"struct layout mismatch for {struct.__name__}")
+    except OSError as exc:
+        _load_error = f"PKDA CUDA library unavailable: {exc}"
+        raise RuntimeError(_load_error) from exc
+    _lib = lib
+    return lib
+
+
+def available() -> bool:
+    try:
+        load()
+        return True
+    except RuntimeError:
+        return False
+
+
+def check(status: int, what: str) -> None:
+    if status != 0:
+        msg = load().pkda_status_string(status).decode()
+        raise RuntimeError(f"{what} failed: {msg} (status {status})")
+
+
+def ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def current_stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def last_launch_count() -> int:
+    return int(load().pkda_last_launch_count())

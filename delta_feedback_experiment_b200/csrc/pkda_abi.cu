@@ -1,0 +1,89 @@
+// extern "C" surface of libpkda_b200.so (declared in include/pkda_b200.h).
+#include "pkda_launch.h"
+
+namespace pkda {
+
+static thread_local int g_launches = 0;
+void note_launch() { ++g_launches; }
+void reset_launch_count() { g_launches = 0; }
+
+int check_problem(const pkda_problem& p) {
+  if (p.n_seqs < 0 || p.total_tokens < 0 || p.heads <= 0 || p.head_dim <= 0) return PKDA_ERR_SHAPE;
+  if (!p.cu_seqlens && (p.seq_len < 0 || (long long)p.n_seqs * p.seq_len != p.total_tokens))
+    return PKDA_ERR_SHAPE;
+  if (p.n_seqs == 0 || p.total_tokens == 0) return PKDA_OK;
+  if (!p.q || !p.k || !p.v || !p.g || !p.g_atk || !p.beta_atk || !p.beta || !p.A_log || !p.dt_bias ||
+      !p.log_atk_scale)
+    return PKDA_ERR_NULL;
+  const void* ptrs[] = {p.q, p.k, p.v, p.g, p.initial_state};
+  for (const void* x : ptrs)
+    if (x && (reinterpret_cast<uintptr_t>(x) & 15)) return PKDA_ERR_ALIGN;
+  if (p.dtype != PKDA_BF16 && p.dtype != PKDA_F32) return PKDA_ERR_DTYPE;
+  return PKDA_OK;
+}
+
+Geo make_geo(const pkda_problem& p, const int* chunk_offsets) {
+  Geo g;
+  g.n_seqs = p.n_seqs;
+  g.seq_len = p.cu_seqlens ? 0 : p.seq_len;
+  g.total_tokens = p.total_tokens;
+  g.heads = p.heads;
+  g.chunks_per_seq = p.cu_seqlens ? 0 : (p.seq_len + kChunk - 1) / kChunk;
+  g.total_chunks = chunk_bound(p);
+  g.cu_seqlens = p.cu_seqlens;
+  g.chunk_offsets = p.cu_seqlens ? chunk_offsets : nullptr;
+  return g;
+}
+
+}  // namespace pkda
+
+extern "C" {
+
+int pkda_recurrent_fwd(const pkda_recurrent_args* args, void* cuda_stream) {
+  if (!args) return PKDA_ERR_NULL;
+  pkda::reset_launch_count();
+  return pkda::recurrent_fwd(args, static_cast<cudaStream_t>(cuda_stream));
+}
+
+size_t pkda_chunk_fwd_workspace_bytes(const pkda_problem* p) {
+  return p ? pkda::chunk_fwd_workspace(*p) : 0;
+}
+
+int pkda_chunk_fwd(const pkda_chunk_fwd_args* args, void* cuda_stream) {
+  if (!args) return PKDA_ERR_NULL;
+  pkda::reset_launch_count();
+  return pkda::chunk_fwd(args, static_cast<cudaStream_t>(cuda_stream));
+}
+
+size_t pkda_chunk_bwd_workspace_bytes(const pkda_problem* p) {
+  return p ? pkda::chunk_bwd_workspace(*p) : 0;
+}
+
+int pkda_chunk_bwd(const pkda_chunk_bwd_args* args, void* cuda_stream) {
+  if (!args) return PKDA_ERR_NULL;
+  pkda::reset_launch_count();
+  return pkda::chunk_bwd(args, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int pkda_abi_version(void) { return PKDA_ABI_VERSION; }
+
+const char* pkda_status_string(int status) {
+  switch (status) {
+    case PKDA_OK: return "ok";
+    case PKDA_ERR_NULL: return "a required pointer is NULL";
+    case PKDA_ERR_SHAPE: return "unsupported geometry";
+    case PKDA_ERR_DTYPE: return "unsupported activation dtype";
+    case PKDA_ERR_WORKSPACE: return "workspace missing or too small";
+    case PKDA_ERR_LAUNCH: return "kernel launch failed";
+    case PKDA_ERR_ALIGN: return "pointer not 16-byte aligned";
+    default: return "unknown status";
+  }
+}
+
+size_t pkda_sizeof_problem(void) { return sizeof(pkda_problem); }
+size_t pkda_sizeof_recurrent_args(void) { return sizeof(pkda_recurrent_args); }
+size_t pkda_sizeof_chunk_fwd_args(void) { return sizeof(pkda_chunk_fwd_args); }
+size_t pkda_sizeof_chunk_bwd_args(void) { return sizeof(pkda_chunk_bwd_args); }
+int pkda_last_launch_count(void) { return pkda::g_launches; }
+
+}  // extern "C"

@@ -1,0 +1,105 @@
+// Pieces shared by the chunked forward and backward kernels (D = 128, chunk 64).
+#pragma once
+
+#include "pkda_common.cuh"
+#include "pkda_launch.h"
+
+namespace pkda {
+
+constexpr int kD = 128;                       // head width handled by the chunked kernels
+constexpr int kLdD = kD + kPad;               // smem row stride of a [*][128] bf16 tile
+constexpr int kLdC = kChunk + kPad;           // smem row stride of a [*][64] bf16 tile
+constexpr int kTileBytes = kChunk * kLdD * 2; // one [64][128] bf16 tile
+
+// Level `lvl` (a power of two < 64) pairs row i (bit lvl set) with row j (bit
+// lvl clear) of the same 2*lvl block.
+__device__ __forceinline__ bool level_pair_ok(int i, int j, int lvl) {
+  return (((i ^ j) & ~(2 * lvl - 1)) == 0) && (i & lvl) && !(j & lvl);
+}
+
+// Builds the gated operands of one level from the log2-domain cumulative decay
+// sG [64][128]: rows with bit lvl set get X * 2^(G_r - G_ref) (into sXq from sQ
+// and sXk from sK), the others get Y * 2^(G_ref - G_r) (into sY from sKt), where
+// ref is the first row of the upper half of the row's 2*lvl block.  Rows of the
+// other kind are left untouched (their products are masked out).  Null
+// destinations are skipped.
+__device__ __forceinline__ void stage_level(bf16* sXq, bf16* sXk, bf16* sY, const bf16* sQ, const bf16* sK,
+                                            const bf16* sKt, const float* sG, int lvl, int tid, int nthreads) {
+  for (int idx = tid; idx < kChunk * kD / 2; idx += nthreads) {
+    const int r = idx >> 6, c2 = (idx & 63) << 1;
+    const int ref = (r & ~(2 * lvl - 1)) + lvl;
+    const float2 Gr = *reinterpret_cast<const float2*>(sG + r * kD + c2);
+    const float2 Gf = *reinterpret_cast<const float2*>(sG + ref * kD + c2);
+    if (r & lvl) {
+      const float f0 = exp2f(Gr.x - Gf.x), f1 = exp2f(Gr.y - Gf.y);
+      if (sXq) {
+        const float2 x = unpack_bf16(*reinterpret_cast<const uint32_t*>(sQ + r * kLdD + c2));
+        *reinterpret_cast<uint32_t*>(sXq + r * kLdD + c2) = pack_bf16(x.x * f0, x.y * f1);
+      }
+      if (sXk) {
+        const float2 x = unpack_bf16(*reinterpret_cast<const uint32_t*>(sK + r * kLdD + c2));
+        *reinterpret_cast<uint32_t*>(sXk + r * kLdD + c2) = pack_bf16(x.x * f0, x.y * f1);
+      }
+    } else if (sY) {
+      const float f0 = exp2f(Gf.x - Gr.x), f1 = exp2f(Gf.y - Gr.y);
+      const float2 x = unpack_bf16(*reinterpret_cast<const uint32_t*>(sKt + r * kLdD + c2));
+      *reinterpret_cast<uint32_t*>(sY + r * kLdD + c2) = pack_bf16(x.x * f0, x.y * f1);
+    }
+  }
+}
+
+// T = (I + L)^-1 for a 64 x 64 strictly lower triangular L (fp32, row stride ld),
+// 256 threads.  Diagonal 16 x 16 blocks by forward substitution (one thread per
+// column), then block rows 1..3: T_IJ = -T_II * sum_{J<=M<I} L_IM T_MJ.
+// sY2 is a [16][64] fp32 scratch.  Ends with a __syncthreads().
+__device__ __forceinline__ void unit_lower_inverse_64(const float* sL, float* sT, float* sY2, int ld, int tid) {
+  if (tid < 64) {
+    const int blk = tid >> 4, col = tid & 15;
+    const float* Lb = sL + (16 * blk) * ld + 16 * blk;
+    float x[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float s = (i == col) ? 1.f : 0.f;
+#pragma unroll
+      for (int m = 0; m < i; ++m) s -= Lb[i * ld + m] * x[m];
+      x[i] = s;
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) sT[(16 * blk + i) * ld + 16 * blk + col] = x[i];
+  } else {
+    for (int e = tid - 64; e < 6 * 256; e += 192) {
+      const int b = e >> 8, r = (e >> 4) & 15, c = e & 15;
+      // upper blocks (I,J), J > I: (0,1) (0,2) (0,3) (1,2) (1,3) (2,3)
+      const int I = b < 3 ? 0 : (b < 5 ? 1 : 2);
+      const int J = b < 3 ? b + 1 : (b < 5 ? b - 1 : 3);
+      sT[(16 * I + r) * ld + 16 * J + c] = 0.f;
+    }
+  }
+  __syncthreads();
+  const int r = tid >> 4, cc = tid & 15;
+#pragma unroll 1
+  for (int I = 1; I < 4; ++I) {
+    for (int J = 0; J < I; ++J) {
+      float s = 0.f;
+      for (int m = 16 * J; m < 16 * I; ++m) s += sL[(16 * I + r) * ld + m] * sT[m * ld + 16 * J + cc];
+      sY2[r * 64 + 16 * J + cc] = s;
+    }
+    __syncthreads();
+    for (int J = 0; J < I; ++J) {
+      float t = 0.f;
+#pragma unroll
+      for (int m = 0; m < 16; ++m) t -= sT[(16 * I + r) * ld + 16 * I + m] * sY2[m * 64 + 16 * J + cc];
+      sT[(16 * I + r) * ld + 16 * J + cc] = t;
+    }
+    __syncthreads();
+  }
+}
+
+// Host-side pieces defined in pkda_chunk_fwd.cu and reused by the backward.
+int check_chunk_problem(const pkda_problem& p);
+int run_prologue(const pkda_problem& p, int* chunk_offsets, float* beta_c, Geo* geo, cudaStream_t st);
+int run_forward_stages(const pkda_problem& p, const Geo& geo, const float* beta_c, bf16* u_ws, bf16* Aqk,
+                       bf16* Akk, bf16* kt, float* gc, const float* a_start, bf16* w, bf16* kg, bf16* v_new,
+                       bf16* h, bf16* qg, float* ST, bool recompute, cudaStream_t st);
+
+}  // namespace pkda

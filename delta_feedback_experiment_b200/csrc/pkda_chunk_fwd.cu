@@ -1,0 +1,703 @@
+// Chunked PKDA forward for D = 128, chunk 64, bf16 activations.
+//
+// Pipeline (one launch each, all on the caller's stream):
+//   offsets   packed input only: cumulative chunk counts per sequence
+//   pack_beta beta -> fp32 [chunks][H][64], zero for rows past a sequence end
+//   atk_local chunk-local preconditioner accumulation (from A = 0) and decay sums
+//   atk_carry sequential over a sequence's chunks: A at every chunk start
+//   intra     per chunk: log-decay cumsum, write keys, gated pair products
+//             M (k x kt) and P (q x kt) by a binary hierarchy of reference rows,
+//             Tm = (I + tril(M) diag(beta))^-1, W = Tm (k*Gam), U = Tm v,
+//             kg = kt * exp(G_last - G), qg = scale q * Gam
+//   scan      sequential over chunks, V split across CTAs: h_n, E = U - W h_n,
+//             S <- Gam_last * S + kg^T (beta E)
+//   out       per chunk: o = qg h_n + P (beta E)
+// With per-channel decay exp(G_i - G_j) cannot be factored as exp(G_i)exp(-G_j)
+// (overflow after a few tokens); level L of the hierarchy pairs rows whose index
+// has bit L set with rows of the same 2L-block whose bit L is clear, both
+// expressed relative to the first row of the upper half, so every factor is <= 1.
+#include "pkda_chunk.cuh"
+
+namespace pkda {
+
+// ------------------------------------------------------------------ small kernels
+__global__ void pkda_chunk_offsets_kernel(const int* cu, int n_seqs, int* offs) {
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    int acc = 0;
+    offs[0] = 0;
+    for (int n = 0; n < n_seqs; ++n) {
+      acc += (cu[n + 1] - cu[n] + kChunk - 1) / kChunk;
+      offs[n + 1] = acc;
+    }
+  }
+}
+
+__global__ void pkda_pack_beta_kernel(Geo geo, const bf16* beta, float* beta_c) {
+  int n, tok0, valid;
+  if (!chunk_lookup(geo, blockIdx.x, n, tok0, valid)) return;
+  const int H = geo.heads;
+  for (int i = threadIdx.x; i < H * kChunk; i += blockDim.x) {
+    int h = i / kChunk, r = i - h * kChunk;
+    float b = r < valid ? to_f(beta[(size_t)(tok0 + r) * H + h]) : 0.f;
+    beta_c[((size_t)blockIdx.x * H + h) * kChunk + r] = b;
+  }
+}
+
+// Chunk-local preconditioner scan from A = 0: loc[c] = sum_j (prod_{m>j} d_m) bP_j k_j[c]^2
+// and the chunk's summed log-decay.  grid (chunks, H), 128 threads (one per channel).
+__global__ void __launch_bounds__(kD)
+pkda_atk_local_kernel(Geo geo, const bf16* k, const float* g_atk, const bf16* beta_atk,
+                      float* ac_local, float* sa) {
+  int n, tok0, valid;
+  if (!chunk_lookup(geo, blockIdx.x, n, tok0, valid)) return;
+  const int h = blockIdx.y, H = geo.heads, c = threadIdx.x;
+  float A = 0.f, gsum = 0.f;
+  for (int r0 = 0; r0 < valid; r0 += 8) {
+    float kc[8], gp[8], bp[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int r = min(r0 + j, valid - 1);
+      const size_t s = (size_t)(tok0 + r) * H + h;
+      kc[j] = to_f(k[s * kD + c]);
+      gp[j] = g_atk[s];
+      bp[j] = to_f(beta_atk[s]);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (r0 + j < valid) {
+        A = __expf(gp[j]) * A + bp[j] * kc[j] * kc[j];
+        gsum += gp[j];
+      }
+    }
+  }
+  ac_local[((size_t)blockIdx.x * H + h) * kD + c] = A;
+  if (c == 0) sa[(size_t)blockIdx.x * H + h] = gsum;
+}
+
+// Sequential carry over the chunks of one (sequence, head): A at each chunk start.
+__global__ void __launch_bounds__(kD)
+pkda_atk_carry_kernel(Geo geo, const float* ac_local, const float* sa, const float* A0,
+                      float* a_start, float* AT) {
+  const int n = blockIdx.x, h = blockIdx.y, H = geo.heads, c = threadIdx.x;
+  const SeqInfo sq = seq_info(geo, n);
+  float A = A0 ? A0[((size_t)n * H + h) * kD + c] : 0.f;
+  for (int i = 0; i < sq.nchunks; ++i) {
+    const size_t ch = (size_t)(sq.chunk0 + i) * H + h;
+    a_start[ch * kD + c] = A;
+    A = __expf(sa[ch]) * A + ac_local[ch * kD + c];
+  }
+  if (AT) AT[((size_t)n * H + h) * kD + c] = A;
+}
+
+// ------------------------------------------------------------------ intra-chunk kernel
+struct IntraParams {
+  Geo geo;
+  const bf16 *q, *k, *v, *g;
+  const float* g_atk;
+  const bf16* beta_atk;
+  const float *A_log, *dt_bias, *log_atk_scale;
+  const float* beta_c;
+  const float* a_start;
+  bf16 *Aqk, *Akk, *kt;
+  float* gc;  // [chunks][H][D] exp of the chunk's total log-decay
+  bf16 *w, *u, *kg, *qg;
+  float scale, ln_x, eps;
+};
+
+namespace intra {
+constexpr int kThreads = 256;
+constexpr int oQ = 0;
+constexpr int oK = oQ + kTileBytes;
+constexpr int oKt = oK + kTileBytes;
+constexpr int oG = oKt + kTileBytes;             // fp32 [64][128]
+constexpr int oStage = oG + kChunk * kD * 4;     // 3 bf16 tiles; aliased later
+constexpr int oTmb = oStage + 3 * kTileBytes;    // bf16 [64][72]
+constexpr int oSmall = oTmb + kChunk * kLdC * 2; // beta[64], pd[64], bp[64]
+constexpr int kSmem = oSmall + 3 * kChunk * 4;
+// aliases inside the staging area
+constexpr int kLdL = 65;
+constexpr int oL = oStage;
+constexpr int oT = oL + kChunk * kLdL * 4;
+constexpr int oY2 = oT + kChunk * kLdL * 4;       // fp32 [16][64]
+static_assert(oY2 + 16 * 64 * 4 <= oTmb, "inverse scratch must fit in the staging area");
+}  // namespace intra
+
+// kRecompute: rebuild w,u,kg,qg only (backward's lean mode); the products, the
+// write keys and the decay totals already exist and are left untouched.
+template <bool kRecompute>
+__global__ void __launch_bounds__(intra::kThreads, 1)
+pkda_intra_fwd_kernel(const IntraParams p) {
+  using namespace intra;
+  extern __shared__ __align__(128) unsigned char smem[];
+  bf16* sQ = reinterpret_cast<bf16*>(smem + oQ);
+  bf16* sK = reinterpret_cast<bf16*>(smem + oK);
+  bf16* sKt = reinterpret_cast<bf16*>(smem + oKt);
+  float* sG = reinterpret_cast<float*>(smem + oG);
+  bf16* sXq = reinterpret_cast<bf16*>(smem + oStage);
+  bf16* sXk = sXq + kChunk * kLdD;
+  bf16* sY = sXk + kChunk * kLdD;
+  bf16* sTmb = reinterpret_cast<bf16*>(smem + oTmb);
+  float* sBeta = reinterpret_cast<float*>(smem + oSmall);
+  float* sPd = sBeta + kChunk;
+  float* sBp = sPd + kChunk;
+  float* sL = reinterpret_cast<float*>(smem + oL);
+  float* sT = reinterpret_cast<float*>(smem + oT);
+  float* sY2 = reinterpret_cast<float*>(smem + oY2);
+
+  int n, tok0, valid;
+  if (!chunk_lookup(p.geo, blockIdx.x, n, tok0, valid)) return;
+  const int h = blockIdx.y, H = p.geo.heads;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const size_t chh = (size_t)blockIdx.x * H + h;
+  const size_t row0 = ((size_t)tok0 * H + h) * kD;  // element offset of (tok0, h, 0)
+  const long gld = (long)H * kD;
+
+  // ---- 1. tiles and per-row scalars
+  tile_load_async(sQ, kLdD, p.q + row0, gld, kChunk, kD, valid, kThreads);
+  tile_load_async(sK, kLdD, p.k + row0, gld, kChunk, kD, valid, kThreads);
+  if (kRecompute) tile_load_async(sKt, kLdD, p.kt + row0, gld, kChunk, kD, valid, kThreads);
+  cp_async_commit();
+  if (tid < kChunk) {
+    const bool ok = tid < valid;
+    const size_t s = (size_t)(tok0 + tid) * H + h;
+    sBeta[tid] = p.beta_c[chh * kChunk + tid];
+    sPd[tid] = ok ? __expf(p.g_atk[s]) : 1.f;
+    sBp[tid] = ok ? to_f(p.beta_atk[s]) : 0.f;
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+
+  // ---- 2. per-channel sequential passes: log2-domain decay cumsum | write keys
+  if (tid < kD) {
+    const int c = tid;
+    const float ea = __expf(p.A_log[h]) * kLog2e;
+    const float bias = p.dt_bias[h * kD + c];
+    float G = 0.f;
+    for (int r0 = 0; r0 < kChunk; r0 += 8) {
+      float raw[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        raw[j] = (r0 + j < valid) ? to_f(p.g[row0 + (size_t)(r0 + j) * gld + c]) : 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (r0 + j < valid) G -= ea * softplus_fast(raw[j] + bias);
+        sG[(r0 + j) * kD + c] = G;
+      }
+    }
+  } else if (!kRecompute) {
+    const int c = tid - kD;
+    float A = p.a_start[chh * kD + c];
+    const float centre = p.log_atk_scale[h];
+    for (int r = 0; r < kChunk; ++r) {
+      const float kc = to_f(sK[r * kLdD + c]);
+      A = sPd[r] * A + sBp[r] * kc * kc;
+      const float dev = __logf(A + p.eps) - centre;
+      const float f = __expf(-p.ln_x * __fdividef(dev, 1.f + fabsf(dev)));
+      const bf16 kt = __float2bfloat16(kc * f);
+      sKt[r * kLdD + c] = kt;
+      if (r < valid) p.kt[row0 + (size_t)r * gld + c] = kt;
+    }
+  }
+  __syncthreads();
+
+  // ---- 3. gated pair products, level by level.  Warp (mat, I): mat 0 = M (rows k),
+  // mat 1 = P (rows q); I = 16-row block; acc[J] covers column block J.
+  const int mat = warp >> 2, I = warp & 3;
+  const int gq = lane >> 2, tq = lane & 3;
+  float acc[4][2][4];
+#pragma unroll
+  for (int a = 0; a < 4; ++a)
+#pragma unroll
+    for (int b = 0; b < 2; ++b)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[a][b][e] = 0.f;
+
+#pragma unroll 1
+  for (int lvl = 32; lvl >= 1; lvl >>= 1) {
+    stage_level(sXq, sXk, sY, sQ, sK, sKt, sG, lvl, tid, kThreads);
+    __syncthreads();
+    const bf16* X = mat ? sXq : sXk;
+#pragma unroll
+    for (int J = 0; J < 4; ++J) {
+      bool use;
+      if (lvl == 32) use = (I >= 2) && (J < 2);
+      else if (lvl == 16) use = (I & 1) && (J == I - 1);
+      else use = (J == I);
+      if (use) {  // warp-uniform
+        float tmp[1][2][4];
+        zero_acc(tmp);
+        warp_gemm<1, 2, false, false>(tmp, X, kLdD, 16 * I, sY, kLdD, 16 * J, 0, kD);
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int i = 16 * I + gq + ((e >> 1) << 3);
+            const int j = 16 * J + 8 * nt + 2 * tq + (e & 1);
+            if (level_pair_ok(i, j, lvl)) acc[J][nt][e] += tmp[0][nt][e];
+          }
+      }
+    }
+    __syncthreads();
+  }
+  if (mat == 1) {  // diagonal of P: ungated q_i . kt_i
+    float tmp[1][2][4];
+    zero_acc(tmp);
+    warp_gemm<1, 2, false, false>(tmp, sQ, kLdD, 16 * I, sKt, kLdD, 16 * I, 0, kD);
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = 16 * I + gq + ((e >> 1) << 3);
+        const int j = 16 * I + 8 * nt + 2 * tq + (e & 1);
+        if (i == j) acc[I][nt][e] += tmp[0][nt][e];
+      }
+  }
+
+  // ---- 4. P -> global (scaled, lower triangle incl. diagonal); L = tril(M,-1) diag(beta) -> smem
+#pragma unroll
+  for (int J = 0; J < 4; ++J)
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int i = 16 * I + gq + 8 * half;
+        const int j = 16 * J + 8 * nt + 2 * tq;
+        const float a0 = acc[J][nt][2 * half], a1 = acc[J][nt][2 * half + 1];
+        if (mat == 1) {
+          if (!kRecompute && i < valid) {
+            const float p0 = (j <= i) ? a0 * p.scale : 0.f;
+            const float p1 = (j + 1 <= i) ? a1 * p.scale : 0.f;
+            *reinterpret_cast<uint32_t*>(p.Aqk + ((size_t)(tok0 + i) * H + h) * kChunk + j) = pack_bf16(p0, p1);
+          }
+        } else {
+          sL[i * kLdL + j] = (j < i) ? a0 * sBeta[j] : 0.f;
+          sL[i * kLdL + j + 1] = (j + 1 < i) ? a1 * sBeta[j + 1] : 0.f;
+        }
+      }
+  __syncthreads();
+
+  // ---- 5. T = (I + L)^-1 in fp32
+  unit_lower_inverse_64(sL, sT, sY2, kLdL, tid);
+  // (ends with a __syncthreads)
+  for (int i = tid; i < kChunk * kChunk / 2; i += kThreads) {
+    const int r = i >> 5, c2 = (i & 31) << 1;
+    const uint32_t pk = pack_bf16(sT[r * kLdL + c2], sT[r * kLdL + c2 + 1]);
+    *reinterpret_cast<uint32_t*>(sTmb + r * kLdC + c2) = pk;
+    if (!kRecompute && r < valid)
+      *reinterpret_cast<uint32_t*>(p.Akk + ((size_t)(tok0 + r) * H + h) * kChunk + c2) = pk;
+  }
+  __syncthreads();
+
+  // ---- 6. decayed operands: Kd -> smem; qg, kg, gc -> global; V tile -> smem
+  bf16* sKd = sXq;
+  bf16* sV = sXk;
+  tile_load_async(sV, kLdD, p.v + row0, gld, kChunk, kD, valid, kThreads);
+  cp_async_commit();
+  for (int i = tid; i < kChunk * kD / 2; i += kThreads) {
+    const int r = i >> 6, c2 = (i & 63) << 1;
+    const float2 G = *reinterpret_cast<const float2*>(sG + r * kD + c2);
+    const float2 Gl = *reinterpret_cast<const float2*>(sG + (kChunk - 1) * kD + c2);
+    const float e0 = exp2f(G.x), e1 = exp2f(G.y);
+    const float2 kk = unpack_bf16(*reinterpret_cast<const uint32_t*>(sK + r * kLdD + c2));
+    *reinterpret_cast<uint32_t*>(sKd + r * kLdD + c2) = pack_bf16(kk.x * e0, kk.y * e1);
+    if (r < valid) {
+      const float2 qq = unpack_bf16(*reinterpret_cast<const uint32_t*>(sQ + r * kLdD + c2));
+      const float2 kt = unpack_bf16(*reinterpret_cast<const uint32_t*>(sKt + r * kLdD + c2));
+      const size_t off = row0 + (size_t)r * gld + c2;
+      *reinterpret_cast<uint32_t*>(p.qg + off) = pack_bf16(qq.x * e0 * p.scale, qq.y * e1 * p.scale);
+      *reinterpret_cast<uint32_t*>(p.kg + off) =
+          pack_bf16(kt.x * exp2f(Gl.x - G.x), kt.y * exp2f(Gl.y - G.y));
+    }
+    if (!kRecompute && r == kChunk - 1) {
+      p.gc[chh * kD + c2] = e0;
+      p.gc[chh * kD + c2 + 1] = e1;
+    }
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+
+  // ---- 7. W = Tm Kd, U = Tm V   (warp: matrix = warp>>2, rows 16*(warp&3), all 128 columns)
+  {
+    float acc2[1][16][4];
+    zero_acc(acc2);
+    warp_gemm<1, 16, false, true>(acc2, sTmb, kLdC, 16 * I, mat ? sV : sKd, kLdD, 0, 0, 16 * (I + 1));
+    bf16* dst = mat ? p.u : p.w;
+#pragma unroll
+    for (int nt = 0; nt < 16; ++nt)
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int i = 16 * I + gq + 8 * half;
+        if (i < valid)
+          *reinterpret_cast<uint32_t*>(dst + row0 + (size_t)i * gld + 8 * nt + 2 * tq) =
+              pack_bf16(acc2[0][nt][2 * half], acc2[0][nt][2 * half + 1]);
+      }
+  }
+}
+
+// ------------------------------------------------------------------ forward state scan
+struct ScanParams {
+  Geo geo;
+  const bf16 *w, *u, *kg;
+  const float *beta_c, *gc;
+  const float* S0;
+  bf16 *h, *v_new;
+  float* ST;
+};
+
+namespace scan {
+constexpr int kThreads = 128;
+template <int VB> struct L {
+  static constexpr int ldv = VB + kPad;
+  static constexpr int oW = 0;
+  static constexpr int oKg = oW + kTileBytes;
+  static constexpr int oU = oKg + kTileBytes;            // bf16 [64][ldv]
+  static constexpr int oBeta = oU + kChunk * ldv * 2;    // f32 [64]
+  static constexpr int oGc = oBeta + kChunk * 4;         // f32 [128]
+  static constexpr int kStage = oGc + kD * 4;
+  static constexpr int oH = 2 * kStage;                  // bf16 [128][ldv]
+  static constexpr int oF = oH + kD * ldv * 2;           // bf16 [64][ldv]
+  static constexpr int kSmem = oF + kChunk * ldv * 2;
+};
+}  // namespace scan
+
+template <int VB, bool kRecompute>
+__global__ void __launch_bounds__(scan::kThreads)
+pkda_scan_fwd_kernel(const ScanParams p) {
+  using Lay = scan::L<VB>;
+  constexpr int ldv = Lay::ldv, NT = VB / 8;
+  extern __shared__ __align__(128) unsigned char smem[];
+  const int VS = kD / VB;
+  const int vs = blockIdx.x % VS;
+  const int nh = blockIdx.x / VS;
+  const int n = nh / p.geo.heads, h = nh - n * p.geo.heads, H = p.geo.heads;
+  const SeqInfo sq = seq_info(p.geo, n);
+  if (sq.nchunks == 0) return;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int gq = lane >> 2, tq = lane & 3;
+  const int v0 = vs * VB;
+  const long gld = (long)H * kD;
+  bf16* sH = reinterpret_cast<bf16*>(smem + Lay::oH);
+  bf16* sF = reinterpret_cast<bf16*>(smem + Lay::oF);
+
+  auto prefetch = [&](int i) {
+    unsigned char* st = smem + (i & 1) * Lay::kStage;
+    const int tok0 = sq.bos + i * kChunk;
+    const int valid = min(kChunk, sq.len - i * kChunk);
+    const size_t row0 = ((size_t)tok0 * H + h) * kD;
+    const size_t chh = (size_t)(sq.chunk0 + i) * H + h;
+    tile_load_async(reinterpret_cast<bf16*>(st + Lay::oW), kLdD, p.w + row0, gld, kChunk, kD, valid, scan::kThreads);
+    tile_load_async(reinterpret_cast<bf16*>(st + Lay::oKg), kLdD, p.kg + row0, gld, kChunk, kD, valid, scan::kThreads);
+    tile_load_async(reinterpret_cast<bf16*>(st + Lay::oU), ldv, p.u + row0 + v0, gld, kChunk, VB, valid, scan::kThreads);
+    if (tid < 16) cp_async16(st + Lay::oBeta + tid * 16, p.beta_c + chh * kChunk + tid * 4, true);
+    else if (tid < 48) cp_async16(st + Lay::oGc + (tid - 16) * 16, p.gc + chh * kD + (tid - 16) * 4, true);
+  };
+
+  // state rows [32*warp, +32) x VB columns, fp32 fragments
+  float S[2][NT][4];
+  const size_t sbase = ((size_t)n * H + h) * kD * kD;
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int r = 32 * warp + 16 * mt + gq + 8 * half, c = v0 + 8 * nt + 2 * tq;
+        float2 s2 = make_float2(0.f, 0.f);
+        if (p.S0) s2 = *reinterpret_cast<const float2*>(p.S0 + sbase + (size_t)r * kD + c);
+        S[mt][nt][2 * half] = s2.x;
+        S[mt][nt][2 * half + 1] = s2.y;
+      }
+
+  prefetch(0);
+  cp_async_commit();
+  for (int i = 0; i < sq.nchunks; ++i) {
+    if (i + 1 < sq.nchunks) prefetch(i + 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    unsigned char* st = smem + (i & 1) * Lay::kStage;
+    const bf16* sW = reinterpret_cast<const bf16*>(st + Lay::oW);
+    const bf16* sKg = reinterpret_cast<const bf16*>(st + Lay::oKg);
+    const bf16* sU = reinterpret_cast<const bf16*>(st + Lay::oU);
+    const float* sBeta = reinterpret_cast<const float*>(st + Lay::oBeta);
+    const float* sGc = reinterpret_cast<const float*>(st + Lay::oGc);
+    const int tok0 = sq.bos + i * kChunk;
+    const int valid = min(kChunk, sq.len - i * kChunk);
+    const size_t chh = (size_t)(sq.chunk0 + i) * H + h;
+
+    // a. chunk-entry state -> bf16 operand tile (and the saved chunk states)
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int r = 32 * warp + 16 * mt + gq + 8 * half, c = 8 * nt + 2 * tq;
+          *reinterpret_cast<uint32_t*>(sH + r * ldv + c) = pack_bf16(S[mt][nt][2 * half], S[mt][nt][2 * half + 1]);
+        }
+    __syncthreads();  // sH complete; stage i landed for every thread
+    {
+      constexpr int cpr = VB / 8;
+      for (int j = tid; j < kD * cpr; j += scan::kThreads) {
+        const int r = j / cpr, c = (j - r * cpr) * 8;
+        *reinterpret_cast<uint4*>(p.h + (chh * kD + r) * kD + v0 + c) =
+            *reinterpret_cast<const uint4*>(sH + r * ldv + c);
+      }
+    }
+    // b. E = U - W h ; F = beta * E
+    {
+      float e[1][NT][4];
+      zero_acc(e);
+      warp_gemm<1, NT, false, true>(e, sW, kLdD, 16 * warp, sH, ldv, 0, 0, kD);
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int r = 16 * warp + gq + 8 * half, c = 8 * nt + 2 * tq;
+          const float2 uu = unpack_bf16(*reinterpret_cast<const uint32_t*>(sU + r * ldv + c));
+          const uint32_t ek = pack_bf16(uu.x - e[0][nt][2 * half], uu.y - e[0][nt][2 * half + 1]);
+          if (r < valid)
+            *reinterpret_cast<uint32_t*>(p.v_new + ((size_t)(tok0 + r) * H + h) * kD + v0 + c) = ek;
+          const float2 er = unpack_bf16(ek);
+          const float b = sBeta[r];
+          *reinterpret_cast<uint32_t*>(sF + r * ldv + c) = pack_bf16(b * er.x, b * er.y);
+        }
+    }
+    __syncthreads();
+    // c. S <- Gam_last * S + kg^T F
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const float gcv = sGc[32 * warp + 16 * mt + gq + 8 * half];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          S[mt][nt][2 * half] *= gcv;
+          S[mt][nt][2 * half + 1] *= gcv;
+        }
+      }
+    warp_gemm<2, NT, true, true>(S, sKg, kLdD, 32 * warp, sF, ldv, 0, 0, kChunk);
+    __syncthreads();  // everyone done with stage i and sF before they are refilled
+  }
+  cp_async_wait<0>();
+  if (!kRecompute && p.ST) {
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int r = 32 * warp + 16 * mt + gq + 8 * half, c = v0 + 8 * nt + 2 * tq;
+          *reinterpret_cast<float2*>(p.ST + sbase + (size_t)r * kD + c) =
+              make_float2(S[mt][nt][2 * half], S[mt][nt][2 * half + 1]);
+        }
+  }
+}
+
+// ------------------------------------------------------------------ output kernel
+struct OutParams {
+  Geo geo;
+  const bf16 *qg, *h, *Aqk, *v_new;
+  const float* beta_c;
+  bf16* o;
+};
+
+namespace outk {
+constexpr int kThreads = 256;
+constexpr int oQg = 0;
+constexpr int oH = oQg + kTileBytes;              // bf16 [128][136]
+constexpr int oP = oH + kD * kLdD * 2;            // bf16 [64][72]
+constexpr int oF = oP + kChunk * kLdC * 2;        // bf16 [64][136]
+constexpr int kSmem = oF + kTileBytes;
+}  // namespace outk
+
+__global__ void __launch_bounds__(outk::kThreads)
+pkda_out_fwd_kernel(const OutParams p) {
+  using namespace outk;
+  extern __shared__ __align__(128) unsigned char smem[];
+  bf16* sQg = reinterpret_cast<bf16*>(smem + oQg);
+  bf16* sH = reinterpret_cast<bf16*>(smem + oH);
+  bf16* sP = reinterpret_cast<bf16*>(smem + oP);
+  bf16* sF = reinterpret_cast<bf16*>(smem + oF);
+  int n, tok0, valid;
+  if (!chunk_lookup(p.geo, blockIdx.x, n, tok0, valid)) return;
+  const int h = blockIdx.y, H = p.geo.heads;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int gq = lane >> 2, tq = lane & 3;
+  const size_t chh = (size_t)blockIdx.x * H + h;
+  const size_t row0 = ((size_t)tok0 * H + h) * kD;
+  const long gld = (long)H * kD;
+
+  tile_load_async(sQg, kLdD, p.qg + row0, gld, kChunk, kD, valid, kThreads);
+  tile_load_async(sH, kLdD, p.h + chh * kD * kD, kD, kD, kD, kD, kThreads);
+  tile_load_async(sP, kLdC, p.Aqk + ((size_t)tok0 * H + h) * kChunk, (long)H * kChunk, kChunk, kChunk, valid, kThreads);
+  cp_async_commit();
+  // F = beta * E (E read from global, rounded exactly as the scan rounded it)
+  for (int i = tid; i < kChunk * kD / 8; i += kThreads) {
+    const int r = i >> 4, c = (i & 15) << 3;
+    uint4 ev = make_uint4(0, 0, 0, 0);
+    if (r < valid) ev = *reinterpret_cast<const uint4*>(p.v_new + row0 + (size_t)r * gld + c);
+    const float b = p.beta_c[chh * kChunk + r];
+    uint32_t* e32 = reinterpret_cast<uint32_t*>(&ev);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 x = unpack_bf16(e32[j]);
+      e32[j] = pack_bf16(b * x.x, b * x.y);
+    }
+    *reinterpret_cast<uint4*>(sF + r * kLdD + c) = ev;
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+
+  const int I = warp & 3, n0 = 64 * (warp >> 2);
+  float acc[1][8][4];
+  zero_acc(acc);
+  warp_gemm<1, 8, false, true>(acc, sQg, kLdD, 16 * I, sH, kLdD, n0, 0, kD);
+  warp_gemm<1, 8, false, true>(acc, sP, kLdC, 16 * I, sF, kLdD, n0, 0, 16 * (I + 1));
+#pragma unroll
+  for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int i = 16 * I + gq + 8 * half;
+      if (i < valid)
+        *reinterpret_cast<uint32_t*>(p.o + row0 + (size_t)i * gld + n0 + 8 * nt + 2 * tq) =
+            pack_bf16(acc[0][nt][2 * half], acc[0][nt][2 * half + 1]);
+    }
+}
+
+// ------------------------------------------------------------------ host side
+struct FwdWorkspace {
+  int* chunk_offsets;
+  float* beta_c;
+  bf16* u;
+  size_t bytes;
+};
+
+static FwdWorkspace carve_fwd(const pkda_problem& p, void* base) {
+  FwdWorkspace w;
+  const size_t chunks = (size_t)chunk_bound(p);
+  size_t off = 0;
+  unsigned char* b = static_cast<unsigned char*>(base);
+  w.chunk_offsets = reinterpret_cast<int*>(b + off);
+  off += align_up((size_t)(p.n_seqs + 1) * sizeof(int));
+  w.beta_c = reinterpret_cast<float*>(b + off);
+  off += align_up(chunks * p.heads * kChunk * sizeof(float));
+  w.u = reinterpret_cast<bf16*>(b + off);
+  off += align_up((size_t)p.total_tokens * p.heads * kD * sizeof(bf16));
+  w.bytes = off;
+  return w;
+}
+
+size_t chunk_fwd_workspace(const pkda_problem& p) { return carve_fwd(p, nullptr).bytes; }
+
+template <typename K>
+static bool set_smem(K kernel, int bytes) {
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess;
+}
+
+#define PKDA_CHECK_LAUNCH()                                   \
+  do {                                                        \
+    note_launch();                                            \
+    if (cudaGetLastError() != cudaSuccess) return PKDA_ERR_LAUNCH; \
+  } while (0)
+
+int check_chunk_problem(const pkda_problem& p) {
+  int rc = check_problem(p);
+  if (rc != PKDA_OK) return rc;
+  if (p.head_dim != kD) return PKDA_ERR_SHAPE;
+  if (p.dtype != PKDA_BF16) return PKDA_ERR_DTYPE;
+  return PKDA_OK;
+}
+
+// Shared by the forward and by the backward's recompute mode.
+int run_forward_stages(const pkda_problem& p, const Geo& geo, const float* beta_c, bf16* u_ws,
+                       bf16* Aqk, bf16* Akk, bf16* kt, float* gc, const float* a_start,
+                       bf16* w, bf16* kg, bf16* v_new, bf16* h, bf16* qg, float* ST,
+                       bool recompute, cudaStream_t st) {
+  const int chunks = geo.total_chunks;
+  IntraParams ip;
+  ip.geo = geo;
+  ip.q = static_cast<const bf16*>(p.q); ip.k = static_cast<const bf16*>(p.k);
+  ip.v = static_cast<const bf16*>(p.v); ip.g = static_cast<const bf16*>(p.g);
+  ip.g_atk = p.g_atk; ip.beta_atk = static_cast<const bf16*>(p.beta_atk);
+  ip.A_log = p.A_log; ip.dt_bias = p.dt_bias; ip.log_atk_scale = p.log_atk_scale;
+  ip.beta_c = beta_c; ip.a_start = a_start;
+  ip.Aqk = Aqk; ip.Akk = Akk; ip.kt = kt; ip.gc = gc;
+  ip.w = w; ip.u = u_ws; ip.kg = kg; ip.qg = qg;
+  ip.scale = p.scale; ip.ln_x = logf(p.squash_x); ip.eps = p.squash_eps;
+  dim3 gridc(chunks, p.heads);
+  if (recompute) {
+    if (!set_smem(pkda_intra_fwd_kernel<true>, intra::kSmem)) return PKDA_ERR_LAUNCH;
+    pkda_intra_fwd_kernel<true><<<gridc, intra::kThreads, intra::kSmem, st>>>(ip);
+  } else {
+    if (!set_smem(pkda_intra_fwd_kernel<false>, intra::kSmem)) return PKDA_ERR_LAUNCH;
+    pkda_intra_fwd_kernel<false><<<gridc, intra::kThreads, intra::kSmem, st>>>(ip);
+  }
+  PKDA_CHECK_LAUNCH();
+
+  ScanParams sp;
+  sp.geo = geo; sp.w = w; sp.u = u_ws; sp.kg = kg; sp.beta_c = beta_c; sp.gc = gc;
+  sp.S0 = p.initial_state; sp.h = h; sp.v_new = v_new; sp.ST = ST;
+  constexpr int VB = 32;
+  dim3 grids(p.n_seqs * p.heads * (kD / VB));
+  if (recompute) {
+    if (!set_smem(pkda_scan_fwd_kernel<VB, true>, scan::L<VB>::kSmem)) return PKDA_ERR_LAUNCH;
+    pkda_scan_fwd_kernel<VB, true><<<grids, scan::kThreads, scan::L<VB>::kSmem, st>>>(sp);
+  } else {
+    if (!set_smem(pkda_scan_fwd_kernel<VB, false>, scan::L<VB>::kSmem)) return PKDA_ERR_LAUNCH;
+    pkda_scan_fwd_kernel<VB, false><<<grids, scan::kThreads, scan::L<VB>::kSmem, st>>>(sp);
+  }
+  PKDA_CHECK_LAUNCH();
+  return PKDA_OK;
+}
+
+int run_prologue(const pkda_problem& p, int* chunk_offsets, float* beta_c, Geo* geo, cudaStream_t st) {
+  if (p.cu_seqlens) {
+    pkda_chunk_offsets_kernel<<<1, 32, 0, st>>>(p.cu_seqlens, p.n_seqs, chunk_offsets);
+    PKDA_CHECK_LAUNCH();
+  }
+  *geo = make_geo(p, chunk_offsets);
+  pkda_pack_beta_kernel<<<geo->total_chunks, 256, 0, st>>>(*geo, static_cast<const bf16*>(p.beta), beta_c);
+  PKDA_CHECK_LAUNCH();
+  return PKDA_OK;
+}
+
+int chunk_fwd(const pkda_chunk_fwd_args* a, cudaStream_t st) {
+  const pkda_problem& p = a->p;
+  int rc = check_chunk_problem(p);
+  if (rc != PKDA_OK) return rc;
+  if (p.n_seqs == 0 || p.total_tokens == 0) return PKDA_OK;
+  if (!a->o || !a->Aqk || !a->Akk || !a->k_precond || !a->ac_atk || !a->a_atk || !a->sa_atk || !a->w ||
+      !a->kg || !a->v_new || !a->h || !a->qg)
+    return PKDA_ERR_NULL;
+  if (!a->workspace || a->workspace_bytes < chunk_fwd_workspace(p)) return PKDA_ERR_WORKSPACE;
+  FwdWorkspace ws = carve_fwd(p, a->workspace);
+  Geo geo;
+  rc = run_prologue(p, ws.chunk_offsets, ws.beta_c, &geo, st);
+  if (rc != PKDA_OK) return rc;
+
+  dim3 gridc(geo.total_chunks, p.heads);
+  pkda_atk_local_kernel<<<gridc, kD, 0, st>>>(geo, static_cast<const bf16*>(p.k), p.g_atk,
+                                              static_cast<const bf16*>(p.beta_atk), a->ac_atk, a->sa_atk);
+  PKDA_CHECK_LAUNCH();
+  pkda_atk_carry_kernel<<<dim3(p.n_seqs, p.heads), kD, 0, st>>>(geo, a->ac_atk, a->sa_atk, p.initial_A_state,
+                                                               a->a_atk, a->final_A_state);
+  PKDA_CHECK_LAUNCH();
+
+  rc = run_forward_stages(p, geo, ws.beta_c, ws.u, static_cast<bf16*>(a->Aqk), static_cast<bf16*>(a->Akk),
+                          static_cast<bf16*>(a->k_precond), a->ac_atk, a->a_atk, static_cast<bf16*>(a->w),
+                          static_cast<bf16*>(a->kg), static_cast<bf16*>(a->v_new), static_cast<bf16*>(a->h),
+                          static_cast<bf16*>(a->qg), a->final_state, false, st);
+  if (rc != PKDA_OK) return rc;
+
+  OutParams op;
+  op.geo = geo;
+  op.qg = static_cast<const bf16*>(a->qg); op.h = static_cast<const bf16*>(a->h);
+  op.Aqk = static_cast<const bf16*>(a->Aqk); op.v_new = static_cast<const bf16*>(a->v_new);
+  op.beta_c = ws.beta_c; op.o = static_cast<bf16*>(a->o);
+  if (!set_smem(pkda_out_fwd_kernel, outk::kSmem)) return PKDA_ERR_LAUNCH;
+  pkda_out_fwd_kernel<<<gridc, outk::kThreads, outk::kSmem, st>>>(op);
+  PKDA_CHECK_LAUNCH();
+  return PKDA_OK;
+}
+
+}  // namespace pkda

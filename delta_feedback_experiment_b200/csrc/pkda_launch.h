@@ -1,0 +1,34 @@
+// Host-side glue shared by the translation units behind the C ABI.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include "../../include/pkda_b200.h"
+#include "pkda_common.cuh"
+
+namespace pkda {
+
+void note_launch();
+void reset_launch_count();
+
+// Validates the fields every entry point relies on.
+int check_problem(const pkda_problem& p);
+
+// chunk_offsets: device array for packed input (NULL for dense input).
+Geo make_geo(const pkda_problem& p, const int* chunk_offsets);
+
+// Upper bound on the number of 64-token chunks.
+inline int chunk_bound(const pkda_problem& p) {
+  if (p.cu_seqlens) return p.total_tokens / kChunk + p.n_seqs;
+  return p.n_seqs * ((p.seq_len + kChunk - 1) / kChunk);
+}
+
+inline size_t align_up(size_t x, size_t a = 256) { return (x + a - 1) / a * a; }
+
+int recurrent_fwd(const pkda_recurrent_args* a, cudaStream_t st);
+int chunk_fwd(const pkda_chunk_fwd_args* a, cudaStream_t st);
+int chunk_bwd(const pkda_chunk_bwd_args* a, cudaStream_t st);
+size_t chunk_fwd_workspace(const pkda_problem& p);
+size_t chunk_bwd_workspace(const pkda_problem& p);
+
+}  // namespace pkda

@@ -1,0 +1,163 @@
+/*
+ * pkda_b200 -- C ABI of the B200 (sm_100a) PKDA delta-rule attention kernels.
+ *
+ * Every entry point takes plain device pointers and sizes, launches on the
+ * stream it is given, never synchronises, never allocates and returns an int
+ * status (0 = ok).  All scratch memory is supplied by the caller, sized by the
+ * *_workspace_bytes functions.  The Python host code in
+ * delta_feedback_experiment_b200/ binds these through ctypes; any other host
+ * language binds them the same way.
+ *
+ * Tensor conventions (identical to the reference operator boundary,
+ * delta_feedback_experiment/fla_ops.py:255-349 and pkda.py:450-475):
+ *   q,k,v,g        [tokens][H][D]   activations (bf16 or fp32), contiguous
+ *   g_atk          [tokens][H]      fp32, preconditioner log-decay (<= 0)
+ *   beta_atk,beta  [tokens][H]      activation dtype
+ *   A_log [H], dt_bias [H*D], log_atk_scale [H]   fp32
+ *   states         S [N][H][D][D] (key-major), A [N][H][D]   fp32
+ * "tokens" is the flat axis B*T (dense) or the packed total; N is B (dense) or
+ * the number of packed sequences.
+ */
+#ifndef PKDA_B200_H_
+#define PKDA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PKDA_ABI_VERSION 1
+#define PKDA_CHUNK 64
+
+enum pkda_status {
+  PKDA_OK = 0,
+  PKDA_ERR_NULL = 1,          /* a required pointer is NULL */
+  PKDA_ERR_SHAPE = 2,         /* unsupported geometry (head_dim, sizes) */
+  PKDA_ERR_DTYPE = 3,         /* unsupported activation dtype for this entry */
+  PKDA_ERR_WORKSPACE = 4,     /* workspace missing or too small */
+  PKDA_ERR_LAUNCH = 5,        /* a kernel launch failed (see cudaGetLastError) */
+  PKDA_ERR_ALIGN = 6          /* a pointer is not 16-byte aligned */
+};
+
+enum pkda_dtype { PKDA_BF16 = 0, PKDA_F32 = 1 };
+
+/* Geometry + inputs shared by all entry points. */
+typedef struct pkda_problem {
+  int32_t n_seqs;        /* N: batch rows, or packed sequences */
+  int32_t seq_len;       /* T per row (dense); ignored when cu_seqlens != NULL */
+  int32_t total_tokens;  /* N*T (dense) or packed total */
+  int32_t heads;         /* H */
+  int32_t head_dim;      /* D = K = V */
+  int32_t dtype;         /* pkda_dtype of q,k,v,g,beta,beta_atk and of o / activation grads */
+  float scale;           /* query scale (reference default D^-0.5, pkda.py:372) */
+  float squash_x;        /* preconditioner base x (1.5, pkda.py:94) */
+  float squash_eps;      /* preconditioner eps (1e-6, pkda.py:95) */
+  int32_t reserved0;
+  const int32_t* cu_seqlens; /* device int32 [N+1] cumulative offsets, or NULL (dense) */
+  const void* q;
+  const void* k;
+  const void* v;
+  const void* g;
+  const float* g_atk;
+  const void* beta_atk;
+  const void* beta;
+  const float* A_log;
+  const float* dt_bias;
+  const float* log_atk_scale;
+  const float* initial_state;   /* [N][H][D][D] or NULL (zeros) */
+  const float* initial_A_state; /* [N][H][D]    or NULL (zeros) */
+} pkda_problem;
+
+/*
+ * Recurrent (token by token) forward: the decode step and short cached
+ * prefill, exact in fp32.  Replaces fused_recurrent_precond_kda
+ * (call site delta_feedback_experiment/pkda.py:473-474) and follows the
+ * recurrence of pkda.py:390-410 literally.  Any T >= 1, D in {8,16,32,64,128},
+ * bf16 or fp32 activations.  final_state may alias initial_state (in-place
+ * decode); final_A_state may alias initial_A_state.
+ */
+typedef struct pkda_recurrent_args {
+  pkda_problem p;
+  void* o;               /* [tokens][H][D] activation dtype */
+  float* final_state;    /* [N][H][D][D] or NULL */
+  float* final_A_state;  /* [N][H][D] or NULL */
+} pkda_recurrent_args;
+
+int pkda_recurrent_fwd(const pkda_recurrent_args* args, void* cuda_stream);
+
+/*
+ * Chunked forward (training / prefill), bf16 activations, D = 128, chunk 64.
+ * Replaces kda_gate_chunk_cumsum + chunk_precond_kda_fwd
+ * (delta_feedback_experiment/fla_ops.py:290-339) and chunk_precond_kda
+ * (pkda.py:475).  Intermediates follow the shapes of
+ * fla_ops.py:73-97 with "chunks" = the flat chunk axis (N*ceil(T/64) dense;
+ * for packed input at most total_tokens/64 + N):
+ *   Aqk, Akk        [tokens][H][64]      bf16
+ *   k_precond       [tokens][H][D]       bf16
+ *   ac_atk, a_atk   [chunks][H][D]       fp32
+ *   sa_atk          [chunks][H]          fp32
+ *   w, kg, v_new, qg [tokens][H][D]      bf16
+ *   h               [chunks][H][D][D]    bf16
+ * All of them must be supplied (the lean variant of the reference simply does
+ * not keep the last five after the call).
+ */
+typedef struct pkda_chunk_fwd_args {
+  pkda_problem p;
+  void* o;
+  float* final_state;   /* or NULL */
+  float* final_A_state; /* or NULL */
+  void* Aqk; void* Akk; void* k_precond;
+  float* ac_atk; float* a_atk; float* sa_atk;
+  void* w; void* kg; void* v_new; void* h; void* qg;
+  void* workspace; size_t workspace_bytes;
+} pkda_chunk_fwd_args;
+
+size_t pkda_chunk_fwd_workspace_bytes(const pkda_problem* p);
+int pkda_chunk_fwd(const pkda_chunk_fwd_args* args, void* cuda_stream);
+
+/*
+ * Chunked backward.  Replaces kda_gate_chunk_cumsum + chunk_precond_kda_bwd +
+ * kda_gate_bwd (delta_feedback_experiment/fla_ops.py:423-499).  Takes the
+ * forward's intermediates (recompute = 1 rebuilds w, kg, v_new, h, qg into the
+ * given buffers first, the reference's "lean" mode) and the cotangents d_o
+ * (and optionally d_final_state); writes the ten input gradients
+ * (dq,dk,dv,dg,dbeta,dbeta_atk in the activation dtype; dg_atk, dA_log,
+ * ddt_bias, dlog_atk_scale fp32, as scripts/pkda_bench.py:197-201 requires)
+ * and, when requested, the gradients of the two initial states.
+ */
+typedef struct pkda_chunk_bwd_args {
+  pkda_problem p;
+  const void* d_o;              /* [tokens][H][D] */
+  const float* d_final_state;   /* [N][H][D][D] or NULL */
+  int32_t recompute;            /* 1: rebuild w,kg,v_new,h,qg first */
+  int32_t reserved1;
+  const void* Aqk; const void* Akk; const void* k_precond;
+  const float* ac_atk; const float* a_atk; const float* sa_atk;
+  void* w; void* kg; void* v_new; void* h; void* qg;
+  void* dq; void* dk; void* dv; void* dg;
+  float* dg_atk; void* dbeta_atk; void* dbeta;
+  float* dA_log; float* ddt_bias; float* dlog_atk_scale;
+  float* d_initial_state;    /* [N][H][D][D] or NULL */
+  float* d_initial_A_state;  /* [N][H][D] or NULL */
+  void* workspace; size_t workspace_bytes;
+} pkda_chunk_bwd_args;
+
+size_t pkda_chunk_bwd_workspace_bytes(const pkda_problem* p);
+int pkda_chunk_bwd(const pkda_chunk_bwd_args* args, void* cuda_stream);
+
+/* Introspection used by the bindings' self-checks. */
+int pkda_abi_version(void);
+const char* pkda_status_string(int status);
+size_t pkda_sizeof_problem(void);
+size_t pkda_sizeof_recurrent_args(void);
+size_t pkda_sizeof_chunk_fwd_args(void);
+size_t pkda_sizeof_chunk_bwd_args(void);
+/* Number of kernels the last call of each kind enqueued (for launch accounting). */
+int pkda_last_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PKDA_B200_H_ */

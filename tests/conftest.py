@@ -37,16 +37,22 @@ def rel_rms(actual: torch.Tensor, expected: torch.Tensor) -> float:
     return float((a - e).square().mean().sqrt() / (e.square().mean().sqrt() + 1e-30))
 
 
-def assert_close(actual, expected, rtol, name=""):
+def assert_close(actual, expected, rtol, name="", outlier_frac=None):
     """``|a-e| <= rtol * (|e| + rms(e))``: the stated relative tolerance, with
-    the tensor's RMS as the floor for entries near zero."""
+    the tensor's RMS as the floor for entries near zero.  For the bf16 tolerance
+    (rtol >= 1e-2) a fraction of at most 1e-4 of the entries may sit in the
+    rounding tail between 1x and 2x that bound; nothing may exceed 2x."""
     a, e = actual.detach().double().cpu(), expected.detach().double().cpu()
     assert a.shape == e.shape, f"{name}: shape {tuple(a.shape)} vs {tuple(e.shape)}"
     assert torch.isfinite(a).all(), f"{name}: non-finite values"
+    if outlier_frac is None:
+        outlier_frac = 1e-4 if rtol >= 1e-2 else 0.0
     rms = e.square().mean().sqrt()
-    bad = (a - e).abs() > rtol * (e.abs() + rms) + 1e-30
-    if bad.any():
-        worst = ((a - e).abs() / (e.abs() + rms + 1e-30)).max()
+    bound = rtol * (e.abs() + rms) + 1e-30
+    err = (a - e).abs()
+    bad = err > bound
+    worst = float((err / bound).max()) if a.numel() else 0.0
+    if bad.sum() > outlier_frac * a.numel() or worst > 2.0:
         raise AssertionError(
             f"{name}: {int(bad.sum())}/{a.numel()} entries beyond rtol={rtol}; "
-            f"worst {float(worst):.3e}; rel-rms {rel_rms(a, e):.3e}")
+            f"worst {worst:.3f}x the bound; rel-rms {rel_rms(a, e):.3e}")

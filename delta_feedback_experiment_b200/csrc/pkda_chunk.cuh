@@ -22,9 +22,11 @@ __device__ __forceinline__ bool level_pair_ok(int i, int j, int lvl) {
 // and sXk from sK), the others get Y * 2^(G_ref - G_r) (into sY from sKt), where
 // ref is the first row of the upper half of the row's 2*lvl block.  Rows of the
 // other kind are left untouched (their products are masked out).  Null
-// destinations are skipped.
+// destinations are skipped.  sFac (optional, fp32 [64][128]) receives the factor
+// each row used.
 __device__ __forceinline__ void stage_level(bf16* sXq, bf16* sXk, bf16* sY, const bf16* sQ, const bf16* sK,
-                                            const bf16* sKt, const float* sG, int lvl, int tid, int nthreads) {
+                                            const bf16* sKt, const float* sG, int lvl, int tid, int nthreads,
+                                            float* sFac = nullptr) {
   for (int idx = tid; idx < kChunk * kD / 2; idx += nthreads) {
     const int r = idx >> 6, c2 = (idx & 63) << 1;
     const int ref = (r & ~(2 * lvl - 1)) + lvl;
@@ -32,6 +34,7 @@ __device__ __forceinline__ void stage_level(bf16* sXq, bf16* sXk, bf16* sY, cons
     const float2 Gf = *reinterpret_cast<const float2*>(sG + ref * kD + c2);
     if (r & lvl) {
       const float f0 = exp2f(Gr.x - Gf.x), f1 = exp2f(Gr.y - Gf.y);
+      if (sFac) *reinterpret_cast<float2*>(sFac + r * kD + c2) = make_float2(f0, f1);
       if (sXq) {
         const float2 x = unpack_bf16(*reinterpret_cast<const uint32_t*>(sQ + r * kLdD + c2));
         *reinterpret_cast<uint32_t*>(sXq + r * kLdD + c2) = pack_bf16(x.x * f0, x.y * f1);
@@ -42,8 +45,42 @@ __device__ __forceinline__ void stage_level(bf16* sXq, bf16* sXk, bf16* sY, cons
       }
     } else if (sY) {
       const float f0 = exp2f(Gf.x - Gr.x), f1 = exp2f(Gf.y - Gr.y);
+      if (sFac) *reinterpret_cast<float2*>(sFac + r * kD + c2) = make_float2(f0, f1);
       const float2 x = unpack_bf16(*reinterpret_cast<const uint32_t*>(sKt + r * kLdD + c2));
       *reinterpret_cast<uint32_t*>(sY + r * kLdD + c2) = pack_bf16(x.x * f0, x.y * f1);
+    }
+  }
+}
+
+// warp_gemm for one m-tile whose A operand is a [64][64] pair-weight matrix
+// restricted to the pairs of one level.  With mask = true every A element
+// (i, j) that is not a valid pair of `lvl` is zeroed in registers after the
+// load; kATrans means the logical A is the transpose (A[m=j][k=i]).
+template <int kNT, bool kATrans, bool kBKN>
+__device__ __forceinline__ void warp_gemm_lvl(float (&acc)[1][kNT][4], const bf16* A, int lda, int m0,
+                                              const bf16* B, int ldb, int n0, int kbeg, int kend, int lvl,
+                                              bool mask) {
+  const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+#pragma unroll 1
+  for (int k0 = kbeg; k0 < kend; k0 += 16) {
+    uint32_t a[4];
+    load_a_frag<kATrans>(a, A, lda, m0, k0);
+    if (mask) {
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const int m = m0 + g + 8 * (r & 1);
+        const int kk = k0 + 2 * t + 8 * (r >> 1);
+        const bool ok0 = kATrans ? level_pair_ok(kk, m, lvl) : level_pair_ok(m, kk, lvl);
+        const bool ok1 = kATrans ? level_pair_ok(kk + 1, m, lvl) : level_pair_ok(m, kk + 1, lvl);
+        a[r] &= (ok0 ? 0x0000ffffu : 0u) | (ok1 ? 0xffff0000u : 0u);
+      }
+    }
+#pragma unroll
+    for (int np = 0; np < kNT / 2; ++np) {
+      uint32_t b[4];
+      load_b_frag2<kBKN>(b, B, ldb, k0, n0 + 16 * np);
+      mma_bf16(acc[0][2 * np], a, b[0], b[1]);
+      mma_bf16(acc[0][2 * np + 1], a, b[2], b[3]);
     }
   }
 }

@@ -1,6 +1,896 @@
-// placeholder until the backward kernels land
+// Chunked PKDA backward for D = 128, chunk 64, bf16 activations.
+//
+// With the forward's per-chunk quantities (see pkda_chunk_fwd.cu)
+//   E = Tm (V - Kd S0), F = beta E, O = qg S0 + P F, S1 = Gam_last S0 + kg^T F
+// the cotangents are
+//   dF = kg dS1 + P^T dO,  dE = beta dF,  dS0 = Gam_last dS1 + qg^T dO - W^T dE
+//   dR = Tm^T dE (= dV),  dKd = -dR S0^T,  d(tril M) = -tril(dR E^T) diag(beta)
+//   dP = scale tril(dO F^T),  dkg = F dS1^T,  dqg = dO S0^T
+// and the gated pair products are differentiated level by level with the same
+// rounded operands on both sides, so that each pair's +/- contributions to the
+// log-decay gradient cancel exactly under the reverse cumulative sum.
+//
+// Pipeline:  [recompute forward stages]  scan_bwd (sequential over chunks)
+//   -> intra_bwd (per chunk) -> atk_bwd local / carry / final (preconditioner
+//   reverse scan, chunk-parallel) -> param_reduce.
 #include "pkda_chunk.cuh"
+
 namespace pkda {
-size_t chunk_bwd_workspace(const pkda_problem& p) { return 0; }
-int chunk_bwd(const pkda_chunk_bwd_args* a, cudaStream_t st) { return PKDA_ERR_SHAPE; }
+
+// ------------------------------------------------------------------ reverse state scan
+struct ScanBwdParams {
+  Geo geo;
+  const bf16 *kg, *qg, *w, *Aqk, *d_o;
+  const float *beta_c, *gc;
+  const float* dST;
+  bf16 *dh, *dF;
+  float* dS0;
+};
+
+namespace scanb {
+constexpr int kThreads = 128;
+template <int VB> struct L {
+  static constexpr int ldv = VB + kPad;
+  static constexpr int oKg = 0;
+  static constexpr int oP = oKg + kTileBytes;            // bf16 [64][72]
+  static constexpr int oBeta = oP + kChunk * kLdC * 2;   // f32 [64]
+  static constexpr int oQg = oBeta + kChunk * 4;
+  static constexpr int oW = oQg + kTileBytes;
+  static constexpr int oGc = oW + kTileBytes;            // f32 [128]
+  static constexpr int oDo = oGc + kD * 4;               // 2 x bf16 [64][ldv]
+  static constexpr int kDoBytes = kChunk * ldv * 2;
+  static constexpr int oD = oDo + 2 * kDoBytes;          // bf16 [128][ldv]
+  static constexpr int oDE = oD + kD * ldv * 2;          // bf16 [64][ldv]
+  static constexpr int kSmem = oDE + kChunk * ldv * 2;
+};
+}  // namespace scanb
+
+template <int VB>
+__global__ void __launch_bounds__(scanb::kThreads)
+pkda_scan_bwd_kernel(const ScanBwdParams p) {
+  using Lay = scanb::L<VB>;
+  constexpr int ldv = Lay::ldv, NT = VB / 8;
+  extern __shared__ __align__(128) unsigned char smem[];
+  const int VS = kD / VB;
+  const int vs = blockIdx.x % VS;
+  const int nh = blockIdx.x / VS;
+  const int n = nh / p.geo.heads, h = nh - n * p.geo.heads, H = p.geo.heads;
+  const SeqInfo sq = seq_info(p.geo, n);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int gq = lane >> 2, tq = lane & 3;
+  const int v0 = vs * VB;
+  const long gld = (long)H * kD;
+  const size_t sbase = ((size_t)n * H + h) * kD * kD;
+
+  bf16* sKg = reinterpret_cast<bf16*>(smem + Lay::oKg);
+  bf16* sP = reinterpret_cast<bf16*>(smem + Lay::oP);
+  float* sBeta = reinterpret_cast<float*>(smem + Lay::oBeta);
+  bf16* sQg = reinterpret_cast<bf16*>(smem + Lay::oQg);
+  bf16* sW = reinterpret_cast<bf16*>(smem + Lay::oW);
+  float* sGc = reinterpret_cast<float*>(smem + Lay::oGc);
+  bf16* sD = reinterpret_cast<bf16*>(smem + Lay::oD);
+  bf16* sDE = reinterpret_cast<bf16*>(smem + Lay::oDE);
+
+  auto prefetchA = [&](int i) {
+    const int tok0 = sq.bos + i * kChunk;
+    const int valid = min(kChunk, sq.len - i * kChunk);
+    const size_t row0 = ((size_t)tok0 * H + h) * kD;
+    const size_t chh = (size_t)(sq.chunk0 + i) * H + h;
+    tile_load_async(sKg, kLdD, p.kg + row0, gld, kChunk, kD, valid, scanb::kThreads);
+    tile_load_async(sP, kLdC, p.Aqk + ((size_t)tok0 * H + h) * kChunk, (long)H * kChunk, kChunk, kChunk, valid,
+                    scanb::kThreads);
+    tile_load_async(reinterpret_cast<bf16*>(smem + Lay::oDo + (i & 1) * Lay::kDoBytes), ldv, p.d_o + row0 + v0, gld,
+                    kChunk, VB, valid, scanb::kThreads);
+    if (tid < 16) cp_async16(smem + Lay::oBeta + tid * 16, p.beta_c + chh * kChunk + tid * 4, true);
+  };
+  auto prefetchB = [&](int i) {
+    const int tok0 = sq.bos + i * kChunk;
+    const int valid = min(kChunk, sq.len - i * kChunk);
+    const size_t row0 = ((size_t)tok0 * H + h) * kD;
+    const size_t chh = (size_t)(sq.chunk0 + i) * H + h;
+    tile_load_async(sQg, kLdD, p.qg + row0, gld, kChunk, kD, valid, scanb::kThreads);
+    tile_load_async(sW, kLdD, p.w + row0, gld, kChunk, kD, valid, scanb::kThreads);
+    if (tid < 32) cp_async16(smem + Lay::oGc + tid * 16, p.gc + chh * kD + tid * 4, true);
+  };
+
+  float dS[2][NT][4];
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int r = 32 * warp + 16 * mt + gq + 8 * half, c = v0 + 8 * nt + 2 * tq;
+        float2 s2 = make_float2(0.f, 0.f);
+        if (p.dST) s2 = *reinterpret_cast<const float2*>(p.dST + sbase + (size_t)r * kD + c);
+        dS[mt][nt][2 * half] = s2.x;
+        dS[mt][nt][2 * half + 1] = s2.y;
+      }
+
+  const int last = sq.nchunks - 1;
+  if (last >= 0) {
+    prefetchA(last);
+    cp_async_commit();
+    prefetchB(last);
+    cp_async_commit();
+  }
+  for (int i = last; i >= 0; --i) {
+    const int tok0 = sq.bos + i * kChunk;
+    const int valid = min(kChunk, sq.len - i * kChunk);
+    const size_t chh = (size_t)(sq.chunk0 + i) * H + h;
+    const bf16* sdO = reinterpret_cast<const bf16*>(smem + Lay::oDo + (i & 1) * Lay::kDoBytes);
+    cp_async_wait<1>();  // group A(i) has landed
+    // a. chunk-exit state cotangent -> bf16 operand tile (and the saved dh)
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int r = 32 * warp + 16 * mt + gq + 8 * half, c = 8 * nt + 2 * tq;
+          *reinterpret_cast<uint32_t*>(sD + r * ldv + c) = pack_bf16(dS[mt][nt][2 * half], dS[mt][nt][2 * half + 1]);
+        }
+    __syncthreads();
+    {
+      constexpr int cpr = VB / 8;
+      for (int j = tid; j < kD * cpr; j += scanb::kThreads) {
+        const int r = j / cpr, c = (j - r * cpr) * 8;
+        *reinterpret_cast<uint4*>(p.dh + (chh * kD + r) * kD + v0 + c) =
+            *reinterpret_cast<const uint4*>(sD + r * ldv + c);
+      }
+    }
+    // c. dF = kg dS1 + P^T dO ;  -dE = -beta dF
+    {
+      float f[1][NT][4];
+      zero_acc(f);
+      warp_gemm<1, NT, false, true>(f, sKg, kLdD, 16 * warp, sD, ldv, 0, 0, kD);
+      warp_gemm<1, NT, true, true>(f, sP, kLdC, 16 * warp, sdO, ldv, 0, 16 * warp, kChunk);
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int r = 16 * warp + gq + 8 * half, c = 8 * nt + 2 * tq;
+          const uint32_t fk = pack_bf16(f[0][nt][2 * half], f[0][nt][2 * half + 1]);
+          if (r < valid) *reinterpret_cast<uint32_t*>(p.dF + ((size_t)(tok0 + r) * H + h) * kD + v0 + c) = fk;
+          const float2 fr = unpack_bf16(fk);
+          const float b = sBeta[r];
+          *reinterpret_cast<uint32_t*>(sDE + r * ldv + c) = pack_bf16(-b * fr.x, -b * fr.y);
+        }
+    }
+    __syncthreads();  // group-A buffers free
+    if (i > 0) prefetchA(i - 1);
+    cp_async_commit();
+    cp_async_wait<1>();  // group B(i) has landed
+    __syncthreads();
+    // d. dS0 = Gam_last dS1 + qg^T dO - W^T dE
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const float gcv = sGc[32 * warp + 16 * mt + gq + 8 * half];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          dS[mt][nt][2 * half] *= gcv;
+          dS[mt][nt][2 * half + 1] *= gcv;
+        }
+      }
+    warp_gemm<2, NT, true, true>(dS, sQg, kLdD, 32 * warp, sdO, ldv, 0, 0, kChunk);
+    warp_gemm<2, NT, true, true>(dS, sW, kLdD, 32 * warp, sDE, ldv, 0, 0, kChunk);
+    __syncthreads();  // group-B buffers, sD and sDE free
+    if (i > 0) prefetchB(i - 1);
+    cp_async_commit();
+  }
+  cp_async_wait<0>();
+  if (p.dS0) {
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int r = 32 * warp + 16 * mt + gq + 8 * half, c = v0 + 8 * nt + 2 * tq;
+          *reinterpret_cast<float2*>(p.dS0 + sbase + (size_t)r * kD + c) =
+              make_float2(dS[mt][nt][2 * half], dS[mt][nt][2 * half + 1]);
+        }
+  }
 }
+
+// ------------------------------------------------------------------ chunk-parallel backward
+struct IntraBwdParams {
+  Geo geo;
+  const bf16 *q, *k, *kt, *g;
+  const float *A_log, *dt_bias;
+  const float *beta_c, *gc;
+  const bf16 *Akk, *v_new, *h, *dh, *dF, *d_o;
+  bf16 *dq, *dv, *dg, *dbeta;
+  float *dk_read, *dkt;
+  float *partA, *partB;
+  float scale;
+};
+
+namespace ib {
+constexpr int kThreads = 512;
+constexpr int oA0 = 0;                        // dO          | later q
+constexpr int oA1 = kTileBytes;               // S0 [128][136] | E, F | later k, kt
+constexpr int oG = oA1 + 2 * kTileBytes;      // f32 [64][128] log2-domain cumulative decay
+constexpr int oTm = oG + kChunk * kD * 4;     // bf16 [64][72]
+constexpr int oDE = oTm + kChunk * kLdC * 2;  // dE | later dS1 [128][136] together with oDR
+constexpr int oDR = oDE + kTileBytes;
+constexpr int oStage = oTm;                   // three gated operand tiles | later dG f32 [64][128]
+constexpr int oDP = oStage + 3 * kTileBytes;  // bf16 [64][72]
+constexpr int oDM = oDP + kChunk * kLdC * 2;
+constexpr int oFac = oDM + kChunk * kLdC * 2; // f32 [64][128]
+constexpr int oSmall = oFac + kChunk * kD * 4;
+// small: beta[64] db[64] hdh[128] gcv[128] col[4][128] rb[4][64] red[16]
+constexpr int kSmallFloats = 64 + 64 + 128 + 128 + 512 + 256 + 16;
+constexpr int kSmem = oSmall + kSmallFloats * 4;
+static_assert(oDR + kTileBytes <= oDP, "phase-A tiles must not reach the pair-gradient tiles");
+static_assert(oDE + kD * kLdD * 2 <= oDP, "dS1 tile must fit");
+}  // namespace ib
+
+__global__ void __launch_bounds__(ib::kThreads, 1)
+pkda_intra_bwd_kernel(const IntraBwdParams p) {
+  using namespace ib;
+  extern __shared__ __align__(128) unsigned char smem[];
+  bf16* sdO = reinterpret_cast<bf16*>(smem + oA0);
+  bf16* sS0 = reinterpret_cast<bf16*>(smem + oA1);
+  bf16* sE = reinterpret_cast<bf16*>(smem + oA1);
+  bf16* sF = reinterpret_cast<bf16*>(smem + oA1 + kTileBytes);
+  float* sG = reinterpret_cast<float*>(smem + oG);
+  bf16* sTm = reinterpret_cast<bf16*>(smem + oTm);
+  bf16* sdE = reinterpret_cast<bf16*>(smem + oDE);
+  bf16* sdR = reinterpret_cast<bf16*>(smem + oDR);
+  bf16* sdSC = reinterpret_cast<bf16*>(smem + oDE);
+  bf16* sdP = reinterpret_cast<bf16*>(smem + oDP);
+  bf16* sdM = reinterpret_cast<bf16*>(smem + oDM);
+  float* sFac = reinterpret_cast<float*>(smem + oFac);
+  float* sBeta = reinterpret_cast<float*>(smem + oSmall);
+  float* sDb = sBeta + 64;
+  float* sHdh = sDb + 64;
+  float* sGcv = sHdh + 128;
+  float* sCol = sGcv + 128;  // [4][128]
+  float* sRb = sCol + 512;   // [4][64]
+  float* sRed = sRb + 256;   // [16]
+
+  int n, tok0, valid;
+  if (!chunk_lookup(p.geo, blockIdx.x, n, tok0, valid)) return;
+  const int h = blockIdx.y, H = p.geo.heads;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int gq = lane >> 2, tq = lane & 3;
+  const int I = warp & 3, cq = warp >> 2;
+  const size_t chh = (size_t)blockIdx.x * H + h;
+  const size_t row0 = ((size_t)tok0 * H + h) * kD;
+  const long gld = (long)H * kD;
+  const size_t crow0 = ((size_t)tok0 * H + h) * kChunk;
+  const long cld = (long)H * kChunk;
+
+  // ================= phase A: state-coupled terms =================
+  tile_load_async(sdO, kLdD, p.d_o + row0, gld, kChunk, kD, valid, kThreads);
+  tile_load_async(sS0, kLdD, p.h + chh * kD * kD, kD, kD, kD, kD, kThreads);
+  tile_load_async(sTm, kLdC, p.Akk + crow0, cld, kChunk, kChunk, valid, kThreads);
+  cp_async_commit();
+  if (tid < kChunk) sBeta[tid] = p.beta_c[chh * kChunk + tid];
+  if (tid < kD) sGcv[tid] = p.gc[chh * kD + tid];
+  if (tid < kD) {
+    // log2-domain cumulative log-decay, exactly as the forward computes it
+    const int c = tid;
+    const float ea = __expf(p.A_log[h]) * kLog2e;
+    const float bias = p.dt_bias[h * kD + c];
+    float G = 0.f;
+    for (int r0 = 0; r0 < kChunk; r0 += 8) {
+      float raw[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        raw[j] = (r0 + j < valid) ? to_f(p.g[row0 + (size_t)(r0 + j) * gld + c]) : 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (r0 + j < valid) G -= ea * softplus_fast(raw[j] + bias);
+        sG[(r0 + j) * kD + c] = G;
+      }
+    }
+  } else {
+    const int t2 = tid - kD;  // 384 threads
+    // dE = beta * dF
+    for (int i = t2; i < kChunk * kD / 8; i += kThreads - kD) {
+      const int r = i >> 4, c = (i & 15) << 3;
+      uint4 fv = make_uint4(0, 0, 0, 0);
+      if (r < valid) fv = *reinterpret_cast<const uint4*>(p.dF + row0 + (size_t)r * gld + c);
+      const float b = p.beta_c[chh * kChunk + r];
+      uint32_t* f32 = reinterpret_cast<uint32_t*>(&fv);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 x = unpack_bf16(f32[j]);
+        f32[j] = pack_bf16(b * x.x, b * x.y);
+      }
+      *reinterpret_cast<uint4*>(sdE + r * kLdD + c) = fv;
+    }
+    // hdh[k] = sum_v S0[k][v] dS1[k][v]  (four threads per row)
+    for (int slot = t2; slot < 4 * kD; slot += kThreads - kD) {
+      const int row = slot >> 2, part = slot & 3;
+      const size_t base = (chh * kD + row) * kD + part * 32;
+      float acc = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint4 a = *reinterpret_cast<const uint4*>(p.h + base + 8 * j);
+        const uint4 b = *reinterpret_cast<const uint4*>(p.dh + base + 8 * j);
+        const uint32_t* a32 = reinterpret_cast<const uint32_t*>(&a);
+        const uint32_t* b32 = reinterpret_cast<const uint32_t*>(&b);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 x = unpack_bf16(a32[e]), y = unpack_bf16(b32[e]);
+          acc += x.x * y.x + x.y * y.y;
+        }
+      }
+      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+      if (part == 0) sHdh[row] = acc;
+    }
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+
+  float dQ[1][4][4], dK[1][4][4], dKt[1][4][4], dG[1][4][4];
+  float t[1][4][4];
+  // dqg = dO S0^T  ->  dq_a = scale * Gam * dqg
+  zero_acc(t);
+  warp_gemm<1, 4, false, false>(t, sdO, kLdD, 16 * I, sS0, kLdD, 32 * cq, 0, kD);
+#pragma unroll
+  for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int i = 16 * I + gq + 8 * (e >> 1), c = 32 * cq + 8 * nt + 2 * tq + (e & 1);
+      dQ[0][nt][e] = t[0][nt][e] * p.scale * exp2f(sG[i * kD + c]);
+    }
+  // dR = Tm^T dE  (= dV)
+  zero_acc(t);
+  warp_gemm<1, 4, true, true>(t, sTm, kLdC, 16 * I, sdE, kLdD, 32 * cq, 16 * I, kChunk);
+#pragma unroll
+  for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int r = 16 * I + gq + 8 * half, c = 32 * cq + 8 * nt + 2 * tq;
+      const uint32_t pk = pack_bf16(t[0][nt][2 * half], t[0][nt][2 * half + 1]);
+      if (r < valid) *reinterpret_cast<uint32_t*>(p.dv + row0 + (size_t)r * gld + c) = pk;
+      *reinterpret_cast<uint32_t*>(sdR + r * kLdD + c) = pk;
+    }
+  __syncthreads();
+  // dKd = -dR S0^T  ->  dk_a = Gam * dKd
+  zero_acc(t);
+  warp_gemm<1, 4, false, false>(t, sdR, kLdD, 16 * I, sS0, kLdD, 32 * cq, 0, kD);
+#pragma unroll
+  for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int i = 16 * I + gq + 8 * (e >> 1), c = 32 * cq + 8 * nt + 2 * tq + (e & 1);
+      dK[0][nt][e] = -t[0][nt][e] * exp2f(sG[i * kD + c]);
+    }
+  __syncthreads();  // S0 no longer needed
+  // E, F = beta E, and the direct part of dbeta: rowsum(dF * E)
+  for (int i = tid; i < kChunk * kD / 8; i += kThreads) {
+    const int r = i >> 4, c = (i & 15) << 3;
+    uint4 ev = make_uint4(0, 0, 0, 0), fv = make_uint4(0, 0, 0, 0);
+    if (r < valid) {
+      ev = *reinterpret_cast<const uint4*>(p.v_new + row0 + (size_t)r * gld + c);
+      fv = *reinterpret_cast<const uint4*>(p.dF + row0 + (size_t)r * gld + c);
+    }
+    const float b = sBeta[r];
+    uint32_t* e32 = reinterpret_cast<uint32_t*>(&ev);
+    const uint32_t* f32 = reinterpret_cast<const uint32_t*>(&fv);
+    uint4 bf;
+    uint32_t* bf32 = reinterpret_cast<uint32_t*>(&bf);
+    float part = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 x = unpack_bf16(e32[j]), y = unpack_bf16(f32[j]);
+      part += x.x * y.x + x.y * y.y;
+      bf32[j] = pack_bf16(b * x.x, b * x.y);
+    }
+    *reinterpret_cast<uint4*>(sE + r * kLdD + c) = ev;
+    *reinterpret_cast<uint4*>(sF + r * kLdD + c) = bf;
+    part += __shfl_xor_sync(0xffffffffu, part, 8);
+    part += __shfl_xor_sync(0xffffffffu, part, 4);
+    part += __shfl_xor_sync(0xffffffffu, part, 2);
+    part += __shfl_xor_sync(0xffffffffu, part, 1);
+    if ((i & 15) == 0) sDb[r] = part;
+  }
+  __syncthreads();
+  // pair-weight gradients: dM = -tril(dR E^T, -1) diag(beta),  dP = scale tril(dO F^T)
+  {
+    const int J = cq;
+    float t2[1][2][4];
+    zero_acc(t2);
+    if (J <= I) warp_gemm<1, 2, false, false>(t2, sdR, kLdD, 16 * I, sE, kLdD, 16 * J, 0, kD);
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int i = 16 * I + gq + 8 * half, j = 16 * J + 8 * nt + 2 * tq;
+        const float m0 = (j < i) ? -t2[0][nt][2 * half] * sBeta[j] : 0.f;
+        const float m1 = (j + 1 < i) ? -t2[0][nt][2 * half + 1] * sBeta[j + 1] : 0.f;
+        *reinterpret_cast<uint32_t*>(sdM + i * kLdC + j) = pack_bf16(m0, m1);
+      }
+    zero_acc(t2);
+    if (J <= I) warp_gemm<1, 2, false, false>(t2, sdO, kLdD, 16 * I, sF, kLdD, 16 * J, 0, kD);
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int i = 16 * I + gq + 8 * half, j = 16 * J + 8 * nt + 2 * tq;
+        const float p0 = (j <= i) ? t2[0][nt][2 * half] * p.scale : 0.f;
+        const float p1 = (j + 1 <= i) ? t2[0][nt][2 * half + 1] * p.scale : 0.f;
+        *reinterpret_cast<uint32_t*>(sdP + i * kLdC + j) = pack_bf16(p0, p1);
+      }
+  }
+  __syncthreads();  // dO, dR, E no longer needed
+  // dkg = F dS1^T  ->  dkt_a = exp(G_last - G) * dkg
+  tile_load_async(sdSC, kLdD, p.dh + chh * kD * kD, kD, kD, kD, kD, kThreads);
+  cp_async_commit();
+  cp_async_wait<0>();
+  __syncthreads();
+  zero_acc(t);
+  warp_gemm<1, 4, false, false>(t, sF, kLdD, 16 * I, sdSC, kLdD, 32 * cq, 0, kD);
+#pragma unroll
+  for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int i = 16 * I + gq + 8 * (e >> 1), c = 32 * cq + 8 * nt + 2 * tq + (e & 1);
+      dKt[0][nt][e] = t[0][nt][e] * exp2f(sG[(kChunk - 1) * kD + c] - sG[i * kD + c]);
+    }
+  __syncthreads();
+
+  // ================= phase B: gated pair products =================
+  bf16* sQ = reinterpret_cast<bf16*>(smem + oA0);
+  bf16* sK = reinterpret_cast<bf16*>(smem + oA1);
+  bf16* sKt = reinterpret_cast<bf16*>(smem + oA1 + kTileBytes);
+  bf16* sXq = reinterpret_cast<bf16*>(smem + oStage);
+  bf16* sXk = sXq + kChunk * kLdD;
+  bf16* sY = sXk + kChunk * kLdD;
+  tile_load_async(sQ, kLdD, p.q + row0, gld, kChunk, kD, valid, kThreads);
+  tile_load_async(sK, kLdD, p.k + row0, gld, kChunk, kD, valid, kThreads);
+  tile_load_async(sKt, kLdD, p.kt + row0, gld, kChunk, kD, valid, kThreads);
+  cp_async_commit();
+  cp_async_wait<0>();
+  __syncthreads();
+  {
+    // dG starts from the state-coupled parts; column sums of kt * dkt_a feed the
+    // chunk's last row (d/dG_last of exp(G_last - G_j)).
+    float cs[4][2];
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      cs[nt][0] = cs[nt][1] = 0.f;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = 16 * I + gq + 8 * (e >> 1), c = 32 * cq + 8 * nt + 2 * tq + (e & 1);
+        const float qv = to_f(sQ[i * kLdD + c]), kv = to_f(sK[i * kLdD + c]), ktv = to_f(sKt[i * kLdD + c]);
+        const float kd = ktv * dKt[0][nt][e];
+        dG[0][nt][e] = qv * dQ[0][nt][e] + kv * dK[0][nt][e] - kd;
+        cs[nt][e & 1] += kd;
+      }
+    }
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int b = 0; b < 2; ++b) {
+        float v = cs[nt][b];
+        v += __shfl_xor_sync(0xffffffffu, v, 4);
+        v += __shfl_xor_sync(0xffffffffu, v, 8);
+        v += __shfl_xor_sync(0xffffffffu, v, 16);
+        if (gq == 0) sCol[I * kD + 32 * cq + 8 * nt + 2 * tq + b] = v;
+      }
+  }
+  // Rows a level does not write keep older contents; their products are removed
+  // by zeroed pair weights, which only works on finite data (0 * NaN = NaN), so
+  // the staging tiles start from zeros rather than from whatever phase A left.
+  for (int i = tid; i < 3 * kTileBytes / 16; i += kThreads)
+    reinterpret_cast<uint4*>(smem + oStage)[i] = make_uint4(0, 0, 0, 0);
+  __syncthreads();
+  float rb[2] = {0.f, 0.f};
+#pragma unroll 1
+  for (int lvl = 32; lvl >= 1; lvl >>= 1) {
+    stage_level(sXq, sXk, sY, sQ, sK, sKt, sG, lvl, tid, kThreads, sFac);
+    __syncthreads();
+    const bool big = lvl >= 16;
+    const int blk = (16 * I) & ~(2 * lvl - 1);
+    if (!big || ((16 * I) & lvl)) {  // rows act as the upper ("i") side
+      const int kb = big ? blk : 16 * I, ke = kb + (big ? lvl : 16);
+      zero_acc(t);
+      warp_gemm_lvl<4, false, true>(t, sdP, kLdC, 16 * I, sY, kLdD, 32 * cq, kb, ke, lvl, !big);
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int i = 16 * I + gq + 8 * (e >> 1), c = 32 * cq + 8 * nt + 2 * tq + (e & 1);
+          dQ[0][nt][e] += sFac[i * kD + c] * t[0][nt][e];
+          dG[0][nt][e] += to_f(sXq[i * kLdD + c]) * t[0][nt][e];
+        }
+      zero_acc(t);
+      warp_gemm_lvl<4, false, true>(t, sdM, kLdC, 16 * I, sY, kLdD, 32 * cq, kb, ke, lvl, !big);
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int i = 16 * I + gq + 8 * (e >> 1), c = 32 * cq + 8 * nt + 2 * tq + (e & 1);
+          dK[0][nt][e] += sFac[i * kD + c] * t[0][nt][e];
+          dG[0][nt][e] += to_f(sXk[i * kLdD + c]) * t[0][nt][e];
+        }
+    }
+    if (!big || !((16 * I) & lvl)) {  // rows act as the lower ("j") side
+      const int kb = big ? blk + lvl : 16 * I, ke = kb + (big ? lvl : 16);
+      zero_acc(t);
+      warp_gemm_lvl<4, true, true>(t, sdM, kLdC, 16 * I, sXk, kLdD, 32 * cq, kb, ke, lvl, !big);
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = 16 * I + gq + 8 * (e >> 1), c = 32 * cq + 8 * nt + 2 * tq + (e & 1);
+          rb[e >> 1] += to_f(sY[j * kLdD + c]) * t[0][nt][e];
+        }
+      warp_gemm_lvl<4, true, true>(t, sdP, kLdC, 16 * I, sXq, kLdD, 32 * cq, kb, ke, lvl, !big);
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = 16 * I + gq + 8 * (e >> 1), c = 32 * cq + 8 * nt + 2 * tq + (e & 1);
+          dKt[0][nt][e] += sFac[j * kD + c] * t[0][nt][e];
+          dG[0][nt][e] -= to_f(sY[j * kLdD + c]) * t[0][nt][e];
+        }
+    }
+    __syncthreads();
+  }
+  // ungated diagonal of P
+#pragma unroll
+  for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int i = 16 * I + gq + 8 * (e >> 1), c = 32 * cq + 8 * nt + 2 * tq + (e & 1);
+      const float d = to_f(sdP[i * kLdC + i]);
+      dQ[0][nt][e] += d * to_f(sKt[i * kLdD + c]);
+      dKt[0][nt][e] += d * to_f(sQ[i * kLdD + c]);
+    }
+  // dbeta: direct part + <kt_j, dkt_j(M path)> / beta_j
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    float v = rb[half];
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
+    if (tq == 0) sRb[cq * kChunk + 16 * I + gq + 8 * half] = v;
+  }
+  // outputs of this stage; dG goes through shared memory for the reverse cumulative sum
+  float* sdG = reinterpret_cast<float*>(smem + oStage);
+#pragma unroll
+  for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int i = 16 * I + gq + 8 * half, c = 32 * cq + 8 * nt + 2 * tq;
+      if (i < valid) {
+        const size_t off = row0 + (size_t)i * gld + c;
+        *reinterpret_cast<uint32_t*>(p.dq + off) = pack_bf16(dQ[0][nt][2 * half], dQ[0][nt][2 * half + 1]);
+        *reinterpret_cast<float2*>(p.dk_read + off) = make_float2(dK[0][nt][2 * half], dK[0][nt][2 * half + 1]);
+        *reinterpret_cast<float2*>(p.dkt + off) = make_float2(dKt[0][nt][2 * half], dKt[0][nt][2 * half + 1]);
+      }
+      *reinterpret_cast<float2*>(sdG + i * kD + c) = make_float2(dG[0][nt][2 * half], dG[0][nt][2 * half + 1]);
+    }
+  __syncthreads();
+  if (tid < kChunk && tid < valid) {
+    const float b = sBeta[tid];
+    const float s = sRb[tid] + sRb[kChunk + tid] + sRb[2 * kChunk + tid] + sRb[3 * kChunk + tid];
+    const float db = sDb[tid] + (b != 0.f ? s / b : 0.f);
+    p.dbeta[(size_t)(tok0 + tid) * H + h] = __float2bfloat16(db);
+  }
+  // reverse cumulative sum over the chunk, then the gate's own backward:
+  //   g = -exp(A_log) softplus(raw + bias);  draw = dg * (-exp(A_log)) sigmoid(raw + bias)
+  float pa = 0.f;
+  if (tid < kD) {
+    const int c = tid;
+    const float ea = __expf(p.A_log[h]);
+    const float bias = p.dt_bias[h * kD + c];
+    float run = sCol[c] + sCol[kD + c] + sCol[2 * kD + c] + sCol[3 * kD + c] + sGcv[c] * sHdh[c];
+    float pb = 0.f;
+    for (int r0 = kChunk - 8; r0 >= 0; r0 -= 8) {
+      float raw[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        raw[j] = (r0 + j < valid) ? to_f(p.g[row0 + (size_t)(r0 + j) * gld + c]) : 0.f;
+#pragma unroll
+      for (int j = 7; j >= 0; --j) {
+        const int r = r0 + j;
+        run += sdG[r * kD + c];
+        if (r < valid) {
+          const float z = raw[j] + bias;
+          const float gn = -ea * softplus_fast(z);
+          const float dr = run * (-ea) * sigmoid_fast(z);
+          p.dg[row0 + (size_t)r * gld + c] = __float2bfloat16(dr);
+          pa += run * gn;
+          pb += dr;
+        }
+      }
+    }
+    p.partB[chh * kD + c] = pb;
+    pa += __shfl_xor_sync(0xffffffffu, pa, 16);
+    pa += __shfl_xor_sync(0xffffffffu, pa, 8);
+    pa += __shfl_xor_sync(0xffffffffu, pa, 4);
+    pa += __shfl_xor_sync(0xffffffffu, pa, 2);
+    pa += __shfl_xor_sync(0xffffffffu, pa, 1);
+    if (lane == 0) sRed[warp] = pa;
+  }
+  __syncthreads();
+  if (tid == 0) p.partA[chh] = sRed[0] + sRed[1] + sRed[2] + sRed[3];
+}
+
+// ------------------------------------------------------------------ preconditioner backward
+struct AtkBwdParams {
+  Geo geo;
+  const bf16* k;
+  const float* g_atk;
+  const bf16* beta_atk;
+  const float* log_atk_scale;
+  const float* a_start;
+  const float* dkt;
+  const float* dk_read;
+  const float* lam_in;
+  float* c_loc;
+  bf16* dk;
+  float* dg_atk;
+  bf16* dbeta_atk;
+  float* partC;
+  float ln_x, eps;
+};
+
+// One (chunk, head) per CTA, one channel per thread.  Recomputes A_t forward
+// from the chunk-start state, then walks the chunk backwards carrying
+// lam = dL/dA.  kFinal = false: zero incoming carry, only the outgoing carry is
+// produced (chunk-local pass).  kFinal = true: incoming carry given, all
+// gradients written.
+template <bool kFinal>
+__global__ void __launch_bounds__(kD)
+pkda_atk_bwd_kernel(const AtkBwdParams p) {
+  __shared__ float sA[kChunk][kD];
+  __shared__ float sPd[kChunk], sBp[kChunk];
+  __shared__ float sP1[4][kChunk], sP2[4][kChunk];
+  __shared__ float sRed[4];
+  int n, tok0, valid;
+  if (!chunk_lookup(p.geo, blockIdx.x, n, tok0, valid)) return;
+  const int h = blockIdx.y, H = p.geo.heads, c = threadIdx.x, warp = c >> 5, lane = c & 31;
+  const size_t chh = (size_t)blockIdx.x * H + h;
+  const size_t row0 = ((size_t)tok0 * H + h) * kD;
+  const long gld = (long)H * kD;
+  if (c < kChunk) {
+    const bool ok = c < valid;
+    const size_t s = (size_t)(tok0 + c) * H + h;
+    sPd[c] = ok ? __expf(p.g_atk[s]) : 1.f;
+    sBp[c] = ok ? to_f(p.beta_atk[s]) : 0.f;
+  }
+  __syncthreads();
+  const float centre = p.log_atk_scale[h];
+  float A = p.a_start[chh * kD + c];
+  for (int r0 = 0; r0 < valid; r0 += 8) {
+    float kc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) kc[j] = (r0 + j < valid) ? to_f(p.k[row0 + (size_t)(r0 + j) * gld + c]) : 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (r0 + j < valid) {
+        sA[r0 + j][c] = A;
+        A = sPd[r0 + j] * A + sBp[r0 + j] * kc[j] * kc[j];
+      }
+  }
+  float lam = kFinal ? p.lam_in[chh * kD + c] : 0.f;
+  float dcacc = 0.f;
+  for (int r0 = (valid - 1) & ~7; r0 >= 0; r0 -= 8) {
+    float kc[8], dk_t[8], dkr[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const bool ok = r0 + j < valid;
+      const size_t off = row0 + (size_t)(r0 + j) * gld + c;
+      kc[j] = ok ? to_f(p.k[off]) : 0.f;
+      dk_t[j] = ok ? p.dkt[off] : 0.f;
+      dkr[j] = (kFinal && ok) ? p.dk_read[off] : 0.f;
+    }
+#pragma unroll
+    for (int j = 7; j >= 0; --j) {
+      const int r = r0 + j;
+      if (r < valid) {  // uniform across the CTA
+        const float Ap = sA[r][c], dec = sPd[r], bp = sBp[r];
+        const float An = dec * Ap + bp * kc[j] * kc[j];
+        const float dev = __logf(An + p.eps) - centre;
+        const float den = 1.f + fabsf(dev);
+        const float Bf = __expf(-p.ln_x * __fdividef(dev, den));
+        const float ddev = -p.ln_x * dk_t[j] * kc[j] * Bf / (den * den);
+        lam += ddev / (An + p.eps);
+        if (kFinal) {
+          dcacc -= ddev;
+          p.dk[row0 + (size_t)r * gld + c] = __float2bfloat16(dkr[j] + dk_t[j] * Bf + 2.f * lam * bp * kc[j]);
+          float x1 = lam * kc[j] * kc[j], x2 = lam * dec * Ap;
+#pragma unroll
+          for (int o = 16; o >= 1; o >>= 1) {
+            x1 += __shfl_xor_sync(0xffffffffu, x1, o);
+            x2 += __shfl_xor_sync(0xffffffffu, x2, o);
+          }
+          if (lane == 0) { sP1[warp][r] = x1; sP2[warp][r] = x2; }
+        }
+        lam *= dec;
+      }
+    }
+  }
+  if (!kFinal) {
+    p.c_loc[chh * kD + c] = lam;
+    return;
+  }
+#pragma unroll
+  for (int o = 16; o >= 1; o >>= 1) dcacc += __shfl_xor_sync(0xffffffffu, dcacc, o);
+  if (lane == 0) sRed[warp] = dcacc;
+  __syncthreads();
+  if (c < valid) {
+    const size_t s = (size_t)(tok0 + c) * H + h;
+    p.dbeta_atk[s] = __float2bfloat16(sP1[0][c] + sP1[1][c] + sP1[2][c] + sP1[3][c]);
+    p.dg_atk[s] = sP2[0][c] + sP2[1][c] + sP2[2][c] + sP2[3][c];
+  }
+  if (c == 0) p.partC[chh] = sRed[0] + sRed[1] + sRed[2] + sRed[3];
+}
+
+// Sequential carry over a sequence's chunks, last to first.
+__global__ void __launch_bounds__(kD)
+pkda_atk_bwd_carry_kernel(Geo geo, const float* c_loc, const float* sa, float* lam_in, float* dA0) {
+  const int n = blockIdx.x, h = blockIdx.y, H = geo.heads, c = threadIdx.x;
+  const SeqInfo sq = seq_info(geo, n);
+  float lam = 0.f;
+  for (int i = sq.nchunks - 1; i >= 0; --i) {
+    const size_t ch = (size_t)(sq.chunk0 + i) * H + h;
+    lam_in[ch * kD + c] = lam;
+    lam = c_loc[ch * kD + c] + __expf(sa[ch]) * lam;
+  }
+  if (dA0) dA0[((size_t)n * H + h) * kD + c] = lam;
+}
+
+// Deterministic reduction of the per-chunk partial sums of the three per-head
+// parameter gradients.  grid (H), 128 threads.
+__global__ void __launch_bounds__(kD)
+pkda_param_reduce_kernel(Geo geo, const float* partA, const float* partB, const float* partC, float* dA_log,
+                         float* ddt_bias, float* dcentre) {
+  __shared__ float sR[2][4];
+  const int h = blockIdx.x, H = geo.heads, c = threadIdx.x, warp = c >> 5, lane = c & 31;
+  const int nreal = geo.cu_seqlens ? geo.chunk_offsets[geo.n_seqs] : geo.total_chunks;
+  float b = 0.f;
+  for (int ch = 0; ch < nreal; ++ch) b += partB[((size_t)ch * H + h) * kD + c];
+  ddt_bias[h * kD + c] = b;
+  float a = 0.f, cc = 0.f;
+  for (int ch = c; ch < nreal; ch += kD) {
+    a += partA[(size_t)ch * H + h];
+    cc += partC[(size_t)ch * H + h];
+  }
+#pragma unroll
+  for (int o = 16; o >= 1; o >>= 1) {
+    a += __shfl_xor_sync(0xffffffffu, a, o);
+    cc += __shfl_xor_sync(0xffffffffu, cc, o);
+  }
+  if (lane == 0) { sR[0][warp] = a; sR[1][warp] = cc; }
+  __syncthreads();
+  if (c == 0) {
+    dA_log[h] = sR[0][0] + sR[0][1] + sR[0][2] + sR[0][3];
+    dcentre[h] = sR[1][0] + sR[1][1] + sR[1][2] + sR[1][3];
+  }
+}
+
+// ------------------------------------------------------------------ host side
+struct BwdWorkspace {
+  int* chunk_offsets;
+  float* beta_c;
+  bf16 *u, *dF, *dh;
+  float *dk_read, *dkt, *partA, *partB, *partC, *c_loc, *lam_in;
+  size_t bytes;
+};
+
+static BwdWorkspace carve_bwd(const pkda_problem& p, void* base) {
+  BwdWorkspace w;
+  const size_t chunks = (size_t)chunk_bound(p), H = p.heads, tok = p.total_tokens;
+  size_t off = 0;
+  unsigned char* b = static_cast<unsigned char*>(base);
+  auto take = [&](size_t bytes) {
+    void* ptr = b + off;
+    off += align_up(bytes);
+    return ptr;
+  };
+  w.chunk_offsets = static_cast<int*>(take((size_t)(p.n_seqs + 1) * sizeof(int)));
+  w.beta_c = static_cast<float*>(take(chunks * H * kChunk * 4));
+  w.u = static_cast<bf16*>(take(tok * H * kD * 2));
+  w.dF = static_cast<bf16*>(take(tok * H * kD * 2));
+  w.dh = static_cast<bf16*>(take(chunks * H * kD * kD * 2));
+  w.dk_read = static_cast<float*>(take(tok * H * kD * 4));
+  w.dkt = static_cast<float*>(take(tok * H * kD * 4));
+  w.partA = static_cast<float*>(take(chunks * H * 4));
+  w.partB = static_cast<float*>(take(chunks * H * kD * 4));
+  w.partC = static_cast<float*>(take(chunks * H * 4));
+  w.c_loc = static_cast<float*>(take(chunks * H * kD * 4));
+  w.lam_in = static_cast<float*>(take(chunks * H * kD * 4));
+  w.bytes = off;
+  return w;
+}
+
+size_t chunk_bwd_workspace(const pkda_problem& p) { return carve_bwd(p, nullptr).bytes; }
+
+#define PKDA_CHECK_LAUNCH()                                        \
+  do {                                                             \
+    note_launch();                                                 \
+    if (cudaGetLastError() != cudaSuccess) return PKDA_ERR_LAUNCH; \
+  } while (0)
+
+template <typename K>
+static bool set_smem(K kernel, int bytes) {
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess;
+}
+
+int chunk_bwd(const pkda_chunk_bwd_args* a, cudaStream_t st) {
+  const pkda_problem& p = a->p;
+  int rc = check_chunk_problem(p);
+  if (rc != PKDA_OK) return rc;
+  if (p.n_seqs == 0 || p.total_tokens == 0) return PKDA_OK;
+  if (!a->d_o || !a->Aqk || !a->Akk || !a->k_precond || !a->ac_atk || !a->a_atk || !a->sa_atk || !a->w ||
+      !a->kg || !a->v_new || !a->h || !a->qg || !a->dq || !a->dk || !a->dv || !a->dg || !a->dg_atk ||
+      !a->dbeta_atk || !a->dbeta || !a->dA_log || !a->ddt_bias || !a->dlog_atk_scale)
+    return PKDA_ERR_NULL;
+  if (!a->workspace || a->workspace_bytes < chunk_bwd_workspace(p)) return PKDA_ERR_WORKSPACE;
+  BwdWorkspace ws = carve_bwd(p, a->workspace);
+  Geo geo;
+  rc = run_prologue(p, ws.chunk_offsets, ws.beta_c, &geo, st);
+  if (rc != PKDA_OK) return rc;
+
+  const bf16* Aqk = static_cast<const bf16*>(a->Aqk);
+  const bf16* Akk = static_cast<const bf16*>(a->Akk);
+  const bf16* kt = static_cast<const bf16*>(a->k_precond);
+  const float* gc = a->ac_atk;
+  bf16* w = static_cast<bf16*>(a->w);
+  bf16* kg = static_cast<bf16*>(a->kg);
+  bf16* v_new = static_cast<bf16*>(a->v_new);
+  bf16* h = static_cast<bf16*>(a->h);
+  bf16* qg = static_cast<bf16*>(a->qg);
+  if (a->recompute) {
+    // The recompute kernels only read the products, write keys and decay totals.
+    rc = run_forward_stages(p, geo, ws.beta_c, ws.u, const_cast<bf16*>(Aqk), const_cast<bf16*>(Akk),
+                            const_cast<bf16*>(kt), const_cast<float*>(gc), a->a_atk, w, kg, v_new, h, qg,
+                            nullptr, true, st);
+    if (rc != PKDA_OK) return rc;
+  }
+
+  constexpr int VB = 32;
+  ScanBwdParams sp;
+  sp.geo = geo; sp.kg = kg; sp.qg = qg; sp.w = w; sp.Aqk = Aqk; sp.d_o = static_cast<const bf16*>(a->d_o);
+  sp.beta_c = ws.beta_c; sp.gc = gc; sp.dST = a->d_final_state; sp.dh = ws.dh; sp.dF = ws.dF;
+  sp.dS0 = a->d_initial_state;
+  if (!set_smem(pkda_scan_bwd_kernel<VB>, scanb::L<VB>::kSmem)) return PKDA_ERR_LAUNCH;
+  pkda_scan_bwd_kernel<VB><<<p.n_seqs * p.heads * (kD / VB), scanb::kThreads, scanb::L<VB>::kSmem, st>>>(sp);
+  PKDA_CHECK_LAUNCH();
+
+  dim3 gridc(geo.total_chunks, p.heads);
+  IntraBwdParams ip;
+  ip.geo = geo;
+  ip.q = static_cast<const bf16*>(p.q); ip.k = static_cast<const bf16*>(p.k); ip.kt = kt;
+  ip.g = static_cast<const bf16*>(p.g); ip.A_log = p.A_log; ip.dt_bias = p.dt_bias;
+  ip.beta_c = ws.beta_c; ip.gc = gc; ip.Akk = Akk; ip.v_new = v_new; ip.h = h; ip.dh = ws.dh; ip.dF = ws.dF;
+  ip.d_o = static_cast<const bf16*>(a->d_o);
+  ip.dq = static_cast<bf16*>(a->dq); ip.dk_read = ws.dk_read; ip.dv = static_cast<bf16*>(a->dv);
+  ip.dg = static_cast<bf16*>(a->dg); ip.dbeta = static_cast<bf16*>(a->dbeta); ip.dkt = ws.dkt;
+  ip.partA = ws.partA; ip.partB = ws.partB; ip.scale = p.scale;
+  if (!set_smem(pkda_intra_bwd_kernel, ib::kSmem)) return PKDA_ERR_LAUNCH;
+  pkda_intra_bwd_kernel<<<gridc, ib::kThreads, ib::kSmem, st>>>(ip);
+  PKDA_CHECK_LAUNCH();
+
+  AtkBwdParams ap;
+  ap.geo = geo; ap.k = static_cast<const bf16*>(p.k); ap.g_atk = p.g_atk;
+  ap.beta_atk = static_cast<const bf16*>(p.beta_atk); ap.log_atk_scale = p.log_atk_scale;
+  ap.a_start = a->a_atk; ap.dkt = ws.dkt; ap.dk_read = ws.dk_read; ap.lam_in = ws.lam_in; ap.c_loc = ws.c_loc;
+  ap.dk = static_cast<bf16*>(a->dk); ap.dg_atk = a->dg_atk; ap.dbeta_atk = static_cast<bf16*>(a->dbeta_atk);
+  ap.partC = ws.partC; ap.ln_x = logf(p.squash_x); ap.eps = p.squash_eps;
+  pkda_atk_bwd_kernel<false><<<gridc, kD, 0, st>>>(ap);
+  PKDA_CHECK_LAUNCH();
+  pkda_atk_bwd_carry_kernel<<<dim3(p.n_seqs, p.heads), kD, 0, st>>>(geo, ws.c_loc, a->sa_atk, ws.lam_in,
+                                                                   a->d_initial_A_state);
+  PKDA_CHECK_LAUNCH();
+  pkda_atk_bwd_kernel<true><<<gridc, kD, 0, st>>>(ap);
+  PKDA_CHECK_LAUNCH();
+  pkda_param_reduce_kernel<<<p.heads, kD, 0, st>>>(geo, ws.partA, ws.partB, ws.partC, a->dA_log, a->ddt_bias,
+                                                   a->dlog_atk_scale);
+  PKDA_CHECK_LAUNCH();
+  return PKDA_OK;
+}
+
+}  // namespace pkda

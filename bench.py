@@ -1,0 +1,409 @@
+"""PKDA hot-path benchmark.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one forward + backward pass of the chunked PKDA operator over one
+batch of synthetic input (benchmark configuration 1: B=8, T=4096, H=16,
+d_k=d_v=128, chunk 64, bf16, fp32 initial state, all ten input gradients plus
+the initial-state gradients).  With N > 1 (launched by torchrun) every rank runs
+that same workload on its own GPU with its own seed: the operator shards by
+row x head with no data-path collective, so scaling is weak and NCCL is used
+only for the start/stop barriers and the max-over-ranks time.
+
+Rank 0 prints ONE JSON line.  ``value`` is whole-job tokens/s with inputs
+resident in HBM; ``e2e`` is the same pass through the public operator with HOST
+(pinned) buffers and the host<->device copies inside the timed region;
+``roofline`` describes the kernel that took the largest share of the step;
+``cpu_baseline`` is the CPU oracle timed on this box's host cores on a bounded
+sample; ``decode`` reports the recurrent decode step (configuration 3) as
+achieved HBM GB/s.  ``--impl reference`` times the CPU implementation alone.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+METRIC = "PKDA fwd+bwd tokens/s/GPU at T=4096; decode state-update GB/s vs HBM peak"
+WORKLOADS = {
+    # name: (B per GPU, T, H, D)
+    "config1": (8, 4096, 16, 128),
+    "config4": (16, 8192, 16, 128),
+    "profile": (2, 4096, 16, 128),   # small case for ncu captures (working set still > L2)
+}
+C = 64
+# Algorithmic work per (token, head) for D=128, chunk 64 (dense counts).
+FWD_FLOPS = 2 * C * (3 * 128 + 2 * 128) + 6 * 128 * 128 + (2 * C * C) // 3          # 182,955
+FWD_BWD_FLOPS = 3 * FWD_FLOPS                                                        # 548,865
+FWD_BYTES, BWD_BYTES = 1288, 2328
+# Per-kernel algorithmic flops per (token, head): the dense contractions each kernel owns.
+K, V = 128, 128
+STAGE_FLOPS = {
+    "intra_fwd": 2 * (2 * C * K) + 2 * C * K + 2 * C * V + (2 * C * C) // 3,   # M, P, Tm*Kd, Tm*V, inverse
+    "scan_fwd": 2 * (2 * K * V),                                              # W*h, kg^T*F
+    "out_fwd": 2 * K * V + 2 * C * V,                                         # qg*h, P*F
+    "scan_bwd": 3 * (2 * K * V) + 2 * C * V,                                  # kg*dS, qg^T*dO, W^T*dE, P^T*dO
+    "intra_bwd": 3 * (2 * K * V) + 3 * (2 * C * V) + 4 * (2 * C * K),
+}
+DECODE_BYTES_PER_UNIT = 2 * 4 * 128 * 128 + 2 * 4 * 128 + 4 * 2 * 128 + 8 + 2 * 128   # 133,384
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            m = json.load(f)
+        return {"hbm_gbs": m["hbm_gbs"], "bf16_tflops": m["bf16_tflops"],
+                "bf16_tflops_sustained": m.get("bf16_tflops_sustained", m["bf16_tflops"]),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
+            "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-i", str(self.index), "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for r in self.rows:
+            if len(r) < 6:
+                continue
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, r[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def cpu_oracle_rate(T: int, H: int, D: int, repeats: int = 1, threads: int | None = None) -> dict:
+    """Times the CPU oracle (forward + autograd backward) on ONE (row, head) unit of
+    length T and converts to whole-token throughput at H heads."""
+    from delta_feedback_experiment_b200.synthetic import INPUT_NAMES, make_inputs
+    from oracle.pkda_oracle import pkda_oracle_with_grads
+    threads = threads or os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    d = make_inputs(1, T, 1, D, seed=123, dist="unit", dtype=torch.bfloat16, with_state=True)
+    best = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        pkda_oracle_with_grads([d[n] for n in INPUT_NAMES], d["do"],
+                               initial_state=d["initial_state"],
+                               initial_A_state=d["initial_A_state"], dtype=torch.float32)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return {"value": T / (best * H), "unit": "tokens/s", "cores": threads, "kind": "port",
+            "sample": f"1 of B*H (row, head) units, T={T}, d={D}, fwd+bwd on the CPU oracle; "
+                      f"{best:.2f} s per unit, scaled by 1/H={H} to whole-token rate",
+            "seconds_per_unit": best}
+
+
+def run_reference(args, rank: int, world: int) -> None:
+    if rank != 0:
+        return
+    B, T, H, D = WORKLOADS[args.workload]
+    # every step is one bounded sample: one (row, head) unit of the workload
+    rates = []
+    t_all = time.perf_counter()
+    for i in range(args.warmup + args.steps):
+        r = cpu_oracle_rate(T, H, D)
+        if i >= args.warmup:
+            rates.append(r)
+    sec = statistics.mean(x["seconds_per_unit"] for x in rates)
+    value = T / (sec * H)
+    base = rates[0]
+    base["value"] = value
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": f"{args.workload}: B={B} T={T} H={H} d={D} chunk=64 fwd+bwd; each step "
+                               "times one (row, head) unit of it on the host cores"},
+        "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "wall_s": time.perf_counter() - t_all,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_decode(device, steps: int, warmup: int, pk: dict) -> dict:
+    """Configuration 3: B=256, H=32, d=128, fp32 state updated in place, one token per step."""
+    from delta_feedback_experiment_b200 import _lib, fused_recurrent_precond_kda
+    from delta_feedback_experiment_b200.synthetic import INPUT_NAMES, make_inputs
+    B, H, D, NIN = 256, 32, 128, 8
+    d = make_inputs(B, NIN, H, D, seed=300, dist="unit", dtype=torch.bfloat16, with_state=True)
+    dev = {n: d[n].to(device) for n in INPUT_NAMES}
+    S = d["initial_state"].to(device)
+    A = d["initial_A_state"].to(device)
+    ins = [{n: dev[n][:, t:t + 1].contiguous() for n in INPUT_NAMES[:7]} for t in range(NIN)]
+
+    def step(i):
+        fused_recurrent_precond_kda(
+            **ins[i % NIN], A_log=dev["A_log"], dt_bias=dev["dt_bias"], initial_state=S,
+            initial_A_state=A, output_final_state=True, log_atk_scale=dev["log_atk_scale"],
+            inplace_state=True)
+
+    for i in range(warmup):
+        step(i)
+    torch.cuda.synchronize(device)
+    _lib.stage_timing(True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        step(i)
+    e1.record()
+    torch.cuda.synchronize(device)
+    stages = _lib.stage_timing_read()
+    _lib.stage_timing(False)
+    wall_ms = e0.elapsed_time(e1) / steps
+    k_ms, k_n = stages["recurrent"]
+    bytes_per_step = DECODE_BYTES_PER_UNIT * B * H
+    achieved = bytes_per_step / (k_ms / k_n * 1e-3) / 1e9
+    return {
+        "workload": f"config3: B={B} H={H} d={D} fp32 state in place, {steps} sequential 1-token steps",
+        "ms_per_step": wall_ms, "kernel_ms": k_ms / k_n,
+        "state_update_gbs_wall": bytes_per_step / (wall_ms * 1e-3) / 1e9,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / pk["hbm_gbs"], "traffic": None,
+                     "algorithmic_bytes_per_launch": bytes_per_step, "peak_source": pk["source"]},
+        "finite": bool(torch.isfinite(S).all().item()),
+    }
+
+
+def run_ours(args, rank: int, world: int, local_rank: int) -> None:
+    import torch.distributed as dist
+    from delta_feedback_experiment_b200 import _lib, chunk_precond_kda, ops
+    from delta_feedback_experiment_b200.synthetic import INPUT_NAMES, make_inputs
+
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device; there is no CPU path")
+    _lib.load()
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    B, T, H, D = WORKLOADS[args.workload]
+    pk = peaks()
+
+    d = make_inputs(B, T, H, D, seed=1000 + rank, dist="unit", dtype=torch.bfloat16, with_state=True)
+    host = {n: d[n].pin_memory() for n in (*INPUT_NAMES, "do", "initial_state", "initial_A_state")}
+    dev = {n: t.to(device) for n, t in host.items()}
+    lean = bool(args.lean)
+
+    def fwd_bwd(t):
+        leaves = [t[n].requires_grad_(True) for n in INPUT_NAMES]
+        S0 = t["initial_state"].requires_grad_(True)
+        A0 = t["initial_A_state"].requires_grad_(True)
+        kw = dict(zip(INPUT_NAMES, leaves))
+        scale_c = kw.pop("log_atk_scale")
+        o, _, _ = chunk_precond_kda(**kw, initial_state=S0, initial_A_state=A0,
+                                    output_final_state=False, log_atk_scale=scale_c,
+                                    disable_recompute=not lean)
+        grads = torch.autograd.grad(o, leaves + [S0, A0], t["do"])
+        return o, grads
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    for _ in range(args.warmup):
+        fwd_bwd(dev)
+    barrier()
+    launches0 = ops.LAUNCHES
+    _lib.stage_timing(True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            fwd_bwd(dev)
+        e1.record()
+        barrier()
+    total_ms = e0.elapsed_time(e1)
+    stages = _lib.stage_timing_read()
+    _lib.stage_timing(False)
+    launches = ops.LAUNCHES - launches0
+    if world > 1:
+        tmax = torch.tensor([total_ms], device=device)
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        total_ms = float(tmax.item())
+        lsum = torch.tensor([launches], device=device, dtype=torch.int64)
+        dist.all_reduce(lsum)
+        launches = int(lsum.item())
+    ms_per_step = total_ms / args.steps
+    value = world * B * T / (ms_per_step * 1e-3)
+
+    # ---- end to end through the public operator with host buffers
+    if args.no_e2e:
+        if world > 1:
+            dist.destroy_process_group()
+        if rank == 0:
+            print(json.dumps({"note": "profiling run (no e2e leg): not a benchmark line",
+                              "ms_per_step": ms_per_step,
+                              "stages_ms_per_step": {n: ms / args.steps for n, (ms, _) in stages.items()}}))
+        return
+    out_host = None
+    e2e_steps = max(1, min(args.steps, 5))
+
+    def e2e_step():
+        nonlocal out_host
+        t = {n: h.to(device, non_blocking=True) for n, h in host.items()}
+        o, grads = fwd_bwd(t)
+        outs = [o, *grads]
+        if out_host is None:
+            out_host = [torch.empty(x.shape, dtype=x.dtype, pin_memory=True) for x in outs]
+        for dst, src in zip(out_host, outs):
+            dst.copy_(src, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+    if world > 1:
+        tmax = torch.tensor([e2e_ms], device=device)
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        e2e_ms = float(tmax.item())
+    h2d = sum(t.numel() * t.element_size() for t in host.values())
+    d2h = sum(t.numel() * t.element_size() for t in out_host)
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    # ---- roofline of the dominant kernel (largest share of the timed step)
+    units = B * T * H  # (token, head) units one launch processes
+    per_launch = {name: ms / n for name, (ms, n) in stages.items()}
+    step_kernel_ms = sum(ms for ms, _ in stages.values()) / args.steps
+    top = max((n for n in stages if n in STAGE_FLOPS), key=lambda n: stages[n][0])
+    top_ms = per_launch[top]
+    achieved_tf = STAGE_FLOPS[top] * units / (top_ms * 1e-3) / 1e12
+    peak_tf = pk["bf16_tflops_sustained"]
+    roofline = {
+        "bound": "tensor", "kernel": f"pkda_{top}_kernel", "achieved": achieved_tf, "peak": peak_tf,
+        "unit": "TFLOP/s", "frac": achieved_tf / peak_tf, "traffic": None,
+        "launch_ms": top_ms, "algorithmic_flops_per_launch": STAGE_FLOPS[top] * units,
+        "peak_source": pk["source"] + " (sustained bf16 GEMM; kernel timed inside a long step)",
+        "share_of_step": stages[top][0] / sum(ms for ms, _ in stages.values()),
+        "whole_step": {
+            "tensor_frac": FWD_BWD_FLOPS * units / (ms_per_step * 1e-3) / 1e12 / peak_tf,
+            "hbm_frac": (FWD_BYTES + BWD_BYTES) * units / (ms_per_step * 1e-3) / 1e9 / pk["hbm_gbs"],
+            "algorithmic_flops": FWD_BWD_FLOPS * units,
+            "algorithmic_bytes": (FWD_BYTES + BWD_BYTES) * units,
+        },
+    }
+    line = {
+        "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {
+            "workload": f"{args.workload}: B={B}/GPU T={T} H={H} d_k=d_v={D} chunk=64 bf16 fwd+bwd, "
+                        "fp32 initial state, ten input gradients + initial-state gradients",
+            "saving": "lean (recompute)" if lean else "full (retained intermediates)",
+            "l2": "no flush: each of q,k,v,g,dO is larger than the 126 MB L2",
+            "parallelism": f"{world} independent replica shard(s) by row x head, no collective",
+        },
+        "roofline": roofline,
+        "e2e": {"value": world * B * T / (e2e_ms * 1e-3), "unit": "tokens/s",
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
+                "steps": e2e_steps},
+        "gpu_launches": launches,
+        "clocks": clocks.summary(),
+        "stages_ms_per_step": {n: ms / args.steps for n, (ms, _) in stages.items()},
+        "kernel_ms_per_step": step_kernel_ms,
+    }
+    if not args.no_decode:
+        line["decode"] = run_decode(device, args.decode_steps, 16, pk)
+    if not args.no_cpu:
+        cb = cpu_oracle_rate(T, H, D)
+        line["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--workload", choices=tuple(WORKLOADS), default="config1")
+    ap.add_argument("--lean", type=int, default=0, help="1: recompute w,kg,v_new,h,qg in backward")
+    ap.add_argument("--decode-steps", type=int, default=1024)
+    ap.add_argument("--no-decode", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="profiling aid: device-resident leg only")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+    else:
+        if world > 1:
+            args.no_decode = True if rank != 0 else args.no_decode
+        run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

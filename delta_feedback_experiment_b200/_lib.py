@@ -73,6 +73,7 @@ EXPORTS = (
     "pkda_chunk_bwd_workspace_bytes", "pkda_chunk_bwd", "pkda_abi_version",
     "pkda_status_string", "pkda_sizeof_problem", "pkda_sizeof_recurrent_args",
     "pkda_sizeof_chunk_fwd_args", "pkda_sizeof_chunk_bwd_args", "pkda_last_launch_count",
+    "pkda_stage_count", "pkda_stage_name", "pkda_stage_timing", "pkda_stage_timing_read",
 )
 
 _lib: Optional[C.CDLL] = None
@@ -96,6 +97,13 @@ def _configure(lib: C.CDLL) -> None:
                  "pkda_sizeof_chunk_fwd_args", "pkda_sizeof_chunk_bwd_args"):
         getattr(lib, name).restype = C.c_size_t
     lib.pkda_last_launch_count.restype = C.c_int
+    lib.pkda_stage_count.restype = C.c_int
+    lib.pkda_stage_name.argtypes = [C.c_int]
+    lib.pkda_stage_name.restype = C.c_char_p
+    lib.pkda_stage_timing.argtypes = [C.c_int]
+    lib.pkda_stage_timing.restype = C.c_int
+    lib.pkda_stage_timing_read.argtypes = [C.POINTER(C.c_float), C.POINTER(C.c_int), C.c_int]
+    lib.pkda_stage_timing_read.restype = C.c_int
 
 
 def load() -> C.CDLL:
@@ -151,3 +159,17 @@ def current_stream() -> int:
 
 def last_launch_count() -> int:
     return int(load().pkda_last_launch_count())
+
+
+def stage_timing(enable: bool) -> None:
+    check(load().pkda_stage_timing(1 if enable else 0), "pkda_stage_timing")
+
+
+def stage_timing_read() -> dict:
+    """``{stage name: (total ms, launches)}`` since the last read."""
+    lib = load()
+    n = lib.pkda_stage_count()
+    ms = (C.c_float * n)()
+    cnt = (C.c_int * n)()
+    check(lib.pkda_stage_timing_read(ms, cnt, n), "pkda_stage_timing_read")
+    return {lib.pkda_stage_name(i).decode(): (float(ms[i]), int(cnt[i])) for i in range(n) if cnt[i]}

@@ -1,11 +1,46 @@
 // extern "C" surface of libpkda_b200.so (declared in include/pkda_b200.h).
+#include <vector>
+
 #include "pkda_launch.h"
 
 namespace pkda {
 
 static thread_local int g_launches = 0;
-void note_launch() { ++g_launches; }
 void reset_launch_count() { g_launches = 0; }
+
+// Optional per-stage timing (used by the benchmark): one event pair per launch,
+// taken from a pool that grows only while timing is enabled.
+struct StageTimer {
+  bool on = false;
+  std::vector<cudaEvent_t> events;  // 2 per record
+  std::vector<int> stage;
+  size_t used = 0;
+  bool open = false;
+};
+static StageTimer g_timer;
+
+void begin_stage(int stage, cudaStream_t st) {
+  if (!g_timer.on) return;
+  if (g_timer.events.size() < 2 * (g_timer.used + 1)) {
+    cudaEvent_t a, b;
+    if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) { g_timer.on = false; return; }
+    g_timer.events.push_back(a);
+    g_timer.events.push_back(b);
+  }
+  if (g_timer.stage.size() <= g_timer.used) g_timer.stage.push_back(stage);
+  else g_timer.stage[g_timer.used] = stage;
+  cudaEventRecord(g_timer.events[2 * g_timer.used], st);
+  g_timer.open = true;
+}
+
+void end_stage(cudaStream_t st) {
+  ++g_launches;
+  if (g_timer.on && g_timer.open) {
+    cudaEventRecord(g_timer.events[2 * g_timer.used + 1], st);
+    ++g_timer.used;
+    g_timer.open = false;
+  }
+}
 
 int check_problem(const pkda_problem& p) {
   if (p.n_seqs < 0 || p.total_tokens < 0 || p.heads <= 0 || p.head_dim <= 0) return PKDA_ERR_SHAPE;
@@ -85,5 +120,36 @@ size_t pkda_sizeof_recurrent_args(void) { return sizeof(pkda_recurrent_args); }
 size_t pkda_sizeof_chunk_fwd_args(void) { return sizeof(pkda_chunk_fwd_args); }
 size_t pkda_sizeof_chunk_bwd_args(void) { return sizeof(pkda_chunk_bwd_args); }
 int pkda_last_launch_count(void) { return pkda::g_launches; }
+
+int pkda_stage_count(void) { return pkda::kStageCount; }
+
+const char* pkda_stage_name(int stage) {
+  static const char* names[] = {"chunk_offsets", "pack_beta", "atk_local", "atk_carry", "intra_fwd", "scan_fwd",
+                                "out_fwd", "scan_bwd", "intra_bwd", "atk_bwd_local", "atk_bwd_carry",
+                                "atk_bwd_final", "param_reduce", "recurrent"};
+  return (stage >= 0 && stage < pkda::kStageCount) ? names[stage] : "?";
+}
+
+int pkda_stage_timing(int enable) {
+  pkda::g_timer.on = enable != 0;
+  pkda::g_timer.used = 0;
+  pkda::g_timer.open = false;
+  return PKDA_OK;
+}
+
+int pkda_stage_timing_read(float* ms, int* counts, int n_stages) {
+  if (!ms || !counts) return PKDA_ERR_NULL;
+  for (int i = 0; i < n_stages; ++i) { ms[i] = 0.f; counts[i] = 0; }
+  pkda::StageTimer& t = pkda::g_timer;
+  for (size_t r = 0; r < t.used; ++r) {
+    if (cudaEventSynchronize(t.events[2 * r + 1]) != cudaSuccess) return PKDA_ERR_LAUNCH;
+    float e = 0.f;
+    if (cudaEventElapsedTime(&e, t.events[2 * r], t.events[2 * r + 1]) != cudaSuccess) return PKDA_ERR_LAUNCH;
+    const int s = t.stage[r];
+    if (s >= 0 && s < n_stages) { ms[s] += e; counts[s] += 1; }
+  }
+  t.used = 0;
+  return PKDA_OK;
+}
 
 }  // extern "C"

@@ -810,7 +810,7 @@ size_t chunk_bwd_workspace(const pkda_problem& p) { return carve_bwd(p, nullptr)
 
 #define PKDA_CHECK_LAUNCH()                                        \
   do {                                                             \
-    note_launch();                                                 \
+    end_stage(st);                                                 \
     if (cudaGetLastError() != cudaSuccess) return PKDA_ERR_LAUNCH; \
   } while (0)
 
@@ -857,6 +857,7 @@ int chunk_bwd(const pkda_chunk_bwd_args* a, cudaStream_t st) {
   sp.beta_c = ws.beta_c; sp.gc = gc; sp.dST = a->d_final_state; sp.dh = ws.dh; sp.dF = ws.dF;
   sp.dS0 = a->d_initial_state;
   if (!set_smem(pkda_scan_bwd_kernel<VB>, scanb::L<VB>::kSmem)) return PKDA_ERR_LAUNCH;
+  begin_stage(kStageScanBwd, st);
   pkda_scan_bwd_kernel<VB><<<p.n_seqs * p.heads * (kD / VB), scanb::kThreads, scanb::L<VB>::kSmem, st>>>(sp);
   PKDA_CHECK_LAUNCH();
 
@@ -871,6 +872,7 @@ int chunk_bwd(const pkda_chunk_bwd_args* a, cudaStream_t st) {
   ip.dg = static_cast<bf16*>(a->dg); ip.dbeta = static_cast<bf16*>(a->dbeta); ip.dkt = ws.dkt;
   ip.partA = ws.partA; ip.partB = ws.partB; ip.scale = p.scale;
   if (!set_smem(pkda_intra_bwd_kernel, ib::kSmem)) return PKDA_ERR_LAUNCH;
+  begin_stage(kStageIntraBwd, st);
   pkda_intra_bwd_kernel<<<gridc, ib::kThreads, ib::kSmem, st>>>(ip);
   PKDA_CHECK_LAUNCH();
 
@@ -880,13 +882,17 @@ int chunk_bwd(const pkda_chunk_bwd_args* a, cudaStream_t st) {
   ap.a_start = a->a_atk; ap.dkt = ws.dkt; ap.dk_read = ws.dk_read; ap.lam_in = ws.lam_in; ap.c_loc = ws.c_loc;
   ap.dk = static_cast<bf16*>(a->dk); ap.dg_atk = a->dg_atk; ap.dbeta_atk = static_cast<bf16*>(a->dbeta_atk);
   ap.partC = ws.partC; ap.ln_x = logf(p.squash_x); ap.eps = p.squash_eps;
+  begin_stage(kStageAtkBwdLocal, st);
   pkda_atk_bwd_kernel<false><<<gridc, kD, 0, st>>>(ap);
   PKDA_CHECK_LAUNCH();
+  begin_stage(kStageAtkBwdCarry, st);
   pkda_atk_bwd_carry_kernel<<<dim3(p.n_seqs, p.heads), kD, 0, st>>>(geo, ws.c_loc, a->sa_atk, ws.lam_in,
                                                                    a->d_initial_A_state);
   PKDA_CHECK_LAUNCH();
+  begin_stage(kStageAtkBwdFinal, st);
   pkda_atk_bwd_kernel<true><<<gridc, kD, 0, st>>>(ap);
   PKDA_CHECK_LAUNCH();
+  begin_stage(kStageParamReduce, st);
   pkda_param_reduce_kernel<<<p.heads, kD, 0, st>>>(geo, ws.partA, ws.partB, ws.partC, a->dA_log, a->ddt_bias,
                                                    a->dlog_atk_scale);
   PKDA_CHECK_LAUNCH();

@@ -594,9 +594,9 @@ static bool set_smem(K kernel, int bytes) {
   return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess;
 }
 
-#define PKDA_CHECK_LAUNCH()                                   \
-  do {                                                        \
-    note_launch();                                            \
+#define PKDA_CHECK_LAUNCH()                                        \
+  do {                                                             \
+    end_stage(st);                                                 \
     if (cudaGetLastError() != cudaSuccess) return PKDA_ERR_LAUNCH; \
   } while (0)
 
@@ -627,9 +627,11 @@ int run_forward_stages(const pkda_problem& p, const Geo& geo, const float* beta_
   dim3 gridc(chunks, p.heads);
   if (recompute) {
     if (!set_smem(pkda_intra_fwd_kernel<true>, intra::kSmem)) return PKDA_ERR_LAUNCH;
+    begin_stage(kStageIntraFwd, st);
     pkda_intra_fwd_kernel<true><<<gridc, intra::kThreads, intra::kSmem, st>>>(ip);
   } else {
     if (!set_smem(pkda_intra_fwd_kernel<false>, intra::kSmem)) return PKDA_ERR_LAUNCH;
+    begin_stage(kStageIntraFwd, st);
     pkda_intra_fwd_kernel<false><<<gridc, intra::kThreads, intra::kSmem, st>>>(ip);
   }
   PKDA_CHECK_LAUNCH();
@@ -641,9 +643,11 @@ int run_forward_stages(const pkda_problem& p, const Geo& geo, const float* beta_
   dim3 grids(p.n_seqs * p.heads * (kD / VB));
   if (recompute) {
     if (!set_smem(pkda_scan_fwd_kernel<VB, true>, scan::L<VB>::kSmem)) return PKDA_ERR_LAUNCH;
+    begin_stage(kStageScanFwd, st);
     pkda_scan_fwd_kernel<VB, true><<<grids, scan::kThreads, scan::L<VB>::kSmem, st>>>(sp);
   } else {
     if (!set_smem(pkda_scan_fwd_kernel<VB, false>, scan::L<VB>::kSmem)) return PKDA_ERR_LAUNCH;
+    begin_stage(kStageScanFwd, st);
     pkda_scan_fwd_kernel<VB, false><<<grids, scan::kThreads, scan::L<VB>::kSmem, st>>>(sp);
   }
   PKDA_CHECK_LAUNCH();
@@ -652,10 +656,12 @@ int run_forward_stages(const pkda_problem& p, const Geo& geo, const float* beta_
 
 int run_prologue(const pkda_problem& p, int* chunk_offsets, float* beta_c, Geo* geo, cudaStream_t st) {
   if (p.cu_seqlens) {
+    begin_stage(kStageOffsets, st);
     pkda_chunk_offsets_kernel<<<1, 32, 0, st>>>(p.cu_seqlens, p.n_seqs, chunk_offsets);
     PKDA_CHECK_LAUNCH();
   }
   *geo = make_geo(p, chunk_offsets);
+  begin_stage(kStagePackBeta, st);
   pkda_pack_beta_kernel<<<geo->total_chunks, 256, 0, st>>>(*geo, static_cast<const bf16*>(p.beta), beta_c);
   PKDA_CHECK_LAUNCH();
   return PKDA_OK;
@@ -676,9 +682,11 @@ int chunk_fwd(const pkda_chunk_fwd_args* a, cudaStream_t st) {
   if (rc != PKDA_OK) return rc;
 
   dim3 gridc(geo.total_chunks, p.heads);
+  begin_stage(kStageAtkLocal, st);
   pkda_atk_local_kernel<<<gridc, kD, 0, st>>>(geo, static_cast<const bf16*>(p.k), p.g_atk,
                                               static_cast<const bf16*>(p.beta_atk), a->ac_atk, a->sa_atk);
   PKDA_CHECK_LAUNCH();
+  begin_stage(kStageAtkCarry, st);
   pkda_atk_carry_kernel<<<dim3(p.n_seqs, p.heads), kD, 0, st>>>(geo, a->ac_atk, a->sa_atk, p.initial_A_state,
                                                                a->a_atk, a->final_A_state);
   PKDA_CHECK_LAUNCH();
@@ -695,6 +703,7 @@ int chunk_fwd(const pkda_chunk_fwd_args* a, cudaStream_t st) {
   op.Aqk = static_cast<const bf16*>(a->Aqk); op.v_new = static_cast<const bf16*>(a->v_new);
   op.beta_c = ws.beta_c; op.o = static_cast<bf16*>(a->o);
   if (!set_smem(pkda_out_fwd_kernel, outk::kSmem)) return PKDA_ERR_LAUNCH;
+  begin_stage(kStageOutFwd, st);
   pkda_out_fwd_kernel<<<gridc, outk::kThreads, outk::kSmem, st>>>(op);
   PKDA_CHECK_LAUNCH();
   return PKDA_OK;

@@ -8,7 +8,17 @@
 
 namespace pkda {
 
-void note_launch();
+// Kernel stages, for launch accounting and the optional per-stage timing.
+enum Stage {
+  kStageOffsets = 0, kStagePackBeta, kStageAtkLocal, kStageAtkCarry, kStageIntraFwd, kStageScanFwd,
+  kStageOutFwd, kStageScanBwd, kStageIntraBwd, kStageAtkBwdLocal, kStageAtkBwdCarry, kStageAtkBwdFinal,
+  kStageParamReduce, kStageRecurrent, kStageCount
+};
+
+// begin_stage / end_stage bracket every kernel launch: they count launches and,
+// when stage timing is switched on, record a CUDA event pair on the stream.
+void begin_stage(int stage, cudaStream_t st);
+void end_stage(cudaStream_t st);
 void reset_launch_count();
 
 // Validates the fields every entry point relies on.

@@ -138,8 +138,9 @@ pkda_recurrent_kernel(const RecParams p) {
 template <int D, typename T>
 static int launch_rec(const RecParams& rp, cudaStream_t st) {
   dim3 grid(rp.geo.n_seqs * rp.geo.heads), block(RecCfg<D>::kThreads);
+  begin_stage(kStageRecurrent, st);
   pkda_recurrent_kernel<D, T><<<grid, block, 0, st>>>(rp);
-  note_launch();
+  end_stage(st);
   return cudaGetLastError() == cudaSuccess ? PKDA_OK : PKDA_ERR_LAUNCH;
 }
 

@@ -14,6 +14,15 @@ from . import _lib
 
 CHUNK_SIZE = _lib.CHUNK
 
+LAUNCHES = 0
+"""Kernels enqueued through this module since import (launch accounting)."""
+
+
+def _count(lib) -> None:
+    global LAUNCHES
+    LAUNCHES += int(lib.pkda_last_launch_count())
+
+
 _DTYPES = {torch.bfloat16: _lib.PKDA_BF16, torch.float32: _lib.PKDA_F32}
 
 
@@ -118,6 +127,7 @@ def recurrent_forward(q, k, v, g, g_atk, beta_atk, beta, A_log, dt_bias, log_atk
             A = torch.empty((N, H, D), device=q.device, dtype=torch.float32)
         args.final_state, args.final_A_state = S.data_ptr(), A.data_ptr()
     _lib.check(lib.pkda_recurrent_fwd(C.byref(args), _lib.current_stream()), "pkda_recurrent_fwd")
+    _count(lib)
     return o, S, A
 
 
@@ -170,6 +180,7 @@ def chunk_forward(q, k, v, g, g_atk, beta_atk, beta, A_log, dt_bias, log_atk_sca
     ws = torch.empty((max(nbytes, 16),), device=dev, dtype=torch.uint8)
     args.workspace, args.workspace_bytes = ws.data_ptr(), nbytes
     _lib.check(lib.pkda_chunk_fwd(C.byref(args), _lib.current_stream()), "pkda_chunk_fwd")
+    _count(lib)
     return o, S, A, saved
 
 
@@ -225,5 +236,6 @@ def chunk_backward(q, k, v, g, g_atk, beta_atk, beta, A_log, dt_bias, log_atk_sc
     ws = torch.empty((max(nbytes, 16),), device=dev, dtype=torch.uint8)
     args.workspace, args.workspace_bytes = ws.data_ptr(), nbytes
     _lib.check(lib.pkda_chunk_bwd(C.byref(args), _lib.current_stream()), "pkda_chunk_bwd")
+    _count(lib)
     grads = [dq, dk, dv, dg, dg_atk, dbeta_atk, dbeta, dA_log, ddt_bias, dcentre]
     return grads, dS0, dA0

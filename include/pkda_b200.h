@@ -154,8 +154,21 @@ size_t pkda_sizeof_problem(void);
 size_t pkda_sizeof_recurrent_args(void);
 size_t pkda_sizeof_chunk_fwd_args(void);
 size_t pkda_sizeof_chunk_bwd_args(void);
-/* Number of kernels the last call of each kind enqueued (for launch accounting). */
+/* Number of kernels the last entry-point call enqueued (for launch accounting). */
 int pkda_last_launch_count(void);
+
+/*
+ * Optional per-kernel timing for benchmarks.  pkda_stage_timing(1) makes every
+ * later launch record a CUDA event pair on its stream (events come from a pool
+ * that grows with cudaEventCreate; not for use under stream capture);
+ * pkda_stage_timing_read waits for the recorded events, adds elapsed
+ * milliseconds and launch counts per stage into ms[0..n) / counts[0..n) and
+ * clears the records.  Stages are numbered 0 .. pkda_stage_count()-1.
+ */
+int pkda_stage_count(void);
+const char* pkda_stage_name(int stage);
+int pkda_stage_timing(int enable);
+int pkda_stage_timing_read(float* ms, int* counts, int n_stages);
 
 #ifdef __cplusplus
 }

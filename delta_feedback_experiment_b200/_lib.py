@@ -74,6 +74,7 @@ EXPORTS = (
     "pkda_status_string", "pkda_sizeof_problem", "pkda_sizeof_recurrent_args",
     "pkda_sizeof_chunk_fwd_args", "pkda_sizeof_chunk_bwd_args", "pkda_last_launch_count",
     "pkda_stage_count", "pkda_stage_name", "pkda_stage_timing", "pkda_stage_timing_read",
+    "pkda_static_scratch_bytes", "pkda_chunk_fwd_static",
 )
 
 _lib: Optional[C.CDLL] = None
@@ -85,6 +86,9 @@ def _configure(lib: C.CDLL) -> None:
     lib.pkda_recurrent_fwd.restype = C.c_int
     lib.pkda_chunk_fwd.argtypes = [C.POINTER(ChunkFwdArgs), C.c_void_p]
     lib.pkda_chunk_fwd.restype = C.c_int
+    lib.pkda_chunk_fwd_static.argtypes = [C.POINTER(ChunkFwdArgs), C.c_void_p]
+    lib.pkda_chunk_fwd_static.restype = C.c_int
+    lib.pkda_static_scratch_bytes.restype = C.c_size_t
     lib.pkda_chunk_bwd.argtypes = [C.POINTER(ChunkBwdArgs), C.c_void_p]
     lib.pkda_chunk_bwd.restype = C.c_int
     for name in ("pkda_chunk_fwd_workspace_bytes", "pkda_chunk_bwd_workspace_bytes"):

@@ -111,6 +111,7 @@ const char* pkda_status_string(int status) {
     case PKDA_ERR_WORKSPACE: return "workspace missing or too small";
     case PKDA_ERR_LAUNCH: return "kernel launch failed";
     case PKDA_ERR_ALIGN: return "pointer not 16-byte aligned";
+    case PKDA_ERR_STATIC_LIMIT: return "problem exceeds the built-in static scratch (use pkda_chunk_fwd with a workspace)";
     default: return "unknown status";
   }
 }

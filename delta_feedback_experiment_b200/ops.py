@@ -239,3 +239,43 @@ def chunk_backward(q, k, v, g, g_atk, beta_atk, beta, A_log, dt_bias, log_atk_sc
     _count(lib)
     grads = [dq, dk, dv, dg, dg_atk, dbeta_atk, dbeta, dA_log, ddt_bias, dcentre]
     return grads, dS0, dA0
+
+
+def static_scratch_bytes() -> int:
+    return int(_lib.load().pkda_static_scratch_bytes())
+
+
+def chunk_forward_static(q, k, v, g, g_atk, beta_atk, beta, A_log, dt_bias, log_atk_scale, scale,
+                         x, eps, o, saved, initial_state=None, initial_A_state=None,
+                         final_state=None, final_A_state=None):
+    """Chunked forward through ``pkda_chunk_fwd_static``: for hosts that must not
+    allocate device memory while the operator runs.  The caller supplies every
+    buffer -- contiguous bf16 inputs, the output ``o`` and the eleven
+    intermediates ``saved`` (shapes of ``intermediate_meta``), optionally the
+    fp32 final-state buffers -- and the library takes its scratch from the fixed
+    array built into it, so nothing is allocated here or below.  Raises
+    ``RuntimeError`` when the problem needs more scratch than that array has
+    (``static_scratch_bytes()``).  Calls share the array: do not let two of them
+    overlap on the GPU, and make the first call on a device outside stream
+    capture."""
+    _require_cuda(q, k, v, g, g_atk, beta_atk, beta, o)
+    lib = _lib.load()
+    tensors = (q, k, v, g, g_atk, beta_atk, beta, A_log, dt_bias, log_atk_scale)
+    if not all(t.is_contiguous() for t in tensors) or g_atk.dtype != torch.float32:
+        raise RuntimeError("the no-allocation entry point needs contiguous inputs (fp32 g_atk)")
+    keep: list = []
+    p = _problem(q, k, v, g, g_atk, beta_atk, beta, A_log, dt_bias, log_atk_scale, scale, x, eps,
+                 initial_state, initial_A_state, None, keep)
+    if len(saved) != 11:
+        raise RuntimeError("eleven intermediate buffers are required")
+    args = _lib.ChunkFwdArgs()
+    args.p = p
+    args.o = o.data_ptr()
+    if final_state is not None:
+        args.final_state, args.final_A_state = final_state.data_ptr(), final_A_state.data_ptr()
+    (args.Aqk, args.Akk, args.k_precond, args.ac_atk, args.a_atk, args.sa_atk, args.w, args.kg,
+     args.v_new, args.h, args.qg) = [t.data_ptr() for t in saved]
+    _lib.check(lib.pkda_chunk_fwd_static(C.byref(args), _lib.current_stream()),
+               "pkda_chunk_fwd_static")
+    _count(lib)
+    return o

@@ -38,7 +38,8 @@ enum pkda_status {
   PKDA_ERR_DTYPE = 3,         /* unsupported activation dtype for this entry */
   PKDA_ERR_WORKSPACE = 4,     /* workspace missing or too small */
   PKDA_ERR_LAUNCH = 5,        /* a kernel launch failed (see cudaGetLastError) */
-  PKDA_ERR_ALIGN = 6          /* a pointer is not 16-byte aligned */
+  PKDA_ERR_ALIGN = 6,         /* a pointer is not 16-byte aligned */
+  PKDA_ERR_STATIC_LIMIT = 7   /* problem needs more scratch than the built-in static array holds */
 };
 
 enum pkda_dtype { PKDA_BF16 = 0, PKDA_F32 = 1 };
@@ -116,6 +117,35 @@ typedef struct pkda_chunk_fwd_args {
 
 size_t pkda_chunk_fwd_workspace_bytes(const pkda_problem* p);
 int pkda_chunk_fwd(const pkda_chunk_fwd_args* args, void* cuda_stream);
+
+/*
+ * pkda_chunk_fwd for hosts that cannot hand over scratch memory.  (No
+ * counterpart in the reference, whose kernels always allocate through torch.)
+ * Some embedders own every byte of device memory themselves and forbid the
+ * code they call from allocating: a serving engine that sized its pools at
+ * start-up, a plugin running inside another framework's execution callback
+ * where cudaMalloc would stall the whole device, a hard real-time loop.  For
+ * them this entry point runs exactly the same kernels as pkda_chunk_fwd but
+ * takes its scratch from a fixed array of PKDA_STATIC_SCRATCH_BYTES that is part
+ * of the library image (so every GPU that loads the library carries those
+ * bytes until the process exits).  args->workspace / workspace_bytes are
+ * ignored; inputs, outputs and the eleven intermediates are still the
+ * caller's.  It calls no cudaMalloc/cudaFree and no allocating library routine.
+ *
+ *  - Limit: pkda_chunk_fwd_workspace_bytes(&args->p) must not exceed
+ *    pkda_static_scratch_bytes() (16 MiB: about 60,000 (token, head) units,
+ *    e.g. B*T = 3,840 tokens at H = 16); larger problems return
+ *    PKDA_ERR_STATIC_LIMIT and launch nothing.
+ *  - The first call on each device looks up the array's device address (with
+ *    that device current).  Make that first call outside any stream capture.
+ *  - All calls on a device share the one array and it keeps whatever the last
+ *    call left; the kernels overwrite every byte they later read, so nothing
+ *    needs clearing.  Two calls whose kernels overlap on the GPU (different
+ *    streams, no ordering between them) race on it: serialise them.
+ */
+#define PKDA_STATIC_SCRATCH_BYTES (16u << 20)
+size_t pkda_static_scratch_bytes(void);
+int pkda_chunk_fwd_static(const pkda_chunk_fwd_args* args, void* cuda_stream);
 
 /*
  * Chunked backward.  Replaces kda_gate_chunk_cumsum + chunk_precond_kda_bwd +

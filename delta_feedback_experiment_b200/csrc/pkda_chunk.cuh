@@ -17,38 +17,108 @@ __device__ __forceinline__ bool level_pair_ok(int i, int j, int lvl) {
   return (((i ^ j) & ~(2 * lvl - 1)) == 0) && (i & lvl) && !(j & lvl);
 }
 
+constexpr int kLdG = kD + 8;                  // smem row stride of a [64][128] fp32 array
+
+// 2^x by the hardware approximation (flushes denormal results to zero, which is
+// what the gating factors want: every argument here is <= 0).
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ void scale8(uint4& x, const float (&f)[8]) {
+  uint32_t* w = reinterpret_cast<uint32_t*>(&x);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 v = unpack_bf16(w[j]);
+    w[j] = pack_bf16(v.x * f[2 * j], v.y * f[2 * j + 1]);
+  }
+}
+
 // Builds the gated operands of one level from the log2-domain cumulative decay
-// sG [64][128]: rows with bit lvl set get X * 2^(G_r - G_ref) (into sXq from sQ
+// sG [64][kLdG]: rows with bit lvl set get X * 2^(G_r - G_ref) (into sXq from sQ
 // and sXk from sK), the others get Y * 2^(G_ref - G_r) (into sY from sKt), where
 // ref is the first row of the upper half of the row's 2*lvl block.  Rows of the
 // other kind are left untouched (their products are masked out).  Null
-// destinations are skipped.  sFac (optional, fp32 [64][128]) receives the factor
-// each row used.
+// destinations are skipped.  sFac (optional, fp32 [64][kLdG]) receives the factor
+// each row used.  Eight channels per thread and step (128-bit accesses).
 __device__ __forceinline__ void stage_level(bf16* sXq, bf16* sXk, bf16* sY, const bf16* sQ, const bf16* sK,
                                             const bf16* sKt, const float* sG, int lvl, int tid, int nthreads,
                                             float* sFac = nullptr) {
-  for (int idx = tid; idx < kChunk * kD / 2; idx += nthreads) {
-    const int r = idx >> 6, c2 = (idx & 63) << 1;
+  for (int idx = tid; idx < kChunk * kD / 8; idx += nthreads) {
+    const int r = idx >> 4, c8 = (idx & 15) << 3;
     const int ref = (r & ~(2 * lvl - 1)) + lvl;
-    const float2 Gr = *reinterpret_cast<const float2*>(sG + r * kD + c2);
-    const float2 Gf = *reinterpret_cast<const float2*>(sG + ref * kD + c2);
-    if (r & lvl) {
-      const float f0 = exp2f(Gr.x - Gf.x), f1 = exp2f(Gr.y - Gf.y);
-      if (sFac) *reinterpret_cast<float2*>(sFac + r * kD + c2) = make_float2(f0, f1);
+    const bool upper = (r & lvl) != 0;
+    const float4 a0 = *reinterpret_cast<const float4*>(sG + r * kLdG + c8);
+    const float4 a1 = *reinterpret_cast<const float4*>(sG + r * kLdG + c8 + 4);
+    const float4 b0 = *reinterpret_cast<const float4*>(sG + ref * kLdG + c8);
+    const float4 b1 = *reinterpret_cast<const float4*>(sG + ref * kLdG + c8 + 4);
+    const float sgn = upper ? 1.f : -1.f;
+    float f[8];
+    f[0] = ex2(sgn * (a0.x - b0.x)); f[1] = ex2(sgn * (a0.y - b0.y));
+    f[2] = ex2(sgn * (a0.z - b0.z)); f[3] = ex2(sgn * (a0.w - b0.w));
+    f[4] = ex2(sgn * (a1.x - b1.x)); f[5] = ex2(sgn * (a1.y - b1.y));
+    f[6] = ex2(sgn * (a1.z - b1.z)); f[7] = ex2(sgn * (a1.w - b1.w));
+    if (sFac) {
+      *reinterpret_cast<float4*>(sFac + r * kLdG + c8) = make_float4(f[0], f[1], f[2], f[3]);
+      *reinterpret_cast<float4*>(sFac + r * kLdG + c8 + 4) = make_float4(f[4], f[5], f[6], f[7]);
+    }
+    if (upper) {
       if (sXq) {
-        const float2 x = unpack_bf16(*reinterpret_cast<const uint32_t*>(sQ + r * kLdD + c2));
-        *reinterpret_cast<uint32_t*>(sXq + r * kLdD + c2) = pack_bf16(x.x * f0, x.y * f1);
+        uint4 x = *reinterpret_cast<const uint4*>(sQ + r * kLdD + c8);
+        scale8(x, f);
+        *reinterpret_cast<uint4*>(sXq + r * kLdD + c8) = x;
       }
       if (sXk) {
-        const float2 x = unpack_bf16(*reinterpret_cast<const uint32_t*>(sK + r * kLdD + c2));
-        *reinterpret_cast<uint32_t*>(sXk + r * kLdD + c2) = pack_bf16(x.x * f0, x.y * f1);
+        uint4 x = *reinterpret_cast<const uint4*>(sK + r * kLdD + c8);
+        scale8(x, f);
+        *reinterpret_cast<uint4*>(sXk + r * kLdD + c8) = x;
       }
     } else if (sY) {
-      const float f0 = exp2f(Gf.x - Gr.x), f1 = exp2f(Gf.y - Gr.y);
-      if (sFac) *reinterpret_cast<float2*>(sFac + r * kD + c2) = make_float2(f0, f1);
-      const float2 x = unpack_bf16(*reinterpret_cast<const uint32_t*>(sKt + r * kLdD + c2));
-      *reinterpret_cast<uint32_t*>(sY + r * kLdD + c2) = pack_bf16(x.x * f0, x.y * f1);
+      uint4 x = *reinterpret_cast<const uint4*>(sKt + r * kLdD + c8);
+      scale8(x, f);
+      *reinterpret_cast<uint4*>(sY + r * kLdD + c8) = x;
     }
+  }
+}
+
+// Elementwise part of the decay gate for one chunk, all threads: log2-domain
+// per-token log-decay  -exp(A_log) log2(e) softplus(raw + bias)  into sG (zero for
+// rows past the sequence end).  The cumulative sum over rows follows separately.
+__device__ __forceinline__ void gate_elementwise(float* sG, const bf16* g_row0, long gld, int valid,
+                                                 const float* bias_h, float ea2, int tid, int nthreads) {
+  for (int idx = tid; idx < kChunk * kD / 8; idx += nthreads) {
+    const int r = idx >> 4, c8 = (idx & 15) << 3;
+    float o[8];
+    if (r < valid) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(g_row0 + (size_t)r * gld + c8);
+      const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw);
+      const float4 bA = *reinterpret_cast<const float4*>(bias_h + c8);
+      const float4 bB = *reinterpret_cast<const float4*>(bias_h + c8 + 4);
+      const float bb[8] = {bA.x, bA.y, bA.z, bA.w, bB.x, bB.y, bB.z, bB.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 v = unpack_bf16(w[j]);
+        o[2 * j] = -ea2 * softplus_fast(v.x + bb[2 * j]);
+        o[2 * j + 1] = -ea2 * softplus_fast(v.y + bb[2 * j + 1]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = 0.f;
+    }
+    *reinterpret_cast<float4*>(sG + r * kLdG + c8) = make_float4(o[0], o[1], o[2], o[3]);
+    *reinterpret_cast<float4*>(sG + r * kLdG + c8 + 4) = make_float4(o[4], o[5], o[6], o[7]);
+  }
+}
+
+// In-place cumulative sum over the 64 rows of sG, one channel per thread (tid < 128).
+__device__ __forceinline__ void gate_cumsum(float* sG, int c) {
+  float run = 0.f;
+#pragma unroll 8
+  for (int r = 0; r < kChunk; ++r) {
+    run += sG[r * kLdG + c];
+    sG[r * kLdG + c] = run;
   }
 }
 
@@ -86,7 +156,7 @@ __device__ __forceinline__ void warp_gemm_lvl(float (&acc)[1][kNT][4], const bf1
 }
 
 // T = (I + L)^-1 for a 64 x 64 strictly lower triangular L (fp32, row stride ld),
-// 256 threads.  Diagonal 16 x 16 blocks by forward substitution (one thread per
+// the first 256 threads of the CTA work, all threads must call.  Diagonal 16 x 16 blocks by forward substitution (one thread per
 // column), then block rows 1..3: T_IJ = -T_II * sum_{J<=M<I} L_IM T_MJ.
 // sY2 is a [16][64] fp32 scratch.  Ends with a __syncthreads().
 __device__ __forceinline__ void unit_lower_inverse_64(const float* sL, float* sT, float* sY2, int ld, int tid) {
@@ -103,7 +173,7 @@ __device__ __forceinline__ void unit_lower_inverse_64(const float* sL, float* sT
     }
 #pragma unroll
     for (int i = 0; i < 16; ++i) sT[(16 * blk + i) * ld + 16 * blk + col] = x[i];
-  } else {
+  } else if (tid < 256) {
     for (int e = tid - 64; e < 6 * 256; e += 192) {
       const int b = e >> 8, r = (e >> 4) & 15, c = e & 15;
       // upper blocks (I,J), J > I: (0,1) (0,2) (0,3) (1,2) (1,3) (2,3)
@@ -116,13 +186,13 @@ __device__ __forceinline__ void unit_lower_inverse_64(const float* sL, float* sT
   const int r = tid >> 4, cc = tid & 15;
 #pragma unroll 1
   for (int I = 1; I < 4; ++I) {
-    for (int J = 0; J < I; ++J) {
+    for (int J = 0; J < I && tid < 256; ++J) {
       float s = 0.f;
       for (int m = 16 * J; m < 16 * I; ++m) s += sL[(16 * I + r) * ld + m] * sT[m * ld + 16 * J + cc];
       sY2[r * 64 + 16 * J + cc] = s;
     }
     __syncthreads();
-    for (int J = 0; J < I; ++J) {
+    for (int J = 0; J < I && tid < 256; ++J) {
       float t = 0.f;
 #pragma unroll
       for (int m = 0; m < 16; ++m) t -= sT[(16 * I + r) * ld + 16 * I + m] * sY2[m * 64 + 16 * J + cc];

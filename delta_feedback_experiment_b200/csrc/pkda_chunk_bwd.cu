@@ -212,21 +212,41 @@ namespace ib {
 constexpr int kThreads = 512;
 constexpr int oA0 = 0;                        // dO          | later q
 constexpr int oA1 = kTileBytes;               // S0 [128][136] | E, F | later k, kt
-constexpr int oG = oA1 + 2 * kTileBytes;      // f32 [64][128] log2-domain cumulative decay
-constexpr int oTm = oG + kChunk * kD * 4;     // bf16 [64][72]
+constexpr int oG = oA1 + 2 * kTileBytes;      // f32 [64][kLdG] log2-domain cumulative decay
+constexpr int oTm = oG + kChunk * kLdG * 4;   // bf16 [64][72]
 constexpr int oDE = oTm + kChunk * kLdC * 2;  // dE | later dS1 [128][136] together with oDR
 constexpr int oDR = oDE + kTileBytes;
 constexpr int oStage = oTm;                   // three gated operand tiles | later dG f32 [64][128]
 constexpr int oDP = oStage + 3 * kTileBytes;  // bf16 [64][72]
 constexpr int oDM = oDP + kChunk * kLdC * 2;
-constexpr int oFac = oDM + kChunk * kLdC * 2; // f32 [64][128]
-constexpr int oSmall = oFac + kChunk * kD * 4;
-// small: beta[64] db[64] hdh[128] gcv[128] col[4][128] rb[4][64] red[16]
-constexpr int kSmallFloats = 64 + 64 + 128 + 128 + 512 + 256 + 16;
+constexpr int oFac = oDM + kChunk * kLdC * 2; // f32 [64][kLdG]
+constexpr int oSmall = oFac + kChunk * kLdG * 4;
+// small: beta[64] db[64] hdh[128] gcv[128] col[4][128] rb[4][64] red[16] bias[128]
+constexpr int kSmallFloats = 64 + 64 + 128 + 128 + 512 + 256 + 16 + 128;
 constexpr int kSmem = oSmall + kSmallFloats * 4;
 static_assert(oDR + kTileBytes <= oDP, "phase-A tiles must not reach the pair-gradient tiles");
 static_assert(oDE + kD * kLdD * 2 <= oDP, "dS1 tile must fit");
 }  // namespace ib
+
+// acc += fac * t and dG += sign * x * t on one warp's [16 x 32] fragment
+// (i0 = first row + lane/4, c0 = first column + 2*(lane%4)); fac is the fp32
+// level factor of each row, x the staged bf16 operand the product was formed with.
+__device__ __forceinline__ void epi_add(float (&acc)[1][4][4], float (&dG)[1][4][4], const float (&t)[1][4][4],
+                                        const float* sFac, const bf16* sX, float sign, int i0, int c0) {
+#pragma unroll
+  for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int i = i0 + 8 * half, c = c0 + 8 * nt;
+      const float2 f = *reinterpret_cast<const float2*>(sFac + i * kLdG + c);
+      const float2 x = unpack_bf16(*reinterpret_cast<const uint32_t*>(sX + i * kLdD + c));
+      const float t0 = t[0][nt][2 * half], t1 = t[0][nt][2 * half + 1];
+      acc[0][nt][2 * half] += f.x * t0;
+      acc[0][nt][2 * half + 1] += f.y * t1;
+      dG[0][nt][2 * half] += sign * x.x * t0;
+      dG[0][nt][2 * half + 1] += sign * x.y * t1;
+    }
+}
 
 __global__ void __launch_bounds__(ib::kThreads, 1)
 pkda_intra_bwd_kernel(const IntraBwdParams p) {
@@ -251,6 +271,7 @@ pkda_intra_bwd_kernel(const IntraBwdParams p) {
   float* sCol = sGcv + 128;  // [4][128]
   float* sRb = sCol + 512;   // [4][64]
   float* sRed = sRb + 256;   // [16]
+  float* sBias = sRed + 16;  // [128]
 
   int n, tok0, valid;
   if (!chunk_lookup(p.geo, blockIdx.x, n, tok0, valid)) return;
@@ -271,23 +292,13 @@ pkda_intra_bwd_kernel(const IntraBwdParams p) {
   cp_async_commit();
   if (tid < kChunk) sBeta[tid] = p.beta_c[chh * kChunk + tid];
   if (tid < kD) sGcv[tid] = p.gc[chh * kD + tid];
+  else if (tid < 2 * kD) sBias[tid - kD] = p.dt_bias[h * kD + tid - kD];
+  __syncthreads();
+  // log2-domain cumulative log-decay, exactly as the forward computes it
+  gate_elementwise(sG, p.g + row0, gld, valid, sBias, __expf(p.A_log[h]) * kLog2e, tid, kThreads);
+  __syncthreads();
   if (tid < kD) {
-    // log2-domain cumulative log-decay, exactly as the forward computes it
-    const int c = tid;
-    const float ea = __expf(p.A_log[h]) * kLog2e;
-    const float bias = p.dt_bias[h * kD + c];
-    float G = 0.f;
-    for (int r0 = 0; r0 < kChunk; r0 += 8) {
-      float raw[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        raw[j] = (r0 + j < valid) ? to_f(p.g[row0 + (size_t)(r0 + j) * gld + c]) : 0.f;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        if (r0 + j < valid) G -= ea * softplus_fast(raw[j] + bias);
-        sG[(r0 + j) * kD + c] = G;
-      }
-    }
+    gate_cumsum(sG, tid);
   } else {
     const int t2 = tid - kD;  // 384 threads
     // dE = beta * dF
@@ -339,7 +350,7 @@ pkda_intra_bwd_kernel(const IntraBwdParams p) {
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const int i = 16 * I + gq + 8 * (e >> 1), c = 32 * cq + 8 * nt + 2 * tq + (e & 1);
-      dQ[0][nt][e] = t[0][nt][e] * p.scale * exp2f(sG[i * kD + c]);
+      dQ[0][nt][e] = t[0][nt][e] * p.scale * ex2(sG[i * kLdG + c]);
     }
   // dR = Tm^T dE  (= dV)
   zero_acc(t);
@@ -362,7 +373,7 @@ pkda_intra_bwd_kernel(const IntraBwdParams p) {
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const int i = 16 * I + gq + 8 * (e >> 1), c = 32 * cq + 8 * nt + 2 * tq + (e & 1);
-      dK[0][nt][e] = -t[0][nt][e] * exp2f(sG[i * kD + c]);
+      dK[0][nt][e] = -t[0][nt][e] * ex2(sG[i * kLdG + c]);
     }
   __syncthreads();  // S0 no longer needed
   // E, F = beta E, and the direct part of dbeta: rowsum(dF * E)
@@ -434,7 +445,7 @@ pkda_intra_bwd_kernel(const IntraBwdParams p) {
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const int i = 16 * I + gq + 8 * (e >> 1), c = 32 * cq + 8 * nt + 2 * tq + (e & 1);
-      dKt[0][nt][e] = t[0][nt][e] * exp2f(sG[(kChunk - 1) * kD + c] - sG[i * kD + c]);
+      dKt[0][nt][e] = t[0][nt][e] * ex2(sG[(kChunk - 1) * kLdG + c] - sG[i * kLdG + c]);
     }
   __syncthreads();
 
@@ -495,24 +506,10 @@ pkda_intra_bwd_kernel(const IntraBwdParams p) {
       const int kb = big ? blk : 16 * I, ke = kb + (big ? lvl : 16);
       zero_acc(t);
       warp_gemm_lvl<4, false, true>(t, sdP, kLdC, 16 * I, sY, kLdD, 32 * cq, kb, ke, lvl, !big);
-#pragma unroll
-      for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int i = 16 * I + gq + 8 * (e >> 1), c = 32 * cq + 8 * nt + 2 * tq + (e & 1);
-          dQ[0][nt][e] += sFac[i * kD + c] * t[0][nt][e];
-          dG[0][nt][e] += to_f(sXq[i * kLdD + c]) * t[0][nt][e];
-        }
+      epi_add(dQ, dG, t, sFac, sXq, 1.f, 16 * I + gq, 32 * cq + 2 * tq);
       zero_acc(t);
       warp_gemm_lvl<4, false, true>(t, sdM, kLdC, 16 * I, sY, kLdD, 32 * cq, kb, ke, lvl, !big);
-#pragma unroll
-      for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int i = 16 * I + gq + 8 * (e >> 1), c = 32 * cq + 8 * nt + 2 * tq + (e & 1);
-          dK[0][nt][e] += sFac[i * kD + c] * t[0][nt][e];
-          dG[0][nt][e] += to_f(sXk[i * kLdD + c]) * t[0][nt][e];
-        }
+      epi_add(dK, dG, t, sFac, sXk, 1.f, 16 * I + gq, 32 * cq + 2 * tq);
     }
     if (!big || !((16 * I) & lvl)) {  // rows act as the lower ("j") side
       const int kb = big ? blk + lvl : 16 * I, ke = kb + (big ? lvl : 16);
@@ -521,19 +518,13 @@ pkda_intra_bwd_kernel(const IntraBwdParams p) {
 #pragma unroll
       for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int j = 16 * I + gq + 8 * (e >> 1), c = 32 * cq + 8 * nt + 2 * tq + (e & 1);
-          rb[e >> 1] += to_f(sY[j * kLdD + c]) * t[0][nt][e];
+        for (int half = 0; half < 2; ++half) {
+          const float2 y = unpack_bf16(*reinterpret_cast<const uint32_t*>(
+              sY + (16 * I + gq + 8 * half) * kLdD + 32 * cq + 8 * nt + 2 * tq));
+          rb[half] += y.x * t[0][nt][2 * half] + y.y * t[0][nt][2 * half + 1];
         }
       warp_gemm_lvl<4, true, true>(t, sdP, kLdC, 16 * I, sXq, kLdD, 32 * cq, kb, ke, lvl, !big);
-#pragma unroll
-      for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int j = 16 * I + gq + 8 * (e >> 1), c = 32 * cq + 8 * nt + 2 * tq + (e & 1);
-          dKt[0][nt][e] += sFac[j * kD + c] * t[0][nt][e];
-          dG[0][nt][e] -= to_f(sY[j * kLdD + c]) * t[0][nt][e];
-        }
+      epi_add(dKt, dG, t, sFac, sY, -1.f, 16 * I + gq, 32 * cq + 2 * tq);
     }
     __syncthreads();
   }
@@ -568,7 +559,7 @@ pkda_intra_bwd_kernel(const IntraBwdParams p) {
         *reinterpret_cast<float2*>(p.dk_read + off) = make_float2(dK[0][nt][2 * half], dK[0][nt][2 * half + 1]);
         *reinterpret_cast<float2*>(p.dkt + off) = make_float2(dKt[0][nt][2 * half], dKt[0][nt][2 * half + 1]);
       }
-      *reinterpret_cast<float2*>(sdG + i * kD + c) = make_float2(dG[0][nt][2 * half], dG[0][nt][2 * half + 1]);
+      *reinterpret_cast<float2*>(sdG + i * kLdG + c) = make_float2(dG[0][nt][2 * half], dG[0][nt][2 * half + 1]);
     }
   __syncthreads();
   if (tid < kChunk && tid < valid) {
@@ -594,7 +585,7 @@ pkda_intra_bwd_kernel(const IntraBwdParams p) {
 #pragma unroll
       for (int j = 7; j >= 0; --j) {
         const int r = r0 + j;
-        run += sdG[r * kD + c];
+        run += sdG[r * kLdG + c];
         if (r < valid) {
           const float z = raw[j] + bias;
           const float gn = -ea * softplus_fast(z);

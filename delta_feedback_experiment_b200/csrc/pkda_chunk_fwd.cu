@@ -105,22 +105,33 @@ struct IntraParams {
 };
 
 namespace intra {
-constexpr int kThreads = 256;
+constexpr int kThreads = 512;
 constexpr int oQ = 0;
 constexpr int oK = oQ + kTileBytes;
 constexpr int oKt = oK + kTileBytes;
-constexpr int oG = oKt + kTileBytes;             // fp32 [64][128]
-constexpr int oStage = oG + kChunk * kD * 4;     // 3 bf16 tiles; aliased later
-constexpr int oTmb = oStage + 3 * kTileBytes;    // bf16 [64][72]
-constexpr int oSmall = oTmb + kChunk * kLdC * 2; // beta[64], pd[64], bp[64]
-constexpr int kSmem = oSmall + 3 * kChunk * 4;
+constexpr int oG = oKt + kTileBytes;              // fp32 [64][kLdG]
+constexpr int oStage = oG + kChunk * kLdG * 4;    // 3 bf16 tiles; aliased (see below)
+constexpr int oTmb = oStage + 3 * kTileBytes;     // bf16 [64][72]: P staging, then Tm
+constexpr int oSmall = oTmb + kChunk * kLdC * 2;  // beta[64] pd[64] bp[64] bias[128]
+constexpr int kSmem = oSmall + (3 * kChunk + kD) * 4;
 // aliases inside the staging area
+constexpr int oAt = oStage;                       // fp32 [64][kLdG] preconditioner states (before the levels)
 constexpr int kLdL = 65;
-constexpr int oL = oStage;
+constexpr int oL = oStage;                        // after the levels: L, T, Y2
 constexpr int oT = oL + kChunk * kLdL * 4;
 constexpr int oY2 = oT + kChunk * kLdL * 4;       // fp32 [16][64]
 static_assert(oY2 + 16 * 64 * 4 <= oTmb, "inverse scratch must fit in the staging area");
+static_assert(kChunk * kLdG * 4 <= 3 * kTileBytes, "A_t array must fit in the staging area");
 }  // namespace intra
+
+// Writes one 16x16 accumulator tile pair (two n8 tiles) through a functor f(i, j, value).
+template <typename F>
+__device__ __forceinline__ void for_tile(const float (&t)[2][4], int i0, int j0, int gq, int tq, F f) {
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) f(i0 + gq + 8 * (e >> 1), j0 + 8 * nt + 2 * tq + (e & 1), t[nt][e]);
+}
 
 // kRecompute: rebuild w,u,kg,qg only (backward's lean mode); the products, the
 // write keys and the decay totals already exist and are left untouched.
@@ -140,6 +151,8 @@ pkda_intra_fwd_kernel(const IntraParams p) {
   float* sBeta = reinterpret_cast<float*>(smem + oSmall);
   float* sPd = sBeta + kChunk;
   float* sBp = sPd + kChunk;
+  float* sBias = sBp + kChunk;
+  float* sAt = reinterpret_cast<float*>(smem + oAt);
   float* sL = reinterpret_cast<float*>(smem + oL);
   float* sT = reinterpret_cast<float*>(smem + oT);
   float* sY2 = reinterpret_cast<float*>(smem + oY2);
@@ -148,6 +161,7 @@ pkda_intra_fwd_kernel(const IntraParams p) {
   if (!chunk_lookup(p.geo, blockIdx.x, n, tok0, valid)) return;
   const int h = blockIdx.y, H = p.geo.heads;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int gq = lane >> 2, tq = lane & 3;
   const size_t chh = (size_t)blockIdx.x * H + h;
   const size_t row0 = ((size_t)tok0 * H + h) * kD;  // element offset of (tok0, h, 0)
   const long gld = (long)H * kD;
@@ -163,83 +177,100 @@ pkda_intra_fwd_kernel(const IntraParams p) {
     sBeta[tid] = p.beta_c[chh * kChunk + tid];
     sPd[tid] = ok ? __expf(p.g_atk[s]) : 1.f;
     sBp[tid] = ok ? to_f(p.beta_atk[s]) : 0.f;
+  } else if (tid < kChunk + kD) {
+    sBias[tid - kChunk] = p.dt_bias[h * kD + tid - kChunk];
   }
+  // zero the P staging tile (upper triangle must read as zero)
+  for (int i = tid; i < kChunk * kLdC / 8; i += kThreads) reinterpret_cast<uint4*>(sTmb)[i] = make_uint4(0, 0, 0, 0);
   cp_async_wait<0>();
   __syncthreads();
 
-  // ---- 2. per-channel sequential passes: log2-domain decay cumsum | write keys
+  // ---- 2. decay gate (elementwise, all threads), then the two per-channel sequential
+  // passes side by side: cumulative sum | preconditioner recurrence A_t
+  gate_elementwise(sG, p.g + row0, gld, valid, sBias, __expf(p.A_log[h]) * kLog2e, tid, kThreads);
+  __syncthreads();
   if (tid < kD) {
-    const int c = tid;
-    const float ea = __expf(p.A_log[h]) * kLog2e;
-    const float bias = p.dt_bias[h * kD + c];
-    float G = 0.f;
-    for (int r0 = 0; r0 < kChunk; r0 += 8) {
-      float raw[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        raw[j] = (r0 + j < valid) ? to_f(p.g[row0 + (size_t)(r0 + j) * gld + c]) : 0.f;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        if (r0 + j < valid) G -= ea * softplus_fast(raw[j] + bias);
-        sG[(r0 + j) * kD + c] = G;
-      }
-    }
-  } else if (!kRecompute) {
+    gate_cumsum(sG, tid);
+  } else if (!kRecompute && tid < 2 * kD) {
     const int c = tid - kD;
     float A = p.a_start[chh * kD + c];
-    const float centre = p.log_atk_scale[h];
+#pragma unroll 8
     for (int r = 0; r < kChunk; ++r) {
       const float kc = to_f(sK[r * kLdD + c]);
       A = sPd[r] * A + sBp[r] * kc * kc;
-      const float dev = __logf(A + p.eps) - centre;
-      const float f = __expf(-p.ln_x * __fdividef(dev, 1.f + fabsf(dev)));
-      const bf16 kt = __float2bfloat16(kc * f);
-      sKt[r * kLdD + c] = kt;
-      if (r < valid) p.kt[row0 + (size_t)r * gld + c] = kt;
+      sAt[r * kLdG + c] = A;
     }
   }
   __syncthreads();
+  if (!kRecompute) {
+    // write keys kt = k * exp(-ln(x) * dev / (1 + |dev|)), dev = log(A + eps) - centre
+    const float centre = p.log_atk_scale[h];
+    for (int idx = tid; idx < kChunk * kD / 8; idx += kThreads) {
+      const int r = idx >> 4, c8 = (idx & 15) << 3;
+      const float4 A0 = *reinterpret_cast<const float4*>(sAt + r * kLdG + c8);
+      const float4 A1 = *reinterpret_cast<const float4*>(sAt + r * kLdG + c8 + 4);
+      const float Av[8] = {A0.x, A0.y, A0.z, A0.w, A1.x, A1.y, A1.z, A1.w};
+      float f[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float dev = __logf(Av[j] + p.eps) - centre;
+        f[j] = __expf(-p.ln_x * __fdividef(dev, 1.f + fabsf(dev)));
+      }
+      uint4 x = *reinterpret_cast<const uint4*>(sK + r * kLdD + c8);
+      scale8(x, f);
+      *reinterpret_cast<uint4*>(sKt + r * kLdD + c8) = x;
+      if (r < valid) *reinterpret_cast<uint4*>(p.kt + row0 + (size_t)r * gld + c8) = x;
+    }
+    __syncthreads();
+  }
 
-  // ---- 3. gated pair products, level by level.  Warp (mat, I): mat 0 = M (rows k),
-  // mat 1 = P (rows q); I = 16-row block; acc[J] covers column block J.
-  const int mat = warp >> 2, I = warp & 3;
-  const int gq = lane >> 2, tq = lane & 3;
-  float acc[4][2][4];
+  // ---- 3. gated pair products, level by level.
+  // warps 0-7 : (mat, I) own the diagonal 16x16 tile (I,I): levels 8,4,2,1 (and the ungated diagonal of P)
+  // warps 8-15: (mat, idx) own one tile of level 32 and (idx < 2) one tile of level 16
+  // mat 0 = M (rows k), mat 1 = P (rows q).
+  const bool diagw = warp < 8;
+  const int mat = (warp >> 2) & 1, I = warp & 3;
+  float accA[2][4], accB[2][4];  // diag warps: accA; off warps: accA = level-32 tile, accB = level-16 tile
 #pragma unroll
-  for (int a = 0; a < 4; ++a)
+  for (int a = 0; a < 2; ++a)
 #pragma unroll
-    for (int b = 0; b < 2; ++b)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) acc[a][b][e] = 0.f;
+    for (int e = 0; e < 4; ++e) accA[a][e] = accB[a][e] = 0.f;
+  const int I32 = 2 + (I >> 1), J32 = I & 1;   // level-32 tile of an off warp
+  const int I16 = 1 + 2 * I, J16 = 2 * I;      // level-16 tile (I < 2)
 
 #pragma unroll 1
   for (int lvl = 32; lvl >= 1; lvl >>= 1) {
     stage_level(sXq, sXk, sY, sQ, sK, sKt, sG, lvl, tid, kThreads);
     __syncthreads();
     const bf16* X = mat ? sXq : sXk;
+    float tmp[1][2][4];
+    zero_acc(tmp);
+    if (lvl == 32 && !diagw) {
+      warp_gemm<1, 2, false, false>(tmp, X, kLdD, 16 * I32, sY, kLdD, 16 * J32, 0, kD);
 #pragma unroll
-    for (int J = 0; J < 4; ++J) {
-      bool use;
-      if (lvl == 32) use = (I >= 2) && (J < 2);
-      else if (lvl == 16) use = (I & 1) && (J == I - 1);
-      else use = (J == I);
-      if (use) {  // warp-uniform
-        float tmp[1][2][4];
-        zero_acc(tmp);
-        warp_gemm<1, 2, false, false>(tmp, X, kLdD, 16 * I, sY, kLdD, 16 * J, 0, kD);
+      for (int a = 0; a < 2; ++a)
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt)
+        for (int e = 0; e < 4; ++e) accA[a][e] = tmp[0][a][e];
+    } else if (lvl == 16 && !diagw && I < 2) {
+      warp_gemm<1, 2, false, false>(tmp, X, kLdD, 16 * I16, sY, kLdD, 16 * J16, 0, kD);
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int i = 16 * I + gq + ((e >> 1) << 3);
-            const int j = 16 * J + 8 * nt + 2 * tq + (e & 1);
-            if (level_pair_ok(i, j, lvl)) acc[J][nt][e] += tmp[0][nt][e];
-          }
-      }
+      for (int a = 0; a < 2; ++a)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) accB[a][e] = tmp[0][a][e];
+    } else if (lvl <= 8 && diagw) {
+      warp_gemm<1, 2, false, false>(tmp, X, kLdD, 16 * I, sY, kLdD, 16 * I, 0, kD);
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int i = 16 * I + gq + ((e >> 1) << 3);
+          const int j = 16 * I + 8 * nt + 2 * tq + (e & 1);
+          if (level_pair_ok(i, j, lvl)) accA[nt][e] += tmp[0][nt][e];
+        }
     }
     __syncthreads();
   }
-  if (mat == 1) {  // diagonal of P: ungated q_i . kt_i
+  if (diagw && mat == 1) {  // diagonal of P: ungated q_i . kt_i
     float tmp[1][2][4];
     zero_acc(tmp);
     warp_gemm<1, 2, false, false>(tmp, sQ, kLdD, 16 * I, sKt, kLdD, 16 * I, 0, kD);
@@ -249,36 +280,37 @@ pkda_intra_fwd_kernel(const IntraParams p) {
       for (int e = 0; e < 4; ++e) {
         const int i = 16 * I + gq + ((e >> 1) << 3);
         const int j = 16 * I + 8 * nt + 2 * tq + (e & 1);
-        if (i == j) acc[I][nt][e] += tmp[0][nt][e];
+        if (i == j) accA[nt][e] += tmp[0][nt][e];
       }
   }
 
-  // ---- 4. P -> global (scaled, lower triangle incl. diagonal); L = tril(M,-1) diag(beta) -> smem
-#pragma unroll
-  for (int J = 0; J < 4; ++J)
-#pragma unroll
-    for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        const int i = 16 * I + gq + 8 * half;
-        const int j = 16 * J + 8 * nt + 2 * tq;
-        const float a0 = acc[J][nt][2 * half], a1 = acc[J][nt][2 * half + 1];
-        if (mat == 1) {
-          if (!kRecompute && i < valid) {
-            const float p0 = (j <= i) ? a0 * p.scale : 0.f;
-            const float p1 = (j + 1 <= i) ? a1 * p.scale : 0.f;
-            *reinterpret_cast<uint32_t*>(p.Aqk + ((size_t)(tok0 + i) * H + h) * kChunk + j) = pack_bf16(p0, p1);
-          }
-        } else {
-          sL[i * kLdL + j] = (j < i) ? a0 * sBeta[j] : 0.f;
-          sL[i * kLdL + j + 1] = (j + 1 < i) ? a1 * sBeta[j + 1] : 0.f;
-        }
-      }
+  // ---- 4. P -> bf16 staging tile (scaled) ; L = tril(M,-1) diag(beta) -> smem fp32
+  for (int i = tid; i < kChunk * kLdL; i += kThreads) sL[i] = 0.f;
   __syncthreads();
+  {
+    auto putP = [&](int i, int j, float v) { if (j <= i) sTmb[i * kLdC + j] = __float2bfloat16(v * p.scale); };
+    auto putL = [&](int i, int j, float v) { if (j < i) sL[i * kLdL + j] = v * sBeta[j]; };
+    if (diagw) {
+      if (mat) for_tile(accA, 16 * I, 16 * I, gq, tq, putP); else for_tile(accA, 16 * I, 16 * I, gq, tq, putL);
+    } else {
+      if (mat) for_tile(accA, 16 * I32, 16 * J32, gq, tq, putP); else for_tile(accA, 16 * I32, 16 * J32, gq, tq, putL);
+      if (I < 2) {
+        if (mat) for_tile(accB, 16 * I16, 16 * J16, gq, tq, putP); else for_tile(accB, 16 * I16, 16 * J16, gq, tq, putL);
+      }
+    }
+  }
+  __syncthreads();
+  if (!kRecompute) {
+    for (int i = tid; i < kChunk * kChunk / 8; i += kThreads) {
+      const int r = i >> 3, c8 = (i & 7) << 3;
+      if (r < valid)
+        *reinterpret_cast<uint4*>(p.Aqk + ((size_t)(tok0 + r) * H + h) * kChunk + c8) =
+            *reinterpret_cast<const uint4*>(sTmb + r * kLdC + c8);
+    }
+  }
 
   // ---- 5. T = (I + L)^-1 in fp32
-  unit_lower_inverse_64(sL, sT, sY2, kLdL, tid);
-  // (ends with a __syncthreads)
+  unit_lower_inverse_64(sL, sT, sY2, kLdL, tid);  // starts with work on sL/sT only; ends with a __syncthreads()
   for (int i = tid; i < kChunk * kChunk / 2; i += kThreads) {
     const int r = i >> 5, c2 = (i & 31) << 1;
     const uint32_t pk = pack_bf16(sT[r * kLdL + c2], sT[r * kLdL + c2 + 1]);
@@ -293,42 +325,55 @@ pkda_intra_fwd_kernel(const IntraParams p) {
   bf16* sV = sXk;
   tile_load_async(sV, kLdD, p.v + row0, gld, kChunk, kD, valid, kThreads);
   cp_async_commit();
-  for (int i = tid; i < kChunk * kD / 2; i += kThreads) {
-    const int r = i >> 6, c2 = (i & 63) << 1;
-    const float2 G = *reinterpret_cast<const float2*>(sG + r * kD + c2);
-    const float2 Gl = *reinterpret_cast<const float2*>(sG + (kChunk - 1) * kD + c2);
-    const float e0 = exp2f(G.x), e1 = exp2f(G.y);
-    const float2 kk = unpack_bf16(*reinterpret_cast<const uint32_t*>(sK + r * kLdD + c2));
-    *reinterpret_cast<uint32_t*>(sKd + r * kLdD + c2) = pack_bf16(kk.x * e0, kk.y * e1);
+  for (int idx = tid; idx < kChunk * kD / 8; idx += kThreads) {
+    const int r = idx >> 4, c8 = (idx & 15) << 3;
+    const float4 g0 = *reinterpret_cast<const float4*>(sG + r * kLdG + c8);
+    const float4 g1 = *reinterpret_cast<const float4*>(sG + r * kLdG + c8 + 4);
+    const float4 l0 = *reinterpret_cast<const float4*>(sG + (kChunk - 1) * kLdG + c8);
+    const float4 l1 = *reinterpret_cast<const float4*>(sG + (kChunk - 1) * kLdG + c8 + 4);
+    const float G[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+    const float Gl[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
+    float e[8], es[8], tl[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      e[j] = ex2(G[j]);
+      es[j] = e[j] * p.scale;
+      tl[j] = ex2(Gl[j] - G[j]);
+    }
+    uint4 kk = *reinterpret_cast<const uint4*>(sK + r * kLdD + c8);
+    scale8(kk, e);
+    *reinterpret_cast<uint4*>(sKd + r * kLdD + c8) = kk;
     if (r < valid) {
-      const float2 qq = unpack_bf16(*reinterpret_cast<const uint32_t*>(sQ + r * kLdD + c2));
-      const float2 kt = unpack_bf16(*reinterpret_cast<const uint32_t*>(sKt + r * kLdD + c2));
-      const size_t off = row0 + (size_t)r * gld + c2;
-      *reinterpret_cast<uint32_t*>(p.qg + off) = pack_bf16(qq.x * e0 * p.scale, qq.y * e1 * p.scale);
-      *reinterpret_cast<uint32_t*>(p.kg + off) =
-          pack_bf16(kt.x * exp2f(Gl.x - G.x), kt.y * exp2f(Gl.y - G.y));
+      uint4 qq = *reinterpret_cast<const uint4*>(sQ + r * kLdD + c8);
+      uint4 kt = *reinterpret_cast<const uint4*>(sKt + r * kLdD + c8);
+      scale8(qq, es);
+      scale8(kt, tl);
+      const size_t off = row0 + (size_t)r * gld + c8;
+      *reinterpret_cast<uint4*>(p.qg + off) = qq;
+      *reinterpret_cast<uint4*>(p.kg + off) = kt;
     }
     if (!kRecompute && r == kChunk - 1) {
-      p.gc[chh * kD + c2] = e0;
-      p.gc[chh * kD + c2 + 1] = e1;
+      *reinterpret_cast<float4*>(p.gc + chh * kD + c8) = make_float4(e[0], e[1], e[2], e[3]);
+      *reinterpret_cast<float4*>(p.gc + chh * kD + c8 + 4) = make_float4(e[4], e[5], e[6], e[7]);
     }
   }
   cp_async_wait<0>();
   __syncthreads();
 
-  // ---- 7. W = Tm Kd, U = Tm V   (warp: matrix = warp>>2, rows 16*(warp&3), all 128 columns)
+  // ---- 7. W = Tm Kd, U = Tm V   (warp: matrix = warp>>3, rows 16*((warp>>1)&3), column half warp&1)
   {
-    float acc2[1][16][4];
+    const int m7 = warp >> 3, I7 = (warp >> 1) & 3, n0 = 64 * (warp & 1);
+    float acc2[1][8][4];
     zero_acc(acc2);
-    warp_gemm<1, 16, false, true>(acc2, sTmb, kLdC, 16 * I, mat ? sV : sKd, kLdD, 0, 0, 16 * (I + 1));
-    bf16* dst = mat ? p.u : p.w;
+    warp_gemm<1, 8, false, true>(acc2, sTmb, kLdC, 16 * I7, m7 ? sV : sKd, kLdD, n0, 0, 16 * (I7 + 1));
+    bf16* dst = m7 ? p.u : p.w;
 #pragma unroll
-    for (int nt = 0; nt < 16; ++nt)
+    for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        const int i = 16 * I + gq + 8 * half;
+        const int i = 16 * I7 + gq + 8 * half;
         if (i < valid)
-          *reinterpret_cast<uint32_t*>(dst + row0 + (size_t)i * gld + 8 * nt + 2 * tq) =
+          *reinterpret_cast<uint32_t*>(dst + row0 + (size_t)i * gld + n0 + 8 * nt + 2 * tq) =
               pack_bf16(acc2[0][nt][2 * half], acc2[0][nt][2 * half + 1]);
       }
   }

@@ -202,6 +202,10 @@ __device__ __forceinline__ void unit_lower_inverse_64(const float* sL, float* sT
   }
 }
 
+// tcgen05 / TMA output stage (pkda_out_tc.cu).
+int launch_out_fwd_tc(const Geo& geo, int total_tokens, const bf16* qg, const bf16* h, const bf16* Aqk,
+                      const bf16* v_new, const float* beta_c, bf16* o, int* status, cudaStream_t st);
+
 // Host-side pieces defined in pkda_chunk_fwd.cu and reused by the backward.
 int check_chunk_problem(const pkda_problem& p);
 int run_prologue(const pkda_problem& p, int* chunk_offsets, float* beta_c, Geo* geo, cudaStream_t st);

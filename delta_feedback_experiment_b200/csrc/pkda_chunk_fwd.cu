@@ -16,6 +16,8 @@
 // (overflow after a few tokens); level L of the hierarchy pairs rows whose index
 // has bit L set with rows of the same 2L-block whose bit L is clear, both
 // expressed relative to the first row of the upper half, so every factor is <= 1.
+#include <cstdlib>
+
 #include "pkda_chunk.cuh"
 
 namespace pkda {
@@ -614,6 +616,7 @@ struct FwdWorkspace {
   int* chunk_offsets;
   float* beta_c;
   bf16* u;
+  int* status;  // device status word: 0 = ok, 1 = a bounded wait in a kernel gave up
   size_t bytes;
 };
 
@@ -628,6 +631,8 @@ static FwdWorkspace carve_fwd(const pkda_problem& p, void* base) {
   off += align_up(chunks * p.heads * kChunk * sizeof(float));
   w.u = reinterpret_cast<bf16*>(b + off);
   off += align_up((size_t)p.total_tokens * p.heads * kD * sizeof(bf16));
+  w.status = reinterpret_cast<int*>(b + off);
+  off += align_up(sizeof(int));
   w.bytes = off;
   return w;
 }
@@ -742,6 +747,17 @@ int chunk_fwd(const pkda_chunk_fwd_args* a, cudaStream_t st) {
                           static_cast<bf16*>(a->qg), a->final_state, false, st);
   if (rc != PKDA_OK) return rc;
 
+  // Output stage: tcgen05 + TMA by default; PKDA_OUT_IMPL=mma selects the mma.sync kernel (A/B runs).
+  static const bool use_mma = [] {
+    const char* e = getenv("PKDA_OUT_IMPL");
+    return e && e[0] == 'm';
+  }();
+  if (!use_mma) {
+    if (cudaMemsetAsync(ws.status, 0, sizeof(int), st) != cudaSuccess) return PKDA_ERR_LAUNCH;
+    return launch_out_fwd_tc(geo, p.total_tokens, static_cast<const bf16*>(a->qg), static_cast<const bf16*>(a->h),
+                             static_cast<const bf16*>(a->Aqk), static_cast<const bf16*>(a->v_new), ws.beta_c,
+                             static_cast<bf16*>(a->o), ws.status, st);
+  }
   OutParams op;
   op.geo = geo;
   op.qg = static_cast<const bf16*>(a->qg); op.h = static_cast<const bf16*>(a->h);

@@ -18,6 +18,18 @@ LAUNCHES = 0
 """Kernels enqueued through this module since import (launch accounting)."""
 
 
+_LAST_STATUS = None
+
+
+def last_device_status() -> int:
+    """Status word the most recent chunked forward's kernels left on the device
+    (0 = ok, 1 = a bounded wait inside a kernel gave up and its CTA skipped its
+    stores).  Synchronises; meant for tests and debugging."""
+    if _LAST_STATUS is None:
+        return 0
+    return int(_LAST_STATUS.view(torch.int32).item())
+
+
 def _count(lib) -> None:
     global LAUNCHES
     LAUNCHES += int(lib.pkda_last_launch_count())
@@ -181,6 +193,8 @@ def chunk_forward(q, k, v, g, g_atk, beta_atk, beta, A_log, dt_bias, log_atk_sca
     args.workspace, args.workspace_bytes = ws.data_ptr(), nbytes
     _lib.check(lib.pkda_chunk_fwd(C.byref(args), _lib.current_stream()), "pkda_chunk_fwd")
     _count(lib)
+    global _LAST_STATUS
+    _LAST_STATUS = ws[nbytes - 256:nbytes - 252] if nbytes >= 256 else None
     return o, S, A, saved
 
 

@@ -133,6 +133,15 @@ def test_stage_outputs_match_cpu_model():
             assert rel_rms(v_new[0, lo:hi, hd], ch["E"]) < 1e-2, tag + "v_new"
 
 
+def test_device_status_word_is_clean():
+    """The tcgen05 output stage bounds every wait and reports a give-up through a
+    status word instead of hanging; a healthy run leaves it at zero."""
+    d = make_inputs(2, 300, 2, 128, seed=62, dist="production", dtype=torch.bfloat16, with_state=True)
+    o, S, A = run_chunk(d)
+    assert ops.last_device_status() == 0
+    check(o, S, A, oracle(d), "status")
+
+
 def test_run_twice_is_bitwise_identical():
     d = make_inputs(2, 130, 2, 128, seed=61, dist="unit", dtype=torch.bfloat16, with_state=True)
     a, b = run_chunk(d), run_chunk(d)

@@ -74,7 +74,7 @@ EXPORTS = (
     "pkda_status_string", "pkda_sizeof_problem", "pkda_sizeof_recurrent_args",
     "pkda_sizeof_chunk_fwd_args", "pkda_sizeof_chunk_bwd_args", "pkda_last_launch_count",
     "pkda_stage_count", "pkda_stage_name", "pkda_stage_timing", "pkda_stage_timing_read",
-    "pkda_static_scratch_bytes", "pkda_chunk_fwd_static",
+    "pkda_static_scratch_bytes", "pkda_chunk_fwd_static", "pkda_set_direct_block_cap",
 )
 
 _lib: Optional[C.CDLL] = None
@@ -89,6 +89,8 @@ def _configure(lib: C.CDLL) -> None:
     lib.pkda_chunk_fwd_static.argtypes = [C.POINTER(ChunkFwdArgs), C.c_void_p]
     lib.pkda_chunk_fwd_static.restype = C.c_int
     lib.pkda_static_scratch_bytes.restype = C.c_size_t
+    lib.pkda_set_direct_block_cap.argtypes = [C.c_int]
+    lib.pkda_set_direct_block_cap.restype = C.c_int
     lib.pkda_chunk_bwd.argtypes = [C.POINTER(ChunkBwdArgs), C.c_void_p]
     lib.pkda_chunk_bwd.restype = C.c_int
     for name in ("pkda_chunk_fwd_workspace_bytes", "pkda_chunk_bwd_workspace_bytes"):
@@ -177,3 +179,8 @@ def stage_timing_read() -> dict:
     cnt = (C.c_int * n)()
     check(lib.pkda_stage_timing_read(ms, cnt, n), "pkda_stage_timing_read")
     return {lib.pkda_stage_name(i).decode(): (float(ms[i]), int(cnt[i])) for i in range(n) if cnt[i]}
+
+
+def set_direct_block_cap(cap: int) -> None:
+    """Testing aid: caps the kernels' direct block size (64 = data-driven default)."""
+    check(load().pkda_set_direct_block_cap(int(cap)), "pkda_set_direct_block_cap")

@@ -8,6 +8,9 @@ namespace pkda {
 static thread_local int g_launches = 0;
 void reset_launch_count() { g_launches = 0; }
 
+static int g_direct_cap = 64;
+int direct_block_cap() { return g_direct_cap; }
+
 // Optional per-stage timing (used by the benchmark): one event pair per launch,
 // taken from a pool that grows only while timing is enabled.
 struct StageTimer {
@@ -121,6 +124,12 @@ size_t pkda_sizeof_recurrent_args(void) { return sizeof(pkda_recurrent_args); }
 size_t pkda_sizeof_chunk_fwd_args(void) { return sizeof(pkda_chunk_fwd_args); }
 size_t pkda_sizeof_chunk_bwd_args(void) { return sizeof(pkda_chunk_bwd_args); }
 int pkda_last_launch_count(void) { return pkda::g_launches; }
+
+int pkda_set_direct_block_cap(int cap) {
+  if (cap < 1 || cap > 64 || (cap & (cap - 1))) return PKDA_ERR_SHAPE;
+  pkda::g_direct_cap = cap;
+  return PKDA_OK;
+}
 
 int pkda_stage_count(void) { return pkda::kStageCount; }
 

@@ -19,6 +19,45 @@ __device__ __forceinline__ bool level_pair_ok(int i, int j, int lvl) {
 
 constexpr int kLdG = kD + 8;                  // smem row stride of a [64][128] fp32 array
 
+// "Direct" pairing: inside a block of b rows (b a power of two) all pairs j < i
+// use ONE reference row, the block's first: row factor 2^(G_i - G_ref) <= 1,
+// column factor 2^(G_ref - G_j) >= 1.  That is only safe while the decay across a
+// b-block stays far inside the fp32 / bf16 exponent range, so each (chunk, head)
+// picks the largest b whose worst block decay is below kDirectLimit (log2 units)
+// and covers the remaining pairs with hierarchy levels >= b.  lvl == 0 denotes the
+// direct level everywhere below.
+constexpr float kDirectLimit = 96.f;
+
+__device__ __forceinline__ bool pair_ok(int i, int j, int lvl, int b) {
+  if (lvl) return level_pair_ok(i, j, lvl);
+  return (((i ^ j) & ~(b - 1)) == 0) && (j < i);
+}
+
+// Per-channel worst block decay for b = 2,4,...,64 (dmax[0..5]) from the cumulative
+// log2-decay column c of sG.
+__device__ __forceinline__ void block_decay_max(const float* sG, int c, float (&dmax)[6]) {
+#pragma unroll
+  for (int e = 0; e < 6; ++e) {
+    const int b = 2 << e;
+    float m = 0.f;
+    for (int bs = 0; bs < kChunk; bs += b) m = fmaxf(m, sG[bs * kLdG + c] - sG[(bs + b - 1) * kLdG + c]);
+    dmax[e] = m;
+  }
+}
+
+// Largest admissible direct block size given the per-warp maxima (nw warps x 6).
+__device__ __forceinline__ int pick_direct_block(const float* sWarpMax, int nw, int cap) {
+  int b = 1;
+#pragma unroll
+  for (int e = 0; e < 6; ++e) {
+    float m = 0.f;
+    for (int w = 0; w < nw; ++w) m = fmaxf(m, sWarpMax[w * 6 + e]);
+    if (m <= kDirectLimit && (2 << e) <= cap) b = 2 << e;
+    else break;
+  }
+  return b;
+}
+
 // 2^x by the hardware approximation (flushes denormal results to zero, which is
 // what the gating factors want: every argument here is <= 0).
 __device__ __forceinline__ float ex2(float x) {
@@ -44,12 +83,12 @@ __device__ __forceinline__ void scale8(uint4& x, const float (&f)[8]) {
 // destinations are skipped.  sFac (optional, fp32 [64][kLdG]) receives the factor
 // each row used.  Eight channels per thread and step (128-bit accesses).
 __device__ __forceinline__ void stage_level(bf16* sXq, bf16* sXk, bf16* sY, const bf16* sQ, const bf16* sK,
-                                            const bf16* sKt, const float* sG, int lvl, int tid, int nthreads,
-                                            float* sFac = nullptr) {
+                                            const bf16* sKt, const float* sG, int lvl, int b, int tid,
+                                            int nthreads, float* sFac = nullptr) {
   for (int idx = tid; idx < kChunk * kD / 8; idx += nthreads) {
     const int r = idx >> 4, c8 = (idx & 15) << 3;
-    const int ref = (r & ~(2 * lvl - 1)) + lvl;
-    const bool upper = (r & lvl) != 0;
+    const int ref = lvl ? (r & ~(2 * lvl - 1)) + lvl : (r & ~(b - 1));
+    const bool upper = lvl ? (r & lvl) != 0 : true;
     const float4 a0 = *reinterpret_cast<const float4*>(sG + r * kLdG + c8);
     const float4 a1 = *reinterpret_cast<const float4*>(sG + r * kLdG + c8 + 4);
     const float4 b0 = *reinterpret_cast<const float4*>(sG + ref * kLdG + c8);
@@ -74,6 +113,14 @@ __device__ __forceinline__ void stage_level(bf16* sXq, bf16* sXk, bf16* sY, cons
         uint4 x = *reinterpret_cast<const uint4*>(sK + r * kLdD + c8);
         scale8(x, f);
         *reinterpret_cast<uint4*>(sXk + r * kLdD + c8) = x;
+      }
+      if (!lvl && sY) {  // direct level: the same row is also a column operand, factor 1/f
+        float fi[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) fi[j] = __fdividef(1.f, f[j]);
+        uint4 x = *reinterpret_cast<const uint4*>(sKt + r * kLdD + c8);
+        scale8(x, fi);
+        *reinterpret_cast<uint4*>(sY + r * kLdD + c8) = x;
       }
     } else if (sY) {
       uint4 x = *reinterpret_cast<const uint4*>(sKt + r * kLdD + c8);
@@ -129,7 +176,7 @@ __device__ __forceinline__ void gate_cumsum(float* sG, int c) {
 template <int kNT, bool kATrans, bool kBKN>
 __device__ __forceinline__ void warp_gemm_lvl(float (&acc)[1][kNT][4], const bf16* A, int lda, int m0,
                                               const bf16* B, int ldb, int n0, int kbeg, int kend, int lvl,
-                                              bool mask) {
+                                              int b, bool mask) {
   const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
 #pragma unroll 1
   for (int k0 = kbeg; k0 < kend; k0 += 16) {
@@ -140,17 +187,17 @@ __device__ __forceinline__ void warp_gemm_lvl(float (&acc)[1][kNT][4], const bf1
       for (int r = 0; r < 4; ++r) {
         const int m = m0 + g + 8 * (r & 1);
         const int kk = k0 + 2 * t + 8 * (r >> 1);
-        const bool ok0 = kATrans ? level_pair_ok(kk, m, lvl) : level_pair_ok(m, kk, lvl);
-        const bool ok1 = kATrans ? level_pair_ok(kk + 1, m, lvl) : level_pair_ok(m, kk + 1, lvl);
+        const bool ok0 = kATrans ? pair_ok(kk, m, lvl, b) : pair_ok(m, kk, lvl, b);
+        const bool ok1 = kATrans ? pair_ok(kk + 1, m, lvl, b) : pair_ok(m, kk + 1, lvl, b);
         a[r] &= (ok0 ? 0x0000ffffu : 0u) | (ok1 ? 0xffff0000u : 0u);
       }
     }
 #pragma unroll
     for (int np = 0; np < kNT / 2; ++np) {
-      uint32_t b[4];
-      load_b_frag2<kBKN>(b, B, ldb, k0, n0 + 16 * np);
-      mma_bf16(acc[0][2 * np], a, b[0], b[1]);
-      mma_bf16(acc[0][2 * np + 1], a, b[2], b[3]);
+      uint32_t bf[4];
+      load_b_frag2<kBKN>(bf, B, ldb, k0, n0 + 16 * np);
+      mma_bf16(acc[0][2 * np], a, bf[0], bf[1]);
+      mma_bf16(acc[0][2 * np + 1], a, bf[2], bf[3]);
     }
   }
 }

@@ -206,6 +206,7 @@ struct IntraBwdParams {
   float *dk_read, *dkt;
   float *partA, *partB;
   float scale;
+  int direct_cap;
 };
 
 namespace ib {
@@ -221,8 +222,8 @@ constexpr int oDP = oStage + 3 * kTileBytes;  // bf16 [64][72]
 constexpr int oDM = oDP + kChunk * kLdC * 2;
 constexpr int oFac = oDM + kChunk * kLdC * 2; // f32 [64][kLdG]
 constexpr int oSmall = oFac + kChunk * kLdG * 4;
-// small: beta[64] db[64] hdh[128] gcv[128] col[4][128] rb[4][64] red[16] bias[128]
-constexpr int kSmallFloats = 64 + 64 + 128 + 128 + 512 + 256 + 16 + 128;
+// small: beta[64] db[64] hdh[128] gcv[128] col[4][128] rb[4][64] red[16] bias[128] warpmax[4][6]
+constexpr int kSmallFloats = 64 + 64 + 128 + 128 + 512 + 256 + 16 + 128 + 24;
 constexpr int kSmem = oSmall + kSmallFloats * 4;
 static_assert(oDR + kTileBytes <= oDP, "phase-A tiles must not reach the pair-gradient tiles");
 static_assert(oDE + kD * kLdD * 2 <= oDP, "dS1 tile must fit");
@@ -230,7 +231,9 @@ static_assert(oDE + kD * kLdD * 2 <= oDP, "dS1 tile must fit");
 
 // acc += fac * t and dG += sign * x * t on one warp's [16 x 32] fragment
 // (i0 = first row + lane/4, c0 = first column + 2*(lane%4)); fac is the fp32
-// level factor of each row, x the staged bf16 operand the product was formed with.
+// level factor of each row (kInverse: its reciprocal, the column factor of the
+// direct level), x the staged bf16 operand the product was formed with.
+template <bool kInverse>
 __device__ __forceinline__ void epi_add(float (&acc)[1][4][4], float (&dG)[1][4][4], const float (&t)[1][4][4],
                                         const float* sFac, const bf16* sX, float sign, int i0, int c0) {
 #pragma unroll
@@ -238,7 +241,8 @@ __device__ __forceinline__ void epi_add(float (&acc)[1][4][4], float (&dG)[1][4]
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
       const int i = i0 + 8 * half, c = c0 + 8 * nt;
-      const float2 f = *reinterpret_cast<const float2*>(sFac + i * kLdG + c);
+      float2 f = *reinterpret_cast<const float2*>(sFac + i * kLdG + c);
+      if (kInverse) { f.x = __fdividef(1.f, f.x); f.y = __fdividef(1.f, f.y); }
       const float2 x = unpack_bf16(*reinterpret_cast<const uint32_t*>(sX + i * kLdD + c));
       const float t0 = t[0][nt][2 * half], t1 = t[0][nt][2 * half + 1];
       acc[0][nt][2 * half] += f.x * t0;
@@ -272,6 +276,7 @@ pkda_intra_bwd_kernel(const IntraBwdParams p) {
   float* sRb = sCol + 512;   // [4][64]
   float* sRed = sRb + 256;   // [16]
   float* sBias = sRed + 16;  // [128]
+  float* sWarpMax = sBias + 128;  // [4][6]
 
   int n, tok0, valid;
   if (!chunk_lookup(p.geo, blockIdx.x, n, tok0, valid)) return;
@@ -299,6 +304,14 @@ pkda_intra_bwd_kernel(const IntraBwdParams p) {
   __syncthreads();
   if (tid < kD) {
     gate_cumsum(sG, tid);
+    float dmax[6];
+    block_decay_max(sG, tid, dmax);
+#pragma unroll
+    for (int e = 0; e < 6; ++e) {
+#pragma unroll
+      for (int o = 16; o >= 1; o >>= 1) dmax[e] = fmaxf(dmax[e], __shfl_xor_sync(0xffffffffu, dmax[e], o));
+      if (lane == 0) sWarpMax[warp * 6 + e] = dmax[e];
+    }
   } else {
     const int t2 = tid - kD;  // 384 threads
     // dE = beta * dF
@@ -496,25 +509,34 @@ pkda_intra_bwd_kernel(const IntraBwdParams p) {
     reinterpret_cast<uint4*>(smem + oStage)[i] = make_uint4(0, 0, 0, 0);
   __syncthreads();
   float rb[2] = {0.f, 0.f};
+  // Direct level (lvl = 0) for pairs inside a b-block, hierarchy levels >= b for the rest.
+  const int bdir = pick_direct_block(sWarpMax, 4, p.direct_cap);
 #pragma unroll 1
-  for (int lvl = 32; lvl >= 1; lvl >>= 1) {
-    stage_level(sXq, sXk, sY, sQ, sK, sKt, sG, lvl, tid, kThreads, sFac);
+  for (int it = (bdir > 1 ? 0 : 1); it <= 6; ++it) {
+    const int lvl = it ? (64 >> it) : 0;
+    if (lvl && lvl < bdir) break;
+    stage_level(sXq, sXk, sY, sQ, sK, sKt, sG, lvl, bdir, tid, kThreads, sFac);
     __syncthreads();
-    const bool big = lvl >= 16;
-    const int blk = (16 * I) & ~(2 * lvl - 1);
+    const bool big = lvl >= 16;               // whole 16-row tiles are upper or lower: no masking
+    const bool wide = !lvl && bdir >= 16;     // direct block made of whole tiles
+    const int blk = lvl ? ((16 * I) & ~(2 * lvl - 1)) : ((16 * I) & ~(bdir - 1));
     if (!big || ((16 * I) & lvl)) {  // rows act as the upper ("i") side
-      const int kb = big ? blk : 16 * I, ke = kb + (big ? lvl : 16);
+      int kb = 16 * I, ke = 16 * I + 16;
+      if (big) { kb = blk; ke = blk + lvl; }
+      else if (wide) { kb = blk; }
       zero_acc(t);
-      warp_gemm_lvl<4, false, true>(t, sdP, kLdC, 16 * I, sY, kLdD, 32 * cq, kb, ke, lvl, !big);
-      epi_add(dQ, dG, t, sFac, sXq, 1.f, 16 * I + gq, 32 * cq + 2 * tq);
+      warp_gemm_lvl<4, false, true>(t, sdP, kLdC, 16 * I, sY, kLdD, 32 * cq, kb, ke, lvl, bdir, !big);
+      epi_add<false>(dQ, dG, t, sFac, sXq, 1.f, 16 * I + gq, 32 * cq + 2 * tq);
       zero_acc(t);
-      warp_gemm_lvl<4, false, true>(t, sdM, kLdC, 16 * I, sY, kLdD, 32 * cq, kb, ke, lvl, !big);
-      epi_add(dK, dG, t, sFac, sXk, 1.f, 16 * I + gq, 32 * cq + 2 * tq);
+      warp_gemm_lvl<4, false, true>(t, sdM, kLdC, 16 * I, sY, kLdD, 32 * cq, kb, ke, lvl, bdir, !big);
+      epi_add<false>(dK, dG, t, sFac, sXk, 1.f, 16 * I + gq, 32 * cq + 2 * tq);
     }
     if (!big || !((16 * I) & lvl)) {  // rows act as the lower ("j") side
-      const int kb = big ? blk + lvl : 16 * I, ke = kb + (big ? lvl : 16);
+      int kb = 16 * I, ke = 16 * I + 16;
+      if (big) { kb = blk + lvl; ke = kb + lvl; }
+      else if (wide) { ke = blk + bdir; }
       zero_acc(t);
-      warp_gemm_lvl<4, true, true>(t, sdM, kLdC, 16 * I, sXk, kLdD, 32 * cq, kb, ke, lvl, !big);
+      warp_gemm_lvl<4, true, true>(t, sdM, kLdC, 16 * I, sXk, kLdD, 32 * cq, kb, ke, lvl, bdir, !big);
 #pragma unroll
       for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
@@ -523,8 +545,9 @@ pkda_intra_bwd_kernel(const IntraBwdParams p) {
               sY + (16 * I + gq + 8 * half) * kLdD + 32 * cq + 8 * nt + 2 * tq));
           rb[half] += y.x * t[0][nt][2 * half] + y.y * t[0][nt][2 * half + 1];
         }
-      warp_gemm_lvl<4, true, true>(t, sdP, kLdC, 16 * I, sXq, kLdD, 32 * cq, kb, ke, lvl, !big);
-      epi_add(dKt, dG, t, sFac, sY, -1.f, 16 * I + gq, 32 * cq + 2 * tq);
+      warp_gemm_lvl<4, true, true>(t, sdP, kLdC, 16 * I, sXq, kLdD, 32 * cq, kb, ke, lvl, bdir, !big);
+      if (lvl) epi_add<false>(dKt, dG, t, sFac, sY, -1.f, 16 * I + gq, 32 * cq + 2 * tq);
+      else epi_add<true>(dKt, dG, t, sFac, sY, -1.f, 16 * I + gq, 32 * cq + 2 * tq);
     }
     __syncthreads();
   }
@@ -861,7 +884,7 @@ int chunk_bwd(const pkda_chunk_bwd_args* a, cudaStream_t st) {
   ip.d_o = static_cast<const bf16*>(a->d_o);
   ip.dq = static_cast<bf16*>(a->dq); ip.dk_read = ws.dk_read; ip.dv = static_cast<bf16*>(a->dv);
   ip.dg = static_cast<bf16*>(a->dg); ip.dbeta = static_cast<bf16*>(a->dbeta); ip.dkt = ws.dkt;
-  ip.partA = ws.partA; ip.partB = ws.partB; ip.scale = p.scale;
+  ip.partA = ws.partA; ip.partB = ws.partB; ip.scale = p.scale; ip.direct_cap = direct_block_cap();
   if (!set_smem(pkda_intra_bwd_kernel, ib::kSmem)) return PKDA_ERR_LAUNCH;
   begin_stage(kStageIntraBwd, st);
   pkda_intra_bwd_kernel<<<gridc, ib::kThreads, ib::kSmem, st>>>(ip);

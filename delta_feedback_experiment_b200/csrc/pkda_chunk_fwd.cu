@@ -104,6 +104,7 @@ struct IntraParams {
   float* gc;  // [chunks][H][D] exp of the chunk's total log-decay
   bf16 *w, *u, *kg, *qg;
   float scale, ln_x, eps;
+  int direct_cap;  // upper limit for the direct block size (64 = no limit, 1 = hierarchy only)
 };
 
 namespace intra {
@@ -115,7 +116,7 @@ constexpr int oG = oKt + kTileBytes;              // fp32 [64][kLdG]
 constexpr int oStage = oG + kChunk * kLdG * 4;    // 3 bf16 tiles; aliased (see below)
 constexpr int oTmb = oStage + 3 * kTileBytes;     // bf16 [64][72]: P staging, then Tm
 constexpr int oSmall = oTmb + kChunk * kLdC * 2;  // beta[64] pd[64] bp[64] bias[128]
-constexpr int kSmem = oSmall + (3 * kChunk + kD) * 4;
+constexpr int kSmem = oSmall + (3 * kChunk + kD + 24) * 4;  // + per-warp block-decay maxima
 // aliases inside the staging area
 constexpr int oAt = oStage;                       // fp32 [64][kLdG] preconditioner states (before the levels)
 constexpr int kLdL = 65;
@@ -154,6 +155,7 @@ pkda_intra_fwd_kernel(const IntraParams p) {
   float* sPd = sBeta + kChunk;
   float* sBp = sPd + kChunk;
   float* sBias = sBp + kChunk;
+  float* sWarpMax = sBias + kD;  // [4][6]
   float* sAt = reinterpret_cast<float*>(smem + oAt);
   float* sL = reinterpret_cast<float*>(smem + oL);
   float* sT = reinterpret_cast<float*>(smem + oT);
@@ -193,6 +195,14 @@ pkda_intra_fwd_kernel(const IntraParams p) {
   __syncthreads();
   if (tid < kD) {
     gate_cumsum(sG, tid);
+    float dmax[6];
+    block_decay_max(sG, tid, dmax);
+#pragma unroll
+    for (int e = 0; e < 6; ++e) {
+#pragma unroll
+      for (int o = 16; o >= 1; o >>= 1) dmax[e] = fmaxf(dmax[e], __shfl_xor_sync(0xffffffffu, dmax[e], o));
+      if (lane == 0) sWarpMax[warp * 6 + e] = dmax[e];
+    }
   } else if (!kRecompute && tid < 2 * kD) {
     const int c = tid - kD;
     float A = p.a_start[chh * kD + c];
@@ -240,26 +250,38 @@ pkda_intra_fwd_kernel(const IntraParams p) {
   const int I32 = 2 + (I >> 1), J32 = I & 1;   // level-32 tile of an off warp
   const int I16 = 1 + 2 * I, J16 = 2 * I;      // level-16 tile (I < 2)
 
+  // Pairs inside a b-block go through the direct level (lvl = 0), the rest through
+  // hierarchy levels >= b.  Each off-diagonal tile is produced exactly once.
+  const int bdir = pick_direct_block(sWarpMax, 4, p.direct_cap);
 #pragma unroll 1
-  for (int lvl = 32; lvl >= 1; lvl >>= 1) {
-    stage_level(sXq, sXk, sY, sQ, sK, sKt, sG, lvl, tid, kThreads);
+  for (int it = (bdir > 1 ? 0 : 1); it <= 6; ++it) {
+    const int lvl = it ? (64 >> it) : 0;  // 0 (direct), 32, 16, 8, 4, 2, 1
+    if (lvl && lvl < bdir) break;
+    stage_level(sXq, sXk, sY, sQ, sK, sKt, sG, lvl, bdir, tid, kThreads);
     __syncthreads();
     const bf16* X = mat ? sXq : sXk;
     float tmp[1][2][4];
-    zero_acc(tmp);
-    if (lvl == 32 && !diagw) {
-      warp_gemm<1, 2, false, false>(tmp, X, kLdD, 16 * I32, sY, kLdD, 16 * J32, 0, kD);
+    if (!diagw) {
+      // level-32 region tile: by hierarchy level 32 unless the direct block covers it (b = 64)
+      if ((lvl == 32) || (lvl == 0 && bdir > 32)) {
+        zero_acc(tmp);
+        warp_gemm<1, 2, false, false>(tmp, X, kLdD, 16 * I32, sY, kLdD, 16 * J32, 0, kD);
 #pragma unroll
-      for (int a = 0; a < 2; ++a)
+        for (int a = 0; a < 2; ++a)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) accA[a][e] = tmp[0][a][e];
-    } else if (lvl == 16 && !diagw && I < 2) {
-      warp_gemm<1, 2, false, false>(tmp, X, kLdD, 16 * I16, sY, kLdD, 16 * J16, 0, kD);
+          for (int e = 0; e < 4; ++e) accA[a][e] = tmp[0][a][e];
+      }
+      // level-16 region tile: by hierarchy level 16 unless the direct block covers it (b >= 32)
+      if (I < 2 && ((lvl == 16 && bdir <= 16) || (lvl == 0 && bdir > 16))) {
+        zero_acc(tmp);
+        warp_gemm<1, 2, false, false>(tmp, X, kLdD, 16 * I16, sY, kLdD, 16 * J16, 0, kD);
 #pragma unroll
-      for (int a = 0; a < 2; ++a)
+        for (int a = 0; a < 2; ++a)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) accB[a][e] = tmp[0][a][e];
-    } else if (lvl <= 8 && diagw) {
+          for (int e = 0; e < 4; ++e) accB[a][e] = tmp[0][a][e];
+      }
+    } else if (lvl <= 8) {
+      zero_acc(tmp);
       warp_gemm<1, 2, false, false>(tmp, X, kLdD, 16 * I, sY, kLdD, 16 * I, 0, kD);
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt)
@@ -267,7 +289,7 @@ pkda_intra_fwd_kernel(const IntraParams p) {
         for (int e = 0; e < 4; ++e) {
           const int i = 16 * I + gq + ((e >> 1) << 3);
           const int j = 16 * I + 8 * nt + 2 * tq + (e & 1);
-          if (level_pair_ok(i, j, lvl)) accA[nt][e] += tmp[0][nt][e];
+          if (pair_ok(i, j, lvl, bdir)) accA[nt][e] += tmp[0][nt][e];
         }
     }
     __syncthreads();
@@ -674,6 +696,7 @@ int run_forward_stages(const pkda_problem& p, const Geo& geo, const float* beta_
   ip.Aqk = Aqk; ip.Akk = Akk; ip.kt = kt; ip.gc = gc;
   ip.w = w; ip.u = u_ws; ip.kg = kg; ip.qg = qg;
   ip.scale = p.scale; ip.ln_x = logf(p.squash_x); ip.eps = p.squash_eps;
+  ip.direct_cap = direct_block_cap();
   dim3 gridc(chunks, p.heads);
   if (recompute) {
     if (!set_smem(pkda_intra_fwd_kernel<true>, intra::kSmem)) return PKDA_ERR_LAUNCH;

@@ -21,6 +21,10 @@ void begin_stage(int stage, cudaStream_t st);
 void end_stage(cudaStream_t st);
 void reset_launch_count();
 
+// Upper limit for the kernels' direct block size (64 unless lowered through
+// pkda_set_direct_block_cap, a testing aid).
+int direct_block_cap();
+
 // Validates the fields every entry point relies on.
 int check_problem(const pkda_problem& p);
 

@@ -188,6 +188,15 @@ size_t pkda_sizeof_chunk_bwd_args(void);
 int pkda_last_launch_count(void);
 
 /*
+ * Testing aid.  The chunked kernels pair tokens inside blocks of b rows through a
+ * single reference row whenever the decay across the block is small enough, and
+ * through a binary hierarchy of reference rows otherwise; b is chosen per
+ * (chunk, head) from the data.  This caps b (a power of two in 1..64; 64 = no cap,
+ * 1 = hierarchy only) so that tests can exercise every variant on the same input.
+ */
+int pkda_set_direct_block_cap(int cap);
+
+/*
  * Optional per-kernel timing for benchmarks.  pkda_stage_timing(1) makes every
  * later launch record a CUDA event pair on its stream (events come from a pool
  * that grows with cudaEventCreate; not for use under stream capture);

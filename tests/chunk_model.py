@@ -60,12 +60,36 @@ def level_mask(n, lvl):
     return ((i // (2 * lvl)) == (j // (2 * lvl))) & ((i & lvl) != 0) & ((j & lvl) == 0)
 
 
+DIRECT = 1
+"""Direct block size b (a power of two, 1..64): pairs inside the same b-block use
+one reference row (the block's first row) instead of hierarchy levels < b.  Only
+valid while the decay across a b-block stays far inside the exponent range; the
+kernels pick the largest admissible b per (chunk, head)."""
+
+
+def direct_factors(G, b):
+    n = G.shape[0]
+    ref = (torch.arange(n) // b) * b
+    Gref = G[ref]
+    return torch.exp(G - Gref), torch.exp(Gref - G)
+
+
+def direct_mask(n, b):
+    i = torch.arange(n)[:, None]
+    j = torch.arange(n)[None, :]
+    return ((i // b) == (j // b)) & (j < i)
+
+
 def gated_pairs(X, Y, G, diag, op_dtype=None):
     """sum_c X[i,c] Y[j,c] exp(G[i,c]-G[j,c]) for i>j (and i==j if diag)."""
     n = X.shape[0]
     out = torch.zeros(n, n, dtype=X.dtype)
+    if DIRECT > 1:
+        rowf, colf = direct_factors(G, DIRECT)
+        out += torch.where(direct_mask(n, DIRECT),
+                           rnd(X * rowf, op_dtype) @ rnd(Y * colf, op_dtype).T, 0.0)
     for lvl in LEVELS:
-        if lvl >= n:
+        if lvl >= n or lvl < DIRECT:
             continue
         rowf, colf = level_factors(G, lvl)
         out += torch.where(level_mask(n, lvl),
@@ -85,11 +109,18 @@ def gated_pairs_bwd(dOut, X, Y, G, diag, op_dtype=None):
     dX = torch.zeros_like(X)
     dY = torch.zeros_like(Y)
     dG = torch.zeros_like(X)
-    for lvl in LEVELS:
-        if lvl >= n:
-            continue
-        rowf, colf = level_factors(G, lvl)
-        dm = rnd(torch.where(level_mask(n, lvl), dOut, 0.0), op_dtype)
+    for lvl in (0,) + LEVELS:
+        if lvl == 0:
+            if DIRECT <= 1:
+                continue
+            rowf, colf = direct_factors(G, DIRECT)
+            mask = direct_mask(n, DIRECT)
+        else:
+            if lvl >= n or lvl < DIRECT:
+                continue
+            rowf, colf = level_factors(G, lvl)
+            mask = level_mask(n, lvl)
+        dm = rnd(torch.where(mask, dOut, 0.0), op_dtype)
         Xl, Yl = rnd(X * rowf, op_dtype), rnd(Y * colf, op_dtype)
         dXl = dm @ Yl
         dYl = dm.T @ Xl

@@ -136,3 +136,23 @@ def test_backward_twice_is_bitwise_identical():
     a, b = run(d), run(d)
     for key in a:
         assert torch.equal(a[key], b[key]), key
+
+
+@pytest.mark.parametrize("cap", [1, 2, 4, 8, 16, 32, 64])
+@pytest.mark.parametrize("dist", ["unit", "production"])
+def test_direct_block_variants(cap, dist):
+    """The kernels pair tokens through one reference row per block of b tokens when
+    the decay allows it and through the reference-row hierarchy otherwise; every
+    cap on b must give the same forward and gradients within tolerance."""
+    from delta_feedback_experiment_b200 import _lib
+    d = make_inputs(2, 192, 2, 128, seed=95, dist=dist, dtype=torch.bfloat16, with_state=True)
+    ref = pkda_oracle_with_grads([d[n] for n in INPUT_NAMES], d["do"],
+                                 initial_state=d["initial_state"],
+                                 initial_A_state=d["initial_A_state"], dtype=torch.float64)
+    _lib.set_direct_block_cap(cap)
+    try:
+        res = run(d)
+    finally:
+        _lib.set_direct_block_cap(64)
+    assert rel_rms(res["o"], ref["o"]) < 0.005
+    check(res, ref, f"cap{cap}-{dist}")

@@ -130,17 +130,27 @@ __device__ __forceinline__ void stage_level(bf16* sXq, bf16* sXk, bf16* sY, cons
   }
 }
 
-// Elementwise part of the decay gate for one chunk, all threads: log2-domain
+// Elementwise part of the decay gate for one chunk, all kNThreads threads: log2-domain
 // per-token log-decay  -exp(A_log) log2(e) softplus(raw + bias)  into sG (zero for
 // rows past the sequence end).  The cumulative sum over rows follows separately.
+template <int kNThreads>
 __device__ __forceinline__ void gate_elementwise(float* sG, const bf16* g_row0, long gld, int valid,
-                                                 const float* bias_h, float ea2, int tid, int nthreads) {
-  for (int idx = tid; idx < kChunk * kD / 8; idx += nthreads) {
-    const int r = idx >> 4, c8 = (idx & 15) << 3;
+                                                 const float* bias_h, float ea2, int tid) {
+  constexpr int kIter = kChunk * kD / 8 / kNThreads;
+  static_assert(kIter * kNThreads * 8 == kChunk * kD, "tile must divide evenly");
+  uint4 raw[kIter];
+#pragma unroll
+  for (int it = 0; it < kIter; ++it) {  // all global loads in flight before any use
+    const int idx = tid + it * kNThreads, r = idx >> 4, c8 = (idx & 15) << 3;
+    raw[it] = make_uint4(0, 0, 0, 0);
+    if (r < valid) raw[it] = *reinterpret_cast<const uint4*>(g_row0 + (size_t)r * gld + c8);
+  }
+#pragma unroll
+  for (int it = 0; it < kIter; ++it) {
+    const int idx = tid + it * kNThreads, r = idx >> 4, c8 = (idx & 15) << 3;
     float o[8];
     if (r < valid) {
-      const uint4 raw = *reinterpret_cast<const uint4*>(g_row0 + (size_t)r * gld + c8);
-      const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw);
+      const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw[it]);
       const float4 bA = *reinterpret_cast<const float4*>(bias_h + c8);
       const float4 bB = *reinterpret_cast<const float4*>(bias_h + c8 + 4);
       const float bb[8] = {bA.x, bA.y, bA.z, bA.w, bB.x, bB.y, bB.z, bB.w};
@@ -202,51 +212,61 @@ __device__ __forceinline__ void warp_gemm_lvl(float (&acc)[1][kNT][4], const bf1
   }
 }
 
-// T = (I + L)^-1 for a 64 x 64 strictly lower triangular L (fp32, row stride ld),
-// the first 256 threads of the CTA work, all threads must call.  Diagonal 16 x 16 blocks by forward substitution (one thread per
-// column), then block rows 1..3: T_IJ = -T_II * sum_{J<=M<I} L_IM T_MJ.
-// sY2 is a [16][64] fp32 scratch.  Ends with a __syncthreads().
-__device__ __forceinline__ void unit_lower_inverse_64(const float* sL, float* sT, float* sY2, int ld, int tid) {
-  if (tid < 64) {
-    const int blk = tid >> 4, col = tid & 15;
-    const float* Lb = sL + (16 * blk) * ld + 16 * blk;
-    float x[16];
+// One doubling step of the triangular inverse: for every pair of inverted diagonal
+// blocks T11, T22 of size N and their coupling block L21, T21 = -T22 (L21 T11).
+// Loops run over full N (the blocks' upper triangles are zero) so they unroll.
+template <int N>
+__device__ __forceinline__ void inverse_merge(const float* sL, float* sT, float* sY2, int ld, int tid, int nthreads) {
+  constexpr int SH = N == 4 ? 2 : (N == 8 ? 3 : (N == 16 ? 4 : 5));
+  for (int o = tid; o < 32 * N; o += nthreads) {
+    const int pr = o >> (2 * SH), r = (o >> SH) & (N - 1), c = o & (N - 1);
+    const int base = pr * 2 * N;
+    const float* Lrow = sL + (base + N + r) * ld + base;
+    const float* Tcol = sT + base * ld + base + c;
+    float s = 0.f;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
+    for (int m = 0; m < N; ++m) s += Lrow[m] * Tcol[m * ld];
+    sY2[o] = s;
+  }
+  __syncthreads();
+  for (int o = tid; o < 32 * N; o += nthreads) {
+    const int pr = o >> (2 * SH), r = (o >> SH) & (N - 1), c = o & (N - 1);
+    const int base = pr * 2 * N;
+    const float* Trow = sT + (base + N + r) * ld + base + N;
+    const float* Ycol = sY2 + (pr << (2 * SH)) + c;
+    float t = 0.f;
+#pragma unroll
+    for (int m = 0; m < N; ++m) t -= Trow[m] * Ycol[m << SH];
+    sT[(base + N + r) * ld + base + c] = t;
+  }
+  __syncthreads();
+}
+
+// T = (I + L)^-1 for a 64 x 64 strictly lower triangular L (fp32, row stride ld),
+// all nthreads threads of the CTA: 4 x 4 diagonal blocks by forward substitution,
+// then four doubling steps.  sY2 is a 1024-float scratch.  Ends with a __syncthreads().
+__device__ __forceinline__ void unit_lower_inverse_64(const float* sL, float* sT, float* sY2, int ld, int tid,
+                                                      int nthreads) {
+  for (int i = tid; i < kChunk * kChunk; i += nthreads) sT[(i >> 6) * ld + (i & 63)] = 0.f;
+  __syncthreads();
+  if (tid < 64) {
+    const int base = (tid >> 2) << 2, col = tid & 3;
+    float x[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
       float s = (i == col) ? 1.f : 0.f;
 #pragma unroll
-      for (int m = 0; m < i; ++m) s -= Lb[i * ld + m] * x[m];
+      for (int m = 0; m < i; ++m) s -= sL[(base + i) * ld + base + m] * x[m];
       x[i] = s;
     }
 #pragma unroll
-    for (int i = 0; i < 16; ++i) sT[(16 * blk + i) * ld + 16 * blk + col] = x[i];
-  } else if (tid < 256) {
-    for (int e = tid - 64; e < 6 * 256; e += 192) {
-      const int b = e >> 8, r = (e >> 4) & 15, c = e & 15;
-      // upper blocks (I,J), J > I: (0,1) (0,2) (0,3) (1,2) (1,3) (2,3)
-      const int I = b < 3 ? 0 : (b < 5 ? 1 : 2);
-      const int J = b < 3 ? b + 1 : (b < 5 ? b - 1 : 3);
-      sT[(16 * I + r) * ld + 16 * J + c] = 0.f;
-    }
+    for (int i = 0; i < 4; ++i) sT[(base + i) * ld + base + col] = x[i];
   }
   __syncthreads();
-  const int r = tid >> 4, cc = tid & 15;
-#pragma unroll 1
-  for (int I = 1; I < 4; ++I) {
-    for (int J = 0; J < I && tid < 256; ++J) {
-      float s = 0.f;
-      for (int m = 16 * J; m < 16 * I; ++m) s += sL[(16 * I + r) * ld + m] * sT[m * ld + 16 * J + cc];
-      sY2[r * 64 + 16 * J + cc] = s;
-    }
-    __syncthreads();
-    for (int J = 0; J < I && tid < 256; ++J) {
-      float t = 0.f;
-#pragma unroll
-      for (int m = 0; m < 16; ++m) t -= sT[(16 * I + r) * ld + 16 * I + m] * sY2[m * 64 + 16 * J + cc];
-      sT[(16 * I + r) * ld + 16 * J + cc] = t;
-    }
-    __syncthreads();
-  }
+  inverse_merge<4>(sL, sT, sY2, ld, tid, nthreads);
+  inverse_merge<8>(sL, sT, sY2, ld, tid, nthreads);
+  inverse_merge<16>(sL, sT, sY2, ld, tid, nthreads);
+  inverse_merge<32>(sL, sT, sY2, ld, tid, nthreads);
 }
 
 // tcgen05 / TMA output stage (pkda_out_tc.cu).

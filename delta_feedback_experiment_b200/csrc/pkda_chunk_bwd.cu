@@ -256,6 +256,7 @@ __global__ void __launch_bounds__(ib::kThreads, 1)
 pkda_intra_bwd_kernel(const IntraBwdParams p) {
   using namespace ib;
   extern __shared__ __align__(128) unsigned char smem[];
+  PKDA_PHASE(0);
   bf16* sdO = reinterpret_cast<bf16*>(smem + oA0);
   bf16* sS0 = reinterpret_cast<bf16*>(smem + oA1);
   bf16* sE = reinterpret_cast<bf16*>(smem + oA1);
@@ -264,7 +265,6 @@ pkda_intra_bwd_kernel(const IntraBwdParams p) {
   bf16* sTm = reinterpret_cast<bf16*>(smem + oTm);
   bf16* sdE = reinterpret_cast<bf16*>(smem + oDE);
   bf16* sdR = reinterpret_cast<bf16*>(smem + oDR);
-  bf16* sdSC = reinterpret_cast<bf16*>(smem + oDE);
   bf16* sdP = reinterpret_cast<bf16*>(smem + oDP);
   bf16* sdM = reinterpret_cast<bf16*>(smem + oDM);
   float* sFac = reinterpret_cast<float*>(smem + oFac);
@@ -294,14 +294,18 @@ pkda_intra_bwd_kernel(const IntraBwdParams p) {
   tile_load_async(sdO, kLdD, p.d_o + row0, gld, kChunk, kD, valid, kThreads);
   tile_load_async(sS0, kLdD, p.h + chh * kD * kD, kD, kD, kD, kD, kThreads);
   tile_load_async(sTm, kLdC, p.Akk + crow0, cld, kChunk, kChunk, valid, kThreads);
+  tile_load_async(sdE, kLdD, p.dF + row0, gld, kChunk, kD, valid, kThreads);  // raw dF; scaled by beta below
+  // dS1 waits in the (not yet used) level-factor array until the dkg product
+  bf16* sdSC = reinterpret_cast<bf16*>(smem + oFac);
+  tile_load_async(sdSC, kLdD, p.dh + chh * kD * kD, kD, kD, kD, kD, kThreads);
   cp_async_commit();
   if (tid < kChunk) sBeta[tid] = p.beta_c[chh * kChunk + tid];
   if (tid < kD) sGcv[tid] = p.gc[chh * kD + tid];
   else if (tid < 2 * kD) sBias[tid - kD] = p.dt_bias[h * kD + tid - kD];
-  __syncthreads();
+  __syncthreads(); PKDA_PHASE(1);
   // log2-domain cumulative log-decay, exactly as the forward computes it
-  gate_elementwise(sG, p.g + row0, gld, valid, sBias, __expf(p.A_log[h]) * kLog2e, tid, kThreads);
-  __syncthreads();
+  gate_elementwise<kThreads>(sG, p.g + row0, gld, valid, sBias, __expf(p.A_log[h]) * kLog2e, tid);
+  __syncthreads(); PKDA_PHASE(2);
   if (tid < kD) {
     gate_cumsum(sG, tid);
     float dmax[6];
@@ -312,46 +316,38 @@ pkda_intra_bwd_kernel(const IntraBwdParams p) {
       for (int o = 16; o >= 1; o >>= 1) dmax[e] = fmaxf(dmax[e], __shfl_xor_sync(0xffffffffu, dmax[e], o));
       if (lane == 0) sWarpMax[warp * 6 + e] = dmax[e];
     }
-  } else {
-    const int t2 = tid - kD;  // 384 threads
-    // dE = beta * dF
-    for (int i = t2; i < kChunk * kD / 8; i += kThreads - kD) {
-      const int r = i >> 4, c = (i & 15) << 3;
-      uint4 fv = make_uint4(0, 0, 0, 0);
-      if (r < valid) fv = *reinterpret_cast<const uint4*>(p.dF + row0 + (size_t)r * gld + c);
-      const float b = p.beta_c[chh * kChunk + r];
-      uint32_t* f32 = reinterpret_cast<uint32_t*>(&fv);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 x = unpack_bf16(f32[j]);
-        f32[j] = pack_bf16(b * x.x, b * x.y);
-      }
-      *reinterpret_cast<uint4*>(sdE + r * kLdD + c) = fv;
-    }
-    // hdh[k] = sum_v S0[k][v] dS1[k][v]  (four threads per row)
-    for (int slot = t2; slot < 4 * kD; slot += kThreads - kD) {
-      const int row = slot >> 2, part = slot & 3;
-      const size_t base = (chh * kD + row) * kD + part * 32;
-      float acc = 0.f;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const uint4 a = *reinterpret_cast<const uint4*>(p.h + base + 8 * j);
-        const uint4 b = *reinterpret_cast<const uint4*>(p.dh + base + 8 * j);
-        const uint32_t* a32 = reinterpret_cast<const uint32_t*>(&a);
-        const uint32_t* b32 = reinterpret_cast<const uint32_t*>(&b);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 x = unpack_bf16(a32[e]), y = unpack_bf16(b32[e]);
-          acc += x.x * y.x + x.y * y.y;
-        }
-      }
-      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-      if (part == 0) sHdh[row] = acc;
-    }
   }
   cp_async_wait<0>();
-  __syncthreads();
+  __syncthreads(); PKDA_PHASE(3);
+  // dE = beta * dF in place;  hdh[k] = sum_v S0[k][v] dS1[k][v] (four threads per state row)
+  for (int i = tid; i < kChunk * kD / 8; i += kThreads) {
+    const int r = i >> 4, c = (i & 15) << 3;
+    const float b = sBeta[r];
+    const float f[8] = {b, b, b, b, b, b, b, b};
+    uint4 x = *reinterpret_cast<const uint4*>(sdE + r * kLdD + c);
+    scale8(x, f);
+    *reinterpret_cast<uint4*>(sdE + r * kLdD + c) = x;
+  }
+  {
+    const int row = tid >> 2, part = tid & 3;
+    float acc = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint4 a = *reinterpret_cast<const uint4*>(sS0 + row * kLdD + part * 32 + 8 * j);
+      const uint4 b = *reinterpret_cast<const uint4*>(sdSC + row * kLdD + part * 32 + 8 * j);
+      const uint32_t* a32 = reinterpret_cast<const uint32_t*>(&a);
+      const uint32_t* b32 = reinterpret_cast<const uint32_t*>(&b);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 x = unpack_bf16(a32[e]), y = unpack_bf16(b32[e]);
+        acc += x.x * y.x + x.y * y.y;
+      }
+    }
+    acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+    acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+    if (part == 0) sHdh[row] = acc;
+  }
+  __syncthreads(); PKDA_PHASE(30);
 
   float dQ[1][4][4], dK[1][4][4], dKt[1][4][4], dG[1][4][4];
   float t[1][4][4];
@@ -377,7 +373,7 @@ pkda_intra_bwd_kernel(const IntraBwdParams p) {
       if (r < valid) *reinterpret_cast<uint32_t*>(p.dv + row0 + (size_t)r * gld + c) = pk;
       *reinterpret_cast<uint32_t*>(sdR + r * kLdD + c) = pk;
     }
-  __syncthreads();
+  __syncthreads(); PKDA_PHASE(4);
   // dKd = -dR S0^T  ->  dk_a = Gam * dKd
   zero_acc(t);
   warp_gemm<1, 4, false, false>(t, sdR, kLdD, 16 * I, sS0, kLdD, 32 * cq, 0, kD);
@@ -388,36 +384,47 @@ pkda_intra_bwd_kernel(const IntraBwdParams p) {
       const int i = 16 * I + gq + 8 * (e >> 1), c = 32 * cq + 8 * nt + 2 * tq + (e & 1);
       dK[0][nt][e] = -t[0][nt][e] * ex2(sG[i * kLdG + c]);
     }
-  __syncthreads();  // S0 no longer needed
+  __syncthreads(); PKDA_PHASE(5);  // S0 no longer needed
   // E, F = beta E, and the direct part of dbeta: rowsum(dF * E)
-  for (int i = tid; i < kChunk * kD / 8; i += kThreads) {
-    const int r = i >> 4, c = (i & 15) << 3;
-    uint4 ev = make_uint4(0, 0, 0, 0), fv = make_uint4(0, 0, 0, 0);
-    if (r < valid) {
-      ev = *reinterpret_cast<const uint4*>(p.v_new + row0 + (size_t)r * gld + c);
-      fv = *reinterpret_cast<const uint4*>(p.dF + row0 + (size_t)r * gld + c);
-    }
-    const float b = sBeta[r];
-    uint32_t* e32 = reinterpret_cast<uint32_t*>(&ev);
-    const uint32_t* f32 = reinterpret_cast<const uint32_t*>(&fv);
-    uint4 bf;
-    uint32_t* bf32 = reinterpret_cast<uint32_t*>(&bf);
-    float part = 0.f;
+  {
+    constexpr int kIter = kChunk * kD / 8 / kThreads;
+    uint4 evs[kIter], fvs[kIter];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 x = unpack_bf16(e32[j]), y = unpack_bf16(f32[j]);
-      part += x.x * y.x + x.y * y.y;
-      bf32[j] = pack_bf16(b * x.x, b * x.y);
+    for (int it = 0; it < kIter; ++it) {  // all global loads in flight before any use
+      const int i = tid + it * kThreads, r = i >> 4, c = (i & 15) << 3;
+      evs[it] = fvs[it] = make_uint4(0, 0, 0, 0);
+      if (r < valid) {
+        evs[it] = *reinterpret_cast<const uint4*>(p.v_new + row0 + (size_t)r * gld + c);
+        fvs[it] = *reinterpret_cast<const uint4*>(p.dF + row0 + (size_t)r * gld + c);
+      }
     }
-    *reinterpret_cast<uint4*>(sE + r * kLdD + c) = ev;
-    *reinterpret_cast<uint4*>(sF + r * kLdD + c) = bf;
-    part += __shfl_xor_sync(0xffffffffu, part, 8);
-    part += __shfl_xor_sync(0xffffffffu, part, 4);
-    part += __shfl_xor_sync(0xffffffffu, part, 2);
-    part += __shfl_xor_sync(0xffffffffu, part, 1);
-    if ((i & 15) == 0) sDb[r] = part;
+#pragma unroll
+    for (int it = 0; it < kIter; ++it) {
+      const int i = tid + it * kThreads, r = i >> 4, c = (i & 15) << 3;
+      uint4 ev = evs[it];
+      const uint4 fv = fvs[it];
+      const float b = sBeta[r];
+      uint32_t* e32 = reinterpret_cast<uint32_t*>(&ev);
+      const uint32_t* f32 = reinterpret_cast<const uint32_t*>(&fv);
+      uint4 bf;
+      uint32_t* bf32 = reinterpret_cast<uint32_t*>(&bf);
+      float part = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 x = unpack_bf16(e32[j]), y = unpack_bf16(f32[j]);
+        part += x.x * y.x + x.y * y.y;
+        bf32[j] = pack_bf16(b * x.x, b * x.y);
+      }
+      *reinterpret_cast<uint4*>(sE + r * kLdD + c) = ev;
+      *reinterpret_cast<uint4*>(sF + r * kLdD + c) = bf;
+      part += __shfl_xor_sync(0xffffffffu, part, 8);
+      part += __shfl_xor_sync(0xffffffffu, part, 4);
+      part += __shfl_xor_sync(0xffffffffu, part, 2);
+      part += __shfl_xor_sync(0xffffffffu, part, 1);
+      if ((i & 15) == 0) sDb[r] = part;
+    }
   }
-  __syncthreads();
+  __syncthreads(); PKDA_PHASE(6);
   // pair-weight gradients: dM = -tril(dR E^T, -1) diag(beta),  dP = scale tril(dO F^T)
   {
     const int J = cq;
@@ -445,12 +452,13 @@ pkda_intra_bwd_kernel(const IntraBwdParams p) {
         *reinterpret_cast<uint32_t*>(sdP + i * kLdC + j) = pack_bf16(p0, p1);
       }
   }
-  __syncthreads();  // dO, dR, E no longer needed
+  __syncthreads(); PKDA_PHASE(7);  // dO, dR, E no longer needed
   // dkg = F dS1^T  ->  dkt_a = exp(G_last - G) * dkg
-  tile_load_async(sdSC, kLdD, p.dh + chh * kD * kD, kD, kD, kD, kD, kThreads);
+  PKDA_PHASE(8);
+  // q and k tiles of the pair-product phase land while the dkg product runs
+  tile_load_async(reinterpret_cast<bf16*>(smem + oA0), kLdD, p.q + row0, gld, kChunk, kD, valid, kThreads);
+  tile_load_async(reinterpret_cast<bf16*>(smem + oA1), kLdD, p.k + row0, gld, kChunk, kD, valid, kThreads);
   cp_async_commit();
-  cp_async_wait<0>();
-  __syncthreads();
   zero_acc(t);
   warp_gemm<1, 4, false, false>(t, sF, kLdD, 16 * I, sdSC, kLdD, 32 * cq, 0, kD);
 #pragma unroll
@@ -460,7 +468,7 @@ pkda_intra_bwd_kernel(const IntraBwdParams p) {
       const int i = 16 * I + gq + 8 * (e >> 1), c = 32 * cq + 8 * nt + 2 * tq + (e & 1);
       dKt[0][nt][e] = t[0][nt][e] * ex2(sG[(kChunk - 1) * kLdG + c] - sG[i * kLdG + c]);
     }
-  __syncthreads();
+  __syncthreads(); PKDA_PHASE(9);
 
   // ================= phase B: gated pair products =================
   bf16* sQ = reinterpret_cast<bf16*>(smem + oA0);
@@ -469,12 +477,10 @@ pkda_intra_bwd_kernel(const IntraBwdParams p) {
   bf16* sXq = reinterpret_cast<bf16*>(smem + oStage);
   bf16* sXk = sXq + kChunk * kLdD;
   bf16* sY = sXk + kChunk * kLdD;
-  tile_load_async(sQ, kLdD, p.q + row0, gld, kChunk, kD, valid, kThreads);
-  tile_load_async(sK, kLdD, p.k + row0, gld, kChunk, kD, valid, kThreads);
   tile_load_async(sKt, kLdD, p.kt + row0, gld, kChunk, kD, valid, kThreads);
   cp_async_commit();
   cp_async_wait<0>();
-  __syncthreads();
+  __syncthreads(); PKDA_PHASE(10);
   {
     // dG starts from the state-coupled parts; column sums of kt * dkt_a feed the
     // chunk's last row (d/dG_last of exp(G_last - G_j)).
@@ -507,7 +513,7 @@ pkda_intra_bwd_kernel(const IntraBwdParams p) {
   // the staging tiles start from zeros rather than from whatever phase A left.
   for (int i = tid; i < 3 * kTileBytes / 16; i += kThreads)
     reinterpret_cast<uint4*>(smem + oStage)[i] = make_uint4(0, 0, 0, 0);
-  __syncthreads();
+  __syncthreads(); PKDA_PHASE(11);
   float rb[2] = {0.f, 0.f};
   // Direct level (lvl = 0) for pairs inside a b-block, hierarchy levels >= b for the rest.
   const int bdir = pick_direct_block(sWarpMax, 4, p.direct_cap);
@@ -516,7 +522,7 @@ pkda_intra_bwd_kernel(const IntraBwdParams p) {
     const int lvl = it ? (64 >> it) : 0;
     if (lvl && lvl < bdir) break;
     stage_level(sXq, sXk, sY, sQ, sK, sKt, sG, lvl, bdir, tid, kThreads, sFac);
-    __syncthreads();
+    __syncthreads(); PKDA_PHASE(12);
     const bool big = lvl >= 16;               // whole 16-row tiles are upper or lower: no masking
     const bool wide = !lvl && bdir >= 16;     // direct block made of whole tiles
     const int blk = lvl ? ((16 * I) & ~(2 * lvl - 1)) : ((16 * I) & ~(bdir - 1));
@@ -549,7 +555,7 @@ pkda_intra_bwd_kernel(const IntraBwdParams p) {
       if (lvl) epi_add<false>(dKt, dG, t, sFac, sY, -1.f, 16 * I + gq, 32 * cq + 2 * tq);
       else epi_add<true>(dKt, dG, t, sFac, sY, -1.f, 16 * I + gq, 32 * cq + 2 * tq);
     }
-    __syncthreads();
+    __syncthreads(); PKDA_PHASE(13);
   }
   // ungated diagonal of P
 #pragma unroll
@@ -584,51 +590,87 @@ pkda_intra_bwd_kernel(const IntraBwdParams p) {
       }
       *reinterpret_cast<float2*>(sdG + i * kLdG + c) = make_float2(dG[0][nt][2 * half], dG[0][nt][2 * half + 1]);
     }
-  __syncthreads();
+  __syncthreads(); PKDA_PHASE(14);
   if (tid < kChunk && tid < valid) {
     const float b = sBeta[tid];
     const float s = sRb[tid] + sRb[kChunk + tid] + sRb[2 * kChunk + tid] + sRb[3 * kChunk + tid];
     const float db = sDb[tid] + (b != 0.f ? s / b : 0.f);
     p.dbeta[(size_t)(tok0 + tid) * H + h] = __float2bfloat16(db);
   }
-  // reverse cumulative sum over the chunk, then the gate's own backward:
-  //   g = -exp(A_log) softplus(raw + bias);  draw = dg * (-exp(A_log)) sigmoid(raw + bias)
-  float pa = 0.f;
+  // reverse cumulative sum over the chunk (one channel per thread, in place) ...
   if (tid < kD) {
     const int c = tid;
-    const float ea = __expf(p.A_log[h]);
-    const float bias = p.dt_bias[h * kD + c];
     float run = sCol[c] + sCol[kD + c] + sCol[2 * kD + c] + sCol[3 * kD + c] + sGcv[c] * sHdh[c];
-    float pb = 0.f;
-    for (int r0 = kChunk - 8; r0 >= 0; r0 -= 8) {
-      float raw[8];
+#pragma unroll 8
+    for (int r = kChunk - 1; r >= 0; --r) {
+      run += sdG[r * kLdG + c];
+      sdG[r * kLdG + c] = run;
+    }
+  }
+  __syncthreads(); PKDA_PHASE(15);
+  // ... then the gate's own backward, elementwise over the tile with all threads:
+  //   g = -exp(A_log) softplus(raw + bias);  draw = dg * (-exp(A_log)) sigmoid(raw + bias)
+  // Per-thread partial sums (dA_log: scalar; ddt_bias: per channel) are reduced in a fixed order.
+  float* sPart = sFac;  // [32][kLdG] per-(row group, channel) partials of ddt_bias (the factors are dead)
+  {
+    const float ea = __expf(p.A_log[h]);
+    float pa = 0.f;
+    float pb[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j)
-        raw[j] = (r0 + j < valid) ? to_f(p.g[row0 + (size_t)(r0 + j) * gld + c]) : 0.f;
+    for (int j = 0; j < 8; ++j) pb[j] = 0.f;
+    const int c8 = (tid & 15) << 3;
+    constexpr int kIter = kChunk * kD / 8 / kThreads;
+    uint4 raws[kIter];
 #pragma unroll
-      for (int j = 7; j >= 0; --j) {
-        const int r = r0 + j;
-        run += sdG[r * kLdG + c];
-        if (r < valid) {
-          const float z = raw[j] + bias;
-          const float gn = -ea * softplus_fast(z);
-          const float dr = run * (-ea) * sigmoid_fast(z);
-          p.dg[row0 + (size_t)r * gld + c] = __float2bfloat16(dr);
-          pa += run * gn;
-          pb += dr;
+    for (int it = 0; it < kIter; ++it) {
+      const int r = (tid + it * kThreads) >> 4;
+      raws[it] = make_uint4(0, 0, 0, 0);
+      if (r < valid) raws[it] = *reinterpret_cast<const uint4*>(p.g + row0 + (size_t)r * gld + c8);
+    }
+#pragma unroll
+    for (int it = 0; it < kIter; ++it) {
+      const int r = (tid + it * kThreads) >> 4;
+      if (r < valid) {
+        const uint32_t* w = reinterpret_cast<const uint32_t*>(&raws[it]);
+        const float4 d0 = *reinterpret_cast<const float4*>(sdG + r * kLdG + c8);
+        const float4 d1 = *reinterpret_cast<const float4*>(sdG + r * kLdG + c8 + 4);
+        const float dgv[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+        uint4 outv;
+        uint32_t* o32 = reinterpret_cast<uint32_t*>(&outv);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 x = unpack_bf16(w[j]);
+          const float z0 = x.x + sBias[c8 + 2 * j], z1 = x.y + sBias[c8 + 2 * j + 1];
+          const float dr0 = dgv[2 * j] * (-ea) * sigmoid_fast(z0), dr1 = dgv[2 * j + 1] * (-ea) * sigmoid_fast(z1);
+          pa += dgv[2 * j] * (-ea * softplus_fast(z0)) + dgv[2 * j + 1] * (-ea * softplus_fast(z1));
+          pb[2 * j] += dr0;
+          pb[2 * j + 1] += dr1;
+          o32[j] = pack_bf16(dr0, dr1);
         }
+        *reinterpret_cast<uint4*>(p.dg + row0 + (size_t)r * gld + c8) = outv;
       }
     }
-    p.partB[chh * kD + c] = pb;
-    pa += __shfl_xor_sync(0xffffffffu, pa, 16);
-    pa += __shfl_xor_sync(0xffffffffu, pa, 8);
-    pa += __shfl_xor_sync(0xffffffffu, pa, 4);
-    pa += __shfl_xor_sync(0xffffffffu, pa, 2);
-    pa += __shfl_xor_sync(0xffffffffu, pa, 1);
+    // thread (tid >> 4) in 0..31 covers rows (tid >> 4) and (tid >> 4) + 32 of channel group c8
+    *reinterpret_cast<float4*>(sPart + (tid >> 4) * kLdG + c8) = make_float4(pb[0], pb[1], pb[2], pb[3]);
+    *reinterpret_cast<float4*>(sPart + (tid >> 4) * kLdG + c8 + 4) = make_float4(pb[4], pb[5], pb[6], pb[7]);
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) pa += __shfl_xor_sync(0xffffffffu, pa, o);
     if (lane == 0) sRed[warp] = pa;
   }
-  __syncthreads();
-  if (tid == 0) p.partA[chh] = sRed[0] + sRed[1] + sRed[2] + sRed[3];
+  __syncthreads(); PKDA_PHASE(16);
+  if (tid < kD) {
+    float acc = 0.f;
+#pragma unroll 8
+    for (int g = 0; g < 32; ++g) acc += sPart[g * kLdG + tid];
+    p.partB[chh * kD + tid] = acc;
+  }
+  if (tid == 0) {
+    float acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < kThreads / 32; ++w) acc += sRed[w];
+    p.partA[chh] = acc;
+  }
+  PKDA_PHASE(17);
 }
 
 // ------------------------------------------------------------------ preconditioner backward
@@ -650,96 +692,202 @@ struct AtkBwdParams {
   float ln_x, eps;
 };
 
-// One (chunk, head) per CTA, one channel per thread.  Recomputes A_t forward
-// from the chunk-start state, then walks the chunk backwards carrying
-// lam = dL/dA.  kFinal = false: zero incoming carry, only the outgoing carry is
-// produced (chunk-local pass).  kFinal = true: incoming carry given, all
-// gradients written.
+// One (chunk, head) per CTA, 256 threads.  The only sequential work is two
+// 64-step first-order scans per channel (A_t forward, lam = dL/dA backward), each
+// a multiply-add per step on shared memory; everything transcendental runs as
+// vectorised elementwise passes over the [64][128] tile with all threads.
+//   kFinal = false: zero incoming carry, only the outgoing carry is produced.
+//   kFinal = true : incoming carry given, all gradients written.
+namespace atkb {
+constexpr int kThreads = 256;
+constexpr int kIter = kChunk * kD / 8 / kThreads;  // 8-channel pieces per thread
+constexpr int oA = 0;                              // f32 [64][kLdG]  A before each token
+constexpr int oLam = oA + kChunk * kLdG * 4;       // f32 [64][kLdG]  dA_local, then lam
+constexpr int oT2 = oLam + kChunk * kLdG * 4;      // f32 [64][kLdG]  dk without the lam term (final only)
+constexpr int kSmemLocal = oT2;
+constexpr int kSmemFinal = oT2 + kChunk * kLdG * 4;
+}  // namespace atkb
+
 template <bool kFinal>
-__global__ void __launch_bounds__(kD)
+__global__ void __launch_bounds__(atkb::kThreads)
 pkda_atk_bwd_kernel(const AtkBwdParams p) {
-  __shared__ float sA[kChunk][kD];
+  using namespace atkb;
+  extern __shared__ __align__(128) unsigned char smem[];
+  float* sA = reinterpret_cast<float*>(smem + oA);
+  float* sLam = reinterpret_cast<float*>(smem + oLam);
+  float* sT2 = reinterpret_cast<float*>(smem + oT2);
   __shared__ float sPd[kChunk], sBp[kChunk];
-  __shared__ float sP1[4][kChunk], sP2[4][kChunk];
-  __shared__ float sRed[4];
+  __shared__ float sRed[kThreads / 32];
   int n, tok0, valid;
   if (!chunk_lookup(p.geo, blockIdx.x, n, tok0, valid)) return;
-  const int h = blockIdx.y, H = p.geo.heads, c = threadIdx.x, warp = c >> 5, lane = c & 31;
+  const int h = blockIdx.y, H = p.geo.heads, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const size_t chh = (size_t)blockIdx.x * H + h;
   const size_t row0 = ((size_t)tok0 * H + h) * kD;
   const long gld = (long)H * kD;
-  if (c < kChunk) {
-    const bool ok = c < valid;
-    const size_t s = (size_t)(tok0 + c) * H + h;
-    sPd[c] = ok ? __expf(p.g_atk[s]) : 1.f;
-    sBp[c] = ok ? to_f(p.beta_atk[s]) : 0.f;
+  const int c8 = (tid & 15) << 3;
+
+  // ---- all global reads of the elementwise pass in flight first
+  uint4 kraw[kIter];
+  float4 dkt0[kIter], dkt1[kIter];
+#pragma unroll
+  for (int it = 0; it < kIter; ++it) {
+    const int r = (tid + it * kThreads) >> 4;
+    kraw[it] = make_uint4(0, 0, 0, 0);
+    dkt0[it] = dkt1[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (r < valid) {
+      const size_t off = row0 + (size_t)r * gld + c8;
+      kraw[it] = *reinterpret_cast<const uint4*>(p.k + off);
+      dkt0[it] = *reinterpret_cast<const float4*>(p.dkt + off);
+      dkt1[it] = *reinterpret_cast<const float4*>(p.dkt + off + 4);
+    }
+  }
+  if (tid < kChunk) {
+    const bool ok = tid < valid;
+    const size_t s = (size_t)(tok0 + tid) * H + h;
+    sPd[tid] = ok ? __expf(p.g_atk[s]) : 1.f;
+    sBp[tid] = ok ? to_f(p.beta_atk[s]) : 0.f;
+  }
+  // k^2 per element parked in sLam for the forward scan
+#pragma unroll
+  for (int it = 0; it < kIter; ++it) {
+    const int r = (tid + it * kThreads) >> 4;
+    const uint32_t* w = reinterpret_cast<const uint32_t*>(&kraw[it]);
+    float q[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 x = unpack_bf16(w[j]);
+      q[2 * j] = x.x * x.x;
+      q[2 * j + 1] = x.y * x.y;
+    }
+    *reinterpret_cast<float4*>(sLam + r * kLdG + c8) = make_float4(q[0], q[1], q[2], q[3]);
+    *reinterpret_cast<float4*>(sLam + r * kLdG + c8 + 4) = make_float4(q[4], q[5], q[6], q[7]);
   }
   __syncthreads();
-  const float centre = p.log_atk_scale[h];
-  float A = p.a_start[chh * kD + c];
-  for (int r0 = 0; r0 < valid; r0 += 8) {
-    float kc[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) kc[j] = (r0 + j < valid) ? to_f(p.k[row0 + (size_t)(r0 + j) * gld + c]) : 0.f;
-#pragma unroll
-    for (int j = 0; j < 8; ++j)
-      if (r0 + j < valid) {
-        sA[r0 + j][c] = A;
-        A = sPd[r0 + j] * A + sBp[r0 + j] * kc[j] * kc[j];
-      }
+  // ---- forward scan: A before every token
+  if (tid < kD) {
+    float A = p.a_start[chh * kD + tid];
+#pragma unroll 8
+    for (int r = 0; r < kChunk; ++r) {
+      sA[r * kLdG + tid] = A;
+      A = sPd[r] * A + sBp[r] * sLam[r * kLdG + tid];
+    }
   }
-  float lam = kFinal ? p.lam_in[chh * kD + c] : 0.f;
+  __syncthreads();
+  // ---- elementwise: dA_local, and (final) the lam-free part of dk
+  const float centre = p.log_atk_scale[h];
   float dcacc = 0.f;
-  for (int r0 = (valid - 1) & ~7; r0 >= 0; r0 -= 8) {
-    float kc[8], dk_t[8], dkr[8];
+#pragma unroll
+  for (int it = 0; it < kIter; ++it) {
+    const int r = (tid + it * kThreads) >> 4;
+    const uint32_t* w = reinterpret_cast<const uint32_t*>(&kraw[it]);
+    const float dk_t[8] = {dkt0[it].x, dkt0[it].y, dkt0[it].z, dkt0[it].w,
+                           dkt1[it].x, dkt1[it].y, dkt1[it].z, dkt1[it].w};
+    const float4 a0 = *reinterpret_cast<const float4*>(sA + r * kLdG + c8);
+    const float4 a1 = *reinterpret_cast<const float4*>(sA + r * kLdG + c8 + 4);
+    const float Ap[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+    const float dec = sPd[r], bp = sBp[r];
+    float kc[8], dal[8], t2[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 x = unpack_bf16(w[j]);
+      kc[2 * j] = x.x;
+      kc[2 * j + 1] = x.y;
+    }
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const bool ok = r0 + j < valid;
-      const size_t off = row0 + (size_t)(r0 + j) * gld + c;
-      kc[j] = ok ? to_f(p.k[off]) : 0.f;
-      dk_t[j] = ok ? p.dkt[off] : 0.f;
-      dkr[j] = (kFinal && ok) ? p.dk_read[off] : 0.f;
+      const float An = dec * Ap[j] + bp * kc[j] * kc[j];
+      const float dev = __logf(An + p.eps) - centre;
+      const float den = 1.f + fabsf(dev);
+      const float Bf = __expf(-p.ln_x * __fdividef(dev, den));
+      const float ddev = -p.ln_x * dk_t[j] * kc[j] * Bf * __fdividef(1.f, den * den);
+      dal[j] = (r < valid) ? __fdividef(ddev, An + p.eps) : 0.f;
+      t2[j] = dk_t[j] * Bf;
+      if (r < valid) dcacc -= ddev;
     }
-#pragma unroll
-    for (int j = 7; j >= 0; --j) {
-      const int r = r0 + j;
-      if (r < valid) {  // uniform across the CTA
-        const float Ap = sA[r][c], dec = sPd[r], bp = sBp[r];
-        const float An = dec * Ap + bp * kc[j] * kc[j];
-        const float dev = __logf(An + p.eps) - centre;
-        const float den = 1.f + fabsf(dev);
-        const float Bf = __expf(-p.ln_x * __fdividef(dev, den));
-        const float ddev = -p.ln_x * dk_t[j] * kc[j] * Bf / (den * den);
-        lam += ddev / (An + p.eps);
-        if (kFinal) {
-          dcacc -= ddev;
-          p.dk[row0 + (size_t)r * gld + c] = __float2bfloat16(dkr[j] + dk_t[j] * Bf + 2.f * lam * bp * kc[j]);
-          float x1 = lam * kc[j] * kc[j], x2 = lam * dec * Ap;
-#pragma unroll
-          for (int o = 16; o >= 1; o >>= 1) {
-            x1 += __shfl_xor_sync(0xffffffffu, x1, o);
-            x2 += __shfl_xor_sync(0xffffffffu, x2, o);
-          }
-          if (lane == 0) { sP1[warp][r] = x1; sP2[warp][r] = x2; }
-        }
-        lam *= dec;
-      }
+    *reinterpret_cast<float4*>(sLam + r * kLdG + c8) = make_float4(dal[0], dal[1], dal[2], dal[3]);
+    *reinterpret_cast<float4*>(sLam + r * kLdG + c8 + 4) = make_float4(dal[4], dal[5], dal[6], dal[7]);
+    if (kFinal) {
+      *reinterpret_cast<float4*>(sT2 + r * kLdG + c8) = make_float4(t2[0], t2[1], t2[2], t2[3]);
+      *reinterpret_cast<float4*>(sT2 + r * kLdG + c8 + 4) = make_float4(t2[4], t2[5], t2[6], t2[7]);
     }
   }
-  if (!kFinal) {
-    p.c_loc[chh * kD + c] = lam;
-    return;
+  __syncthreads();
+  // ---- reverse scan: lam_r = dL/dA_r (after token r), carried across tokens by the decay
+  if (tid < kD) {
+    float lam = kFinal ? p.lam_in[chh * kD + tid] : 0.f;
+#pragma unroll 8
+    for (int r = kChunk - 1; r >= 0; --r) {
+      lam += sLam[r * kLdG + tid];
+      sLam[r * kLdG + tid] = lam;
+      lam *= sPd[r];
+    }
+    if (!kFinal) p.c_loc[chh * kD + tid] = lam;
+  }
+  if (!kFinal) return;
+  __syncthreads();
+  // ---- outputs: dk, and per token the channel sums for d beta_atk and d g_atk
+  float4 dkr0[kIter], dkr1[kIter];
+#pragma unroll
+  for (int it = 0; it < kIter; ++it) {
+    const int r = (tid + it * kThreads) >> 4;
+    dkr0[it] = dkr1[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (r < valid) {
+      const size_t off = row0 + (size_t)r * gld + c8;
+      dkr0[it] = *reinterpret_cast<const float4*>(p.dk_read + off);
+      dkr1[it] = *reinterpret_cast<const float4*>(p.dk_read + off + 4);
+    }
+  }
+#pragma unroll
+  for (int it = 0; it < kIter; ++it) {
+    const int r = (tid + it * kThreads) >> 4;
+    const uint32_t* w = reinterpret_cast<const uint32_t*>(&kraw[it]);
+    const float dkr[8] = {dkr0[it].x, dkr0[it].y, dkr0[it].z, dkr0[it].w,
+                          dkr1[it].x, dkr1[it].y, dkr1[it].z, dkr1[it].w};
+    const float4 l0 = *reinterpret_cast<const float4*>(sLam + r * kLdG + c8);
+    const float4 l1 = *reinterpret_cast<const float4*>(sLam + r * kLdG + c8 + 4);
+    const float4 a0 = *reinterpret_cast<const float4*>(sA + r * kLdG + c8);
+    const float4 a1 = *reinterpret_cast<const float4*>(sA + r * kLdG + c8 + 4);
+    const float4 u0 = *reinterpret_cast<const float4*>(sT2 + r * kLdG + c8);
+    const float4 u1 = *reinterpret_cast<const float4*>(sT2 + r * kLdG + c8 + 4);
+    const float lam[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
+    const float Ap[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+    const float t2[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+    const float dec = sPd[r], bp = sBp[r];
+    float x1 = 0.f, x2 = 0.f;
+    uint4 outv;
+    uint32_t* o32 = reinterpret_cast<uint32_t*>(&outv);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 kc = unpack_bf16(w[j]);
+      const float d0 = dkr[2 * j] + t2[2 * j] + 2.f * lam[2 * j] * bp * kc.x;
+      const float d1 = dkr[2 * j + 1] + t2[2 * j + 1] + 2.f * lam[2 * j + 1] * bp * kc.y;
+      o32[j] = pack_bf16(d0, d1);
+      x1 += lam[2 * j] * kc.x * kc.x + lam[2 * j + 1] * kc.y * kc.y;
+      x2 += lam[2 * j] * Ap[2 * j] + lam[2 * j + 1] * Ap[2 * j + 1];
+    }
+    if (r < valid) *reinterpret_cast<uint4*>(p.dk + row0 + (size_t)r * gld + c8) = outv;
+    // 16 consecutive lanes share a token: fixed-order shuffle reduction
+#pragma unroll
+    for (int o = 8; o >= 1; o >>= 1) {
+      x1 += __shfl_xor_sync(0xffffffffu, x1, o);
+      x2 += __shfl_xor_sync(0xffffffffu, x2, o);
+    }
+    if ((tid & 15) == 0 && r < valid) {
+      const size_t s = (size_t)(tok0 + r) * H + h;
+      p.dbeta_atk[s] = __float2bfloat16(x1);
+      p.dg_atk[s] = x2 * dec;
+    }
   }
 #pragma unroll
   for (int o = 16; o >= 1; o >>= 1) dcacc += __shfl_xor_sync(0xffffffffu, dcacc, o);
   if (lane == 0) sRed[warp] = dcacc;
   __syncthreads();
-  if (c < valid) {
-    const size_t s = (size_t)(tok0 + c) * H + h;
-    p.dbeta_atk[s] = __float2bfloat16(sP1[0][c] + sP1[1][c] + sP1[2][c] + sP1[3][c]);
-    p.dg_atk[s] = sP2[0][c] + sP2[1][c] + sP2[2][c] + sP2[3][c];
+  if (tid == 0) {
+    float acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < kThreads / 32; ++w) acc += sRed[w];
+    p.partC[chh] = acc;
   }
-  if (c == 0) p.partC[chh] = sRed[0] + sRed[1] + sRed[2] + sRed[3];
 }
 
 // Sequential carry over a sequence's chunks, last to first.
@@ -897,14 +1045,16 @@ int chunk_bwd(const pkda_chunk_bwd_args* a, cudaStream_t st) {
   ap.dk = static_cast<bf16*>(a->dk); ap.dg_atk = a->dg_atk; ap.dbeta_atk = static_cast<bf16*>(a->dbeta_atk);
   ap.partC = ws.partC; ap.ln_x = logf(p.squash_x); ap.eps = p.squash_eps;
   begin_stage(kStageAtkBwdLocal, st);
-  pkda_atk_bwd_kernel<false><<<gridc, kD, 0, st>>>(ap);
+  if (!set_smem(pkda_atk_bwd_kernel<false>, atkb::kSmemLocal)) return PKDA_ERR_LAUNCH;
+  pkda_atk_bwd_kernel<false><<<gridc, atkb::kThreads, atkb::kSmemLocal, st>>>(ap);
   PKDA_CHECK_LAUNCH();
   begin_stage(kStageAtkBwdCarry, st);
   pkda_atk_bwd_carry_kernel<<<dim3(p.n_seqs, p.heads), kD, 0, st>>>(geo, ws.c_loc, a->sa_atk, ws.lam_in,
                                                                    a->d_initial_A_state);
   PKDA_CHECK_LAUNCH();
   begin_stage(kStageAtkBwdFinal, st);
-  pkda_atk_bwd_kernel<true><<<gridc, kD, 0, st>>>(ap);
+  if (!set_smem(pkda_atk_bwd_kernel<true>, atkb::kSmemFinal)) return PKDA_ERR_LAUNCH;
+  pkda_atk_bwd_kernel<true><<<gridc, atkb::kThreads, atkb::kSmemFinal, st>>>(ap);
   PKDA_CHECK_LAUNCH();
   begin_stage(kStageParamReduce, st);
   pkda_param_reduce_kernel<<<p.heads, kD, 0, st>>>(geo, ws.partA, ws.partB, ws.partC, a->dA_log, a->ddt_bias,
@@ -914,3 +1064,9 @@ int chunk_bwd(const pkda_chunk_bwd_args* a, cudaStream_t st) {
 }
 
 }  // namespace pkda
+
+#ifdef PKDA_PHASE_PROFILE
+extern "C" int pkda_phase_prof_bwd(long long* out) {
+  return cudaMemcpyFromSymbol(out, g_phase_prof, sizeof(long long) * 64) == cudaSuccess ? 0 : 1;
+}
+#endif

@@ -143,6 +143,7 @@ __global__ void __launch_bounds__(intra::kThreads, 1)
 pkda_intra_fwd_kernel(const IntraParams p) {
   using namespace intra;
   extern __shared__ __align__(128) unsigned char smem[];
+  PKDA_PHASE(0);
   bf16* sQ = reinterpret_cast<bf16*>(smem + oQ);
   bf16* sK = reinterpret_cast<bf16*>(smem + oK);
   bf16* sKt = reinterpret_cast<bf16*>(smem + oKt);
@@ -187,12 +188,12 @@ pkda_intra_fwd_kernel(const IntraParams p) {
   // zero the P staging tile (upper triangle must read as zero)
   for (int i = tid; i < kChunk * kLdC / 8; i += kThreads) reinterpret_cast<uint4*>(sTmb)[i] = make_uint4(0, 0, 0, 0);
   cp_async_wait<0>();
-  __syncthreads();
+  __syncthreads(); PKDA_PHASE(1);
 
   // ---- 2. decay gate (elementwise, all threads), then the two per-channel sequential
   // passes side by side: cumulative sum | preconditioner recurrence A_t
-  gate_elementwise(sG, p.g + row0, gld, valid, sBias, __expf(p.A_log[h]) * kLog2e, tid, kThreads);
-  __syncthreads();
+  gate_elementwise<kThreads>(sG, p.g + row0, gld, valid, sBias, __expf(p.A_log[h]) * kLog2e, tid);
+  __syncthreads(); PKDA_PHASE(2);
   if (tid < kD) {
     gate_cumsum(sG, tid);
     float dmax[6];
@@ -213,7 +214,7 @@ pkda_intra_fwd_kernel(const IntraParams p) {
       sAt[r * kLdG + c] = A;
     }
   }
-  __syncthreads();
+  __syncthreads(); PKDA_PHASE(3);
   if (!kRecompute) {
     // write keys kt = k * exp(-ln(x) * dev / (1 + |dev|)), dev = log(A + eps) - centre
     const float centre = p.log_atk_scale[h];
@@ -233,7 +234,7 @@ pkda_intra_fwd_kernel(const IntraParams p) {
       *reinterpret_cast<uint4*>(sKt + r * kLdD + c8) = x;
       if (r < valid) *reinterpret_cast<uint4*>(p.kt + row0 + (size_t)r * gld + c8) = x;
     }
-    __syncthreads();
+    __syncthreads(); PKDA_PHASE(4);
   }
 
   // ---- 3. gated pair products, level by level.
@@ -258,7 +259,7 @@ pkda_intra_fwd_kernel(const IntraParams p) {
     const int lvl = it ? (64 >> it) : 0;  // 0 (direct), 32, 16, 8, 4, 2, 1
     if (lvl && lvl < bdir) break;
     stage_level(sXq, sXk, sY, sQ, sK, sKt, sG, lvl, bdir, tid, kThreads);
-    __syncthreads();
+    __syncthreads(); PKDA_PHASE(5);
     const bf16* X = mat ? sXq : sXk;
     float tmp[1][2][4];
     if (!diagw) {
@@ -292,7 +293,7 @@ pkda_intra_fwd_kernel(const IntraParams p) {
           if (pair_ok(i, j, lvl, bdir)) accA[nt][e] += tmp[0][nt][e];
         }
     }
-    __syncthreads();
+    __syncthreads(); PKDA_PHASE(6);
   }
   if (diagw && mat == 1) {  // diagonal of P: ungated q_i . kt_i
     float tmp[1][2][4];
@@ -310,7 +311,7 @@ pkda_intra_fwd_kernel(const IntraParams p) {
 
   // ---- 4. P -> bf16 staging tile (scaled) ; L = tril(M,-1) diag(beta) -> smem fp32
   for (int i = tid; i < kChunk * kLdL; i += kThreads) sL[i] = 0.f;
-  __syncthreads();
+  __syncthreads(); PKDA_PHASE(7);
   {
     auto putP = [&](int i, int j, float v) { if (j <= i) sTmb[i * kLdC + j] = __float2bfloat16(v * p.scale); };
     auto putL = [&](int i, int j, float v) { if (j < i) sL[i * kLdL + j] = v * sBeta[j]; };
@@ -323,7 +324,7 @@ pkda_intra_fwd_kernel(const IntraParams p) {
       }
     }
   }
-  __syncthreads();
+  __syncthreads(); PKDA_PHASE(8);
   if (!kRecompute) {
     for (int i = tid; i < kChunk * kChunk / 8; i += kThreads) {
       const int r = i >> 3, c8 = (i & 7) << 3;
@@ -334,7 +335,7 @@ pkda_intra_fwd_kernel(const IntraParams p) {
   }
 
   // ---- 5. T = (I + L)^-1 in fp32
-  unit_lower_inverse_64(sL, sT, sY2, kLdL, tid);  // starts with work on sL/sT only; ends with a __syncthreads()
+  unit_lower_inverse_64(sL, sT, sY2, kLdL, tid, kThreads);  // ends with a __syncthreads()
   for (int i = tid; i < kChunk * kChunk / 2; i += kThreads) {
     const int r = i >> 5, c2 = (i & 31) << 1;
     const uint32_t pk = pack_bf16(sT[r * kLdL + c2], sT[r * kLdL + c2 + 1]);
@@ -342,7 +343,7 @@ pkda_intra_fwd_kernel(const IntraParams p) {
     if (!kRecompute && r < valid)
       *reinterpret_cast<uint32_t*>(p.Akk + ((size_t)(tok0 + r) * H + h) * kChunk + c2) = pk;
   }
-  __syncthreads();
+  __syncthreads(); PKDA_PHASE(9);
 
   // ---- 6. decayed operands: Kd -> smem; qg, kg, gc -> global; V tile -> smem
   bf16* sKd = sXq;
@@ -382,7 +383,7 @@ pkda_intra_fwd_kernel(const IntraParams p) {
     }
   }
   cp_async_wait<0>();
-  __syncthreads();
+  __syncthreads(); PKDA_PHASE(10);
 
   // ---- 7. W = Tm Kd, U = Tm V   (warp: matrix = warp>>3, rows 16*((warp>>1)&3), column half warp&1)
   {
@@ -401,6 +402,7 @@ pkda_intra_fwd_kernel(const IntraParams p) {
               pack_bf16(acc2[0][nt][2 * half], acc2[0][nt][2 * half + 1]);
       }
   }
+  PKDA_PHASE(11);
 }
 
 // ------------------------------------------------------------------ forward state scan
@@ -794,3 +796,9 @@ int chunk_fwd(const pkda_chunk_fwd_args* a, cudaStream_t st) {
 }
 
 }  // namespace pkda
+
+#ifdef PKDA_PHASE_PROFILE
+extern "C" int pkda_phase_prof_fwd(long long* out) {
+  return cudaMemcpyFromSymbol(out, g_phase_prof, sizeof(long long) * 64) == cudaSuccess ? 0 : 1;
+}
+#endif

@@ -14,6 +14,18 @@
 
 #include "../../include/pkda_b200.h"
 
+// Optional phase timestamps (development builds only, -DPKDA_PHASE_PROFILE): one
+// CTA records clock64() at numbered points of a kernel.
+#ifdef PKDA_PHASE_PROFILE
+static __device__ long long g_phase_prof[64];
+#define PKDA_PHASE(k)                                                                   \
+  do {                                                                                  \
+    if (threadIdx.x == 0 && blockIdx.x == 300 && blockIdx.y == 3) g_phase_prof[k] = clock64(); \
+  } while (0)
+#else
+#define PKDA_PHASE(k)
+#endif
+
 namespace pkda {
 
 constexpr int kChunk = 64;

@@ -86,7 +86,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-i", str(self.index), "-lms", "100"],
+                 "-i", str(self.index), "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -233,6 +233,8 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     device = torch.device("cuda", local_rank)
     torch.cuda.set_device(device)
     if world > 1:
+        # keep NCCL's own banner off stdout: rank 0 prints exactly one JSON line there
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=device)
     B, T, H, D = WORKLOADS[args.workload]
     pk = peaks()
@@ -265,13 +267,14 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     launches0 = ops.LAUNCHES
     _lib.stage_timing(True)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local_rank) as clocks:
-        barrier()
-        e0.record()
-        for _ in range(args.steps):
-            fwd_bwd(dev)
-        e1.record()
-        barrier()
+    clocks = ClockSampler(local_rank)
+    clocks.__enter__()  # sampled over both timed regions (device-resident steps, then end-to-end steps)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        fwd_bwd(dev)
+    e1.record()
+    barrier()
     total_ms = e0.elapsed_time(e1)
     stages = _lib.stage_timing_read()
     _lib.stage_timing(False)
@@ -288,6 +291,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
 
     # ---- end to end through the public operator with host buffers
     if args.no_e2e:
+        clocks.__exit__(None, None, None)
         if world > 1:
             dist.destroy_process_group()
         if rank == 0:
@@ -316,6 +320,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     e1.record()
     barrier()
     e2e_ms = e0.elapsed_time(e1) / e2e_steps
+    clocks.__exit__(None, None, None)
     if world > 1:
         tmax = torch.tensor([e2e_ms], device=device)
         dist.all_reduce(tmax, op=dist.ReduceOp.MAX)

@@ -28,7 +28,7 @@ struct ScanBwdParams {
 };
 
 namespace scanb {
-constexpr int kThreads = 128;
+template <int VB> __host__ __device__ constexpr int threads() { return 128 * (VB / 32); }  // 4 warps per 32 value columns
 template <int VB> struct L {
   static constexpr int ldv = VB + kPad;
   static constexpr int oKg = 0;
@@ -46,10 +46,10 @@ template <int VB> struct L {
 }  // namespace scanb
 
 template <int VB>
-__global__ void __launch_bounds__(scanb::kThreads)
+__global__ void __launch_bounds__(scanb::threads<VB>())
 pkda_scan_bwd_kernel(const ScanBwdParams p) {
   using Lay = scanb::L<VB>;
-  constexpr int ldv = Lay::ldv, NT = VB / 8;
+  constexpr int ldv = Lay::ldv, NT = 4, kT = scanb::threads<VB>();
   extern __shared__ __align__(128) unsigned char smem[];
   const int VS = kD / VB;
   const int vs = blockIdx.x % VS;
@@ -58,6 +58,7 @@ pkda_scan_bwd_kernel(const ScanBwdParams p) {
   const SeqInfo sq = seq_info(p.geo, n);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int gq = lane >> 2, tq = lane & 3;
+  const int wr = warp & 3, c0 = 32 * (warp >> 2);  // this warp: rows [32 wr, +32), columns [c0, +32) of the slice
   const int v0 = vs * VB;
   const long gld = (long)H * kD;
   const size_t sbase = ((size_t)n * H + h) * kD * kD;
@@ -76,11 +77,11 @@ pkda_scan_bwd_kernel(const ScanBwdParams p) {
     const int valid = min(kChunk, sq.len - i * kChunk);
     const size_t row0 = ((size_t)tok0 * H + h) * kD;
     const size_t chh = (size_t)(sq.chunk0 + i) * H + h;
-    tile_load_async(sKg, kLdD, p.kg + row0, gld, kChunk, kD, valid, scanb::kThreads);
+    tile_load_async(sKg, kLdD, p.kg + row0, gld, kChunk, kD, valid, kT);
     tile_load_async(sP, kLdC, p.Aqk + ((size_t)tok0 * H + h) * kChunk, (long)H * kChunk, kChunk, kChunk, valid,
-                    scanb::kThreads);
+                    kT);
     tile_load_async(reinterpret_cast<bf16*>(smem + Lay::oDo + (i & 1) * Lay::kDoBytes), ldv, p.d_o + row0 + v0, gld,
-                    kChunk, VB, valid, scanb::kThreads);
+                    kChunk, VB, valid, kT);
     if (tid < 16) cp_async16(smem + Lay::oBeta + tid * 16, p.beta_c + chh * kChunk + tid * 4, true);
   };
   auto prefetchB = [&](int i) {
@@ -88,8 +89,8 @@ pkda_scan_bwd_kernel(const ScanBwdParams p) {
     const int valid = min(kChunk, sq.len - i * kChunk);
     const size_t row0 = ((size_t)tok0 * H + h) * kD;
     const size_t chh = (size_t)(sq.chunk0 + i) * H + h;
-    tile_load_async(sQg, kLdD, p.qg + row0, gld, kChunk, kD, valid, scanb::kThreads);
-    tile_load_async(sW, kLdD, p.w + row0, gld, kChunk, kD, valid, scanb::kThreads);
+    tile_load_async(sQg, kLdD, p.qg + row0, gld, kChunk, kD, valid, kT);
+    tile_load_async(sW, kLdD, p.w + row0, gld, kChunk, kD, valid, kT);
     if (tid < 32) cp_async16(smem + Lay::oGc + tid * 16, p.gc + chh * kD + tid * 4, true);
   };
 
@@ -100,7 +101,7 @@ pkda_scan_bwd_kernel(const ScanBwdParams p) {
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        const int r = 32 * warp + 16 * mt + gq + 8 * half, c = v0 + 8 * nt + 2 * tq;
+        const int r = 32 * wr + 16 * mt + gq + 8 * half, c = v0 + c0 + 8 * nt + 2 * tq;
         float2 s2 = make_float2(0.f, 0.f);
         if (p.dST) s2 = *reinterpret_cast<const float2*>(p.dST + sbase + (size_t)r * kD + c);
         dS[mt][nt][2 * half] = s2.x;
@@ -127,13 +128,13 @@ pkda_scan_bwd_kernel(const ScanBwdParams p) {
       for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
-          const int r = 32 * warp + 16 * mt + gq + 8 * half, c = 8 * nt + 2 * tq;
+          const int r = 32 * wr + 16 * mt + gq + 8 * half, c = c0 + 8 * nt + 2 * tq;
           *reinterpret_cast<uint32_t*>(sD + r * ldv + c) = pack_bf16(dS[mt][nt][2 * half], dS[mt][nt][2 * half + 1]);
         }
     __syncthreads();
     {
       constexpr int cpr = VB / 8;
-      for (int j = tid; j < kD * cpr; j += scanb::kThreads) {
+      for (int j = tid; j < kD * cpr; j += kT) {
         const int r = j / cpr, c = (j - r * cpr) * 8;
         *reinterpret_cast<uint4*>(p.dh + (chh * kD + r) * kD + v0 + c) =
             *reinterpret_cast<const uint4*>(sD + r * ldv + c);
@@ -143,13 +144,13 @@ pkda_scan_bwd_kernel(const ScanBwdParams p) {
     {
       float f[1][NT][4];
       zero_acc(f);
-      warp_gemm<1, NT, false, true>(f, sKg, kLdD, 16 * warp, sD, ldv, 0, 0, kD);
-      warp_gemm<1, NT, true, true>(f, sP, kLdC, 16 * warp, sdO, ldv, 0, 16 * warp, kChunk);
+      warp_gemm<1, NT, false, true>(f, sKg, kLdD, 16 * wr, sD, ldv, c0, 0, kD);
+      warp_gemm<1, NT, true, true>(f, sP, kLdC, 16 * wr, sdO, ldv, c0, 16 * wr, kChunk);
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
-          const int r = 16 * warp + gq + 8 * half, c = 8 * nt + 2 * tq;
+          const int r = 16 * wr + gq + 8 * half, c = c0 + 8 * nt + 2 * tq;
           const uint32_t fk = pack_bf16(f[0][nt][2 * half], f[0][nt][2 * half + 1]);
           if (r < valid) *reinterpret_cast<uint32_t*>(p.dF + ((size_t)(tok0 + r) * H + h) * kD + v0 + c) = fk;
           const float2 fr = unpack_bf16(fk);
@@ -167,15 +168,15 @@ pkda_scan_bwd_kernel(const ScanBwdParams p) {
     for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        const float gcv = sGc[32 * warp + 16 * mt + gq + 8 * half];
+        const float gcv = sGc[32 * wr + 16 * mt + gq + 8 * half];
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
           dS[mt][nt][2 * half] *= gcv;
           dS[mt][nt][2 * half + 1] *= gcv;
         }
       }
-    warp_gemm<2, NT, true, true>(dS, sQg, kLdD, 32 * warp, sdO, ldv, 0, 0, kChunk);
-    warp_gemm<2, NT, true, true>(dS, sW, kLdD, 32 * warp, sDE, ldv, 0, 0, kChunk);
+    warp_gemm<2, NT, true, true>(dS, sQg, kLdD, 32 * wr, sdO, ldv, c0, 0, kChunk);
+    warp_gemm<2, NT, true, true>(dS, sW, kLdD, 32 * wr, sDE, ldv, c0, 0, kChunk);
     __syncthreads();  // group-B buffers, sD and sDE free
     if (i > 0) prefetchB(i - 1);
     cp_async_commit();
@@ -188,7 +189,7 @@ pkda_scan_bwd_kernel(const ScanBwdParams p) {
       for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
-          const int r = 32 * warp + 16 * mt + gq + 8 * half, c = v0 + 8 * nt + 2 * tq;
+          const int r = 32 * wr + 16 * mt + gq + 8 * half, c = v0 + c0 + 8 * nt + 2 * tq;
           *reinterpret_cast<float2*>(p.dS0 + sbase + (size_t)r * kD + c) =
               make_float2(dS[mt][nt][2 * half], dS[mt][nt][2 * half + 1]);
         }
@@ -981,6 +982,13 @@ static bool set_smem(K kernel, int bytes) {
   return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess;
 }
 
+template <int VB>
+static int launch_scan_bwd(const ScanBwdParams& sp, int units, cudaStream_t st) {
+  if (!set_smem(pkda_scan_bwd_kernel<VB>, scanb::L<VB>::kSmem)) return PKDA_ERR_LAUNCH;
+  pkda_scan_bwd_kernel<VB><<<units * (kD / VB), scanb::threads<VB>(), scanb::L<VB>::kSmem, st>>>(sp);
+  return cudaGetLastError() == cudaSuccess ? PKDA_OK : PKDA_ERR_LAUNCH;
+}
+
 int chunk_bwd(const pkda_chunk_bwd_args* a, cudaStream_t st) {
   const pkda_problem& p = a->p;
   int rc = check_chunk_problem(p);
@@ -1013,15 +1021,20 @@ int chunk_bwd(const pkda_chunk_bwd_args* a, cudaStream_t st) {
     if (rc != PKDA_OK) return rc;
   }
 
-  constexpr int VB = 32;
   ScanBwdParams sp;
   sp.geo = geo; sp.kg = kg; sp.qg = qg; sp.w = w; sp.Aqk = Aqk; sp.d_o = static_cast<const bf16*>(a->d_o);
   sp.beta_c = ws.beta_c; sp.gc = gc; sp.dST = a->d_final_state; sp.dh = ws.dh; sp.dF = ws.dF;
   sp.dS0 = a->d_initial_state;
-  if (!set_smem(pkda_scan_bwd_kernel<VB>, scanb::L<VB>::kSmem)) return PKDA_ERR_LAUNCH;
-  begin_stage(kStageScanBwd, st);
-  pkda_scan_bwd_kernel<VB><<<p.n_seqs * p.heads * (kD / VB), scanb::kThreads, scanb::L<VB>::kSmem, st>>>(sp);
-  PKDA_CHECK_LAUNCH();
+  {
+    const int units = p.n_seqs * p.heads;
+    const int vb = units >= 120 ? 128 : (units >= 60 ? 64 : 32);
+    begin_stage(kStageScanBwd, st);
+    if (vb == 128) rc = launch_scan_bwd<128>(sp, units, st);
+    else if (vb == 64) rc = launch_scan_bwd<64>(sp, units, st);
+    else rc = launch_scan_bwd<32>(sp, units, st);
+    end_stage(st);
+    if (rc != PKDA_OK) return rc;
+  }
 
   dim3 gridc(geo.total_chunks, p.heads);
   IntraBwdParams ip;

@@ -416,7 +416,7 @@ struct ScanParams {
 };
 
 namespace scan {
-constexpr int kThreads = 128;
+template <int VB> __host__ __device__ constexpr int threads() { return 128 * (VB / 32); }  // 4 warps per 32 value columns
 template <int VB> struct L {
   static constexpr int ldv = VB + kPad;
   static constexpr int oW = 0;
@@ -432,10 +432,10 @@ template <int VB> struct L {
 }  // namespace scan
 
 template <int VB, bool kRecompute>
-__global__ void __launch_bounds__(scan::kThreads)
+__global__ void __launch_bounds__(scan::threads<VB>())
 pkda_scan_fwd_kernel(const ScanParams p) {
   using Lay = scan::L<VB>;
-  constexpr int ldv = Lay::ldv, NT = VB / 8;
+  constexpr int ldv = Lay::ldv, NT = 4, kT = scan::threads<VB>();
   extern __shared__ __align__(128) unsigned char smem[];
   const int VS = kD / VB;
   const int vs = blockIdx.x % VS;
@@ -445,6 +445,7 @@ pkda_scan_fwd_kernel(const ScanParams p) {
   if (sq.nchunks == 0) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int gq = lane >> 2, tq = lane & 3;
+  const int wr = warp & 3, c0 = 32 * (warp >> 2);  // this warp: state rows [32 wr, +32), columns [c0, +32) of the slice
   const int v0 = vs * VB;
   const long gld = (long)H * kD;
   bf16* sH = reinterpret_cast<bf16*>(smem + Lay::oH);
@@ -456,9 +457,9 @@ pkda_scan_fwd_kernel(const ScanParams p) {
     const int valid = min(kChunk, sq.len - i * kChunk);
     const size_t row0 = ((size_t)tok0 * H + h) * kD;
     const size_t chh = (size_t)(sq.chunk0 + i) * H + h;
-    tile_load_async(reinterpret_cast<bf16*>(st + Lay::oW), kLdD, p.w + row0, gld, kChunk, kD, valid, scan::kThreads);
-    tile_load_async(reinterpret_cast<bf16*>(st + Lay::oKg), kLdD, p.kg + row0, gld, kChunk, kD, valid, scan::kThreads);
-    tile_load_async(reinterpret_cast<bf16*>(st + Lay::oU), ldv, p.u + row0 + v0, gld, kChunk, VB, valid, scan::kThreads);
+    tile_load_async(reinterpret_cast<bf16*>(st + Lay::oW), kLdD, p.w + row0, gld, kChunk, kD, valid, kT);
+    tile_load_async(reinterpret_cast<bf16*>(st + Lay::oKg), kLdD, p.kg + row0, gld, kChunk, kD, valid, kT);
+    tile_load_async(reinterpret_cast<bf16*>(st + Lay::oU), ldv, p.u + row0 + v0, gld, kChunk, VB, valid, kT);
     if (tid < 16) cp_async16(st + Lay::oBeta + tid * 16, p.beta_c + chh * kChunk + tid * 4, true);
     else if (tid < 48) cp_async16(st + Lay::oGc + (tid - 16) * 16, p.gc + chh * kD + (tid - 16) * 4, true);
   };
@@ -472,7 +473,7 @@ pkda_scan_fwd_kernel(const ScanParams p) {
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        const int r = 32 * warp + 16 * mt + gq + 8 * half, c = v0 + 8 * nt + 2 * tq;
+        const int r = 32 * wr + 16 * mt + gq + 8 * half, c = v0 + c0 + 8 * nt + 2 * tq;
         float2 s2 = make_float2(0.f, 0.f);
         if (p.S0) s2 = *reinterpret_cast<const float2*>(p.S0 + sbase + (size_t)r * kD + c);
         S[mt][nt][2 * half] = s2.x;
@@ -495,6 +496,7 @@ pkda_scan_fwd_kernel(const ScanParams p) {
     const int valid = min(kChunk, sq.len - i * kChunk);
     const size_t chh = (size_t)(sq.chunk0 + i) * H + h;
 
+    PKDA_SCAN_PHASE(i, 0);
     // a. chunk-entry state -> bf16 operand tile (and the saved chunk states)
 #pragma unroll
     for (int mt = 0; mt < 2; ++mt)
@@ -502,13 +504,14 @@ pkda_scan_fwd_kernel(const ScanParams p) {
       for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
-          const int r = 32 * warp + 16 * mt + gq + 8 * half, c = 8 * nt + 2 * tq;
+          const int r = 32 * wr + 16 * mt + gq + 8 * half, c = c0 + 8 * nt + 2 * tq;
           *reinterpret_cast<uint32_t*>(sH + r * ldv + c) = pack_bf16(S[mt][nt][2 * half], S[mt][nt][2 * half + 1]);
         }
     __syncthreads();  // sH complete; stage i landed for every thread
+    PKDA_SCAN_PHASE(i, 1);
     {
       constexpr int cpr = VB / 8;
-      for (int j = tid; j < kD * cpr; j += scan::kThreads) {
+      for (int j = tid; j < kD * cpr; j += kT) {
         const int r = j / cpr, c = (j - r * cpr) * 8;
         *reinterpret_cast<uint4*>(p.h + (chh * kD + r) * kD + v0 + c) =
             *reinterpret_cast<const uint4*>(sH + r * ldv + c);
@@ -518,12 +521,12 @@ pkda_scan_fwd_kernel(const ScanParams p) {
     {
       float e[1][NT][4];
       zero_acc(e);
-      warp_gemm<1, NT, false, true>(e, sW, kLdD, 16 * warp, sH, ldv, 0, 0, kD);
+      warp_gemm<1, NT, false, true>(e, sW, kLdD, 16 * wr, sH, ldv, c0, 0, kD);
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
-          const int r = 16 * warp + gq + 8 * half, c = 8 * nt + 2 * tq;
+          const int r = 16 * wr + gq + 8 * half, c = c0 + 8 * nt + 2 * tq;
           const float2 uu = unpack_bf16(*reinterpret_cast<const uint32_t*>(sU + r * ldv + c));
           const uint32_t ek = pack_bf16(uu.x - e[0][nt][2 * half], uu.y - e[0][nt][2 * half + 1]);
           if (r < valid)
@@ -534,20 +537,22 @@ pkda_scan_fwd_kernel(const ScanParams p) {
         }
     }
     __syncthreads();
+    PKDA_SCAN_PHASE(i, 2);
     // c. S <- Gam_last * S + kg^T F
 #pragma unroll
     for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        const float gcv = sGc[32 * warp + 16 * mt + gq + 8 * half];
+        const float gcv = sGc[32 * wr + 16 * mt + gq + 8 * half];
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
           S[mt][nt][2 * half] *= gcv;
           S[mt][nt][2 * half + 1] *= gcv;
         }
       }
-    warp_gemm<2, NT, true, true>(S, sKg, kLdD, 32 * warp, sF, ldv, 0, 0, kChunk);
+    warp_gemm<2, NT, true, true>(S, sKg, kLdD, 32 * wr, sF, ldv, c0, 0, kChunk);
     __syncthreads();  // everyone done with stage i and sF before they are refilled
+    PKDA_SCAN_PHASE(i, 3);
   }
   cp_async_wait<0>();
   if (!kRecompute && p.ST) {
@@ -557,7 +562,7 @@ pkda_scan_fwd_kernel(const ScanParams p) {
       for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
-          const int r = 32 * warp + 16 * mt + gq + 8 * half, c = v0 + 8 * nt + 2 * tq;
+          const int r = 32 * wr + 16 * mt + gq + 8 * half, c = v0 + c0 + 8 * nt + 2 * tq;
           *reinterpret_cast<float2*>(p.ST + sbase + (size_t)r * kD + c) =
               make_float2(S[mt][nt][2 * half], S[mt][nt][2 * half + 1]);
         }
@@ -682,6 +687,13 @@ int check_chunk_problem(const pkda_problem& p) {
   return PKDA_OK;
 }
 
+template <int VB, bool kRecompute>
+static int launch_scan_fwd(const ScanParams& sp, int units, cudaStream_t st) {
+  if (!set_smem(pkda_scan_fwd_kernel<VB, kRecompute>, scan::L<VB>::kSmem)) return PKDA_ERR_LAUNCH;
+  pkda_scan_fwd_kernel<VB, kRecompute><<<units * (kD / VB), scan::threads<VB>(), scan::L<VB>::kSmem, st>>>(sp);
+  return cudaGetLastError() == cudaSuccess ? PKDA_OK : PKDA_ERR_LAUNCH;
+}
+
 // Shared by the forward and by the backward's recompute mode.
 int run_forward_stages(const pkda_problem& p, const Geo& geo, const float* beta_c, bf16* u_ws,
                        bf16* Aqk, bf16* Akk, bf16* kt, float* gc, const float* a_start,
@@ -714,18 +726,17 @@ int run_forward_stages(const pkda_problem& p, const Geo& geo, const float* beta_
   ScanParams sp;
   sp.geo = geo; sp.w = w; sp.u = u_ws; sp.kg = kg; sp.beta_c = beta_c; sp.gc = gc;
   sp.S0 = p.initial_state; sp.h = h; sp.v_new = v_new; sp.ST = ST;
-  constexpr int VB = 32;
-  dim3 grids(p.n_seqs * p.heads * (kD / VB));
-  if (recompute) {
-    if (!set_smem(pkda_scan_fwd_kernel<VB, true>, scan::L<VB>::kSmem)) return PKDA_ERR_LAUNCH;
-    begin_stage(kStageScanFwd, st);
-    pkda_scan_fwd_kernel<VB, true><<<grids, scan::kThreads, scan::L<VB>::kSmem, st>>>(sp);
-  } else {
-    if (!set_smem(pkda_scan_fwd_kernel<VB, false>, scan::L<VB>::kSmem)) return PKDA_ERR_LAUNCH;
-    begin_stage(kStageScanFwd, st);
-    pkda_scan_fwd_kernel<VB, false><<<grids, scan::kThreads, scan::L<VB>::kSmem, st>>>(sp);
-  }
-  PKDA_CHECK_LAUNCH();
+  // Value columns per CTA: as wide as possible (no redundant reads of W and kg, all
+  // warps of an SM on one chain) while still leaving about one CTA per SM.
+  const int units = p.n_seqs * p.heads;
+  const int vb = units >= 120 ? 128 : (units >= 60 ? 64 : 32);
+  int rc = PKDA_ERR_LAUNCH;
+  begin_stage(kStageScanFwd, st);
+  if (vb == 128) rc = recompute ? launch_scan_fwd<128, true>(sp, units, st) : launch_scan_fwd<128, false>(sp, units, st);
+  else if (vb == 64) rc = recompute ? launch_scan_fwd<64, true>(sp, units, st) : launch_scan_fwd<64, false>(sp, units, st);
+  else rc = recompute ? launch_scan_fwd<32, true>(sp, units, st) : launch_scan_fwd<32, false>(sp, units, st);
+  end_stage(st);
+  if (rc != PKDA_OK) return rc;
   return PKDA_OK;
 }
 

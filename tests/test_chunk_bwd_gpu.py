@@ -156,3 +156,21 @@ def test_direct_block_variants(cap, dist):
         _lib.set_direct_block_cap(64)
     assert rel_rms(res["o"], ref["o"]) < 0.005
     check(res, ref, f"cap{cap}-{dist}")
+
+
+@pytest.mark.parametrize("B", [4, 8])
+def test_wide_state_slices_match_narrow_ones(B):
+    """The state-scan kernels split the value axis across CTAs according to how
+    many (row, head) units there are (32, 64 or all 128 columns per CTA).  Rows are
+    independent, so a batch large enough to select the wide variants must agree
+    bitwise with the same rows run one at a time (narrow variant)."""
+    H, T = 16, 130
+    d = make_inputs(B, T, H, 128, seed=97, dist="production", dtype=torch.bfloat16, with_state=True)
+    dS = torch.randn(B, H, 128, 128, generator=torch.Generator().manual_seed(6)) * 0.1
+    full = run(d, dS=dS)
+    for b in range(0, B, 3):
+        one = {k: (v[b:b + 1] if torch.is_tensor(v) and v.dim() >= 3 and v.shape[0] == B else v)
+               for k, v in d.items()}
+        part = run(one, dS=dS[b:b + 1])
+        for key in ("o", "dq", "dk", "dv", "dg", "dbeta", "dg_atk", "dbeta_atk", "dinitial_state"):
+            assert torch.equal(full[key][b:b + 1], part[key]), (b, key)

@@ -273,11 +273,16 @@ __device__ __forceinline__ void unit_lower_inverse_64(const float* sL, float* sT
 int launch_out_fwd_tc(const Geo& geo, int total_tokens, const bf16* qg, const bf16* h, const bf16* Aqk,
                       const bf16* v_new, const float* beta_c, bf16* o, int* status, cudaStream_t st);
 
+// tcgen05 / TMA forward state scan (pkda_scan_tc.cu): one CTA per (sequence, head).
+int launch_scan_fwd_tc(const Geo& geo, int total_tokens, int units, const bf16* w, const bf16* kg, const bf16* u,
+                       const float* beta_c, const float* gc, const float* S0, bf16* h, bf16* v_new, float* ST,
+                       int* status, bool recompute, cudaStream_t st);
+
 // Host-side pieces defined in pkda_chunk_fwd.cu and reused by the backward.
 int check_chunk_problem(const pkda_problem& p);
 int run_prologue(const pkda_problem& p, int* chunk_offsets, float* beta_c, Geo* geo, cudaStream_t st);
 int run_forward_stages(const pkda_problem& p, const Geo& geo, const float* beta_c, bf16* u_ws, bf16* Aqk,
                        bf16* Akk, bf16* kt, float* gc, const float* a_start, bf16* w, bf16* kg, bf16* v_new,
-                       bf16* h, bf16* qg, float* ST, bool recompute, cudaStream_t st);
+                       bf16* h, bf16* qg, float* ST, bool recompute, int* status, cudaStream_t st);
 
 }  // namespace pkda

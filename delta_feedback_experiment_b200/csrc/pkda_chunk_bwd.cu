@@ -940,6 +940,7 @@ struct BwdWorkspace {
   float* beta_c;
   bf16 *u, *dF, *dh;
   float *dk_read, *dkt, *partA, *partB, *partC, *c_loc, *lam_in;
+  int* status;
   size_t bytes;
 };
 
@@ -965,6 +966,7 @@ static BwdWorkspace carve_bwd(const pkda_problem& p, void* base) {
   w.partC = static_cast<float*>(take(chunks * H * 4));
   w.c_loc = static_cast<float*>(take(chunks * H * kD * 4));
   w.lam_in = static_cast<float*>(take(chunks * H * kD * 4));
+  w.status = static_cast<int*>(take(sizeof(int)));
   w.bytes = off;
   return w;
 }
@@ -1015,9 +1017,10 @@ int chunk_bwd(const pkda_chunk_bwd_args* a, cudaStream_t st) {
   bf16* qg = static_cast<bf16*>(a->qg);
   if (a->recompute) {
     // The recompute kernels only read the products, write keys and decay totals.
+    if (cudaMemsetAsync(ws.status, 0, sizeof(int), st) != cudaSuccess) return PKDA_ERR_LAUNCH;
     rc = run_forward_stages(p, geo, ws.beta_c, ws.u, const_cast<bf16*>(Aqk), const_cast<bf16*>(Akk),
                             const_cast<bf16*>(kt), const_cast<float*>(gc), a->a_atk, w, kg, v_new, h, qg,
-                            nullptr, true, st);
+                            nullptr, true, ws.status, st);
     if (rc != PKDA_OK) return rc;
   }
 

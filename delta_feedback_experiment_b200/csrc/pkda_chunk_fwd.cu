@@ -698,7 +698,7 @@ static int launch_scan_fwd(const ScanParams& sp, int units, cudaStream_t st) {
 int run_forward_stages(const pkda_problem& p, const Geo& geo, const float* beta_c, bf16* u_ws,
                        bf16* Aqk, bf16* Akk, bf16* kt, float* gc, const float* a_start,
                        bf16* w, bf16* kg, bf16* v_new, bf16* h, bf16* qg, float* ST,
-                       bool recompute, cudaStream_t st) {
+                       bool recompute, int* status, cudaStream_t st) {
   const int chunks = geo.total_chunks;
   IntraParams ip;
   ip.geo = geo;
@@ -731,8 +731,16 @@ int run_forward_stages(const pkda_problem& p, const Geo& geo, const float* beta_
   const int units = p.n_seqs * p.heads;
   const int vb = units >= 120 ? 128 : (units >= 60 ? 64 : 32);
   int rc = PKDA_ERR_LAUNCH;
+  // Full-width slices run on tcgen05 / TMEM / TMA; PKDA_SCAN_IMPL=mma keeps the mma.sync kernel (A/B runs).
+  static const bool scan_mma = [] {
+    const char* e = getenv("PKDA_SCAN_IMPL");
+    return e && e[0] == 'm';
+  }();
   begin_stage(kStageScanFwd, st);
-  if (vb == 128) rc = recompute ? launch_scan_fwd<128, true>(sp, units, st) : launch_scan_fwd<128, false>(sp, units, st);
+  if (vb == 128 && status && !scan_mma)
+    rc = launch_scan_fwd_tc(geo, p.total_tokens, units, w, kg, u_ws, beta_c, gc, p.initial_state, h, v_new, ST,
+                            status, recompute, st);
+  else if (vb == 128) rc = recompute ? launch_scan_fwd<128, true>(sp, units, st) : launch_scan_fwd<128, false>(sp, units, st);
   else if (vb == 64) rc = recompute ? launch_scan_fwd<64, true>(sp, units, st) : launch_scan_fwd<64, false>(sp, units, st);
   else rc = recompute ? launch_scan_fwd<32, true>(sp, units, st) : launch_scan_fwd<32, false>(sp, units, st);
   end_stage(st);
@@ -777,10 +785,11 @@ int chunk_fwd(const pkda_chunk_fwd_args* a, cudaStream_t st) {
                                                                a->a_atk, a->final_A_state);
   PKDA_CHECK_LAUNCH();
 
+  if (cudaMemsetAsync(ws.status, 0, sizeof(int), st) != cudaSuccess) return PKDA_ERR_LAUNCH;
   rc = run_forward_stages(p, geo, ws.beta_c, ws.u, static_cast<bf16*>(a->Aqk), static_cast<bf16*>(a->Akk),
                           static_cast<bf16*>(a->k_precond), a->ac_atk, a->a_atk, static_cast<bf16*>(a->w),
                           static_cast<bf16*>(a->kg), static_cast<bf16*>(a->v_new), static_cast<bf16*>(a->h),
-                          static_cast<bf16*>(a->qg), a->final_state, false, st);
+                          static_cast<bf16*>(a->qg), a->final_state, false, ws.status, st);
   if (rc != PKDA_OK) return rc;
 
   // Output stage: tcgen05 + TMA by default; PKDA_OUT_IMPL=mma selects the mma.sync kernel (A/B runs).
@@ -789,7 +798,6 @@ int chunk_fwd(const pkda_chunk_fwd_args* a, cudaStream_t st) {
     return e && e[0] == 'm';
   }();
   if (!use_mma) {
-    if (cudaMemsetAsync(ws.status, 0, sizeof(int), st) != cudaSuccess) return PKDA_ERR_LAUNCH;
     return launch_out_fwd_tc(geo, p.total_tokens, static_cast<const bf16*>(a->qg), static_cast<const bf16*>(a->h),
                              static_cast<const bf16*>(a->Aqk), static_cast<const bf16*>(a->v_new), ws.beta_c,
                              static_cast<bf16*>(a->o), ws.status, st);

@@ -26,9 +26,14 @@ static __device__ long long g_phase_prof[64];
   do {                                                                                  \
     if (threadIdx.x == 0 && blockIdx.x == 37 && (i) >= 10 && (i) < 12) g_phase_prof[32 + 4 * ((i) - 10) + (k)] = clock64(); \
   } while (0)
+#define PKDA_SCANTC_PHASE(i, k)                                                          \
+  do {                                                                                  \
+    if (threadIdx.x == 0 && blockIdx.x == 37 && (i) >= 10 && (i) < 12) g_phase_prof[6 * ((i) - 10) + (k)] = clock64(); \
+  } while (0)
 #else
 #define PKDA_PHASE(k)
 #define PKDA_SCAN_PHASE(i, k)
+#define PKDA_SCANTC_PHASE(i, k)
 #endif
 
 namespace pkda {

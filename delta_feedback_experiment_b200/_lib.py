@@ -68,8 +68,19 @@ class ChunkBwdArgs(C.Structure):
     ]
 
 
+class RecurrentBwdArgs(C.Structure):
+    _fields_ = [
+        ("p", Problem), ("d_o", C.c_void_p), ("d_final_state", C.c_void_p),
+        ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p), ("dg", C.c_void_p),
+        ("dg_atk", C.c_void_p), ("dbeta_atk", C.c_void_p), ("dbeta", C.c_void_p),
+        ("dA_log", C.c_void_p), ("ddt_bias", C.c_void_p), ("dlog_atk_scale", C.c_void_p),
+        ("d_initial_state", C.c_void_p), ("d_initial_A_state", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
+
+
 EXPORTS = (
-    "pkda_recurrent_fwd", "pkda_chunk_fwd_workspace_bytes", "pkda_chunk_fwd",
+    "pkda_recurrent_fwd", "pkda_recurrent_bwd", "pkda_recurrent_bwd_workspace_bytes", "pkda_chunk_fwd_workspace_bytes", "pkda_chunk_fwd",
     "pkda_chunk_bwd_workspace_bytes", "pkda_chunk_bwd", "pkda_abi_version",
     "pkda_status_string", "pkda_sizeof_problem", "pkda_sizeof_recurrent_args",
     "pkda_sizeof_chunk_fwd_args", "pkda_sizeof_chunk_bwd_args", "pkda_last_launch_count",
@@ -84,6 +95,10 @@ _load_error: Optional[str] = None
 def _configure(lib: C.CDLL) -> None:
     lib.pkda_recurrent_fwd.argtypes = [C.POINTER(RecurrentArgs), C.c_void_p]
     lib.pkda_recurrent_fwd.restype = C.c_int
+    lib.pkda_recurrent_bwd.argtypes = [C.POINTER(RecurrentBwdArgs), C.c_void_p]
+    lib.pkda_recurrent_bwd.restype = C.c_int
+    lib.pkda_recurrent_bwd_workspace_bytes.argtypes = [C.POINTER(Problem)]
+    lib.pkda_recurrent_bwd_workspace_bytes.restype = C.c_size_t
     lib.pkda_chunk_fwd.argtypes = [C.POINTER(ChunkFwdArgs), C.c_void_p]
     lib.pkda_chunk_fwd.restype = C.c_int
     lib.pkda_chunk_fwd_static.argtypes = [C.POINTER(ChunkFwdArgs), C.c_void_p]

@@ -83,6 +83,16 @@ int pkda_recurrent_fwd(const pkda_recurrent_args* args, void* cuda_stream) {
   return pkda::recurrent_fwd(args, static_cast<cudaStream_t>(cuda_stream));
 }
 
+size_t pkda_recurrent_bwd_workspace_bytes(const pkda_problem* p) {
+  return p ? pkda::recurrent_bwd_workspace(*p) : 0;
+}
+
+int pkda_recurrent_bwd(const pkda_recurrent_bwd_args* args, void* cuda_stream) {
+  if (!args) return PKDA_ERR_NULL;
+  pkda::reset_launch_count();
+  return pkda::recurrent_bwd(args, static_cast<cudaStream_t>(cuda_stream));
+}
+
 size_t pkda_chunk_fwd_workspace_bytes(const pkda_problem* p) {
   return p ? pkda::chunk_fwd_workspace(*p) : 0;
 }

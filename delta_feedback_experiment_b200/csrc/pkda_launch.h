@@ -42,6 +42,10 @@ inline size_t align_up(size_t x, size_t a = 256) { return (x + a - 1) / a * a; }
 int recurrent_fwd(const pkda_recurrent_args* a, cudaStream_t st);
 int chunk_fwd(const pkda_chunk_fwd_args* a, cudaStream_t st);
 int chunk_bwd(const pkda_chunk_bwd_args* a, cudaStream_t st);
+int recurrent_bwd(const pkda_recurrent_bwd_args* a, cudaStream_t st);
+size_t recurrent_bwd_workspace(const pkda_problem& p);
+int recurrent_fwd_checkpointed(const pkda_problem& p, const int* chunk_offsets, void* o_scratch, float* Sb,
+                               float* Ab, cudaStream_t st);
 size_t chunk_fwd_workspace(const pkda_problem& p);
 size_t chunk_bwd_workspace(const pkda_problem& p);
 

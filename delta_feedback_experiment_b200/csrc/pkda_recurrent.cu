@@ -9,16 +9,9 @@
 //   S  <- diag(exp(g)) S ;  e = v - S^T k ;  S <- S + (beta kw) e^T ;  o = S^T (scale q)
 #include "pkda_common.cuh"
 #include "pkda_launch.h"
+#include "pkda_recurrent.cuh"
 
 namespace pkda {
-
-template <int D> struct RecCfg {
-  static constexpr int kThreads = D >= 32 ? 256 : (D == 16 ? 64 : 32);
-  static constexpr int kVQ = D / 4;                                        // threads across v
-  static constexpr int kKW = (kThreads / kVQ) < D ? (kThreads / kVQ) : D;  // row groups
-  static constexpr int kActive = kVQ * kKW;
-  static constexpr int kR = D / kKW;                                       // rows per thread
-};
 
 struct RecParams {
   Geo geo;
@@ -29,11 +22,15 @@ struct RecParams {
   const float *S0, *A0;
   void* o;
   float *ST, *AT;
+  float *Sb, *Ab;  // optional checkpoints at every 64-token boundary: [chunks][H][D][D], [chunks][H][D]
   float scale, ln_x, eps;
 };
 
-template <int D, typename T>
-__global__ void __launch_bounds__(RecCfg<D>::kThreads)
+// kCkpt: also store the states entering every 64-token chunk (first pass of the exact
+// backward); a separate instantiation so that the decode kernel keeps its register budget
+// (two CTAs per SM at D = 128).
+template <int D, typename T, bool kCkpt>
+__global__ void __launch_bounds__(RecCfg<D>::kThreads, D == 128 ? 2 : 1)
 pkda_recurrent_kernel(const RecParams p) {
   using Cfg = RecCfg<D>;
   constexpr int VQ = Cfg::kVQ, KW = Cfg::kKW, R = Cfg::kR;
@@ -77,6 +74,15 @@ pkda_recurrent_kernel(const RecParams p) {
   T* o = static_cast<T*>(p.o);
 
   for (int t = 0; t < sq.len; ++t) {
+    if (kCkpt && (t & (kChunk - 1)) == 0) {  // checkpoint the state entering this chunk
+      const size_t chh = (size_t)(sq.chunk0 + t / kChunk) * H + h;
+      if (active) {
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+          *reinterpret_cast<float4*>(p.Sb + chh * D * D + (size_t)(krow0 + r) * D + 4 * vq) = S[r];
+      }
+      if (tid < D) p.Ab[chh * D + tid] = A;
+    }
     const size_t tok = (size_t)(sq.bos + t);
     const size_t sidx = tok * H + h;
     if (tid < D) {
@@ -137,9 +143,11 @@ pkda_recurrent_kernel(const RecParams p) {
 
 template <int D, typename T>
 static int launch_rec(const RecParams& rp, cudaStream_t st) {
+  const bool ckpt = rp.Sb != nullptr;
   dim3 grid(rp.geo.n_seqs * rp.geo.heads), block(RecCfg<D>::kThreads);
   begin_stage(kStageRecurrent, st);
-  pkda_recurrent_kernel<D, T><<<grid, block, 0, st>>>(rp);
+  if (ckpt) pkda_recurrent_kernel<D, T, true><<<grid, block, 0, st>>>(rp);
+  else pkda_recurrent_kernel<D, T, false><<<grid, block, 0, st>>>(rp);
   end_stage(st);
   return cudaGetLastError() == cudaSuccess ? PKDA_OK : PKDA_ERR_LAUNCH;
 }
@@ -168,7 +176,24 @@ int recurrent_fwd(const pkda_recurrent_args* a, cudaStream_t st) {
   rp.beta_atk = p.beta_atk; rp.beta = p.beta;
   rp.A_log = p.A_log; rp.dt_bias = p.dt_bias; rp.log_atk_scale = p.log_atk_scale;
   rp.S0 = p.initial_state; rp.A0 = p.initial_A_state;
-  rp.o = a->o; rp.ST = a->final_state; rp.AT = a->final_A_state;
+  rp.o = a->o; rp.ST = a->final_state; rp.AT = a->final_A_state; rp.Sb = nullptr; rp.Ab = nullptr;
+  rp.scale = p.scale; rp.ln_x = logf(p.squash_x); rp.eps = p.squash_eps;
+  if (p.dtype == PKDA_BF16) return dispatch_rec<bf16>(p.head_dim, rp, st);
+  if (p.dtype == PKDA_F32) return dispatch_rec<float>(p.head_dim, rp, st);
+  return PKDA_ERR_DTYPE;
+}
+
+// Forward pass that also leaves the states at every chunk boundary (first pass of
+// the exact backward).
+int recurrent_fwd_checkpointed(const pkda_problem& p, const int* chunk_offsets, void* o_scratch, float* Sb,
+                               float* Ab, cudaStream_t st) {
+  RecParams rp;
+  rp.geo = make_geo(p, chunk_offsets);
+  rp.q = p.q; rp.k = p.k; rp.v = p.v; rp.g = p.g; rp.g_atk = p.g_atk;
+  rp.beta_atk = p.beta_atk; rp.beta = p.beta;
+  rp.A_log = p.A_log; rp.dt_bias = p.dt_bias; rp.log_atk_scale = p.log_atk_scale;
+  rp.S0 = p.initial_state; rp.A0 = p.initial_A_state;
+  rp.o = o_scratch; rp.ST = nullptr; rp.AT = nullptr; rp.Sb = Sb; rp.Ab = Ab;
   rp.scale = p.scale; rp.ln_x = logf(p.squash_x); rp.eps = p.squash_eps;
   if (p.dtype == PKDA_BF16) return dispatch_rec<bf16>(p.head_dim, rp, st);
   if (p.dtype == PKDA_F32) return dispatch_rec<float>(p.head_dim, rp, st);

@@ -103,8 +103,12 @@ def _pkda_recurrence_backward(
         raise RuntimeError(
             f"PKDA backward received {len(saved)} intermediates, not {expected}")
     if not _chunk_capable(q):
-        raise RuntimeError(
-            "PKDA backward is implemented for bf16 activations with head width 128")
+        # fp32 activations or another head width: exact backward (ignores ``saved``)
+        grads, _, _ = ops.recurrent_backward(
+            q, k, v, g, g_atk, beta_atk, beta, A_log, dt_bias, log_atk_scale,
+            scale, squash_x, squash_eps, do)
+        inputs = (q, k, v, g, g_atk, beta_atk, beta, A_log, dt_bias, log_atk_scale)
+        return [gr.reshape(t.shape).to(t.dtype) for gr, t in zip(grads, inputs)]
     grads, _, _ = ops.chunk_backward(
         q, k, v, g, g_atk, beta_atk, beta, A_log, dt_bias, log_atk_scale,
         scale, squash_x, squash_eps, saved, do, lean=lean)

@@ -255,6 +255,53 @@ def chunk_backward(q, k, v, g, g_atk, beta_atk, beta, A_log, dt_bias, log_atk_sc
     return grads, dS0, dA0
 
 
+def recurrent_backward(q, k, v, g, g_atk, beta_atk, beta, A_log, dt_bias, log_atk_scale, scale, x,
+                       eps, do, initial_state=None, initial_A_state=None, cu_seqlens=None,
+                       d_final_state=None, want_state_grads=False):
+    """Exact fp32 backward of the recurrence (any supported head width, bf16 or
+    fp32 activations); needs no saved intermediates.  Returns the ten gradients
+    (plus ``dS0, dA0`` when ``want_state_grads``)."""
+    _require_cuda(q, k, v, g, g_atk, beta_atk, beta, do)
+    lib = _lib.load()
+    keep: list = []
+    p = _problem(q, k, v, g, g_atk, beta_atk, beta, A_log, dt_bias, log_atk_scale, scale, x, eps,
+                 initial_state, initial_A_state, cu_seqlens, keep)
+    B, T, H, D = q.shape
+    N = p.n_seqs
+    dev, act = q.device, q.dtype
+    args = _lib.RecurrentBwdArgs()
+    args.p = p
+    do_c = do.to(act).contiguous()
+    args.d_o = do_c.data_ptr()
+    if d_final_state is not None:
+        dST = d_final_state.to(torch.float32).contiguous()
+        keep.append(dST)
+        args.d_final_state = dST.data_ptr()
+    dq, dk, dv, dg = (torch.empty((B, T, H, D), device=dev, dtype=act) for _ in range(4))
+    dg_atk = torch.empty((B, T, H), device=dev, dtype=torch.float32)
+    dbeta_atk = torch.empty((B, T, H), device=dev, dtype=act)
+    dbeta = torch.empty((B, T, H), device=dev, dtype=act)
+    dA_log = torch.empty((H,), device=dev, dtype=torch.float32)
+    ddt_bias = torch.empty((H * D,), device=dev, dtype=torch.float32)
+    dcentre = torch.empty((H,), device=dev, dtype=torch.float32)
+    args.dq, args.dk, args.dv, args.dg = (t.data_ptr() for t in (dq, dk, dv, dg))
+    args.dg_atk, args.dbeta_atk, args.dbeta = dg_atk.data_ptr(), dbeta_atk.data_ptr(), dbeta.data_ptr()
+    args.dA_log, args.ddt_bias, args.dlog_atk_scale = (
+        dA_log.data_ptr(), ddt_bias.data_ptr(), dcentre.data_ptr())
+    dS0 = dA0 = None
+    if want_state_grads:
+        dS0 = torch.empty((N, H, D, D), device=dev, dtype=torch.float32)
+        dA0 = torch.empty((N, H, D), device=dev, dtype=torch.float32)
+        args.d_initial_state, args.d_initial_A_state = dS0.data_ptr(), dA0.data_ptr()
+    nbytes = lib.pkda_recurrent_bwd_workspace_bytes(C.byref(p))
+    ws = torch.empty((max(nbytes, 16),), device=dev, dtype=torch.uint8)
+    args.workspace, args.workspace_bytes = ws.data_ptr(), nbytes
+    _lib.check(lib.pkda_recurrent_bwd(C.byref(args), _lib.current_stream()), "pkda_recurrent_bwd")
+    _count(lib)
+    grads = [dq, dk, dv, dg, dg_atk, dbeta_atk, dbeta, dA_log, ddt_bias, dcentre]
+    return grads, dS0, dA0
+
+
 def static_scratch_bytes() -> int:
     return int(_lib.load().pkda_static_scratch_bytes())
 

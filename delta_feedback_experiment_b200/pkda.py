@@ -85,6 +85,36 @@ class _ChunkPKDA(torch.autograd.Function):
                 None, None, None, None, None, None)
 
 
+class _ExactPKDA(torch.autograd.Function):
+    """Token-by-token kernels (exact fp32 arithmetic) with autograd: the path for
+    fp32 activations and for head widths other than 128."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, g, g_atk, beta_atk, beta, A_log, dt_bias, log_atk_scale,
+                initial_state, initial_A_state, scale, x, eps, cu_seqlens, output_final_state):
+        o, S, A = ops.recurrent_forward(
+            q, k, v, g, g_atk, beta_atk, beta, A_log, dt_bias, log_atk_scale, scale, x, eps,
+            initial_state, initial_A_state, cu_seqlens, output_final_state)
+        ctx.save_for_backward(q, k, v, g, g_atk, beta_atk, beta, A_log, dt_bias, log_atk_scale,
+                              initial_state, initial_A_state, cu_seqlens)
+        ctx.conf = (scale, x, eps)
+        if S is not None:
+            ctx.mark_non_differentiable(A)
+            return o, S, A
+        return o, None, None
+
+    @staticmethod
+    def backward(ctx, do, dS, _dA):
+        t = ctx.saved_tensors
+        inputs, S0, A0, cu = t[:10], t[10], t[11], t[12]
+        scale, x, eps = ctx.conf
+        want = S0 is not None or A0 is not None
+        grads, dS0, dA0 = ops.recurrent_backward(*inputs, scale, x, eps, do, S0, A0, cu, dS, want)
+        out = [gr.reshape(i.shape).to(i.dtype) for gr, i in zip(grads, inputs)]
+        return (*out, dS0 if S0 is not None else None, dA0 if A0 is not None else None,
+                None, None, None, None, None)
+
+
 def chunk_precond_kda(
     q: Tensor, k: Tensor, v: Tensor, g: Tensor, g_atk: Tensor, beta_atk: Tensor, beta: Tensor,
     A_log: Tensor, dt_bias: Tensor,
@@ -97,9 +127,9 @@ def chunk_precond_kda(
 ) -> tuple[Tensor, Optional[Tensor], Optional[Tensor]]:
     """Chunked recurrence seeded from / returning recurrent state, with packed
     sequences (``[1, T_total, H, D]`` tensors, ``cu_seqlens`` ``[N+1]``, states
-    ``[N,H,D,D]`` / ``[N,H,D]``).  Differentiable for bf16 activations with head
-    width 128; other head widths and fp32 run the exact token-by-token kernel
-    (forward only).  ``disable_recompute=False`` (the reference's choice,
+    ``[N,H,D,D]`` / ``[N,H,D]``).  bf16 activations with head width 128 take the
+    chunked tensor-core kernels; fp32 activations and other head widths take the
+    exact token-by-token kernels.  Both are differentiable.  ``disable_recompute=False`` (the reference's choice,
     ``pkda.py:468``) keeps only the six always-saved intermediates."""
     del cu_seqlens_cpu
     _check_flags(use_gate_in_kernel, use_qk_l2norm_in_kernel)
@@ -109,12 +139,9 @@ def chunk_precond_kda(
         return _ChunkPKDA.apply(q, k, v, g, g_atk, beta_atk, beta, A_log, dt_bias, log_atk_scale,
                                 initial_state, initial_A_state, scale, x, eps, cu_seqlens,
                                 output_final_state, not disable_recompute)
-    if torch.is_grad_enabled() and any(t.requires_grad for t in (q, k, v, g, beta)):
-        raise RuntimeError("PKDA backward is implemented for bf16 activations with head width 128")
-    with torch.no_grad():
-        return ops.recurrent_forward(
-            q, k, v, g, g_atk, beta_atk, beta, A_log, dt_bias, log_atk_scale, scale, x, eps,
-            initial_state, initial_A_state, cu_seqlens, output_final_state)
+    return _ExactPKDA.apply(q, k, v, g, g_atk, beta_atk, beta, A_log, dt_bias, log_atk_scale,
+                            initial_state, initial_A_state, scale, x, eps, cu_seqlens,
+                            output_final_state)
 
 
 def pkda_cuda_recurrence(

@@ -89,6 +89,30 @@ typedef struct pkda_recurrent_args {
 int pkda_recurrent_fwd(const pkda_recurrent_args* args, void* cuda_stream);
 
 /*
+ * Exact backward of the recurrence (fp32 arithmetic throughout): the gradient
+ * path for fp32 activations and for head widths other than 128, and an
+ * independent check of the chunked backward.  Same gradients as
+ * pkda_chunk_bwd (replaces the same reference code,
+ * delta_feedback_experiment/fla_ops.py:423-499, and the autograd of
+ * pkda.py:355-410); needs no saved intermediates: a checkpointed forward pass
+ * runs first inside the call.  D in {8,16,32,64,128}, bf16 or fp32.
+ */
+typedef struct pkda_recurrent_bwd_args {
+  pkda_problem p;
+  const void* d_o;              /* [tokens][H][D] activation dtype */
+  const float* d_final_state;   /* [N][H][D][D] or NULL */
+  void* dq; void* dk; void* dv; void* dg;     /* activation dtype */
+  float* dg_atk; void* dbeta_atk; void* dbeta;
+  float* dA_log; float* ddt_bias; float* dlog_atk_scale;
+  float* d_initial_state;    /* or NULL */
+  float* d_initial_A_state;  /* or NULL */
+  void* workspace; size_t workspace_bytes;
+} pkda_recurrent_bwd_args;
+
+size_t pkda_recurrent_bwd_workspace_bytes(const pkda_problem* p);
+int pkda_recurrent_bwd(const pkda_recurrent_bwd_args* args, void* cuda_stream);
+
+/*
  * Chunked forward (training / prefill), bf16 activations, D = 128, chunk 64.
  * Replaces kda_gate_chunk_cumsum + chunk_precond_kda_fwd
  * (delta_feedback_experiment/fla_ops.py:290-339) and chunk_precond_kda

@@ -42,6 +42,7 @@ WORKLOADS = {
     "config1": (8, 4096, 16, 128),
     "config4": (16, 8192, 16, 128),
     "profile": (2, 4096, 16, 128),   # small case for ncu captures (working set still > L2)
+    "profile_wide": (8, 1024, 16, 128),  # same size, 128 (row, head) units: takes the tcgen05 state scan
 }
 C = 64
 # Algorithmic work per (token, head) for D=128, chunk 64 (dense counts).

@@ -58,6 +58,11 @@ STAGE_FLOPS = {
     "scan_bwd": 3 * (2 * K * V) + 2 * C * V,                                  # kg*dS, qg^T*dO, W^T*dE, P^T*dO
     "intra_bwd": 3 * (2 * K * V) + 3 * (2 * C * V) + 4 * (2 * C * K),
 }
+# DRAM traffic per (token, head) of each kernel: dram__bytes_read.sum + dram__bytes_write.sum of one
+# ncu capture on the quarter-size workload (131,072 units), divided by its units; the traffic grows
+# in proportion to the units, so a launch of any size moves this many bytes per unit.
+STAGE_TRAFFIC_PER_UNIT = {"intra_fwd": 2215, "scan_fwd": 1242, "out_fwd": 1297, "scan_bwd": 1732,
+                          "intra_bwd": 4511}
 DECODE_BYTES_PER_UNIT = 2 * 4 * 128 * 128 + 2 * 4 * 128 + 4 * 2 * 128 + 8 + 2 * 128   # 133,384
 
 
@@ -223,6 +228,58 @@ def run_decode(device, steps: int, warmup: int, pk: dict) -> dict:
     }
 
 
+def run_layer_ops(device, B: int, T: int, H: int, D: int, steps: int, warmup: int, pk: dict) -> dict:
+    """The two fused operators next to the recurrence on the headline shape: Q|K|V convolution
+    (+SiLU +L2 norm) and RMS-norm x sigmoid gate, forward and backward, each against the HBM roofline
+    with its algorithmic bytes (every input read once, every output written once)."""
+    from delta_feedback_experiment_b200 import _lib, layer_ops
+    W = H * D
+    gen = torch.Generator().manual_seed(77)
+    x = torch.randn(B, T, 3 * W, generator=gen).bfloat16().to(device)
+    wconv = (torch.randn(3 * W, 4, generator=gen) * 0.5).to(device)
+    dqkv = [torch.randn(B, T, W, generator=gen).bfloat16().to(device) for _ in range(3)]
+    o = torch.randn(B, T, H, D, generator=gen).bfloat16().to(device)
+    gate = torch.randn(B, T, H, D, generator=gen).bfloat16().to(device)
+    wnorm = torch.ones(D, device=device)
+    rstd_box = []
+
+    def once():
+        layer_ops.qkv_conv_forward(x, wconv, D, 2 * W, 1e-6)
+        layer_ops.qkv_conv_backward(x, wconv, *dqkv, D, 2 * W, 1e-6)
+        _, rstd = layer_ops.norm_gate_forward(o, gate, wnorm, 1e-6)
+        layer_ops.norm_gate_backward(o, gate, wnorm, rstd, dqkv[0].view(B, T, H, D), 1e-6)
+
+    for _ in range(warmup):
+        once()
+    torch.cuda.synchronize(device)
+    _lib.stage_timing(True)
+    for _ in range(steps):
+        once()
+    torch.cuda.synchronize(device)
+    stages = _lib.stage_timing_read()
+    _lib.stage_timing(False)
+    tokens, rows = B * T, B * T * H
+    algo = {  # bytes per launch
+        "qkv_conv_fwd": tokens * (2 * 3 * W * 2),
+        "qkv_conv_bwd": tokens * (3 * 3 * W * 2),
+        "norm_gate_fwd": rows * (3 * D * 2 + 4),
+        "norm_gate_bwd": rows * (5 * D * 2 + 4),
+    }
+    out = {"workload": f"B={B} T={T} H={H} d={D} bf16 (x [B,T,{3 * W}], 4 taps; o, gate [B,T,H,{D}]); "
+                       "working sets larger than L2"}
+    for name, nbytes in algo.items():
+        ms, n = stages[name]
+        achieved = nbytes / (ms / n * 1e-3) / 1e9
+        out[name] = {"kernel_ms": ms / n, "roofline": {
+            "bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+            "frac": achieved / pk["hbm_gbs"], "traffic": None, "algorithmic_bytes_per_launch": nbytes,
+            "peak_source": pk["source"]}}
+    for name in ("qkv_conv_dw", "norm_gate_dw"):
+        ms, n = stages[name]
+        out[name] = {"kernel_ms": ms / n}
+    return out
+
+
 def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     import torch.distributed as dist
     from delta_feedback_experiment_b200 import _lib, chunk_precond_kda, ops
@@ -344,7 +401,9 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     peak_tf = pk["bf16_tflops_sustained"]
     roofline = {
         "bound": "tensor", "kernel": f"pkda_{top}_kernel", "achieved": achieved_tf, "peak": peak_tf,
-        "unit": "TFLOP/s", "frac": achieved_tf / peak_tf, "traffic": None,
+        "unit": "TFLOP/s", "frac": achieved_tf / peak_tf,
+        "traffic": STAGE_TRAFFIC_PER_UNIT[top] * units if D == 128 else None,
+        "traffic_source": "ncu capture of a quarter-size launch, scaled by the units processed",
         "launch_ms": top_ms, "algorithmic_flops_per_launch": STAGE_FLOPS[top] * units,
         "peak_source": pk["source"] + " (sustained bf16 GEMM; kernel timed inside a long step)",
         "share_of_step": stages[top][0] / sum(ms for ms, _ in stages.values()),
@@ -377,6 +436,8 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     }
     if not args.no_decode:
         line["decode"] = run_decode(device, args.decode_steps, 16, pk)
+    if not args.no_layer:
+        line["layer_ops"] = run_layer_ops(device, B, T, H, D, 10, 3, pk)
     if not args.no_cpu:
         cb = cpu_oracle_rate(T, H, D)
         line["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
@@ -396,6 +457,7 @@ def main() -> None:
     ap.add_argument("--decode-steps", type=int, default=1024)
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-layer", action="store_true", help="skip the convolution / norm-gate operators")
     ap.add_argument("--no-e2e", action="store_true", help="profiling aid: device-resident leg only")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -408,6 +470,7 @@ def main() -> None:
     else:
         if world > 1:
             args.no_decode = True if rank != 0 else args.no_decode
+            args.no_layer = True if rank != 0 else args.no_layer
         run_ours(args, rank, world, local_rank)
 
 

@@ -79,6 +79,28 @@ class RecurrentBwdArgs(C.Structure):
     ]
 
 
+class QkvConvArgs(C.Structure):
+    _fields_ = [
+        ("batch", C.c_int32), ("seq_len", C.c_int32), ("channels", C.c_int32), ("taps", C.c_int32),
+        ("head_dim", C.c_int32), ("norm_channels", C.c_int32), ("dtype", C.c_int32), ("eps", C.c_float),
+        ("x", C.c_void_p), ("weight", C.c_void_p),
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p),
+        ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p),
+        ("dx", C.c_void_p), ("dweight", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
+
+
+class NormGateArgs(C.Structure):
+    _fields_ = [
+        ("rows", C.c_longlong), ("dim", C.c_int32), ("dtype", C.c_int32), ("eps", C.c_float),
+        ("x", C.c_void_p), ("gate", C.c_void_p), ("weight", C.c_void_p),
+        ("y", C.c_void_p), ("rstd", C.c_void_p), ("dy", C.c_void_p),
+        ("dx", C.c_void_p), ("dgate", C.c_void_p), ("dweight", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
+
+
 EXPORTS = (
     "pkda_recurrent_fwd", "pkda_recurrent_bwd", "pkda_recurrent_bwd_workspace_bytes", "pkda_chunk_fwd_workspace_bytes", "pkda_chunk_fwd",
     "pkda_chunk_bwd_workspace_bytes", "pkda_chunk_bwd", "pkda_abi_version",
@@ -86,6 +108,9 @@ EXPORTS = (
     "pkda_sizeof_chunk_fwd_args", "pkda_sizeof_chunk_bwd_args", "pkda_last_launch_count",
     "pkda_stage_count", "pkda_stage_name", "pkda_stage_timing", "pkda_stage_timing_read",
     "pkda_static_scratch_bytes", "pkda_chunk_fwd_static", "pkda_set_direct_block_cap",
+    "pkda_qkv_conv_fwd", "pkda_qkv_conv_bwd_workspace_bytes", "pkda_qkv_conv_bwd",
+    "pkda_norm_gate_fwd", "pkda_norm_gate_bwd_workspace_bytes", "pkda_norm_gate_bwd",
+    "pkda_sizeof_qkv_conv_args", "pkda_sizeof_norm_gate_args",
 )
 
 _lib: Optional[C.CDLL] = None
@@ -111,11 +136,18 @@ def _configure(lib: C.CDLL) -> None:
     for name in ("pkda_chunk_fwd_workspace_bytes", "pkda_chunk_bwd_workspace_bytes"):
         getattr(lib, name).argtypes = [C.POINTER(Problem)]
         getattr(lib, name).restype = C.c_size_t
+    for name, struct in (("pkda_qkv_conv", QkvConvArgs), ("pkda_norm_gate", NormGateArgs)):
+        for suffix in ("_fwd", "_bwd"):
+            getattr(lib, name + suffix).argtypes = [C.POINTER(struct), C.c_void_p]
+            getattr(lib, name + suffix).restype = C.c_int
+        getattr(lib, name + "_bwd_workspace_bytes").argtypes = [C.POINTER(struct)]
+        getattr(lib, name + "_bwd_workspace_bytes").restype = C.c_size_t
     lib.pkda_abi_version.restype = C.c_int
     lib.pkda_status_string.argtypes = [C.c_int]
     lib.pkda_status_string.restype = C.c_char_p
     for name in ("pkda_sizeof_problem", "pkda_sizeof_recurrent_args",
-                 "pkda_sizeof_chunk_fwd_args", "pkda_sizeof_chunk_bwd_args"):
+                 "pkda_sizeof_chunk_fwd_args", "pkda_sizeof_chunk_bwd_args",
+                 "pkda_sizeof_qkv_conv_args", "pkda_sizeof_norm_gate_args"):
         getattr(lib, name).restype = C.c_size_t
     lib.pkda_last_launch_count.restype = C.c_int
     lib.pkda_stage_count.restype = C.c_int
@@ -145,7 +177,9 @@ def load() -> C.CDLL:
         sizes = ((lib.pkda_sizeof_problem(), Problem),
                  (lib.pkda_sizeof_recurrent_args(), RecurrentArgs),
                  (lib.pkda_sizeof_chunk_fwd_args(), ChunkFwdArgs),
-                 (lib.pkda_sizeof_chunk_bwd_args(), ChunkBwdArgs))
+                 (lib.pkda_sizeof_chunk_bwd_args(), ChunkBwdArgs),
+                 (lib.pkda_sizeof_qkv_conv_args(), QkvConvArgs),
+                 (lib.pkda_sizeof_norm_gate_args(), NormGateArgs))
         for size, struct in sizes:
             if size != C.sizeof(struct):
                 raise OSError(f"struct layout mismatch for {struct.__name__}")

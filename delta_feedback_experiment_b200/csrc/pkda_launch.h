@@ -12,7 +12,8 @@ namespace pkda {
 enum Stage {
   kStageOffsets = 0, kStagePackBeta, kStageAtkLocal, kStageAtkCarry, kStageIntraFwd, kStageScanFwd,
   kStageOutFwd, kStageScanBwd, kStageIntraBwd, kStageAtkBwdLocal, kStageAtkBwdCarry, kStageAtkBwdFinal,
-  kStageParamReduce, kStageRecurrent, kStageCount
+  kStageParamReduce, kStageRecurrent, kStageConvFwd, kStageConvBwd, kStageConvDw, kStageNormGateFwd,
+  kStageNormGateBwd, kStageNormGateDw, kStageCount
 };
 
 // begin_stage / end_stage bracket every kernel launch: they count launches and,
@@ -48,5 +49,11 @@ int recurrent_fwd_checkpointed(const pkda_problem& p, const int* chunk_offsets, 
                                float* Ab, cudaStream_t st);
 size_t chunk_fwd_workspace(const pkda_problem& p);
 size_t chunk_bwd_workspace(const pkda_problem& p);
+int qkv_conv_fwd(const pkda_qkv_conv_args* a, cudaStream_t st);
+int qkv_conv_bwd(const pkda_qkv_conv_args* a, cudaStream_t st);
+size_t qkv_conv_bwd_workspace(const pkda_qkv_conv_args& a);
+int norm_gate_fwd(const pkda_norm_gate_args* a, cudaStream_t st);
+int norm_gate_bwd(const pkda_norm_gate_args* a, cudaStream_t st);
+size_t norm_gate_bwd_workspace(const pkda_norm_gate_args& a);
 
 }  // namespace pkda

@@ -1,0 +1,222 @@
+"""The two fused operators next to the recurrence inside the PKDA layer, behind
+the reference's operator names and signatures:
+
+* ``pkda_qkv_conv(x, weight, head_dim, norm_channels, eps) -> (q, k, v)`` --
+  ``delta_feedback::pkda_qkv_conv`` of the reference
+  (``delta_feedback_experiment/fla_ops.py:134-249``): causal depthwise short
+  convolution over the concatenated Q|K|V projection, SiLU, per-head L2
+  normalisation of the first ``norm_channels`` channels, three output slabs.
+* ``pkda_norm_gate(x, gate, weight, eps) -> (y, rstd)`` --
+  ``delta_feedback::pkda_norm_gate`` (``fla_ops.py:572-657``): per-head RMS
+  normalisation times a learned weight times ``sigmoid(gate)``.
+
+Both are registered as ``torch.library.custom_op`` with fake implementations and
+autograd, as the reference registers them, and both call the C ABI of
+``libpkda_b200.so``; there is no other implementation behind them.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+from torch import Tensor
+
+from . import _lib, ops
+
+_DTYPES = {torch.bfloat16: _lib.PKDA_BF16, torch.float32: _lib.PKDA_F32}
+
+
+def _dtype_code(t: Tensor) -> int:
+    if t.dtype not in _DTYPES:
+        raise RuntimeError(f"PKDA layer operators take bf16 or fp32 activations, got {t.dtype}")
+    return _DTYPES[t.dtype]
+
+
+def _workspace(nbytes: int, device) -> Tensor:
+    return torch.empty((max(int(nbytes), 16),), device=device, dtype=torch.uint8)
+
+
+# ----------------------------------------------------------------- convolution
+def _conv_args(x: Tensor, weight: Tensor, head_dim: int, norm_channels: int, eps: float):
+    if x.dim() != 3 or weight.dim() != 2 or weight.shape[0] != x.shape[-1] or x.shape[-1] % 3:
+        raise RuntimeError("pkda_qkv_conv expects x [B,T,3W] and weight [3W,taps]")
+    a = _lib.QkvConvArgs()
+    a.batch, a.seq_len, a.channels = x.shape
+    a.taps = weight.shape[1]
+    a.head_dim, a.norm_channels, a.eps = int(head_dim), int(norm_channels), float(eps)
+    a.dtype = _dtype_code(x)
+    return a
+
+
+def qkv_conv_forward(x: Tensor, weight: Tensor, head_dim: int, norm_channels: int, eps: float):
+    ops._require_cuda(x, weight)
+    lib = _lib.load()
+    x = x.contiguous()
+    w32 = weight.detach().to(torch.float32).contiguous()
+    a = _conv_args(x, w32, head_dim, norm_channels, eps)
+    B, T, C3 = x.shape
+    q, k, v = (torch.empty((B, T, C3 // 3), device=x.device, dtype=x.dtype) for _ in range(3))
+    a.x, a.weight = x.data_ptr(), w32.data_ptr()
+    a.q, a.k, a.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
+    _lib.check(lib.pkda_qkv_conv_fwd(C.byref(a), _lib.current_stream()), "pkda_qkv_conv_fwd")
+    ops._count(lib)
+    return q, k, v
+
+
+def qkv_conv_backward(x: Tensor, weight: Tensor, dq: Tensor, dk: Tensor, dv: Tensor, head_dim: int,
+                      norm_channels: int, eps: float):
+    ops._require_cuda(x, weight, dq, dk, dv)
+    lib = _lib.load()
+    x = x.contiguous()
+    w32 = weight.detach().to(torch.float32).contiguous()
+    dq, dk, dv = (t.to(x.dtype).contiguous() for t in (dq, dk, dv))
+    a = _conv_args(x, w32, head_dim, norm_channels, eps)
+    dx = torch.empty_like(x)
+    dw = torch.empty_like(w32)
+    a.x, a.weight = x.data_ptr(), w32.data_ptr()
+    a.dq, a.dk, a.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+    a.dx, a.dweight = dx.data_ptr(), dw.data_ptr()
+    nbytes = lib.pkda_qkv_conv_bwd_workspace_bytes(C.byref(a))
+    ws = _workspace(nbytes, x.device)
+    a.workspace, a.workspace_bytes = ws.data_ptr(), nbytes
+    _lib.check(lib.pkda_qkv_conv_bwd(C.byref(a), _lib.current_stream()), "pkda_qkv_conv_bwd")
+    ops._count(lib)
+    return dx, dw.to(weight.dtype)
+
+
+@torch.library.custom_op("delta_feedback::pkda_qkv_conv", mutates_args=(), device_types="cuda")
+def pkda_qkv_conv(x: Tensor, weight: Tensor, head_dim: int, norm_channels: int,
+                  eps: float) -> tuple[Tensor, Tensor, Tensor]:
+    """Signature and meaning of the reference's operator (``fla_ops.py:137-170``)."""
+    return qkv_conv_forward(x, weight, head_dim, norm_channels, eps)
+
+
+@pkda_qkv_conv.register_fake
+def _pkda_qkv_conv_fake(x, weight, head_dim, norm_channels, eps):
+    batch, length, _ = x.shape
+    width = weight.shape[0] // 3
+    return tuple(x.new_empty(batch, length, width) for _ in range(3))
+
+
+@torch.library.custom_op("delta_feedback::pkda_qkv_conv_backward", mutates_args=(),
+                         device_types="cuda")
+def _pkda_qkv_conv_backward(x: Tensor, weight: Tensor, dq: Tensor, dk: Tensor, dv: Tensor,
+                            head_dim: int, norm_channels: int, eps: float) -> tuple[Tensor, Tensor]:
+    return qkv_conv_backward(x, weight, dq, dk, dv, head_dim, norm_channels, eps)
+
+
+@_pkda_qkv_conv_backward.register_fake
+def _pkda_qkv_conv_backward_fake(x, weight, dq, dk, dv, head_dim, norm_channels, eps):
+    return torch.empty_like(x), torch.empty_like(weight)
+
+
+def _conv_setup_context(ctx, inputs, output) -> None:
+    x, weight, head_dim, norm_channels, eps = inputs
+    ctx.save_for_backward(x, weight)
+    ctx.geometry = (head_dim, norm_channels, eps)
+
+
+def _conv_backward(ctx, dq, dk, dv):
+    x, weight = ctx.saved_tensors
+    head_dim, norm_channels, eps = ctx.geometry
+    dx, dw = _pkda_qkv_conv_backward(x, weight, dq, dk, dv, head_dim, norm_channels, eps)
+    return dx, dw, None, None, None
+
+
+pkda_qkv_conv.register_autograd(_conv_backward, setup_context=_conv_setup_context)
+
+
+# ------------------------------------------------------------------- norm gate
+def _ng_args(x: Tensor, gate: Tensor, weight: Tensor, eps: float):
+    if gate.shape != x.shape or weight.dim() != 1 or weight.shape[0] != x.shape[-1]:
+        raise RuntimeError("pkda_norm_gate expects x, gate [..., D] and weight [D]")
+    a = _lib.NormGateArgs()
+    a.dim = x.shape[-1]
+    a.rows = x.numel() // x.shape[-1]
+    a.dtype = _dtype_code(x)
+    a.eps = float(eps)
+    return a
+
+
+def norm_gate_forward(x: Tensor, gate: Tensor, weight: Tensor, eps: float):
+    ops._require_cuda(x, gate, weight)
+    lib = _lib.load()
+    x = x.contiguous()
+    gate = gate.to(x.dtype).contiguous()
+    w32 = weight.detach().to(torch.float32).contiguous()
+    a = _ng_args(x, gate, w32, eps)
+    y = torch.empty_like(x)
+    rstd = torch.empty((a.rows,), device=x.device, dtype=torch.float32)
+    a.x, a.gate, a.weight = x.data_ptr(), gate.data_ptr(), w32.data_ptr()
+    a.y, a.rstd = y.data_ptr(), rstd.data_ptr()
+    _lib.check(lib.pkda_norm_gate_fwd(C.byref(a), _lib.current_stream()), "pkda_norm_gate_fwd")
+    ops._count(lib)
+    return y, rstd
+
+
+def norm_gate_backward(x: Tensor, gate: Tensor, weight: Tensor, rstd: Tensor, dy: Tensor, eps: float):
+    ops._require_cuda(x, gate, weight, rstd, dy)
+    lib = _lib.load()
+    x = x.contiguous()
+    gate_c = gate.to(x.dtype).contiguous()
+    dy = dy.to(x.dtype).contiguous()
+    w32 = weight.detach().to(torch.float32).contiguous()
+    rstd = rstd.to(torch.float32).contiguous()
+    a = _ng_args(x, gate_c, w32, eps)
+    dx, dg = torch.empty_like(x), torch.empty_like(x)
+    dw = torch.empty_like(w32)
+    a.x, a.gate, a.weight = x.data_ptr(), gate_c.data_ptr(), w32.data_ptr()
+    a.rstd, a.dy = rstd.data_ptr(), dy.data_ptr()
+    a.dx, a.dgate, a.dweight = dx.data_ptr(), dg.data_ptr(), dw.data_ptr()
+    nbytes = lib.pkda_norm_gate_bwd_workspace_bytes(C.byref(a))
+    ws = _workspace(nbytes, x.device)
+    a.workspace, a.workspace_bytes = ws.data_ptr(), nbytes
+    _lib.check(lib.pkda_norm_gate_bwd(C.byref(a), _lib.current_stream()), "pkda_norm_gate_bwd")
+    ops._count(lib)
+    return dx, dg.to(gate.dtype), dw.to(weight.dtype)
+
+
+@torch.library.custom_op("delta_feedback::pkda_norm_gate", mutates_args=(), device_types="cuda")
+def pkda_norm_gate(x: Tensor, gate: Tensor, weight: Tensor, eps: float) -> tuple[Tensor, Tensor]:
+    """Signature and meaning of the reference's operator (``fla_ops.py:575-593``);
+    ``rstd`` has one fp32 entry per row and feeds the backward."""
+    return norm_gate_forward(x, gate, weight, eps)
+
+
+@pkda_norm_gate.register_fake
+def _pkda_norm_gate_fake(x, gate, weight, eps):
+    rows = x.numel() // x.shape[-1]
+    return torch.empty_like(x), torch.empty((rows,), device=x.device, dtype=torch.float32)
+
+
+@torch.library.custom_op("delta_feedback::pkda_norm_gate_backward", mutates_args=(),
+                         device_types="cuda")
+def _pkda_norm_gate_backward(x: Tensor, gate: Tensor, weight: Tensor, rstd: Tensor, dy: Tensor,
+                             eps: float) -> tuple[Tensor, Tensor, Tensor]:
+    return norm_gate_backward(x, gate, weight, rstd, dy, eps)
+
+
+@_pkda_norm_gate_backward.register_fake
+def _pkda_norm_gate_backward_fake(x, gate, weight, rstd, dy, eps):
+    return torch.empty_like(x), torch.empty_like(gate), torch.empty_like(weight)
+
+
+def _norm_gate_setup_context(ctx, inputs, output) -> None:
+    x, gate, weight, eps = inputs
+    _y, rstd = output
+    ctx.save_for_backward(x, gate, weight, rstd)
+    ctx.eps = eps
+    ctx.mark_non_differentiable(rstd)
+
+
+def _norm_gate_backward(ctx, dy, _drstd):
+    x, gate, weight, rstd = ctx.saved_tensors
+    dx, dg, dw = _pkda_norm_gate_backward(x, gate, weight, rstd, dy, ctx.eps)
+    return dx, dg, dw, None
+
+
+pkda_norm_gate.register_autograd(_norm_gate_backward, setup_context=_norm_gate_setup_context)
+
+__all__ = ["pkda_qkv_conv", "pkda_norm_gate", "qkv_conv_forward", "qkv_conv_backward",
+           "norm_gate_forward", "norm_gate_backward"]

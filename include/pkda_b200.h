@@ -233,6 +233,74 @@ const char* pkda_stage_name(int stage);
 int pkda_stage_timing(int enable);
 int pkda_stage_timing_read(float* ms, int* counts, int n_stages);
 
+/* ------------------------------------------------------------------------
+ * Neighbours of the recurrence inside the PKDA layer.
+ *
+ * pkda_qkv_conv_*  replace the custom ops delta_feedback::pkda_qkv_conv and
+ * delta_feedback::pkda_qkv_conv_backward (delta_feedback_experiment/fla_ops.py:134-249;
+ * portable definition delta_feedback_experiment/pkda.py:197-220 and :41-44): a
+ * causal depthwise convolution of `taps` (1..4) taps over the concatenated Q|K|V
+ * projection, SiLU, and a per-head L2 normalisation of the first `norm_channels`
+ * channels, y = s * rsqrt(sum_head(s^2) + eps); outputs are three separate slabs.
+ *   x       [batch][seq_len][channels]          channels = 3 * slab width
+ *   weight  [channels][taps] fp32; tap j multiplies x[t - (taps-1) + j]
+ *   q,k,v   [batch][seq_len][channels / 3]      activation dtype
+ * Tokens before the start of a row read as zero (callers that continue a cached
+ * row prepend the taps-1 previous projections as the reference does,
+ * pkda.py:239-260).  head_dim must be a power of two in 4..128 and divide the slab
+ * width; norm_channels must be a multiple of head_dim.
+ */
+typedef struct pkda_qkv_conv_args {
+  int batch, seq_len, channels, taps, head_dim, norm_channels;
+  int dtype;                 /* PKDA_BF16 or PKDA_F32: x, q, k, v and their gradients */
+  float eps;
+  const void* x;
+  const float* weight;
+  void *q, *k, *v;           /* forward outputs (unused by the backward) */
+  const void *dq, *dk, *dv;  /* backward inputs */
+  void* dx;                  /* backward output, layout of x */
+  float* dweight;            /* backward output [channels][taps] fp32 */
+  void* workspace;           /* backward only: pkda_qkv_conv_bwd_workspace_bytes() bytes */
+  size_t workspace_bytes;
+} pkda_qkv_conv_args;
+
+int pkda_qkv_conv_fwd(const pkda_qkv_conv_args* args, void* cuda_stream);
+size_t pkda_qkv_conv_bwd_workspace_bytes(const pkda_qkv_conv_args* args);
+int pkda_qkv_conv_bwd(const pkda_qkv_conv_args* args, void* cuda_stream);
+
+/*
+ * pkda_norm_gate_*  replace delta_feedback::pkda_norm_gate and
+ * delta_feedback::pkda_norm_gate_backward (fla_ops.py:572-657; portable
+ * definition pkda.py:543-547): per-row RMS normalisation with a learned weight and
+ * a sigmoid output gate,
+ *   rstd = rsqrt(mean(x^2) + eps),  y = x * rstd * weight * sigmoid(gate).
+ *   x, gate, y [rows][dim] activation dtype; weight [dim] fp32; rstd [rows] fp32.
+ * dim must be a power of two in 8..256.  The backward returns dx, dgate and the
+ * fp32 weight gradient [dim] (summed over rows in a fixed order).
+ */
+typedef struct pkda_norm_gate_args {
+  long long rows;
+  int dim;
+  int dtype;
+  float eps;
+  const void *x, *gate;
+  const float* weight;
+  void* y;                /* forward output */
+  float* rstd;            /* forward output, backward input */
+  const void* dy;         /* backward input */
+  void *dx, *dgate;       /* backward outputs */
+  float* dweight;         /* backward output [dim] */
+  void* workspace;        /* backward only: pkda_norm_gate_bwd_workspace_bytes() bytes */
+  size_t workspace_bytes;
+} pkda_norm_gate_args;
+
+int pkda_norm_gate_fwd(const pkda_norm_gate_args* args, void* cuda_stream);
+size_t pkda_norm_gate_bwd_workspace_bytes(const pkda_norm_gate_args* args);
+int pkda_norm_gate_bwd(const pkda_norm_gate_args* args, void* cuda_stream);
+
+size_t pkda_sizeof_qkv_conv_args(void);
+size_t pkda_sizeof_norm_gate_args(void);
+
 #ifdef __cplusplus
 }
 #endif

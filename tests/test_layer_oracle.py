@@ -1,0 +1,67 @@
+"""Pins the CPU oracle of the two operators next to the recurrence against the
+golden vectors the reference itself produced (``tests/golden/make_layer_golden.py``
+ran ``PreconditionedKDA._project`` and ``PreconditionedKDA.forward`` on CPU,
+``delta_feedback_experiment/pkda.py:197-220,290-316,543-547``)."""
+
+import pytest
+import torch
+
+from conftest import assert_close, load_golden
+from oracle.pkda_layer_oracle import norm_gate_oracle, qkv_conv_oracle
+
+CONV_CASES = ["layer_conv_small", "layer_conv_d128", "layer_conv_taps3_history", "layer_conv_d64_history"]
+GATE_CASES = ["layer_gate_small", "layer_gate_d128", "layer_gate_d64"]
+
+
+def conv_inputs(g):
+    """Rows the fused operator sees: the histories, if any, come first."""
+    if "prefix" in g:
+        return torch.cat((g["prefix"], g["x"]), dim=1), g["prefix"].shape[1]
+    return g["x"], 0
+
+
+@pytest.mark.parametrize("name", CONV_CASES)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+def test_conv_oracle_matches_reference_golden(name, dtype):
+    g = load_golden(name)
+    rows, skip = conv_inputs(g)
+    x = rows.clone().requires_grad_(True)
+    w = g["weight"].clone().requires_grad_(True)
+    q, k, v = qkv_conv_oracle(x, w, int(g["head_dim"]), int(g["norm_channels"]), float(g["eps"]), dtype)
+    for key, val in (("q", q), ("k", k), ("v", v)):
+        assert_close(val[:, skip:], g[key], 2e-5, f"{name}:{key}")
+    loss = sum((val[:, skip:] * g["d" + key].to(dtype)).sum() for key, val in (("q", q), ("k", k), ("v", v)))
+    dx, dw = torch.autograd.grad(loss, [x, w])
+    assert_close(dx[:, skip:], g["dx"], 2e-4, f"{name}:dx")
+    assert_close(dw, g["dweight"], 2e-4, f"{name}:dweight")
+    if skip:
+        assert_close(dx[:, :skip], g["dprefix"], 2e-4, f"{name}:dprefix")
+
+
+@pytest.mark.parametrize("name", GATE_CASES)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+def test_norm_gate_oracle_matches_reference_golden(name, dtype):
+    g = load_golden(name)
+    x = g["x"].clone().requires_grad_(True)
+    gate = g["gate"].clone().requires_grad_(True)
+    w = g["weight"].clone().requires_grad_(True)
+    y, rstd = norm_gate_oracle(x, gate, w, float(g["eps"]), dtype)
+    assert_close(y, g["y"], 2e-5, f"{name}:y")
+    assert rstd.shape == (x.numel() // x.shape[-1],)
+    dx, dg, dw = torch.autograd.grad((y * g["dy"].to(dtype)).sum(), [x, gate, w])
+    assert_close(dx, g["dx"], 2e-4, f"{name}:dx")
+    assert_close(dg, g["dgate"], 2e-4, f"{name}:dgate")
+    assert_close(dw, g["dweight"], 2e-4, f"{name}:dweight")
+
+
+def test_conv_is_causal_and_row_independent():
+    gen = torch.Generator().manual_seed(5)
+    x = torch.randn(2, 12, 48, generator=gen)
+    w = torch.randn(48, 4, generator=gen)
+    base = qkv_conv_oracle(x, w, 8, 32, 1e-6)
+    x2 = x.clone()
+    x2[0, 7:] += 1.0          # the future of row 0 changes ...
+    x2[1] = torch.randn(12, 48, generator=gen)   # ... and all of row 1
+    other = qkv_conv_oracle(x2, w, 8, 32, 1e-6)
+    for a, b in zip(base, other):
+        assert torch.equal(a[0, :7], b[0, :7])

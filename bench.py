@@ -296,6 +296,10 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         dist.init_process_group("nccl", device_id=device)
     B, T, H, D = WORKLOADS[args.workload]
     pk = peaks()
+    if args.only_layer:  # profiling aid: the convolution / norm-gate operators alone
+        print(json.dumps({"note": "profiling run (layer operators only): not a benchmark line",
+                          "layer_ops": run_layer_ops(device, B, T, H, D, args.steps, args.warmup, pk)}), flush=True)
+        return
 
     d = make_inputs(B, T, H, D, seed=1000 + rank, dist="unit", dtype=torch.bfloat16, with_state=True)
     host = {n: d[n].pin_memory() for n in (*INPUT_NAMES, "do", "initial_state", "initial_A_state")}
@@ -459,6 +463,7 @@ def main() -> None:
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-layer", action="store_true", help="skip the convolution / norm-gate operators")
     ap.add_argument("--no-e2e", action="store_true", help="profiling aid: device-resident leg only")
+    ap.add_argument("--only-layer", action="store_true", help="profiling aid: layer operators only")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -242,9 +242,74 @@ __device__ __forceinline__ void inverse_merge(const float* sL, float* sT, float*
   __syncthreads();
 }
 
+// The same merge on the tensor cores for N = 16 and 32: both products as
+// mma.sync m16n8k8 TF32 with every fp32 operand split into a high and a low TF32
+// part (three MMAs per step: lo*hi + hi*lo + hi*hi), which keeps fp32-level
+// accuracy (the dropped lo*lo term is 2^-22 relative).  One warp per 16 x 8
+// output tile; operands come straight from the fp32 arrays in shared memory.
+__device__ __forceinline__ void tf32_split(float x, uint32_t& hi, uint32_t& lo) {
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(x));
+  const float rest = x - __uint_as_float(hi);
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(rest));
+}
+
+__device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+// d[16 x 8] += A[16 x K] B[K x 8],  A(r, m) = Ap[r * lda + m],  B(m, c) = Bp[m * ldb + c].
+template <int K>
+__device__ __forceinline__ void tile_mma_3xtf32(float (&d)[4], const float* Ap, int lda, const float* Bp, int ldb,
+                                                int lane) {
+  const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+  for (int k0 = 0; k0 < K; k0 += 8) {
+    const float a[4] = {Ap[g * lda + k0 + t], Ap[(g + 8) * lda + k0 + t], Ap[g * lda + k0 + t + 4],
+                        Ap[(g + 8) * lda + k0 + t + 4]};
+    const float b[2] = {Bp[(k0 + t) * ldb + g], Bp[(k0 + t + 4) * ldb + g]};
+    uint32_t ah[4], al[4], bh[2], bl[2];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) tf32_split(a[e], ah[e], al[e]);
+#pragma unroll
+    for (int e = 0; e < 2; ++e) tf32_split(b[e], bh[e], bl[e]);
+    mma_tf32(d, al, bh);
+    mma_tf32(d, ah, bl);
+    mma_tf32(d, ah, bh);
+  }
+}
+
+template <int N>
+__device__ __forceinline__ void inverse_merge_tc(const float* sL, float* sT, float* sY2, int ld, int tid) {
+  constexpr int kMT = N / 16, kNT = N / 8, kTiles = (32 / N) * kMT * kNT;  // N = 32: 8 tiles, N = 16: 4 tiles
+  const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int pr = warp / (kMT * kNT), mt = (warp / kNT) % kMT, nt = warp % kNT;
+  const int base = pr * 2 * N;
+  if (warp < kTiles) {  // Y = L21 T11
+    float d[4] = {0.f, 0.f, 0.f, 0.f};
+    tile_mma_3xtf32<N>(d, sL + (base + N + 16 * mt) * ld + base, ld, sT + base * ld + base + 8 * nt, ld, lane);
+    float* y = sY2 + pr * N * N + (16 * mt + g) * N + 8 * nt + 2 * t;
+    *reinterpret_cast<float2*>(y) = make_float2(d[0], d[1]);
+    *reinterpret_cast<float2*>(y + 8 * N) = make_float2(d[2], d[3]);
+  }
+  __syncthreads();
+  if (warp < kTiles) {  // T21 = -T22 Y
+    float d[4] = {0.f, 0.f, 0.f, 0.f};
+    tile_mma_3xtf32<N>(d, sT + (base + N + 16 * mt) * ld + base + N, ld, sY2 + pr * N * N + 8 * nt, N, lane);
+    float* o = sT + (base + N + 16 * mt + g) * ld + base + 8 * nt + 2 * t;
+    o[0] = -d[0];
+    o[1] = -d[1];
+    o[8 * ld] = -d[2];
+    o[8 * ld + 1] = -d[3];
+  }
+  __syncthreads();
+}
+
 // T = (I + L)^-1 for a 64 x 64 strictly lower triangular L (fp32, row stride ld),
 // all nthreads threads of the CTA: 4 x 4 diagonal blocks by forward substitution,
-// then four doubling steps.  sY2 is a 1024-float scratch.  Ends with a __syncthreads().
+// then four doubling steps (the last two on the tensor cores; at least 256 threads).  sY2 is a 1024-float scratch.  Ends with a __syncthreads().
 __device__ __forceinline__ void unit_lower_inverse_64(const float* sL, float* sT, float* sY2, int ld, int tid,
                                                       int nthreads) {
   for (int i = tid; i < kChunk * kChunk; i += nthreads) sT[(i >> 6) * ld + (i & 63)] = 0.f;
@@ -265,8 +330,8 @@ __device__ __forceinline__ void unit_lower_inverse_64(const float* sL, float* sT
   __syncthreads();
   inverse_merge<4>(sL, sT, sY2, ld, tid, nthreads);
   inverse_merge<8>(sL, sT, sY2, ld, tid, nthreads);
-  inverse_merge<16>(sL, sT, sY2, ld, tid, nthreads);
-  inverse_merge<32>(sL, sT, sY2, ld, tid, nthreads);
+  inverse_merge_tc<16>(sL, sT, sY2, ld, tid);
+  inverse_merge_tc<32>(sL, sT, sY2, ld, tid);
 }
 
 // tcgen05 / TMA output stage (pkda_out_tc.cu).

@@ -693,190 +693,222 @@ struct AtkBwdParams {
   float ln_x, eps;
 };
 
-// One (chunk, head) per CTA, 256 threads.  The only sequential work is two
-// 64-step first-order scans per channel (A_t forward, lam = dL/dA backward), each
-// a multiply-add per step on shared memory; everything transcendental runs as
-// vectorised elementwise passes over the [64][128] tile with all threads.
+// One (chunk, head) per CTA, 256 threads, everything in registers.  Warp w owns
+// rows 8w..8w+7 of the chunk, lane l owns channels 4l..4l+3, so a whole token row
+// lives in one warp (128-bit loads of the fp32 gradients, 64-bit loads of k) and a
+// thread holds its 8 x 4 elements for the whole kernel; all global loads are
+// issued before the first use.  Both first-order scans over the 64 rows (A_t
+// forward, lam = dL/dA backward) are blocked: a thread scans its 8 rows, the
+// eight row blocks exchange one (decay product, end value) pair through shared
+// memory, and each block continues from the carry it is owed -- every factor is a
+// product of decays <= 1, so nothing overflows.  The per-row channel sums are
+// transposed butterfly reductions (9 shuffles for 8 rows).
 //   kFinal = false: zero incoming carry, only the outgoing carry is produced.
 //   kFinal = true : incoming carry given, all gradients written.
 namespace atkb {
 constexpr int kThreads = 256;
-constexpr int kIter = kChunk * kD / 8 / kThreads;  // 8-channel pieces per thread
-constexpr int oA = 0;                              // f32 [64][kLdG]  A before each token
-constexpr int oLam = oA + kChunk * kLdG * 4;       // f32 [64][kLdG]  dA_local, then lam
-constexpr int oT2 = oLam + kChunk * kLdG * 4;      // f32 [64][kLdG]  dk without the lam term (final only)
-constexpr int kSmemLocal = oT2;
-constexpr int kSmemFinal = oT2 + kChunk * kLdG * 4;
+constexpr int kRows = 8;  // rows per warp
 }  // namespace atkb
 
+// Sums each of v[0..7] over the 32 lanes.  On return lane l holds in v[0] the
+// total of entry ((l >> 4) & 1) * 4 + ((l >> 3) & 1) * 2 + ((l >> 2) & 1).
+__device__ __forceinline__ void row_sums8(float (&v)[8], int lane) {
+  const bool hi16 = lane & 16, hi8 = lane & 8, hi4 = lane & 4;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float keep = hi16 ? v[j + 4] : v[j], send = hi16 ? v[j] : v[j + 4];
+    v[j] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+  }
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const float keep = hi8 ? v[j + 2] : v[j], send = hi8 ? v[j] : v[j + 2];
+    v[j] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+  }
+  {
+    const float keep = hi4 ? v[1] : v[0], send = hi4 ? v[0] : v[1];
+    v[0] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+  }
+  v[0] += __shfl_xor_sync(0xffffffffu, v[0], 2);
+  v[0] += __shfl_xor_sync(0xffffffffu, v[0], 1);
+}
+
 template <bool kFinal>
-__global__ void __launch_bounds__(atkb::kThreads)
+__global__ void __launch_bounds__(atkb::kThreads, 2)
 pkda_atk_bwd_kernel(const AtkBwdParams p) {
   using namespace atkb;
-  extern __shared__ __align__(128) unsigned char smem[];
-  float* sA = reinterpret_cast<float*>(smem + oA);
-  float* sLam = reinterpret_cast<float*>(smem + oLam);
-  float* sT2 = reinterpret_cast<float*>(smem + oT2);
-  __shared__ float sPd[kChunk], sBp[kChunk];
-  __shared__ float sRed[kThreads / 32];
+  __shared__ __align__(16) float sEnd[8][kD];  // per row block: end value of its zero-start scan
+  __shared__ float sDec[8];                    // per row block: product of its decays
+  __shared__ float sRed[8];
   int n, tok0, valid;
   if (!chunk_lookup(p.geo, blockIdx.x, n, tok0, valid)) return;
   const int h = blockIdx.y, H = p.geo.heads, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const size_t chh = (size_t)blockIdx.x * H + h;
-  const size_t row0 = ((size_t)tok0 * H + h) * kD;
+  const int c4 = lane << 2, r0 = warp * kRows;
+  const size_t col0 = ((size_t)tok0 * H + h) * kD + c4;
   const long gld = (long)H * kD;
-  const int c8 = (tid & 15) << 3;
 
-  // ---- all global reads of the elementwise pass in flight first
-  uint4 kraw[kIter];
-  float4 dkt0[kIter], dkt1[kIter];
+  // ---- every global read in flight first
+  uint2 kraw[kRows];
+  float4 dkt[kRows], dkr[kRows];
+  float pd[kRows], bp[kRows];
 #pragma unroll
-  for (int it = 0; it < kIter; ++it) {
-    const int r = (tid + it * kThreads) >> 4;
-    kraw[it] = make_uint4(0, 0, 0, 0);
-    dkt0[it] = dkt1[it] = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (r < valid) {
-      const size_t off = row0 + (size_t)r * gld + c8;
-      kraw[it] = *reinterpret_cast<const uint4*>(p.k + off);
-      dkt0[it] = *reinterpret_cast<const float4*>(p.dkt + off);
-      dkt1[it] = *reinterpret_cast<const float4*>(p.dkt + off + 4);
+  for (int i = 0; i < kRows; ++i) {
+    const int r = r0 + i;
+    const bool ok = r < valid;
+    kraw[i] = make_uint2(0, 0);
+    dkt[i] = dkr[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    pd[i] = 0.f;
+    bp[i] = 0.f;
+    if (ok) {
+      const size_t off = col0 + (size_t)r * gld;
+      kraw[i] = *reinterpret_cast<const uint2*>(p.k + off);
+      dkt[i] = *reinterpret_cast<const float4*>(p.dkt + off);
+      if (kFinal) dkr[i] = *reinterpret_cast<const float4*>(p.dk_read + off);
+      const size_t s = (size_t)(tok0 + r) * H + h;
+      pd[i] = p.g_atk[s];          // the log-decay for now
+      bp[i] = to_f(p.beta_atk[s]);
     }
   }
-  if (tid < kChunk) {
-    const bool ok = tid < valid;
-    const size_t s = (size_t)(tok0 + tid) * H + h;
-    sPd[tid] = ok ? __expf(p.g_atk[s]) : 1.f;
-    sBp[tid] = ok ? to_f(p.beta_atk[s]) : 0.f;
-  }
-  // k^2 per element parked in sLam for the forward scan
-#pragma unroll
-  for (int it = 0; it < kIter; ++it) {
-    const int r = (tid + it * kThreads) >> 4;
-    const uint32_t* w = reinterpret_cast<const uint32_t*>(&kraw[it]);
-    float q[8];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 x = unpack_bf16(w[j]);
-      q[2 * j] = x.x * x.x;
-      q[2 * j + 1] = x.y * x.y;
-    }
-    *reinterpret_cast<float4*>(sLam + r * kLdG + c8) = make_float4(q[0], q[1], q[2], q[3]);
-    *reinterpret_cast<float4*>(sLam + r * kLdG + c8 + 4) = make_float4(q[4], q[5], q[6], q[7]);
-  }
-  __syncthreads();
-  // ---- forward scan: A before every token
-  if (tid < kD) {
-    float A = p.a_start[chh * kD + tid];
-#pragma unroll 8
-    for (int r = 0; r < kChunk; ++r) {
-      sA[r * kLdG + tid] = A;
-      A = sPd[r] * A + sBp[r] * sLam[r * kLdG + tid];
-    }
-  }
-  __syncthreads();
-  // ---- elementwise: dA_local, and (final) the lam-free part of dk
+  const float4 a0 = *reinterpret_cast<const float4*>(p.a_start + chh * kD + c4);
+  float4 lin = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (kFinal) lin = *reinterpret_cast<const float4*>(p.lam_in + chh * kD + c4);
   const float centre = p.log_atk_scale[h];
+  float dblk = 1.f;
+#pragma unroll
+  for (int i = 0; i < kRows; ++i) {
+    pd[i] = __expf(pd[i]);  // rows past the end: exp(0) = 1, beta 0: the state passes through
+    dblk *= pd[i];
+  }
+  // ---- forward scan, pass 1: the block's end value from a zero start
+  {
+    float a[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < kRows; ++i) {
+      const float2 x = unpack_bf16(kraw[i].x), y = unpack_bf16(kraw[i].y);
+      const float kc[4] = {x.x, x.y, y.x, y.y};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) a[e] = pd[i] * a[e] + bp[i] * kc[e] * kc[e];
+    }
+    *reinterpret_cast<float4*>(&sEnd[warp][c4]) = make_float4(a[0], a[1], a[2], a[3]);
+    if (lane == 0) sDec[warp] = dblk;
+  }
+  __syncthreads();
+  float A[4] = {a0.x, a0.y, a0.z, a0.w};  // state before this block's first row
+  for (int b = 0; b < warp; ++b) {
+    const float d = sDec[b];
+    const float4 e4 = *reinterpret_cast<const float4*>(&sEnd[b][c4]);
+    A[0] = d * A[0] + e4.x; A[1] = d * A[1] + e4.y; A[2] = d * A[2] + e4.z; A[3] = d * A[3] + e4.w;
+  }
+  const float Ain[4] = {A[0], A[1], A[2], A[3]};
+  // ---- pass 2: true states; dA_local into dkt, the lam-free part of dk into dkr
   float dcacc = 0.f;
 #pragma unroll
-  for (int it = 0; it < kIter; ++it) {
-    const int r = (tid + it * kThreads) >> 4;
-    const uint32_t* w = reinterpret_cast<const uint32_t*>(&kraw[it]);
-    const float dk_t[8] = {dkt0[it].x, dkt0[it].y, dkt0[it].z, dkt0[it].w,
-                           dkt1[it].x, dkt1[it].y, dkt1[it].z, dkt1[it].w};
-    const float4 a0 = *reinterpret_cast<const float4*>(sA + r * kLdG + c8);
-    const float4 a1 = *reinterpret_cast<const float4*>(sA + r * kLdG + c8 + 4);
-    const float Ap[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-    const float dec = sPd[r], bp = sBp[r];
-    float kc[8], dal[8], t2[8];
+  for (int i = 0; i < kRows; ++i) {
+    const bool ok = r0 + i < valid;
+    const float2 x = unpack_bf16(kraw[i].x), y = unpack_bf16(kraw[i].y);
+    const float kc[4] = {x.x, x.y, y.x, y.y};
+    float* dk_t = reinterpret_cast<float*>(&dkt[i]);
+    float* dk_r = reinterpret_cast<float*>(&dkr[i]);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 x = unpack_bf16(w[j]);
-      kc[2 * j] = x.x;
-      kc[2 * j + 1] = x.y;
-    }
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float An = dec * Ap[j] + bp * kc[j] * kc[j];
+    for (int e = 0; e < 4; ++e) {
+      const float An = pd[i] * A[e] + bp[i] * kc[e] * kc[e];
       const float dev = __logf(An + p.eps) - centre;
       const float den = 1.f + fabsf(dev);
-      const float Bf = __expf(-p.ln_x * __fdividef(dev, den));
-      const float ddev = -p.ln_x * dk_t[j] * kc[j] * Bf * __fdividef(1.f, den * den);
-      dal[j] = (r < valid) ? __fdividef(ddev, An + p.eps) : 0.f;
-      t2[j] = dk_t[j] * Bf;
-      if (r < valid) dcacc -= ddev;
-    }
-    *reinterpret_cast<float4*>(sLam + r * kLdG + c8) = make_float4(dal[0], dal[1], dal[2], dal[3]);
-    *reinterpret_cast<float4*>(sLam + r * kLdG + c8 + 4) = make_float4(dal[4], dal[5], dal[6], dal[7]);
-    if (kFinal) {
-      *reinterpret_cast<float4*>(sT2 + r * kLdG + c8) = make_float4(t2[0], t2[1], t2[2], t2[3]);
-      *reinterpret_cast<float4*>(sT2 + r * kLdG + c8 + 4) = make_float4(t2[4], t2[5], t2[6], t2[7]);
+      const float rden = __fdividef(1.f, den);
+      const float Bf = __expf(-p.ln_x * dev * rden);
+      const float ddev = -p.ln_x * dk_t[e] * kc[e] * Bf * rden * rden;
+      if (kFinal) dk_r[e] += dk_t[e] * Bf;
+      dk_t[e] = ok ? __fdividef(ddev, An + p.eps) : 0.f;
+      if (ok) dcacc -= ddev;
+      A[e] = An;
     }
   }
-  __syncthreads();
-  // ---- reverse scan: lam_r = dL/dA_r (after token r), carried across tokens by the decay
-  if (tid < kD) {
-    float lam = kFinal ? p.lam_in[chh * kD + tid] : 0.f;
-#pragma unroll 8
-    for (int r = kChunk - 1; r >= 0; --r) {
-      lam += sLam[r * kLdG + tid];
-      sLam[r * kLdG + tid] = lam;
-      lam *= sPd[r];
-    }
-    if (!kFinal) p.c_loc[chh * kD + tid] = lam;
-  }
-  if (!kFinal) return;
-  __syncthreads();
-  // ---- outputs: dk, and per token the channel sums for d beta_atk and d g_atk
-  float4 dkr0[kIter], dkr1[kIter];
+  if (!kFinal) {
+    // outgoing carry = sum_r (prod_{j<=r} decay_j) dA_local_r : block partial, then blocks in order
+    float w = 1.f, part[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-  for (int it = 0; it < kIter; ++it) {
-    const int r = (tid + it * kThreads) >> 4;
-    dkr0[it] = dkr1[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int i = 0; i < kRows; ++i) {
+      w *= pd[i];
+      const float* d = reinterpret_cast<const float*>(&dkt[i]);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) part[e] += w * d[e];
+    }
+    __syncthreads();  // every warp has read the forward end values
+    *reinterpret_cast<float4*>(&sEnd[warp][c4]) = make_float4(part[0], part[1], part[2], part[3]);
+    __syncthreads();
+    if (tid < kD) {
+      float acc = 0.f, w2 = 1.f;
+#pragma unroll
+      for (int b = 0; b < 8; ++b) {
+        acc += w2 * sEnd[b][tid];
+        w2 *= sDec[b];
+      }
+      p.c_loc[chh * kD + tid] = acc;
+    }
+    return;
+  }
+  // ---- reverse scan: block-local lam from a zero incoming value (into dkt), outgoing value exchanged
+  {
+    float l[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = kRows - 1; i >= 0; --i) {
+      float* d = reinterpret_cast<float*>(&dkt[i]);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        l[e] += d[e];
+        d[e] = l[e];
+        l[e] *= pd[i];
+      }
+    }
+    __syncthreads();  // every warp has read the forward end values
+    *reinterpret_cast<float4*>(&sEnd[warp][c4]) = make_float4(l[0], l[1], l[2], l[3]);
+  }
+  __syncthreads();
+  float L[4] = {lin.x, lin.y, lin.z, lin.w};  // lam arriving at the end of this block
+  for (int b = 7; b > warp; --b) {
+    const float d = sDec[b];
+    const float4 e4 = *reinterpret_cast<const float4*>(&sEnd[b][c4]);
+    L[0] = d * L[0] + e4.x; L[1] = d * L[1] + e4.y; L[2] = d * L[2] + e4.z; L[3] = d * L[3] + e4.w;
+  }
+  // suffix[i] = product of the decays of rows i+1 .. 7 of this block
+  float suf[kRows];
+  suf[kRows - 1] = 1.f;
+#pragma unroll
+  for (int i = kRows - 2; i >= 0; --i) suf[i] = suf[i + 1] * pd[i + 1];
+  // ---- pass 3: outputs, walking the rows forward again for the state before each row
+  float x1[kRows], x2[kRows];
+  A[0] = Ain[0]; A[1] = Ain[1]; A[2] = Ain[2]; A[3] = Ain[3];
+#pragma unroll
+  for (int i = 0; i < kRows; ++i) {
+    const int r = r0 + i;
+    const float2 x = unpack_bf16(kraw[i].x), y = unpack_bf16(kraw[i].y);
+    const float kc[4] = {x.x, x.y, y.x, y.y};
+    const float* ll = reinterpret_cast<const float*>(&dkt[i]);
+    const float* t2 = reinterpret_cast<const float*>(&dkr[i]);
+    float o[4];
+    x1[i] = 0.f;
+    x2[i] = 0.f;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float lam = ll[e] + suf[i] * L[e];
+      o[e] = t2[e] + 2.f * lam * bp[i] * kc[e];
+      const float k2 = kc[e] * kc[e];
+      x1[i] += lam * k2;
+      x2[i] += lam * A[e];
+      A[e] = pd[i] * A[e] + bp[i] * k2;
+    }
+    x2[i] *= pd[i];
+    if (r < valid)
+      *reinterpret_cast<uint2*>(p.dk + col0 + (size_t)r * gld) = make_uint2(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]));
+  }
+  row_sums8(x1, lane);
+  row_sums8(x2, lane);
+  if ((lane & 3) == 0) {
+    const int r = r0 + ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
     if (r < valid) {
-      const size_t off = row0 + (size_t)r * gld + c8;
-      dkr0[it] = *reinterpret_cast<const float4*>(p.dk_read + off);
-      dkr1[it] = *reinterpret_cast<const float4*>(p.dk_read + off + 4);
-    }
-  }
-#pragma unroll
-  for (int it = 0; it < kIter; ++it) {
-    const int r = (tid + it * kThreads) >> 4;
-    const uint32_t* w = reinterpret_cast<const uint32_t*>(&kraw[it]);
-    const float dkr[8] = {dkr0[it].x, dkr0[it].y, dkr0[it].z, dkr0[it].w,
-                          dkr1[it].x, dkr1[it].y, dkr1[it].z, dkr1[it].w};
-    const float4 l0 = *reinterpret_cast<const float4*>(sLam + r * kLdG + c8);
-    const float4 l1 = *reinterpret_cast<const float4*>(sLam + r * kLdG + c8 + 4);
-    const float4 a0 = *reinterpret_cast<const float4*>(sA + r * kLdG + c8);
-    const float4 a1 = *reinterpret_cast<const float4*>(sA + r * kLdG + c8 + 4);
-    const float4 u0 = *reinterpret_cast<const float4*>(sT2 + r * kLdG + c8);
-    const float4 u1 = *reinterpret_cast<const float4*>(sT2 + r * kLdG + c8 + 4);
-    const float lam[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
-    const float Ap[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-    const float t2[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
-    const float dec = sPd[r], bp = sBp[r];
-    float x1 = 0.f, x2 = 0.f;
-    uint4 outv;
-    uint32_t* o32 = reinterpret_cast<uint32_t*>(&outv);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 kc = unpack_bf16(w[j]);
-      const float d0 = dkr[2 * j] + t2[2 * j] + 2.f * lam[2 * j] * bp * kc.x;
-      const float d1 = dkr[2 * j + 1] + t2[2 * j + 1] + 2.f * lam[2 * j + 1] * bp * kc.y;
-      o32[j] = pack_bf16(d0, d1);
-      x1 += lam[2 * j] * kc.x * kc.x + lam[2 * j + 1] * kc.y * kc.y;
-      x2 += lam[2 * j] * Ap[2 * j] + lam[2 * j + 1] * Ap[2 * j + 1];
-    }
-    if (r < valid) *reinterpret_cast<uint4*>(p.dk + row0 + (size_t)r * gld + c8) = outv;
-    // 16 consecutive lanes share a token: fixed-order shuffle reduction
-#pragma unroll
-    for (int o = 8; o >= 1; o >>= 1) {
-      x1 += __shfl_xor_sync(0xffffffffu, x1, o);
-      x2 += __shfl_xor_sync(0xffffffffu, x2, o);
-    }
-    if ((tid & 15) == 0 && r < valid) {
       const size_t s = (size_t)(tok0 + r) * H + h;
-      p.dbeta_atk[s] = __float2bfloat16(x1);
-      p.dg_atk[s] = x2 * dec;
+      p.dbeta_atk[s] = __float2bfloat16(x1[0]);
+      p.dg_atk[s] = x2[0];
     }
   }
 #pragma unroll
@@ -1061,16 +1093,14 @@ int chunk_bwd(const pkda_chunk_bwd_args* a, cudaStream_t st) {
   ap.dk = static_cast<bf16*>(a->dk); ap.dg_atk = a->dg_atk; ap.dbeta_atk = static_cast<bf16*>(a->dbeta_atk);
   ap.partC = ws.partC; ap.ln_x = logf(p.squash_x); ap.eps = p.squash_eps;
   begin_stage(kStageAtkBwdLocal, st);
-  if (!set_smem(pkda_atk_bwd_kernel<false>, atkb::kSmemLocal)) return PKDA_ERR_LAUNCH;
-  pkda_atk_bwd_kernel<false><<<gridc, atkb::kThreads, atkb::kSmemLocal, st>>>(ap);
+  pkda_atk_bwd_kernel<false><<<gridc, atkb::kThreads, 0, st>>>(ap);
   PKDA_CHECK_LAUNCH();
   begin_stage(kStageAtkBwdCarry, st);
   pkda_atk_bwd_carry_kernel<<<dim3(p.n_seqs, p.heads), kD, 0, st>>>(geo, ws.c_loc, a->sa_atk, ws.lam_in,
                                                                    a->d_initial_A_state);
   PKDA_CHECK_LAUNCH();
   begin_stage(kStageAtkBwdFinal, st);
-  if (!set_smem(pkda_atk_bwd_kernel<true>, atkb::kSmemFinal)) return PKDA_ERR_LAUNCH;
-  pkda_atk_bwd_kernel<true><<<gridc, atkb::kThreads, atkb::kSmemFinal, st>>>(ap);
+  pkda_atk_bwd_kernel<true><<<gridc, atkb::kThreads, 0, st>>>(ap);
   PKDA_CHECK_LAUNCH();
   begin_stage(kStageParamReduce, st);
   pkda_param_reduce_kernel<<<p.heads, kD, 0, st>>>(geo, ws.partA, ws.partB, ws.partC, a->dA_log, a->ddt_bias,

@@ -239,6 +239,11 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool pr
   int bytes = pred ? 16 : 0;  // src-size 0 => zero fill
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" :: "r"(s), "l"(gmem), "r"(bytes));
 }
+__device__ __forceinline__ void cp_async4(void* smem, const void* gmem, bool pred) {
+  uint32_t s = smem_u32(smem);
+  int bytes = pred ? 4 : 0;
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" :: "r"(s), "l"(gmem), "r"(bytes));
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N> __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;\n" :: "n"(N));

@@ -5,10 +5,13 @@
 //   dyh = dy * w * sig,  xh = x * rstd,
 //   dx = rstd * (dyh - xh * mean_c(dyh * xh)),  dgate = dy * xh * w * sig * (1 - sig),
 //   dw = sum over rows of dy * xh * sig.
-// Streaming kernels: a row of `dim` channels is held by dim/8 adjacent lanes
-// (128-bit loads and stores for bf16), the row statistics are shuffle reductions,
-// each thread keeps several rows in flight, and the weight gradient is reduced in
-// a fixed order (registers -> shared memory -> one partial per CTA -> second kernel).
+// Streaming kernels.  A row of `dim` channels is held by dim/8 adjacent lanes; a
+// thread's 8 channels of a row are one "unit".  Every thread streams its own units
+// through a private ring of cp.async stages in shared memory (it only ever reads
+// back what it copied itself, so the ring needs no barrier), which keeps several
+// hundred bytes per thread in flight without holding them in registers.  Row
+// statistics are shuffle reductions; the weight gradient is reduced in a fixed order
+// (registers -> shared memory -> one partial per CTA -> second kernel).
 #include "pkda_common.cuh"
 #include "pkda_launch.h"
 
@@ -17,7 +20,14 @@ namespace pkda {
 namespace ng {
 constexpr int kThreads = 256;
 constexpr int kVec = 8;
-constexpr int kRowsInFlight = 4;  // rows per thread whose loads are issued together
+constexpr int kStages = 4;
+constexpr int kUnits = 2;  // units (rows) per thread and stage
+template <typename T> __host__ __device__ constexpr int unit_bytes() { return kVec * (int)sizeof(T); }
+// ring: [stage][tensor][unit][thread] unit_bytes, then (backward) [stage][unit][thread] floats for rstd
+template <typename T> __host__ __device__ constexpr int fwd_smem() { return kStages * 2 * kUnits * kThreads * unit_bytes<T>(); }
+template <typename T> __host__ __device__ constexpr int bwd_smem() {
+  return kStages * 3 * kUnits * kThreads * unit_bytes<T>() + kStages * kUnits * kThreads * 4;
+}
 }  // namespace ng
 
 struct NormGateParams {
@@ -66,46 +76,71 @@ template <> struct Vec8<float> {
 };
 
 __device__ __forceinline__ float lane_group_sum(float v, int lanes) {
-  for (int o = lanes >> 1; o >= 1; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+#pragma unroll
+  for (int o = 16; o >= 1; o >>= 1)
+    if (lanes > o) v += __shfl_xor_sync(0xffffffffu, v, o);  // uniform predicate, no loop control
   return v;
 }
 
-// Rows are dealt to (CTA, row slot) in a grid-stride loop; a CTA iteration covers
-// kRowsInFlight * (kThreads / lanes) rows.
+// One unit (8 channels of T) global -> this thread's slot of the ring.
+template <typename T>
+__device__ __forceinline__ void copy_unit(T* slot, const T* g, bool ok) {
+  cp_async16(slot, ok ? g : g, ok);
+  if (sizeof(T) == 4) cp_async16(slot + 4, ok ? g + 4 : g, ok);
+}
+
+// Iteration `it` of a CTA covers rows  (it * gridDim.x + blockIdx.x) * slots * kUnits + u * slots + slot.
 template <typename T>
 __global__ void __launch_bounds__(ng::kThreads)
 pkda_norm_gate_fwd_kernel(const NormGateParams p) {
   using namespace ng;
-  const int lane_in_row = threadIdx.x % p.lanes, slot = threadIdx.x / p.lanes;
-  const int slots = kThreads / p.lanes;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  T* ring = reinterpret_cast<T*>(smem_raw);
+  const int tid = threadIdx.x;
+  const int lane_in_row = tid % p.lanes, slot = tid / p.lanes, slots = kThreads / p.lanes;
   const int c0 = lane_in_row * kVec;
+  const long long per_iter = (long long)slots * kUnits;
+  const long long n_iter_all = (p.rows + per_iter - 1) / per_iter;
+  const int n_iter = (int)((n_iter_all - blockIdx.x + gridDim.x - 1) / gridDim.x);  // iterations of this CTA
   float w[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) w[j] = p.w[c0 + j];
-  const long long per_iter = (long long)slots * kRowsInFlight;
-  for (long long base = (long long)blockIdx.x * per_iter; base < p.rows; base += (long long)gridDim.x * per_iter) {
-    float x[kRowsInFlight][8], g[kRowsInFlight][8];
+  auto row_of = [&](int it, int u) { return ((long long)it * gridDim.x + blockIdx.x) * per_iter + (long long)u * slots + slot; };
+  auto slot_ptr = [&](int stage, int tensor, int u) {
+    return ring + ((size_t)((stage * 2 + tensor) * kUnits + u) * kThreads + tid) * kVec;
+  };
+  auto issue = [&](int it) {
+    if (it < n_iter) {
+      const int stage = it % kStages;
 #pragma unroll
-    for (int u = 0; u < kRowsInFlight; ++u) {
-      const long long r = base + (long long)u * slots + slot;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) x[u][j] = g[u][j] = 0.f;
-      if (r < p.rows) {
-        Vec8<T>::load(static_cast<const T*>(p.x) + r * p.dim + c0, x[u]);
-        Vec8<T>::load(static_cast<const T*>(p.gate) + r * p.dim + c0, g[u]);
+      for (int u = 0; u < kUnits; ++u) {
+        const long long r = row_of(it, u);
+        const bool ok = r < p.rows;
+        const size_t off = ok ? (size_t)r * p.dim + c0 : 0;
+        copy_unit(slot_ptr(stage, 0, u), static_cast<const T*>(p.x) + off, ok);
+        copy_unit(slot_ptr(stage, 1, u), static_cast<const T*>(p.gate) + off, ok);
       }
     }
+    cp_async_commit();
+  };
 #pragma unroll
-    for (int u = 0; u < kRowsInFlight; ++u) {
-      const long long r = base + (long long)u * slots + slot;
-      float ss = 0.f;
+  for (int s = 0; s < kStages - 1; ++s) issue(s);
+  for (int it = 0; it < n_iter; ++it) {
+    issue(it + kStages - 1);
+    cp_async_wait<kStages - 1>();
+    const int stage = it % kStages;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) ss += x[u][j] * x[u][j];
+    for (int u = 0; u < kUnits; ++u) {
+      const long long r = row_of(it, u);
+      float x[8], g[8], y[8], ss = 0.f;
+      Vec8<T>::load(slot_ptr(stage, 0, u), x);
+      Vec8<T>::load(slot_ptr(stage, 1, u), g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += x[j] * x[j];
       ss = lane_group_sum(ss, p.lanes);
       const float rstd = rsqrtf(ss * p.inv_dim + p.eps);
-      float y[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) y[j] = x[u][j] * rstd * w[j] * Vec8<T>::sigmoid(g[u][j]);
+      for (int j = 0; j < 8; ++j) y[j] = x[j] * rstd * w[j] * Vec8<T>::sigmoid(g[j]);
       if (r < p.rows) {
         Vec8<T>::store(static_cast<T*>(p.y) + r * p.dim + c0, y);
         if (lane_in_row == 0) p.rstd[r] = rstd;
@@ -118,87 +153,128 @@ template <typename T>
 __global__ void __launch_bounds__(ng::kThreads)
 pkda_norm_gate_bwd_kernel(const NormGateParams p) {
   using namespace ng;
-  __shared__ float sPart[kThreads][kVec + 1];
-  const int lane_in_row = threadIdx.x % p.lanes, slot = threadIdx.x / p.lanes;
-  const int slots = kThreads / p.lanes;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  T* ring = reinterpret_cast<T*>(smem_raw);
+  float* ring_r = reinterpret_cast<float*>(smem_raw + (size_t)kStages * 3 * kUnits * kThreads * unit_bytes<T>());
+  const int tid = threadIdx.x;
+  const int lane_in_row = tid % p.lanes, slot = tid / p.lanes, slots = kThreads / p.lanes;
   const int c0 = lane_in_row * kVec;
+  const long long per_iter = (long long)slots * kUnits;
+  const long long n_iter_all = (p.rows + per_iter - 1) / per_iter;
+  const int n_iter = (int)((n_iter_all - blockIdx.x + gridDim.x - 1) / gridDim.x);
   float w[8], dwacc[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     w[j] = p.w[c0 + j];
     dwacc[j] = 0.f;
   }
-  constexpr int kInFlight = 2;
-  const long long per_iter = (long long)slots * kInFlight;
-  for (long long base = (long long)blockIdx.x * per_iter; base < p.rows; base += (long long)gridDim.x * per_iter) {
-    float x[kInFlight][8], g[kInFlight][8], dy[kInFlight][8], rs[kInFlight];
+  auto row_of = [&](int it, int u) { return ((long long)it * gridDim.x + blockIdx.x) * per_iter + (long long)u * slots + slot; };
+  auto slot_ptr = [&](int stage, int tensor, int u) {
+    return ring + ((size_t)((stage * 3 + tensor) * kUnits + u) * kThreads + tid) * kVec;
+  };
+  auto issue = [&](int it) {
+    if (it < n_iter) {
+      const int stage = it % kStages;
 #pragma unroll
-    for (int u = 0; u < kInFlight; ++u) {
-      const long long r = base + (long long)u * slots + slot;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) x[u][j] = g[u][j] = dy[u][j] = 0.f;
-      rs[u] = 0.f;
-      if (r < p.rows) {
-        Vec8<T>::load(static_cast<const T*>(p.x) + r * p.dim + c0, x[u]);
-        Vec8<T>::load(static_cast<const T*>(p.gate) + r * p.dim + c0, g[u]);
-        Vec8<T>::load(static_cast<const T*>(p.dy) + r * p.dim + c0, dy[u]);
-        rs[u] = p.rstd[r];
+      for (int u = 0; u < kUnits; ++u) {
+        const long long r = row_of(it, u);
+        const bool ok = r < p.rows;
+        const size_t off = ok ? (size_t)r * p.dim + c0 : 0;
+        copy_unit(slot_ptr(stage, 0, u), static_cast<const T*>(p.x) + off, ok);
+        copy_unit(slot_ptr(stage, 1, u), static_cast<const T*>(p.gate) + off, ok);
+        copy_unit(slot_ptr(stage, 2, u), static_cast<const T*>(p.dy) + off, ok);
+        cp_async4(ring_r + (stage * kUnits + u) * kThreads + tid, p.rstd + (ok ? r : 0), ok);
       }
     }
+    cp_async_commit();
+  };
 #pragma unroll
-    for (int u = 0; u < kInFlight; ++u) {
-      const long long r = base + (long long)u * slots + slot;
-      float xh[8], dyh[8], sg[8], dot = 0.f;
+  for (int s = 0; s < kStages - 1; ++s) issue(s);
+  for (int it = 0; it < n_iter; ++it) {
+    issue(it + kStages - 1);
+    cp_async_wait<kStages - 1>();
+    const int stage = it % kStages;
+#pragma unroll
+    for (int u = 0; u < kUnits; ++u) {
+      const long long r = row_of(it, u);
+      float x[8], g[8], dy[8], dx[8], dg[8], dot = 0.f;
+      Vec8<T>::load(slot_ptr(stage, 0, u), x);
+      Vec8<T>::load(slot_ptr(stage, 1, u), g);
+      Vec8<T>::load(slot_ptr(stage, 2, u), dy);
+      const float rs = ring_r[(stage * kUnits + u) * kThreads + tid];
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        sg[j] = Vec8<T>::sigmoid(g[u][j]);
-        xh[j] = x[u][j] * rs[u];
-        dyh[j] = dy[u][j] * w[j] * sg[j];
-        dot += dyh[j] * xh[j];
-        dwacc[j] += dy[u][j] * xh[j] * sg[j];
+        const float sg = Vec8<T>::sigmoid(g[j]);
+        const float xh = x[j] * rs;
+        const float t = dy[j] * xh * sg;   // dy * xh * sig
+        dwacc[j] += t;
+        dot += t * w[j];                   // dyh * xh
+        dg[j] = t * w[j] * (1.f - sg);
+        dx[j] = dy[j] * w[j] * sg;         // dyh
+        x[j] = xh;
       }
       dot = lane_group_sum(dot, p.lanes) * p.inv_dim;
-      float dx[8], dg[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        dx[j] = rs[u] * (dyh[j] - xh[j] * dot);
-        dg[j] = dy[u][j] * xh[j] * w[j] * sg[j] * (1.f - sg[j]);
-      }
+      for (int j = 0; j < 8; ++j) dx[j] = rs * (dx[j] - x[j] * dot);
       if (r < p.rows) {
         Vec8<T>::store(static_cast<T*>(p.dx) + r * p.dim + c0, dx);
         Vec8<T>::store(static_cast<T*>(p.dgate) + r * p.dim + c0, dg);
       }
     }
   }
-#pragma unroll
-  for (int j = 0; j < 8; ++j) sPart[threadIdx.x][j] = dwacc[j];
+  cp_async_wait<0>();
   __syncthreads();
-  if (threadIdx.x < p.dim) {
-    const int c = threadIdx.x, lr = c / kVec, j = c % kVec;
+  float* sPart = reinterpret_cast<float*>(smem_raw);  // [kThreads][kVec + 1]
+#pragma unroll
+  for (int j = 0; j < 8; ++j) sPart[tid * (kVec + 1) + j] = dwacc[j];
+  __syncthreads();
+  if (tid < p.dim) {
+    const int lr = tid / kVec, j = tid % kVec;
     float a = 0.f;
-    for (int s = 0; s < slots; ++s) a += sPart[s * p.lanes + lr][j];
-    p.part[(size_t)blockIdx.x * p.dim + c] = a;
+    for (int s = 0; s < slots; ++s) a += sPart[(s * p.lanes + lr) * (kVec + 1) + j];
+    p.part[(size_t)blockIdx.x * p.dim + tid] = a;
   }
 }
 
-__global__ void pkda_norm_gate_dw_kernel(const float* part, float* dw, int dim, int groups) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= dim) return;
+// Sums the per-CTA partials: thread (sub, c) adds every kSub-th partial of channel c,
+// then the kSub sub-sums are added in order.
+__global__ void __launch_bounds__(1024) pkda_norm_gate_dw_kernel(const float* part, float* dw, int dim, int groups) {
+  __shared__ float sSub[1024];
+  const int c = threadIdx.x % dim, sub = threadIdx.x / dim, nsub = 1024 / dim;
   float a = 0.f;
-  for (int g = 0; g < groups; ++g) a += part[(size_t)g * dim + c];
-  dw[c] = a;
+  for (int g = sub; g < groups; g += nsub) a += part[(size_t)g * dim + c];
+  sSub[threadIdx.x] = a;
+  __syncthreads();
+  if (sub == 0) {
+    float t = 0.f;
+    for (int s2 = 0; s2 < nsub; ++s2) t += sSub[s2 * dim + c];
+    dw[c] = t;
+  }
 }
 
 // ------------------------------------------------------------------ host side
-static int ng_grid(const pkda_norm_gate_args& a, int in_flight) {
-  const int lanes = a.dim / ng::kVec;
-  const long long per_iter = (long long)(ng::kThreads / lanes) * in_flight;
-  const long long want = (a.rows + per_iter - 1) / per_iter;
-  int sms = 148;
-  int dev = 0;
+static int sm_count() {
+  int sms = 148, dev = 0;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const long long cap = (long long)sms * 8;
+  return sms;
+}
+
+// Persistent grid: as many CTAs as are resident at once (never more than 8 per SM,
+// the bound the backward's partial buffer is sized for), fewer for small inputs.
+template <typename K> static int ng_grid(const pkda_norm_gate_args& a, K kernel, int smem) {
+  const int lanes = a.dim / ng::kVec;
+  const long long per_iter = (long long)(ng::kThreads / lanes) * ng::kUnits;
+  const long long want = (a.rows + per_iter - 1) / per_iter;
+  int per_sm = 1;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, ng::kThreads, smem) != cudaSuccess || per_sm < 1)
+    per_sm = 1;
+  if (per_sm > 8) per_sm = 8;
+  const long long cap = (long long)sm_count() * per_sm;
   return (int)(want < 1 ? 1 : (want < cap ? want : cap));
+}
+
+template <typename K> static bool ng_allow_smem(K kernel, int bytes) {
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess;
 }
 
 static int ng_check(const pkda_norm_gate_args& a, NormGateParams& p) {
@@ -218,10 +294,19 @@ int norm_gate_fwd(const pkda_norm_gate_args* a, cudaStream_t st) {
   if (a->rows == 0) return PKDA_OK;
   if (!a->x || !a->gate || !a->weight || !a->y || !a->rstd) return PKDA_ERR_NULL;
   if (!ng_aligned(a->x) || !ng_aligned(a->gate) || !ng_aligned(a->y)) return PKDA_ERR_ALIGN;
-  const int grid = ng_grid(*a, ng::kRowsInFlight);
-  begin_stage(kStageNormGateFwd, st);
-  if (a->dtype == PKDA_BF16) pkda_norm_gate_fwd_kernel<bf16><<<grid, ng::kThreads, 0, st>>>(p);
-  else pkda_norm_gate_fwd_kernel<float><<<grid, ng::kThreads, 0, st>>>(p);
+  if (a->dtype == PKDA_BF16) {
+    constexpr int smem = ng::fwd_smem<bf16>();
+    if (!ng_allow_smem(pkda_norm_gate_fwd_kernel<bf16>, smem)) return PKDA_ERR_LAUNCH;
+    const int grid = ng_grid(*a, pkda_norm_gate_fwd_kernel<bf16>, smem);
+    begin_stage(kStageNormGateFwd, st);
+    pkda_norm_gate_fwd_kernel<bf16><<<grid, ng::kThreads, smem, st>>>(p);
+  } else {
+    constexpr int smem = ng::fwd_smem<float>();
+    if (!ng_allow_smem(pkda_norm_gate_fwd_kernel<float>, smem)) return PKDA_ERR_LAUNCH;
+    const int grid = ng_grid(*a, pkda_norm_gate_fwd_kernel<float>, smem);
+    begin_stage(kStageNormGateFwd, st);
+    pkda_norm_gate_fwd_kernel<float><<<grid, ng::kThreads, smem, st>>>(p);
+  }
   end_stage(st);
   return cudaGetLastError() == cudaSuccess ? PKDA_OK : PKDA_ERR_LAUNCH;
 }
@@ -229,9 +314,7 @@ int norm_gate_fwd(const pkda_norm_gate_args* a, cudaStream_t st) {
 size_t norm_gate_bwd_workspace(const pkda_norm_gate_args& a) {
   NormGateParams p;
   if (ng_check(a, p) != PKDA_OK) return 0;
-  int sms = 148, dev = 0;
-  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  return align_up((size_t)sms * 8 * a.dim * sizeof(float));  // the grid never exceeds 8 CTAs per SM
+  return align_up((size_t)sm_count() * 8 * a.dim * sizeof(float));  // the grid never exceeds 8 CTAs per SM
 }
 
 int norm_gate_bwd(const pkda_norm_gate_args* a, cudaStream_t st) {
@@ -246,13 +329,23 @@ int norm_gate_bwd(const pkda_norm_gate_args* a, cudaStream_t st) {
     return PKDA_ERR_ALIGN;
   if (!a->workspace || a->workspace_bytes < norm_gate_bwd_workspace(*a)) return PKDA_ERR_WORKSPACE;
   p.part = static_cast<float*>(a->workspace);
-  const int grid = ng_grid(*a, 2);
-  begin_stage(kStageNormGateBwd, st);
-  if (a->dtype == PKDA_BF16) pkda_norm_gate_bwd_kernel<bf16><<<grid, ng::kThreads, 0, st>>>(p);
-  else pkda_norm_gate_bwd_kernel<float><<<grid, ng::kThreads, 0, st>>>(p);
+  int grid = 1;
+  if (a->dtype == PKDA_BF16) {
+    constexpr int smem = ng::bwd_smem<bf16>();
+    if (!ng_allow_smem(pkda_norm_gate_bwd_kernel<bf16>, smem)) return PKDA_ERR_LAUNCH;
+    grid = ng_grid(*a, pkda_norm_gate_bwd_kernel<bf16>, smem);
+    begin_stage(kStageNormGateBwd, st);
+    pkda_norm_gate_bwd_kernel<bf16><<<grid, ng::kThreads, smem, st>>>(p);
+  } else {
+    constexpr int smem = ng::bwd_smem<float>();
+    if (!ng_allow_smem(pkda_norm_gate_bwd_kernel<float>, smem)) return PKDA_ERR_LAUNCH;
+    grid = ng_grid(*a, pkda_norm_gate_bwd_kernel<float>, smem);
+    begin_stage(kStageNormGateBwd, st);
+    pkda_norm_gate_bwd_kernel<float><<<grid, ng::kThreads, smem, st>>>(p);
+  }
   end_stage(st);
   begin_stage(kStageNormGateDw, st);
-  pkda_norm_gate_dw_kernel<<<(a->dim + 127) / 128, 128, 0, st>>>(p.part, a->dweight, a->dim, grid);
+  pkda_norm_gate_dw_kernel<<<1, 1024, 0, st>>>(p.part, a->dweight, a->dim, grid);
   end_stage(st);
   return cudaGetLastError() == cudaSuccess ? PKDA_OK : PKDA_ERR_LAUNCH;
 }

@@ -247,7 +247,7 @@ int pkda_stage_timing_read(float* ms, int* counts, int n_stages);
  *   q,k,v   [batch][seq_len][channels / 3]      activation dtype
  * Tokens before the start of a row read as zero (callers that continue a cached
  * row prepend the taps-1 previous projections as the reference does,
- * pkda.py:239-260).  head_dim must be a power of two in 4..128 and divide the slab
+ * pkda.py:239-260).  head_dim must be a power of two in 8..128 and divide the slab
  * width; norm_channels must be a multiple of head_dim.
  */
 typedef struct pkda_qkv_conv_args {

@@ -46,7 +46,7 @@ CONV_SHAPES = [
     # B, T, H, D, taps  (ragged strips, channel counts off the 256-channel CTA width, every tap count)
     (2, 200, 4, 128, 4),
     (3, 67, 3, 32, 4),
-    (1, 64, 1, 4, 1),
+    (1, 64, 1, 8, 1),
     (2, 129, 5, 16, 2),
     (1, 3, 2, 64, 3),
     (4, 1, 2, 128, 4),

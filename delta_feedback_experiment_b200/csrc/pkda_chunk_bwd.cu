@@ -14,6 +14,7 @@
 //   -> intra_bwd (per chunk) -> atk_bwd local / carry / final (preconditioner
 //   reverse scan, chunk-parallel) -> param_reduce.
 #include "pkda_chunk.cuh"
+#include "pkda_tc.cuh"
 
 namespace pkda {
 
@@ -208,6 +209,16 @@ struct IntraBwdParams {
   float *partA, *partB;
   float scale;
   int direct_cap;
+  int use_tma;   // the five phase-A tiles of full chunks arrive by TMA (tensor maps valid)
+  int* status;   // set to 1 if a bounded wait gives up
+};
+
+// Tensor maps of the phase-A tiles.  Each box is wider than the data it needs (136
+// or 72 columns for 128 or 64) so that the rows land in shared memory with the
+// padded pitch the ldmatrix reads want; the surplus columns are the neighbouring
+// head's data or, past the end of a row, zero fill.
+struct IntraBwdMaps {
+  CUtensorMap d_o, dF, h, dh, Akk;
 };
 
 namespace ib {
@@ -225,7 +236,12 @@ constexpr int oFac = oDM + kChunk * kLdC * 2; // f32 [64][kLdG]
 constexpr int oSmall = oFac + kChunk * kLdG * 4;
 // small: beta[64] db[64] hdh[128] gcv[128] col[4][128] rb[4][64] red[16] bias[128] warpmax[4][6]
 constexpr int kSmallFloats = 64 + 64 + 128 + 128 + 512 + 256 + 16 + 128 + 24;
-constexpr int kSmem = oSmall + kSmallFloats * 4;
+constexpr int oBar = oSmall + kSmallFloats * 4;  // one mbarrier
+constexpr int kSmem = oBar + 16;
+constexpr uint32_t kTmaBytes = (3 * kChunk + 2 * kD) * kLdD * 2 - kChunk * kLdD * 2 + kChunk * kLdC * 2;
+static_assert(kTmaBytes == (2 * kChunk + 2 * kD) * kLdD * 2 + kChunk * kLdC * 2, "dO, dF, S0, dS1 and Tm tiles");
+static_assert(oBar % 8 == 0 && oA1 % 128 == 0 && oTm % 128 == 0 && oDE % 128 == 0 && oFac % 128 == 0,
+              "TMA destinations and the mbarrier must be aligned");
 static_assert(oDR + kTileBytes <= oDP, "phase-A tiles must not reach the pair-gradient tiles");
 static_assert(oDE + kD * kLdD * 2 <= oDP, "dS1 tile must fit");
 }  // namespace ib
@@ -254,7 +270,7 @@ __device__ __forceinline__ void epi_add(float (&acc)[1][4][4], float (&dG)[1][4]
 }
 
 __global__ void __launch_bounds__(ib::kThreads, 1)
-pkda_intra_bwd_kernel(const IntraBwdParams p) {
+pkda_intra_bwd_kernel(const IntraBwdParams p, const __grid_constant__ IntraBwdMaps maps) {
   using namespace ib;
   extern __shared__ __align__(128) unsigned char smem[];
   PKDA_PHASE(0);
@@ -292,14 +308,32 @@ pkda_intra_bwd_kernel(const IntraBwdParams p) {
   const long cld = (long)H * kChunk;
 
   // ================= phase A: state-coupled terms =================
-  tile_load_async(sdO, kLdD, p.d_o + row0, gld, kChunk, kD, valid, kThreads);
-  tile_load_async(sS0, kLdD, p.h + chh * kD * kD, kD, kD, kD, kD, kThreads);
-  tile_load_async(sTm, kLdC, p.Akk + crow0, cld, kChunk, kChunk, valid, kThreads);
-  tile_load_async(sdE, kLdD, p.dF + row0, gld, kChunk, kD, valid, kThreads);  // raw dF; scaled by beta below
   // dS1 waits in the (not yet used) level-factor array until the dkg product
   bf16* sdSC = reinterpret_cast<bf16*>(smem + oFac);
-  tile_load_async(sdSC, kLdD, p.dh + chh * kD * kD, kD, kD, kD, kD, kThreads);
-  cp_async_commit();
+  // Full chunks: one thread starts five TMA tile copies and everybody goes on to the
+  // gate computation while they land.  Ragged chunks (rows past the sequence end must
+  // read as zero) take 16-byte cp.async copies.
+  const bool by_tma = p.use_tma && valid == kChunk;
+  const uint32_t bar = smem_u32(smem + oBar);
+  if (by_tma) {
+    if (tid == 0) {
+      tc::mbar_init(bar, 1);
+      tc::fence_barrier_init();
+      tc::mbar_expect_tx(bar, kTmaBytes);
+      tc::tma_load_2d(smem_u32(sdO), &maps.d_o, bar, h * kD, tok0);
+      tc::tma_load_2d(smem_u32(sS0), &maps.h, bar, 0, (int)(chh * kD));
+      tc::tma_load_2d(smem_u32(sTm), &maps.Akk, bar, h * kChunk, tok0);
+      tc::tma_load_2d(smem_u32(sdE), &maps.dF, bar, h * kD, tok0);  // raw dF; scaled by beta below
+      tc::tma_load_2d(smem_u32(sdSC), &maps.dh, bar, 0, (int)(chh * kD));
+    }
+  } else {
+    tile_load_async(sdO, kLdD, p.d_o + row0, gld, kChunk, kD, valid, kThreads);
+    tile_load_async(sS0, kLdD, p.h + chh * kD * kD, kD, kD, kD, kD, kThreads);
+    tile_load_async(sTm, kLdC, p.Akk + crow0, cld, kChunk, kChunk, valid, kThreads);
+    tile_load_async(sdE, kLdD, p.dF + row0, gld, kChunk, kD, valid, kThreads);
+    tile_load_async(sdSC, kLdD, p.dh + chh * kD * kD, kD, kD, kD, kD, kThreads);
+    cp_async_commit();
+  }
   if (tid < kChunk) sBeta[tid] = p.beta_c[chh * kChunk + tid];
   if (tid < kD) sGcv[tid] = p.gc[chh * kD + tid];
   else if (tid < 2 * kD) sBias[tid - kD] = p.dt_bias[h * kD + tid - kD];
@@ -318,7 +352,11 @@ pkda_intra_bwd_kernel(const IntraBwdParams p) {
       if (lane == 0) sWarpMax[warp * 6 + e] = dmax[e];
     }
   }
-  cp_async_wait<0>();
+  if (by_tma) {
+    if (!tc::mbar_wait(bar, 0) && tid == 0) atomicExch(p.status, 1);  // gave up: flag it, results are void
+  } else {
+    cp_async_wait<0>();
+  }
   __syncthreads(); PKDA_PHASE(3);
   // dE = beta * dF in place;  hdh[k] = sum_v S0[k][v] dS1[k][v] (four threads per state row)
   for (int i = tid; i < kChunk * kD / 8; i += kThreads) {
@@ -732,46 +770,96 @@ __device__ __forceinline__ void row_sums8(float (&v)[8], int lane) {
   v[0] += __shfl_xor_sync(0xffffffffu, v[0], 1);
 }
 
+// Thread-private prefetch slots in dynamic shared memory (a thread only reads back
+// what it copied itself, so they need no barrier): per row k (8 B), dkt (16 B),
+// dk_read (16 B, final pass only), the row's log-decay (4 B); per tile the chunk's
+// entry state and incoming carry (16 B each).
+namespace atkb {
+template <bool kFinal> __host__ __device__ constexpr int slot_bytes() {
+  return kRows * (8 + 16 + (kFinal ? 16 : 0) + 4) + 16 + (kFinal ? 16 : 0);
+}
+template <bool kFinal> __host__ __device__ constexpr int smem_bytes() { return kThreads * slot_bytes<kFinal>(); }
+}  // namespace atkb
+
 template <bool kFinal>
 __global__ void __launch_bounds__(atkb::kThreads, 2)
-pkda_atk_bwd_kernel(const AtkBwdParams p) {
+pkda_atk_bwd_kernel(const AtkBwdParams p, int n_tiles) {
   using namespace atkb;
+  extern __shared__ __align__(16) unsigned char slots[];
   __shared__ __align__(16) float sEnd[8][kD];  // per row block: end value of its zero-start scan
   __shared__ float sDec[8];                    // per row block: product of its decays
   __shared__ float sRed[8];
-  int n, tok0, valid;
-  if (!chunk_lookup(p.geo, blockIdx.x, n, tok0, valid)) return;
-  const int h = blockIdx.y, H = p.geo.heads, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const size_t chh = (size_t)blockIdx.x * H + h;
+  const int H = p.geo.heads, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int c4 = lane << 2, r0 = warp * kRows;
-  const size_t col0 = ((size_t)tok0 * H + h) * kD + c4;
   const long gld = (long)H * kD;
+  // slot layout: arrays of [kRows][kThreads] (then [kThreads]) so that a warp's accesses are contiguous
+  uint2* sK = reinterpret_cast<uint2*>(slots);
+  float4* sDkt = reinterpret_cast<float4*>(slots + kThreads * kRows * 8);
+  float4* sDkr = sDkt + kThreads * kRows;
+  float* sLg = reinterpret_cast<float*>(sDkr + (kFinal ? kThreads * kRows : 0));
+  float4* sA0 = reinterpret_cast<float4*>(sLg + kThreads * kRows);
+  float4* sLin = sA0 + kThreads;
 
-  // ---- every global read in flight first
+  // A persistent CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...; a tile is one (chunk, head).
+  // The next tile's data is requested before the current tile is computed.
+  int tok0_n = 0, valid_n = 0;
+  bool live_n = false;
+  uint32_t bpraw_n[kRows / 2];  // the next tile's beta_atk (bf16 pairs), by plain loads
+  auto request = [&](int tile) {
+    live_n = false;
+    if (tile < n_tiles) {
+      int n;
+      live_n = chunk_lookup(p.geo, tile / H, n, tok0_n, valid_n);
+    }
+    if (live_n) {
+      const int hh = tile % H;
+      const size_t col0 = ((size_t)tok0_n * H + hh) * kD + c4;
+#pragma unroll
+      for (int i = 0; i < kRows; ++i) {
+        const int r = r0 + i;
+        const bool ok = r < valid_n;
+        const size_t off = ok ? col0 + (size_t)r * gld : 0;
+        const size_t s = ok ? (size_t)(tok0_n + r) * H + hh : 0;
+        // 8-byte copy as two 4-byte pieces (cp.async sizes are 4, 8 or 16)
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;\n" ::"r"(smem_u32(sK + i * kThreads + tid)),
+                     "l"(p.k + off), "r"(ok ? 8 : 0));
+        cp_async16(sDkt + i * kThreads + tid, p.dkt + off, ok);
+        if (kFinal) cp_async16(sDkr + i * kThreads + tid, p.dk_read + off, ok);
+        cp_async4(sLg + i * kThreads + tid, p.g_atk + s, ok);
+        const float bpv = ok ? to_f(p.beta_atk[s]) : 0.f;
+        if (i & 1) bpraw_n[i >> 1] = pack_bf16(__uint_as_float(bpraw_n[i >> 1]), bpv);
+        else bpraw_n[i >> 1] = __float_as_uint(bpv);
+      }
+      cp_async16(sA0 + tid, p.a_start + (size_t)tile * kD + c4, true);
+      if (kFinal) cp_async16(sLin + tid, p.lam_in + (size_t)tile * kD + c4, true);
+    }
+    cp_async_commit();
+  };
+  request(blockIdx.x);
+  for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+  const bool live = live_n;
+  const int tok0 = tok0_n, valid = valid_n, h = tile % H;
+  const size_t chh = (size_t)tile;
+  const size_t col0 = ((size_t)tok0 * H + h) * kD + c4;
+  cp_async_wait<0>();
+  // ---- this tile's data: shared-memory slots -> registers
   uint2 kraw[kRows];
   float4 dkt[kRows], dkr[kRows];
   float pd[kRows], bp[kRows];
 #pragma unroll
   for (int i = 0; i < kRows; ++i) {
-    const int r = r0 + i;
-    const bool ok = r < valid;
-    kraw[i] = make_uint2(0, 0);
-    dkt[i] = dkr[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-    pd[i] = 0.f;
-    bp[i] = 0.f;
-    if (ok) {
-      const size_t off = col0 + (size_t)r * gld;
-      kraw[i] = *reinterpret_cast<const uint2*>(p.k + off);
-      dkt[i] = *reinterpret_cast<const float4*>(p.dkt + off);
-      if (kFinal) dkr[i] = *reinterpret_cast<const float4*>(p.dk_read + off);
-      const size_t s = (size_t)(tok0 + r) * H + h;
-      pd[i] = p.g_atk[s];          // the log-decay for now
-      bp[i] = to_f(p.beta_atk[s]);
-    }
+    kraw[i] = sK[i * kThreads + tid];
+    dkt[i] = sDkt[i * kThreads + tid];
+    dkr[i] = kFinal ? sDkr[i * kThreads + tid] : make_float4(0.f, 0.f, 0.f, 0.f);
+    pd[i] = sLg[i * kThreads + tid];  // the log-decay for now (zero fill past the end: decay 1)
+    const float2 b2 = unpack_bf16(bpraw_n[i >> 1]);
+    bp[i] = (i & 1) ? b2.y : b2.x;
   }
-  const float4 a0 = *reinterpret_cast<const float4*>(p.a_start + chh * kD + c4);
+  const float4 a0 = sA0[tid];
   float4 lin = make_float4(0.f, 0.f, 0.f, 0.f);
-  if (kFinal) lin = *reinterpret_cast<const float4*>(p.lam_in + chh * kD + c4);
+  if (kFinal) lin = sLin[tid];
+  request(tile + gridDim.x);  // the slots are free again: next tile's copies fly during the computation
+  if (!live) continue;        // (uniform) index past the last real chunk of a packed batch
   const float centre = p.log_atk_scale[h];
   float dblk = 1.f;
 #pragma unroll
@@ -845,7 +933,8 @@ pkda_atk_bwd_kernel(const AtkBwdParams p) {
       }
       p.c_loc[chh * kD + tid] = acc;
     }
-    return;
+    __syncthreads();  // the exchange arrays are reused by the next tile
+    continue;
   }
   // ---- reverse scan: block-local lam from a zero incoming value (into dkt), outgoing value exchanged
   {
@@ -921,6 +1010,9 @@ pkda_atk_bwd_kernel(const AtkBwdParams p) {
     for (int w = 0; w < kThreads / 32; ++w) acc += sRed[w];
     p.partC[chh] = acc;
   }
+  __syncthreads();  // the exchange arrays are reused by the next tile
+  }  // tile loop
+  cp_async_wait<0>();
 }
 
 // Sequential carry over a sequence's chunks, last to first.
@@ -1047,9 +1139,9 @@ int chunk_bwd(const pkda_chunk_bwd_args* a, cudaStream_t st) {
   bf16* v_new = static_cast<bf16*>(a->v_new);
   bf16* h = static_cast<bf16*>(a->h);
   bf16* qg = static_cast<bf16*>(a->qg);
+  if (cudaMemsetAsync(ws.status, 0, sizeof(int), st) != cudaSuccess) return PKDA_ERR_LAUNCH;
   if (a->recompute) {
     // The recompute kernels only read the products, write keys and decay totals.
-    if (cudaMemsetAsync(ws.status, 0, sizeof(int), st) != cudaSuccess) return PKDA_ERR_LAUNCH;
     rc = run_forward_stages(p, geo, ws.beta_c, ws.u, const_cast<bf16*>(Aqk), const_cast<bf16*>(Akk),
                             const_cast<bf16*>(kt), const_cast<float*>(gc), a->a_atk, w, kg, v_new, h, qg,
                             nullptr, true, ws.status, st);
@@ -1081,9 +1173,25 @@ int chunk_bwd(const pkda_chunk_bwd_args* a, cudaStream_t st) {
   ip.dq = static_cast<bf16*>(a->dq); ip.dk_read = ws.dk_read; ip.dv = static_cast<bf16*>(a->dv);
   ip.dg = static_cast<bf16*>(a->dg); ip.dbeta = static_cast<bf16*>(a->dbeta); ip.dkt = ws.dkt;
   ip.partA = ws.partA; ip.partB = ws.partB; ip.scale = p.scale; ip.direct_cap = direct_block_cap();
+  IntraBwdMaps maps;
+  {
+    const uint64_t H = p.heads, tok = p.total_tokens, rows = (uint64_t)geo.total_chunks * H * kD;
+    const uint64_t act_dims[2] = {H * kD, tok}, act_str[1] = {H * kD * 2};
+    const uint32_t act_box[2] = {kLdD, kChunk};
+    const uint64_t st_dims[2] = {kD, rows}, st_str[1] = {kD * 2};
+    const uint32_t st_box[2] = {kLdD, kD};
+    const uint64_t pr_dims[2] = {H * kChunk, tok}, pr_str[1] = {H * kChunk * 2};
+    const uint32_t pr_box[2] = {kLdC, kChunk};
+    ip.use_tma = tok >= kChunk && encode_bf16_map(&maps.d_o, ip.d_o, 2, act_dims, act_str, act_box, false) &&
+                 encode_bf16_map(&maps.dF, ip.dF, 2, act_dims, act_str, act_box, false) &&
+                 encode_bf16_map(&maps.h, ip.h, 2, st_dims, st_str, st_box, false) &&
+                 encode_bf16_map(&maps.dh, ip.dh, 2, st_dims, st_str, st_box, false) &&
+                 encode_bf16_map(&maps.Akk, ip.Akk, 2, pr_dims, pr_str, pr_box, false);
+    ip.status = ws.status;
+  }
   if (!set_smem(pkda_intra_bwd_kernel, ib::kSmem)) return PKDA_ERR_LAUNCH;
   begin_stage(kStageIntraBwd, st);
-  pkda_intra_bwd_kernel<<<gridc, ib::kThreads, ib::kSmem, st>>>(ip);
+  pkda_intra_bwd_kernel<<<gridc, ib::kThreads, ib::kSmem, st>>>(ip, maps);
   PKDA_CHECK_LAUNCH();
 
   AtkBwdParams ap;
@@ -1093,14 +1201,20 @@ int chunk_bwd(const pkda_chunk_bwd_args* a, cudaStream_t st) {
   ap.dk = static_cast<bf16*>(a->dk); ap.dg_atk = a->dg_atk; ap.dbeta_atk = static_cast<bf16*>(a->dbeta_atk);
   ap.partC = ws.partC; ap.ln_x = logf(p.squash_x); ap.eps = p.squash_eps;
   begin_stage(kStageAtkBwdLocal, st);
-  pkda_atk_bwd_kernel<false><<<gridc, atkb::kThreads, 0, st>>>(ap);
+  const int atk_tiles = geo.total_chunks * p.heads;
+  int sms = 148, dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int atk_grid = atk_tiles < 2 * sms ? atk_tiles : 2 * sms;  // persistent: two CTAs per SM
+  if (!set_smem(pkda_atk_bwd_kernel<false>, atkb::smem_bytes<false>())) return PKDA_ERR_LAUNCH;
+  pkda_atk_bwd_kernel<false><<<atk_grid, atkb::kThreads, atkb::smem_bytes<false>(), st>>>(ap, atk_tiles);
   PKDA_CHECK_LAUNCH();
   begin_stage(kStageAtkBwdCarry, st);
   pkda_atk_bwd_carry_kernel<<<dim3(p.n_seqs, p.heads), kD, 0, st>>>(geo, ws.c_loc, a->sa_atk, ws.lam_in,
                                                                    a->d_initial_A_state);
   PKDA_CHECK_LAUNCH();
   begin_stage(kStageAtkBwdFinal, st);
-  pkda_atk_bwd_kernel<true><<<gridc, atkb::kThreads, 0, st>>>(ap);
+  if (!set_smem(pkda_atk_bwd_kernel<true>, atkb::smem_bytes<true>())) return PKDA_ERR_LAUNCH;
+  pkda_atk_bwd_kernel<true><<<atk_grid, atkb::kThreads, atkb::smem_bytes<true>(), st>>>(ap, atk_tiles);
   PKDA_CHECK_LAUNCH();
   begin_stage(kStageParamReduce, st);
   pkda_param_reduce_kernel<<<p.heads, kD, 0, st>>>(geo, ws.partA, ws.partB, ws.partC, a->dA_log, a->ddt_bias,

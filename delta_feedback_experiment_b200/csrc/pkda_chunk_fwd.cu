@@ -187,12 +187,12 @@ pkda_intra_fwd_kernel(const IntraParams p) {
   }
   // zero the P staging tile (upper triangle must read as zero)
   for (int i = tid; i < kChunk * kLdC / 8; i += kThreads) reinterpret_cast<uint4*>(sTmb)[i] = make_uint4(0, 0, 0, 0);
-  cp_async_wait<0>();
   __syncthreads(); PKDA_PHASE(1);
 
-  // ---- 2. decay gate (elementwise, all threads), then the two per-channel sequential
-  // passes side by side: cumulative sum | preconditioner recurrence A_t
+  // ---- 2. decay gate (elementwise, all threads; the q and k tiles are still landing), then
+  // the two per-channel sequential passes side by side: cumulative sum | preconditioner recurrence A_t
   gate_elementwise<kThreads>(sG, p.g + row0, gld, valid, sBias, __expf(p.A_log[h]) * kLog2e, tid);
+  cp_async_wait<0>();
   __syncthreads(); PKDA_PHASE(2);
   if (tid < kD) {
     gate_cumsum(sG, tid);

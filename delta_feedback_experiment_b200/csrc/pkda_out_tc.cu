@@ -149,7 +149,7 @@ static EncodeTiledFn encode_fn() {
 }
 
 bool encode_bf16_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides,
-                     const uint32_t* box) {
+                     const uint32_t* box, bool swizzle128) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   cuuint64_t gdim[5], gstr[5];
@@ -161,7 +161,8 @@ bool encode_bf16_map(CUtensorMap* map, const void* base, int rank, const uint64_
     if (i > 0) gstr[i - 1] = strides[i - 1];
   }
   return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), gdim, gstr, bdim, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 

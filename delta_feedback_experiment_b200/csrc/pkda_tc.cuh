@@ -156,11 +156,11 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 
 }  // namespace tc
 
-// Host: encodes a bf16 tile map with 128-byte swizzle.  dims/strides innermost
-// first; strides in bytes for dims 1..rank-1.  Returns false if the driver entry
-// point is unavailable or the encode fails.
+// Host: encodes a bf16 tile map, with 128-byte swizzle or (swizzle128 = false) as
+// plain rows.  dims/strides innermost first; strides in bytes for dims 1..rank-1.
+// Returns false if the driver entry point is unavailable or the encode fails.
 bool encode_bf16_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides,
-                     const uint32_t* box);
+                     const uint32_t* box, bool swizzle128 = true);
 
 // Byte offset of element (row, col) in a 128-byte-swizzled tile made of blocks of
 // [rows][64 bf16]: block = col / 64, 16-byte piece (col % 64) / 8 XOR-ed with row % 8.

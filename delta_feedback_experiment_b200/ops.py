@@ -19,6 +19,7 @@ LAUNCHES = 0
 
 
 _LAST_STATUS = None
+_LAST_BWD_STATUS = None
 
 
 def last_device_status() -> int:
@@ -28,6 +29,14 @@ def last_device_status() -> int:
     if _LAST_STATUS is None:
         return 0
     return int(_LAST_STATUS.view(torch.int32).item())
+
+
+def last_backward_status() -> int:
+    """The same for the most recent chunked backward (its results are void if a
+    bounded wait gave up)."""
+    if _LAST_BWD_STATUS is None:
+        return 0
+    return int(_LAST_BWD_STATUS.view(torch.int32).item())
 
 
 def _count(lib) -> None:
@@ -251,6 +260,8 @@ def chunk_backward(q, k, v, g, g_atk, beta_atk, beta, A_log, dt_bias, log_atk_sc
     args.workspace, args.workspace_bytes = ws.data_ptr(), nbytes
     _lib.check(lib.pkda_chunk_bwd(C.byref(args), _lib.current_stream()), "pkda_chunk_bwd")
     _count(lib)
+    global _LAST_BWD_STATUS
+    _LAST_BWD_STATUS = ws[nbytes - 256:nbytes - 252] if nbytes >= 256 else None
     grads = [dq, dk, dv, dg, dg_atk, dbeta_atk, dbeta, dA_log, ddt_bias, dcentre]
     return grads, dS0, dA0
 

@@ -42,6 +42,8 @@ def run(d, cu=None, with_state=True, dS=None, lean=True):
 
 
 def check(res, ref, tag):
+    from delta_feedback_experiment_b200 import ops
+    assert ops.last_backward_status() == 0, f"{tag}: a bounded wait in a backward kernel gave up"
     for n in INPUT_NAMES:
         a, e = res["d" + n], ref["d" + n]
         assert a.dtype == (torch.float32 if n in FP32_GRADS else torch.bfloat16), n

@@ -6,9 +6,11 @@ from .fla_ops import (CHUNK_SIZE, PKDA_INTERMEDIATES, PKDA_RETAINED, fla_ops_ava
                       pkda_recurrence)
 from .pkda import (chunk_precond_kda, fused_recurrent_precond_kda, pkda_cuda_available,
                    pkda_cuda_recurrence)
+from .layer_ops import pkda_norm_gate, pkda_qkv_conv
+from .host_pipeline import HostStep
 
 __all__ = [
     "CHUNK_SIZE", "PKDA_INTERMEDIATES", "PKDA_RETAINED", "fla_ops_available", "pkda_recurrence",
     "chunk_precond_kda", "fused_recurrent_precond_kda", "pkda_cuda_available",
-    "pkda_cuda_recurrence",
+    "pkda_cuda_recurrence", "pkda_qkv_conv", "pkda_norm_gate", "HostStep",
 ]

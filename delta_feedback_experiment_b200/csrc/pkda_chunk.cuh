@@ -133,24 +133,34 @@ __device__ __forceinline__ void stage_level(bf16* sXq, bf16* sXk, bf16* sY, cons
 // Elementwise part of the decay gate for one chunk, all kNThreads threads: log2-domain
 // per-token log-decay  -exp(A_log) log2(e) softplus(raw + bias)  into sG (zero for
 // rows past the sequence end).  The cumulative sum over rows follows separately.
+// The raw gate of the tile is fetched first (gate_load, at the top of a kernel, so
+// that the loads fly while other data is set up) and converted later (gate_apply).
 template <int kNThreads>
-__device__ __forceinline__ void gate_elementwise(float* sG, const bf16* g_row0, long gld, int valid,
-                                                 const float* bias_h, float ea2, int tid) {
-  constexpr int kIter = kChunk * kD / 8 / kNThreads;
+struct GateRaw {
+  static constexpr int kIter = kChunk * kD / 8 / kNThreads;
   static_assert(kIter * kNThreads * 8 == kChunk * kD, "tile must divide evenly");
   uint4 raw[kIter];
+};
+
+template <int kNThreads>
+__device__ __forceinline__ void gate_load(GateRaw<kNThreads>& gr, const bf16* g_row0, long gld, int valid, int tid) {
 #pragma unroll
-  for (int it = 0; it < kIter; ++it) {  // all global loads in flight before any use
+  for (int it = 0; it < GateRaw<kNThreads>::kIter; ++it) {
     const int idx = tid + it * kNThreads, r = idx >> 4, c8 = (idx & 15) << 3;
-    raw[it] = make_uint4(0, 0, 0, 0);
-    if (r < valid) raw[it] = *reinterpret_cast<const uint4*>(g_row0 + (size_t)r * gld + c8);
+    gr.raw[it] = make_uint4(0, 0, 0, 0);
+    if (r < valid) gr.raw[it] = *reinterpret_cast<const uint4*>(g_row0 + (size_t)r * gld + c8);
   }
+}
+
+template <int kNThreads>
+__device__ __forceinline__ void gate_apply(const GateRaw<kNThreads>& gr, float* sG, int valid, const float* bias_h,
+                                           float ea2, int tid) {
 #pragma unroll
-  for (int it = 0; it < kIter; ++it) {
+  for (int it = 0; it < GateRaw<kNThreads>::kIter; ++it) {
     const int idx = tid + it * kNThreads, r = idx >> 4, c8 = (idx & 15) << 3;
     float o[8];
     if (r < valid) {
-      const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw[it]);
+      const uint32_t* w = reinterpret_cast<const uint32_t*>(&gr.raw[it]);
       const float4 bA = *reinterpret_cast<const float4*>(bias_h + c8);
       const float4 bB = *reinterpret_cast<const float4*>(bias_h + c8 + 4);
       const float bb[8] = {bA.x, bA.y, bA.z, bA.w, bB.x, bB.y, bB.z, bB.w};
@@ -167,6 +177,14 @@ __device__ __forceinline__ void gate_elementwise(float* sG, const bf16* g_row0, 
     *reinterpret_cast<float4*>(sG + r * kLdG + c8) = make_float4(o[0], o[1], o[2], o[3]);
     *reinterpret_cast<float4*>(sG + r * kLdG + c8 + 4) = make_float4(o[4], o[5], o[6], o[7]);
   }
+}
+
+template <int kNThreads>
+__device__ __forceinline__ void gate_elementwise(float* sG, const bf16* g_row0, long gld, int valid,
+                                                 const float* bias_h, float ea2, int tid) {
+  GateRaw<kNThreads> gr;
+  gate_load(gr, g_row0, gld, valid, tid);
+  gate_apply(gr, sG, valid, bias_h, ea2, tid);
 }
 
 // In-place cumulative sum over the 64 rows of sG, one channel per thread (tid < 128).

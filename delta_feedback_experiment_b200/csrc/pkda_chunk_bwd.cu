@@ -308,6 +308,8 @@ pkda_intra_bwd_kernel(const IntraBwdParams p, const __grid_constant__ IntraBwdMa
   const long cld = (long)H * kChunk;
 
   // ================= phase A: state-coupled terms =================
+  GateRaw<kThreads> graw;  // the raw gate is needed first: fetch it first
+  gate_load(graw, p.g + row0, gld, valid, tid);
   // dS1 waits in the (not yet used) level-factor array until the dkg product
   bf16* sdSC = reinterpret_cast<bf16*>(smem + oFac);
   // Full chunks: one thread starts five TMA tile copies and everybody goes on to the
@@ -339,7 +341,7 @@ pkda_intra_bwd_kernel(const IntraBwdParams p, const __grid_constant__ IntraBwdMa
   else if (tid < 2 * kD) sBias[tid - kD] = p.dt_bias[h * kD + tid - kD];
   __syncthreads(); PKDA_PHASE(1);
   // log2-domain cumulative log-decay, exactly as the forward computes it
-  gate_elementwise<kThreads>(sG, p.g + row0, gld, valid, sBias, __expf(p.A_log[h]) * kLog2e, tid);
+  gate_apply(graw, sG, valid, sBias, __expf(p.A_log[h]) * kLog2e, tid);
   __syncthreads(); PKDA_PHASE(2);
   if (tid < kD) {
     gate_cumsum(sG, tid);

@@ -171,7 +171,9 @@ pkda_intra_fwd_kernel(const IntraParams p) {
   const size_t row0 = ((size_t)tok0 * H + h) * kD;  // element offset of (tok0, h, 0)
   const long gld = (long)H * kD;
 
-  // ---- 1. tiles and per-row scalars
+  // ---- 1. tiles and per-row scalars (the raw gate first: it is needed first)
+  GateRaw<kThreads> graw;
+  gate_load(graw, p.g + row0, gld, valid, tid);
   tile_load_async(sQ, kLdD, p.q + row0, gld, kChunk, kD, valid, kThreads);
   tile_load_async(sK, kLdD, p.k + row0, gld, kChunk, kD, valid, kThreads);
   if (kRecompute) tile_load_async(sKt, kLdD, p.kt + row0, gld, kChunk, kD, valid, kThreads);
@@ -191,7 +193,7 @@ pkda_intra_fwd_kernel(const IntraParams p) {
 
   // ---- 2. decay gate (elementwise, all threads; the q and k tiles are still landing), then
   // the two per-channel sequential passes side by side: cumulative sum | preconditioner recurrence A_t
-  gate_elementwise<kThreads>(sG, p.g + row0, gld, valid, sBias, __expf(p.A_log[h]) * kLog2e, tid);
+  gate_apply(graw, sG, valid, sBias, __expf(p.A_log[h]) * kLog2e, tid);
   cp_async_wait<0>();
   __syncthreads(); PKDA_PHASE(2);
   if (tid < kD) {

@@ -215,6 +215,7 @@ def run_decode(device, steps: int, warmup: int, pk: dict) -> dict:
     _lib.stage_timing(False)
     wall_ms = e0.elapsed_time(e1) / steps
     k_ms, k_n = stages["recurrent"]
+    fused = run_decode_fused(device, dev, S, A, B, H, D, min(steps, 256), warmup, pk)
     bytes_per_step = DECODE_BYTES_PER_UNIT * B * H
     achieved = bytes_per_step / (k_ms / k_n * 1e-3) / 1e9
     return {
@@ -225,7 +226,51 @@ def run_decode(device, steps: int, warmup: int, pk: dict) -> dict:
                      "frac": achieved / pk["hbm_gbs"], "traffic": None,
                      "algorithmic_bytes_per_launch": bytes_per_step, "peak_source": pk["source"]},
         "finite": bool(torch.isfinite(S).all().item()),
+        "fused_step": fused,
     }
+
+
+def run_decode_fused(device, dev, S, A, B, H, D, steps, warmup, pk) -> dict:
+    """The same decode step with the layer's convolution (over the cached history) and RMS-norm gate
+    fused into the launch: one kernel per step, cache (histories, S, A) updated in place."""
+    from delta_feedback_experiment_b200 import _lib
+    from delta_feedback_experiment_b200.layer_ops import pkda_decode_step
+    W, taps, NIN = H * D, 4, 8
+    gen = torch.Generator().manual_seed(301)
+    bf = lambda t: t.bfloat16().to(device)
+    qkv = [bf(torch.randn(B, 3 * W, generator=gen)) for _ in range(NIN)]
+    gate = [bf(torch.randn(B, H, D, generator=gen)) for _ in range(NIN)]
+    conv = [bf(torch.randn(B, W, taps - 1, generator=gen)) for _ in range(3)]
+    conv_w = (torch.randn(3 * W, taps, generator=gen) * 0.5).to(device)
+    norm_w = torch.ones(D, device=device)
+    ins = [{n: dev[n][:, t].contiguous() for n in ("g", "g_atk", "beta_atk", "beta")} for t in range(NIN)]
+
+    def step(i):
+        j = i % NIN
+        return pkda_decode_step(qkv[j], conv, conv_w, ins[j]["g"], ins[j]["g_atk"], ins[j]["beta_atk"], ins[j]["beta"],
+                                dev["A_log"], dev["dt_bias"], dev["log_atk_scale"], S, A, gate[j], norm_w, D)
+
+    for i in range(warmup):
+        step(i)
+    torch.cuda.synchronize(device)
+    _lib.stage_timing(True)
+    out = None
+    for i in range(steps):
+        out = step(i)
+    torch.cuda.synchronize(device)
+    stages = _lib.stage_timing_read()
+    _lib.stage_timing(False)
+    k_ms, k_n = stages["decode_step"]
+    # per (row, head): state and a_state read+write, the projection row, histories read+write, raw decay,
+    # gate logits, output, four scalars
+    per_unit = 2 * 4 * D * D + 2 * 4 * D + 3 * D * 2 + 2 * 3 * D * (taps - 1) * 2 + 3 * D * 2 + 12
+    nbytes = per_unit * B * H
+    achieved = nbytes / (k_ms / k_n * 1e-3) / 1e9
+    return {"kernel_ms": k_ms / k_n, "launches_per_step": 1,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                         "frac": achieved / pk["hbm_gbs"], "traffic": None,
+                         "algorithmic_bytes_per_launch": nbytes, "peak_source": pk["source"]},
+            "finite": bool(torch.isfinite(out.float()).all().item())}
 
 
 def run_layer_ops(device, B: int, T: int, H: int, D: int, steps: int, warmup: int, pk: dict) -> dict:

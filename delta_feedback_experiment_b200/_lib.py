@@ -101,6 +101,21 @@ class NormGateArgs(C.Structure):
     ]
 
 
+class DecodeStepArgs(C.Structure):
+    _fields_ = [
+        ("batch", C.c_int32), ("heads", C.c_int32), ("head_dim", C.c_int32), ("taps", C.c_int32),
+        ("dtype", C.c_int32),
+        ("scale", C.c_float), ("squash_x", C.c_float), ("squash_eps", C.c_float), ("qk_eps", C.c_float),
+        ("norm_eps", C.c_float),
+        ("qkv", C.c_void_p), ("conv_q", C.c_void_p), ("conv_k", C.c_void_p), ("conv_v", C.c_void_p),
+        ("conv_weight", C.c_void_p), ("g", C.c_void_p), ("g_atk", C.c_void_p),
+        ("beta_atk", C.c_void_p), ("beta", C.c_void_p),
+        ("A_log", C.c_void_p), ("dt_bias", C.c_void_p), ("log_atk_scale", C.c_void_p),
+        ("state", C.c_void_p), ("a_state", C.c_void_p), ("gate", C.c_void_p),
+        ("norm_weight", C.c_void_p), ("out", C.c_void_p),
+    ]
+
+
 EXPORTS = (
     "pkda_recurrent_fwd", "pkda_recurrent_bwd", "pkda_recurrent_bwd_workspace_bytes", "pkda_chunk_fwd_workspace_bytes", "pkda_chunk_fwd",
     "pkda_chunk_bwd_workspace_bytes", "pkda_chunk_bwd", "pkda_abi_version",
@@ -111,6 +126,7 @@ EXPORTS = (
     "pkda_qkv_conv_fwd", "pkda_qkv_conv_bwd_workspace_bytes", "pkda_qkv_conv_bwd",
     "pkda_norm_gate_fwd", "pkda_norm_gate_bwd_workspace_bytes", "pkda_norm_gate_bwd",
     "pkda_sizeof_qkv_conv_args", "pkda_sizeof_norm_gate_args",
+    "pkda_decode_step", "pkda_sizeof_decode_step_args",
 )
 
 _lib: Optional[C.CDLL] = None
@@ -142,12 +158,15 @@ def _configure(lib: C.CDLL) -> None:
             getattr(lib, name + suffix).restype = C.c_int
         getattr(lib, name + "_bwd_workspace_bytes").argtypes = [C.POINTER(struct)]
         getattr(lib, name + "_bwd_workspace_bytes").restype = C.c_size_t
+    lib.pkda_decode_step.argtypes = [C.POINTER(DecodeStepArgs), C.c_void_p]
+    lib.pkda_decode_step.restype = C.c_int
     lib.pkda_abi_version.restype = C.c_int
     lib.pkda_status_string.argtypes = [C.c_int]
     lib.pkda_status_string.restype = C.c_char_p
     for name in ("pkda_sizeof_problem", "pkda_sizeof_recurrent_args",
                  "pkda_sizeof_chunk_fwd_args", "pkda_sizeof_chunk_bwd_args",
-                 "pkda_sizeof_qkv_conv_args", "pkda_sizeof_norm_gate_args"):
+                 "pkda_sizeof_qkv_conv_args", "pkda_sizeof_norm_gate_args",
+                 "pkda_sizeof_decode_step_args"):
         getattr(lib, name).restype = C.c_size_t
     lib.pkda_last_launch_count.restype = C.c_int
     lib.pkda_stage_count.restype = C.c_int
@@ -179,7 +198,8 @@ def load() -> C.CDLL:
                  (lib.pkda_sizeof_chunk_fwd_args(), ChunkFwdArgs),
                  (lib.pkda_sizeof_chunk_bwd_args(), ChunkBwdArgs),
                  (lib.pkda_sizeof_qkv_conv_args(), QkvConvArgs),
-                 (lib.pkda_sizeof_norm_gate_args(), NormGateArgs))
+                 (lib.pkda_sizeof_norm_gate_args(), NormGateArgs),
+                 (lib.pkda_sizeof_decode_step_args(), DecodeStepArgs))
         for size, struct in sizes:
             if size != C.sizeof(struct):
                 raise OSError(f"struct layout mismatch for {struct.__name__}")

@@ -1,0 +1,219 @@
+// One cached decoding step of the PKDA layer's token mixer in ONE launch:
+//   Q|K|V short convolution over the cached projection history (+ SiLU, per-head
+//   L2 norm of Q and K)  ->  one step of the recurrence on the cached state  ->
+//   per-head RMS norm x sigmoid output gate,
+// with the convolution histories, the matrix state S and the preconditioner
+// state A updated in place.  It replaces, for T = 1, the reference's sequence of
+// pkda_qkv_conv on the history-prefixed rows (delta_feedback_experiment/pkda.py:239-288),
+// fused_recurrent_precond_kda (pkda.py:473-474) and pkda_norm_gate (pkda.py:539-541),
+// and the cache bookkeeping around them (model.py:775-787): no torch.cat of the
+// history, no clone of the new history, no q/k/v/o round trips through HBM.
+//
+// One CTA owns one (row, head) and keeps the D x D fp32 state in registers, so the
+// step still moves the state through HBM exactly once in each direction; everything
+// else the step touches is about 3 % of that.
+#include "pkda_common.cuh"
+#include "pkda_launch.h"
+#include "pkda_recurrent.cuh"
+
+namespace pkda {
+
+struct DecodeParams {
+  int batch, heads, taps;
+  float scale, ln_x, eps, qk_eps, norm_eps;
+  const void* qkv;
+  void* conv[3];
+  const float* conv_w;
+  const void* g;
+  const float* g_atk;
+  const void *beta_atk, *beta;
+  const float *A_log, *dt_bias, *log_atk_scale;
+  float *S, *A;
+  const void* gate;
+  const float* norm_w;
+  void* out;
+};
+
+template <typename T> __device__ __forceinline__ float round_to(float x) { return to_f(from_f<T>(x)); }
+
+template <int D, typename T>
+__global__ void __launch_bounds__(RecCfg<D>::kThreads, D == 128 ? 2 : 1)
+pkda_decode_step_kernel(const DecodeParams p) {
+  using Cfg = RecCfg<D>;
+  constexpr int VQ = Cfg::kVQ, KW = Cfg::kKW, R = Cfg::kR, kThreads = Cfg::kThreads;
+  constexpr int kWarps = kThreads / 32;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int H = p.heads;
+  const int n = blockIdx.x / H, h = blockIdx.x - n * H;
+  const int W = H * D;
+
+  __shared__ float s_qkv[3][D];  // silu(conv) of q, k, v; then q, k normalised and rounded
+  __shared__ float s_k[D], s_wk[D], s_q[D], s_al[D];
+  __shared__ __align__(16) float s_v[D];
+  __shared__ __align__(16) float s_red[2][KW][D];
+  __shared__ float s_stat[kWarps + 2];
+
+  const bool active = tid < Cfg::kActive;
+  const int kq = tid / VQ, vq = tid - kq * VQ;
+  const int krow0 = kq * R;
+
+  // ---- the state first: its loads are the step's memory time
+  float4 S[R];
+  const size_t sbase = ((size_t)n * H + h) * D * D;
+  if (active) {
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+      S[r] = *reinterpret_cast<const float4*>(p.S + sbase + (size_t)(krow0 + r) * D + 4 * vq);
+  }
+
+  // ---- convolution over the cached history, SiLU; the history moves up by one token
+  const T* qkv = static_cast<const T*>(p.qkv) + (size_t)n * 3 * W;
+  const int hist = p.taps - 1;
+  for (int item = tid; item < 3 * D; item += kThreads) {
+    const int slab = item / D, d = item - slab * D;
+    const int cs = h * D + d;                 // channel inside the slab
+    const float* w = p.conv_w + (size_t)(slab * W + cs) * p.taps;
+    T* hs = static_cast<T*>(p.conv[slab]) + ((size_t)n * W + cs) * hist;
+    const T xn = qkv[slab * W + cs];
+    float y = w[hist] * to_f(xn);
+    T prev[3];
+    for (int j = 0; j < hist; ++j) {
+      prev[j] = hs[j];
+      y += w[j] * to_f(prev[j]);
+    }
+    for (int j = 0; j + 1 < hist; ++j) hs[j] = prev[j + 1];
+    if (hist > 0) hs[hist - 1] = xn;
+    s_qkv[slab][d] = y / (1.f + expf(-y));
+  }
+  __syncthreads();
+  // ---- per-head L2 norm of q (warp 0) and k (warp 1); q, k, v rounded to the activation type,
+  // as the separate operators hand them over
+  if (warp < 2) {
+    float ss = 0.f;
+    for (int d = lane; d < D; d += 32) ss += s_qkv[warp][d] * s_qkv[warp][d];
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (lane == 0) s_stat[kWarps + warp] = rsqrtf(ss + p.qk_eps);
+  }
+  __syncthreads();
+
+  float A = 0.f;
+  const float ea = expf(p.A_log[h]);
+  const float centre = p.log_atk_scale[h];
+  const size_t sidx = (size_t)n * H + h;
+  if (tid < D) {
+    const float qn = round_to<T>(s_qkv[0][tid] * s_stat[kWarps + 0]);
+    const float kc = round_to<T>(s_qkv[1][tid] * s_stat[kWarps + 1]);
+    const float vv = round_to<T>(s_qkv[2][tid]);
+    A = p.A[sidx * D + tid];
+    const float pd = expf(p.g_atk[sidx]);
+    A = pd * A + to_f(static_cast<const T*>(p.beta_atk)[sidx]) * kc * kc;
+    const float kw = kc * precond_factor(A, p.eps, centre, p.ln_x);
+    s_k[tid] = kc;
+    s_wk[tid] = to_f(static_cast<const T*>(p.beta)[sidx]) * kw;
+    s_q[tid] = qn * p.scale;
+    s_al[tid] = expf(-ea * softplus_acc(to_f(static_cast<const T*>(p.g)[sidx * D + tid]) + p.dt_bias[h * D + tid]));
+    s_v[tid] = vv;
+  }
+  __syncthreads();
+  // ---- S <- diag(exp g) S ;  e = v - S^T k ;  S <- S + (beta kw) e^T ;  o = S^T (scale q)
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (active) {
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const float al = s_al[krow0 + r], kk = s_k[krow0 + r];
+      S[r].x *= al; S[r].y *= al; S[r].z *= al; S[r].w *= al;
+      acc.x += S[r].x * kk; acc.y += S[r].y * kk; acc.z += S[r].z * kk; acc.w += S[r].w * kk;
+    }
+    *reinterpret_cast<float4*>(&s_red[0][kq][4 * vq]) = acc;
+  }
+  __syncthreads();
+  if (active) {
+    float4 e = *reinterpret_cast<const float4*>(&s_v[4 * vq]);
+#pragma unroll
+    for (int w = 0; w < KW; ++w) {
+      const float4 pr = *reinterpret_cast<const float4*>(&s_red[0][w][4 * vq]);
+      e.x -= pr.x; e.y -= pr.y; e.z -= pr.z; e.w -= pr.w;
+    }
+    acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const float wk = s_wk[krow0 + r], qq = s_q[krow0 + r];
+      S[r].x += wk * e.x; S[r].y += wk * e.y; S[r].z += wk * e.z; S[r].w += wk * e.w;
+      acc.x += S[r].x * qq; acc.y += S[r].y * qq; acc.z += S[r].z * qq; acc.w += S[r].w * qq;
+      *reinterpret_cast<float4*>(p.S + sbase + (size_t)(krow0 + r) * D + 4 * vq) = S[r];
+    }
+    *reinterpret_cast<float4*>(&s_red[1][kq][4 * vq]) = acc;
+  }
+  __syncthreads();
+  // ---- o, then RMS norm x weight x sigmoid(gate)
+  float o = 0.f;
+  if (tid < D) {
+#pragma unroll
+    for (int w = 0; w < KW; ++w) o += s_red[1][w][tid];
+    o = round_to<T>(o);
+    p.A[sidx * D + tid] = A;
+  }
+  T* out = static_cast<T*>(p.out) + sidx * D;
+  if (!p.gate) {
+    if (tid < D) out[tid] = from_f<T>(o);
+    return;
+  }
+  float sq = (tid < D) ? o * o : 0.f;
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, off);
+  if (lane == 0) s_stat[warp] = sq;
+  __syncthreads();
+  if (tid < D) {
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) tot += s_stat[w];
+    const float rstd = rsqrtf(tot / (float)D + p.norm_eps);
+    const float gl = to_f(static_cast<const T*>(p.gate)[sidx * D + tid]);
+    out[tid] = from_f<T>(o * rstd * p.norm_w[tid] / (1.f + expf(-gl)));
+  }
+}
+
+template <int D, typename T>
+static int launch_decode(const DecodeParams& dp, cudaStream_t st) {
+  begin_stage(kStageDecodeStep, st);
+  pkda_decode_step_kernel<D, T><<<dp.batch * dp.heads, RecCfg<D>::kThreads, 0, st>>>(dp);
+  end_stage(st);
+  return cudaGetLastError() == cudaSuccess ? PKDA_OK : PKDA_ERR_LAUNCH;
+}
+
+template <typename T>
+static int dispatch_decode(int D, const DecodeParams& dp, cudaStream_t st) {
+  switch (D) {
+    case 8: return launch_decode<8, T>(dp, st);
+    case 16: return launch_decode<16, T>(dp, st);
+    case 32: return launch_decode<32, T>(dp, st);
+    case 64: return launch_decode<64, T>(dp, st);
+    case 128: return launch_decode<128, T>(dp, st);
+    default: return PKDA_ERR_SHAPE;
+  }
+}
+
+int decode_step(const pkda_decode_step_args* a, cudaStream_t st) {
+  if (a->batch < 0 || a->heads <= 0 || a->taps < 1 || a->taps > 4) return PKDA_ERR_SHAPE;
+  if (a->dtype != PKDA_BF16 && a->dtype != PKDA_F32) return PKDA_ERR_DTYPE;
+  if (a->batch == 0) return PKDA_OK;
+  if (!a->qkv || !a->conv_weight || !a->g || !a->g_atk || !a->beta_atk || !a->beta || !a->A_log || !a->dt_bias ||
+      !a->log_atk_scale || !a->state || !a->a_state || !a->out)
+    return PKDA_ERR_NULL;
+  if (a->taps > 1 && (!a->conv_q || !a->conv_k || !a->conv_v)) return PKDA_ERR_NULL;
+  if (a->gate && !a->norm_weight) return PKDA_ERR_NULL;
+  if (reinterpret_cast<uintptr_t>(a->state) & 15) return PKDA_ERR_ALIGN;
+  DecodeParams dp;
+  dp.batch = a->batch; dp.heads = a->heads; dp.taps = a->taps;
+  dp.scale = a->scale; dp.ln_x = logf(a->squash_x); dp.eps = a->squash_eps; dp.qk_eps = a->qk_eps;
+  dp.norm_eps = a->norm_eps;
+  dp.qkv = a->qkv; dp.conv[0] = a->conv_q; dp.conv[1] = a->conv_k; dp.conv[2] = a->conv_v;
+  dp.conv_w = a->conv_weight; dp.g = a->g; dp.g_atk = a->g_atk; dp.beta_atk = a->beta_atk; dp.beta = a->beta;
+  dp.A_log = a->A_log; dp.dt_bias = a->dt_bias; dp.log_atk_scale = a->log_atk_scale;
+  dp.S = a->state; dp.A = a->a_state; dp.gate = a->gate; dp.norm_w = a->norm_weight; dp.out = a->out;
+  if (a->dtype == PKDA_BF16) return dispatch_decode<bf16>(a->head_dim, dp, st);
+  return dispatch_decode<float>(a->head_dim, dp, st);
+}
+
+}  // namespace pkda

@@ -13,7 +13,7 @@ enum Stage {
   kStageOffsets = 0, kStagePackBeta, kStageAtkLocal, kStageAtkCarry, kStageIntraFwd, kStageScanFwd,
   kStageOutFwd, kStageScanBwd, kStageIntraBwd, kStageAtkBwdLocal, kStageAtkBwdCarry, kStageAtkBwdFinal,
   kStageParamReduce, kStageRecurrent, kStageConvFwd, kStageConvBwd, kStageConvDw, kStageNormGateFwd,
-  kStageNormGateBwd, kStageNormGateDw, kStageCount
+  kStageNormGateBwd, kStageNormGateDw, kStageDecodeStep, kStageCount
 };
 
 // begin_stage / end_stage bracket every kernel launch: they count launches and,
@@ -55,5 +55,6 @@ size_t qkv_conv_bwd_workspace(const pkda_qkv_conv_args& a);
 int norm_gate_fwd(const pkda_norm_gate_args* a, cudaStream_t st);
 int norm_gate_bwd(const pkda_norm_gate_args* a, cudaStream_t st);
 size_t norm_gate_bwd_workspace(const pkda_norm_gate_args& a);
+int decode_step(const pkda_decode_step_args* a, cudaStream_t st);
 
 }  // namespace pkda

@@ -3,11 +3,14 @@
 //   s = silu(y)
 //   out = s * rsqrt(sum over the head of s^2 + eps)        for c < norm_channels (Q and K)
 //   out = s                                                otherwise (V)
-// written as three slabs q, k, v.  Pure streaming work.  A CTA stages a tile of
-// tokens x 256 channels (plus the halo rows the filter reaches into) in shared
-// memory with 16-byte cp.async copies -- all of a CTA's loads are in flight at
-// once and several CTAs share an SM -- and then every thread walks a few tokens of
-// 4 adjacent channels with the filter window in registers.  The per-head sums are
+// written as three slabs q, k, v.  Pure streaming work.  A CTA owns 256 channels
+// and a span of token tiles; each tile (plus the halo rows the filter reaches into)
+// is staged in shared memory with 16-byte cp.async copies, double buffered, so the
+// next tile lands while the current one is computed.  A thread walks a few tokens of
+// 4 adjacent channels with the filter window in registers; the arithmetic is
+// written on pairs of channels with the packed fp32x2 instructions of sm_100
+// (fma.rn.f32x2 and friends: one issue slot for two lanes of work), because these
+// kernels are bound by instruction issue, not by DRAM.  The per-head sums are
 // shuffle reductions inside a warp (a head is at most 32 lanes).  The backward
 // recomputes the pre-activation instead of saving it: phase A turns the tile of
 // output gradients into the gradient of the pre-activation (fp32, in shared
@@ -27,16 +30,18 @@ constexpr int kLanes = kTileCh / kVec;
 constexpr int kGroups = kThreads / kLanes;  // token groups per CTA (4)
 constexpr int kMaxTaps = 4;
 constexpr int kHalo = kMaxTaps - 1;
-constexpr int kFwdTokens = 64;   // tokens per forward CTA (16 per group)
+constexpr int kFwdTokens = 64;   // tokens per forward tile (16 per group)
+constexpr int kFwdTiles = 4;     // tiles one forward CTA walks
 constexpr int kBwdTokens = 32;   // tokens per backward tile (8 per group)
 constexpr int kBwdTiles = 8;     // tiles one backward CTA walks (one weight-gradient partial per CTA)
 constexpr int kBwdDyRows = kBwdTokens + kHalo;             // 35
 constexpr int kBwdDyPerGroup = (kBwdDyRows + kGroups - 1) / kGroups;  // 9
-template <typename T> constexpr int fwd_smem() { return (kFwdTokens + kHalo) * kTileCh * (int)sizeof(T); }
-template <typename T> constexpr int bwd_smem() {
-  return (kBwdTokens + 2 * kHalo) * kTileCh * (int)sizeof(T) + kBwdDyRows * kTileCh * (int)sizeof(T) +
-         kBwdDyRows * kTileCh * 4;
+template <typename T> __host__ __device__ constexpr int fwd_stage() { return (kFwdTokens + kHalo) * kTileCh * (int)sizeof(T); }
+template <typename T> __host__ __device__ constexpr int fwd_smem() { return 2 * fwd_stage<T>(); }
+template <typename T> __host__ __device__ constexpr int bwd_stage() {
+  return ((kBwdTokens + 2 * kHalo) + kBwdDyRows) * kTileCh * (int)sizeof(T);
 }
+template <typename T> __host__ __device__ constexpr int bwd_smem() { return 2 * bwd_stage<T>() + kBwdDyRows * kTileCh * 4; }
 }  // namespace conv
 
 struct ConvParams {
@@ -50,33 +55,45 @@ struct ConvParams {
   float* part;  // [gridDim.y][channels][taps]
 };
 
+// Packed fp32x2 arithmetic (two channels per instruction).
+__device__ __forceinline__ float2 f2(float a, float b) { return make_float2(a, b); }
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
+
+// Four adjacent channels as two pairs.
 template <typename T> struct Vec4;
 template <> struct Vec4<bf16> {
-  static __device__ __forceinline__ void load(const bf16* p, float (&f)[4]) {
+  static __device__ __forceinline__ void load(const bf16* p, float2 (&f)[2]) {
     const uint2 u = *reinterpret_cast<const uint2*>(p);
-    const float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y);
-    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+    f[0] = unpack_bf16(u.x);
+    f[1] = unpack_bf16(u.y);
   }
-  static __device__ __forceinline__ void store(bf16* p, const float (&f)[4]) {
-    *reinterpret_cast<uint2*>(p) = make_uint2(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]));
+  static __device__ __forceinline__ void store(bf16* p, const float2 (&f)[2]) {
+    *reinterpret_cast<uint2*>(p) = make_uint2(pack_bf16(f[0].x, f[0].y), pack_bf16(f[1].x, f[1].y));
   }
   // 0.5 * (1 + tanh(y / 2)) with the single-instruction tanh: relative error 2^-11,
   // below the bf16 rounding of the result.
-  static __device__ __forceinline__ float sigmoid(float y) {
-    float t;
-    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * y));
-    return fmaf(0.5f, t, 0.5f);
+  static __device__ __forceinline__ float2 sigmoid(float2 y) {
+    const float2 h = mul2(y, f2(0.5f, 0.5f));
+    float2 t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t.x) : "f"(h.x));
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t.y) : "f"(h.y));
+    return fma2(t, f2(0.5f, 0.5f), f2(0.5f, 0.5f));
   }
 };
 template <> struct Vec4<float> {
-  static __device__ __forceinline__ void load(const float* p, float (&f)[4]) {
+  static __device__ __forceinline__ void load(const float* p, float2 (&f)[2]) {
     const float4 u = *reinterpret_cast<const float4*>(p);
-    f[0] = u.x; f[1] = u.y; f[2] = u.z; f[3] = u.w;
+    f[0] = f2(u.x, u.y);
+    f[1] = f2(u.z, u.w);
   }
-  static __device__ __forceinline__ void store(float* p, const float (&f)[4]) {
-    *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+  static __device__ __forceinline__ void store(float* p, const float2 (&f)[2]) {
+    *reinterpret_cast<float4*>(p) = make_float4(f[0].x, f[0].y, f[1].x, f[1].y);
   }
-  static __device__ __forceinline__ float sigmoid(float y) { return 1.f / (1.f + expf(-y)); }
+  static __device__ __forceinline__ float2 sigmoid(float2 y) {
+    return f2(1.f / (1.f + expf(-y.x)), 1.f / (1.f + expf(-y.y)));
+  }
 };
 
 // Sum over the kHeadLanes adjacent lanes of one head (a power of two <= 32; a
@@ -88,22 +105,56 @@ __device__ __forceinline__ float head_sum(float v) {
   return v;
 }
 
+// Two sums at once: the two halves of the head first trade one value each, so the
+// butterfly runs on a single register (log2(L) + 1 shuffles instead of 2 log2(L)).
+template <int kHeadLanes>
+__device__ __forceinline__ void head_sum2(float& a, float& b, int lane) {
+  if (kHeadLanes == 1) return;
+  constexpr int kHalf = kHeadLanes / 2;
+  const bool upper = lane & kHalf;
+  float keep = upper ? b : a;
+  const float send = upper ? a : b;
+  keep += __shfl_xor_sync(0xffffffffu, send, kHalf);
+#pragma unroll
+  for (int o = kHalf >> 1; o >= 1; o >>= 1) keep += __shfl_xor_sync(0xffffffffu, keep, o);
+  const float other = __shfl_xor_sync(0xffffffffu, keep, kHalf);
+  a = upper ? other : keep;
+  b = upper ? keep : other;
+}
+
 // Stages rows [t_first, t_first + rows) x 256 channels of a [seq_len][row_channels]
 // matrix into shared memory; rows outside [0, seq_len) and channels past the end
 // read as zero.
 template <typename T>
+__device__ __forceinline__ void stage_col(T* scol, const T* gcol, bool col_ok, int t_first, int rows, int seq_len,
+                                          size_t row_stride) {
+  constexpr int kPiece = 16 / (int)sizeof(T), kPerRow = conv::kTileCh / kPiece;
+  constexpr int kRowStep = conv::kThreads / kPerRow;  // a thread keeps its column piece, rows advance
+  const int r0 = threadIdx.x / kPerRow;
+  if (col_ok && t_first >= 0 && t_first + rows <= seq_len) {  // whole tile inside the row: no per-copy tests
+    const T* g = gcol + (size_t)(t_first + r0) * row_stride;
+    T* d = scol + r0 * conv::kTileCh;
+    for (int r = r0; r < rows; r += kRowStep) {
+      cp_async16(d, g, true);
+      g += kRowStep * row_stride;
+      d += kRowStep * conv::kTileCh;
+    }
+  } else {
+    for (int r = r0; r < rows; r += kRowStep) {
+      const int t = t_first + r;
+      const bool ok = col_ok && t >= 0 && t < seq_len;
+      cp_async16(scol + r * conv::kTileCh, gcol + (ok ? (size_t)t * row_stride : 0), ok);
+    }
+  }
+}
+
+template <typename T>
 __device__ __forceinline__ void stage_rows(T* s, const T* g, int t_first, int rows, int seq_len, int c_first,
                                            int row_channels) {
   constexpr int kPiece = 16 / (int)sizeof(T), kPerRow = conv::kTileCh / kPiece;
-  constexpr int kRowStep = conv::kThreads / kPerRow;  // a thread keeps its column piece, rows advance
   const int pc = (threadIdx.x % kPerRow) * kPiece, c = c_first + pc;
   const bool col_ok = c < row_channels;
-  const T* gcol = g + (col_ok ? c : 0);
-  for (int r = threadIdx.x / kPerRow; r < rows; r += kRowStep) {
-    const int t = t_first + r;
-    const bool ok = col_ok && t >= 0 && t < seq_len;
-    cp_async16(s + r * conv::kTileCh + pc, gcol + (ok ? (size_t)t * row_channels : 0), ok);
-  }
+  stage_col(s + pc, g + (col_ok ? c : 0), col_ok, t_first, rows, seq_len, (size_t)row_channels);
 }
 
 // The same for the output gradients, which live in three slabs [seq_len][slab]:
@@ -113,84 +164,186 @@ template <typename T>
 __device__ __forceinline__ void stage_grad_rows(T* s, const T* g0, const T* g1, const T* g2, int t_first, int rows,
                                                 int seq_len, int c_first, int channels, int slab) {
   constexpr int kPiece = 16 / (int)sizeof(T), kPerRow = conv::kTileCh / kPiece;
-  constexpr int kRowStep = conv::kThreads / kPerRow;
   const int pc = (threadIdx.x % kPerRow) * kPiece, c = c_first + pc;
   const bool col_ok = c < channels;
   const int id = col_ok ? c / slab : 0;
   const T* gcol = (id == 0 ? g0 : id == 1 ? g1 : g2) + (col_ok ? c - id * slab : 0);
-  for (int r = threadIdx.x / kPerRow; r < rows; r += kRowStep) {
-    const int t = t_first + r;
-    const bool ok = col_ok && t >= 0 && t < seq_len;
-    cp_async16(s + r * conv::kTileCh + pc, gcol + (ok ? (size_t)t * slab : 0), ok);
+  stage_col(s + pc, gcol, col_ok, t_first, rows, seq_len, (size_t)slab);
+}
+
+// Filter taps of the thread's four channels as pairs: w[pair][tap], padded to four taps.
+__device__ __forceinline__ void load_taps(const ConvParams& p, int c, bool active, float2 (&w)[2][4]) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int jj = j - (conv::kMaxTaps - p.taps);  // tap j of the filter padded to four taps
+    float v[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = (active && jj >= 0) ? p.w[(size_t)(c + i) * p.taps + jj] : 0.f;
+    w[0][j] = f2(v[0], v[1]);
+    w[1][j] = f2(v[2], v[3]);
   }
 }
 
-__device__ __forceinline__ void load_taps(const ConvParams& p, int c, bool active, float (&w)[4][4]) {
+// Pre-activation of one token for the thread's two channel pairs.
+__device__ __forceinline__ void conv4(float2 (&y)[2], const float2 (&w)[2][4], const float2 (&w0)[2],
+                                      const float2 (&w1)[2], const float2 (&w2)[2], const float2 (&x)[2]) {
 #pragma unroll
-  for (int i = 0; i < 4; ++i)
+  for (int pr = 0; pr < 2; ++pr) {
+    float2 a = mul2(w[pr][0], w0[pr]);
+    a = fma2(w[pr][1], w1[pr], a);
+    a = fma2(w[pr][2], w2[pr], a);
+    y[pr] = fma2(w[pr][3], x[pr], a);
+  }
+}
+
+// Forward for one group of 16 consecutive tokens of the thread's four channels:
+// two halves of 8 tokens whose 11 input rows sit in registers, addressed statically.
+// kGuard: the group reaches past the end of the row (stores are tested).
+template <typename T, int kHeadLanes, bool kGuard>
+__device__ __forceinline__ void conv_fwd_tokens(const T* col, T* orow, size_t ostride, const float2 (&w)[2][4],
+                                                bool active, bool normed, float eps, int nvalid) {
+  using namespace conv;
+  constexpr int kHalf = kFwdTokens / kGroups / 2;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int jj = j - (conv::kMaxTaps - p.taps);  // tap j of the filter padded to four taps
-      w[i][j] = (active && jj >= 0) ? p.w[(size_t)(c + i) * p.taps + jj] : 0.f;
+  for (int hseg = 0; hseg < 2; ++hseg) {
+    float2 xr[kHalf + kHalo][2];
+#pragma unroll
+    for (int j = 0; j < kHalf + kHalo; ++j) Vec4<T>::load(col + (kHalf * hseg + j) * kTileCh, xr[j]);
+#pragma unroll
+    for (int u = 0; u < kHalf; ++u) {
+      float2 y[2], s[2];
+      conv4(y, w, xr[u], xr[u + 1], xr[u + 2], xr[u + 3]);
+      s[0] = mul2(y[0], Vec4<T>::sigmoid(y[0]));
+      s[1] = mul2(y[1], Vec4<T>::sigmoid(y[1]));
+      const float2 sq = fma2(s[1], s[1], mul2(s[0], s[0]));
+      const float ss = head_sum<kHeadLanes>(sq.x + sq.y);
+      const float r = normed ? rsqrtf(ss + eps) : 1.f;
+      s[0] = mul2(s[0], f2(r, r));
+      s[1] = mul2(s[1], f2(r, r));
+      const int tok = kHalf * hseg + u;
+      if (active && (!kGuard || tok < nvalid)) Vec4<T>::store(orow + (size_t)tok * ostride, s);
     }
+  }
+}
+
+// Backward phase A for one group: the gradient of the pre-activation of kTokens
+// consecutive tokens (fp32, to shared memory) and the weight gradient of the first
+// kOwn of them (the rest are look-ahead rows owned by the next tile).
+template <typename T, int kHeadLanes, int kTokens, int kOwn>
+__device__ __forceinline__ void conv_bwd_phase_a(const T* xc, const T* dc, float* yc, const float2 (&w)[2][4],
+                                                 float2 (&dwacc)[2][4], bool normed, float eps, int lane32) {
+  using namespace conv;
+  float2 xr[kTokens + kHalo][2];
+#pragma unroll
+  for (int j = 0; j < kTokens + kHalo; ++j) Vec4<T>::load(xc + j * kTileCh, xr[j]);
+#pragma unroll
+  for (int u = 0; u < kTokens; ++u) {
+    float2 da[2], y[2], sg[2], s[2];
+    Vec4<T>::load(dc + u * kTileCh, da);
+    conv4(y, w, xr[u], xr[u + 1], xr[u + 2], xr[u + 3]);
+    sg[0] = Vec4<T>::sigmoid(y[0]);
+    sg[1] = Vec4<T>::sigmoid(y[1]);
+    s[0] = mul2(y[0], sg[0]);
+    s[1] = mul2(y[1], sg[1]);
+    const float2 sq = fma2(s[1], s[1], mul2(s[0], s[0]));
+    const float2 sdv = fma2(s[1], da[1], mul2(s[0], da[0]));
+    float ss = sq.x + sq.y, sdot = sdv.x + sdv.y;
+    head_sum2<kHeadLanes>(ss, sdot, lane32);
+    const float r = normed ? rsqrtf(ss + eps) : 1.f;
+    const float back = normed ? -r * r * r * sdot : 0.f;
+    float2 dy[2];
+#pragma unroll
+    for (int pr = 0; pr < 2; ++pr) {
+      const float2 ds = fma2(s[pr], f2(back, back), mul2(da[pr], f2(r, r)));  // r d - s r^3 <s, d>
+      const float2 om = fma2(sg[pr], f2(-1.f, -1.f), f2(1.f, 1.f));          // 1 - sig
+      dy[pr] = mul2(ds, fma2(s[pr], om, sg[pr]));                             // silu' = sig + y sig (1 - sig)
+    }
+    *reinterpret_cast<float4*>(yc + u * kTileCh) = make_float4(dy[0].x, dy[0].y, dy[1].x, dy[1].y);
+    if (u < kOwn) {
+#pragma unroll
+      for (int pr = 0; pr < 2; ++pr)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) dwacc[pr][j] = fma2(dy[pr], xr[u + j][pr], dwacc[pr][j]);
+    }
+  }
+}
+
+// Backward phase B for one group of 8 own tokens: dx[t] = sum_j w[j] dy[t + 3 - j].
+template <typename T, bool kGuard>
+__device__ __forceinline__ void conv_bwd_phase_b(const float* dc, T* drow, size_t dstride, const float2 (&w)[2][4],
+                                                 bool active, int nvalid) {
+  using namespace conv;
+  constexpr int kPer = kBwdTokens / kGroups;
+  float2 dr[kPer + kHalo][2];
+#pragma unroll
+  for (int j = 0; j < kPer + kHalo; ++j) {
+    const float4 d4 = *reinterpret_cast<const float4*>(dc + j * kTileCh);
+    dr[j][0] = f2(d4.x, d4.y);
+    dr[j][1] = f2(d4.z, d4.w);
+  }
+#pragma unroll
+  for (int u = 0; u < kPer; ++u) {
+    float2 dxv[2];
+#pragma unroll
+    for (int pr = 0; pr < 2; ++pr) {
+      float2 a = mul2(w[pr][3], dr[u][pr]);
+      a = fma2(w[pr][2], dr[u + 1][pr], a);
+      a = fma2(w[pr][1], dr[u + 2][pr], a);
+      dxv[pr] = fma2(w[pr][0], dr[u + 3][pr], a);
+    }
+    if (active && (!kGuard || u < nvalid)) Vec4<T>::store(drow + (size_t)u * dstride, dxv);
+  }
 }
 
 template <typename T, int kHeadLanes>
-__global__ void __launch_bounds__(conv::kThreads)
+__global__ void __launch_bounds__(conv::kThreads, 3)
 pkda_qkv_conv_fwd_kernel(const ConvParams p) {
   using namespace conv;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  T* sx = reinterpret_cast<T*>(smem_raw);
+  T* stage[2] = {reinterpret_cast<T*>(smem_raw), reinterpret_cast<T*>(smem_raw + fwd_stage<T>())};
   const int b = blockIdx.y / p.spans_per_row;
-  const int t0 = (blockIdx.y - b * p.spans_per_row) * kFwdTokens;
+  const int span0 = (blockIdx.y - b * p.spans_per_row) * (kFwdTokens * kFwdTiles);
   const int cb = blockIdx.x * kTileCh;
   const int lane = threadIdx.x % kLanes, grp = threadIdx.x / kLanes;
   const int c = cb + kVec * lane;
   const bool active = c < p.channels;
-  stage_rows(sx, static_cast<const T*>(p.x) + (size_t)b * p.seq_len * p.channels, t0 - kHalo, kFwdTokens + kHalo,
-             p.seq_len, cb, p.channels);
+  const T* xrow = static_cast<const T*>(p.x) + (size_t)b * p.seq_len * p.channels;
+  const int ntiles = min(kFwdTiles, (p.seq_len - span0 + kFwdTokens - 1) / kFwdTokens);
+  stage_rows(stage[0], xrow, span0 - kHalo, kFwdTokens + kHalo, p.seq_len, cb, p.channels);
   cp_async_commit();
-  float w[4][4];
+  float2 w[2][4];
   load_taps(p, c, active, w);
   const int cc = active ? c : 0;
   const int slab_id = cc / p.slab, cs = cc - slab_id * p.slab;
   const bool normed = active && c < p.norm_channels;
   T* out = static_cast<T*>(slab_id == 0 ? p.q : slab_id == 1 ? p.k : p.v) + (size_t)b * p.seq_len * p.slab + cs;
-  cp_async_wait<0>();
-  __syncthreads();
-  constexpr int kPer = kFwdTokens / kGroups;  // 16 tokens per thread
-  const T* col = sx + kVec * lane;
-  float win[3][4];
-#pragma unroll
-  for (int j = 0; j < 3; ++j) Vec4<T>::load(col + (kPer * grp + j) * kTileCh, win[j]);
-#pragma unroll
-  for (int u = 0; u < kPer; ++u) {
-    const int t = t0 + kPer * grp + u;
-    float xa[4], s[4], ss = 0.f;
-    Vec4<T>::load(col + (kPer * grp + kHalo + u) * kTileCh, xa);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float y = w[i][0] * win[0][i] + w[i][1] * win[1][i] + w[i][2] * win[2][i] + w[i][3] * xa[i];
-      s[i] = y * Vec4<T>::sigmoid(y);
-      ss += s[i] * s[i];
-      win[0][i] = win[1][i]; win[1][i] = win[2][i]; win[2][i] = xa[i];
+  constexpr int kPer = kFwdTokens / kGroups;  // 16 tokens per thread and tile
+  for (int tile = 0; tile < ntiles; ++tile) {
+    const int t0 = span0 + tile * kFwdTokens;
+    if (tile + 1 < ntiles) {
+      stage_rows(stage[(tile + 1) & 1], xrow, t0 + kFwdTokens - kHalo, kFwdTokens + kHalo, p.seq_len, cb, p.channels);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
     }
-    ss = head_sum<kHeadLanes>(ss);
-    const float r = normed ? rsqrtf(ss + p.eps) : 1.f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) s[i] *= r;
-    if (active && t < p.seq_len) Vec4<T>::store(out + (size_t)t * p.slab, s);
+    __syncthreads();
+    const T* col = stage[tile & 1] + kVec * lane + (kPer * grp) * kTileCh;
+    T* orow = out + (size_t)(t0 + kPer * grp) * p.slab;
+    const int nvalid = p.seq_len - (t0 + kPer * grp);  // tokens of this group inside the row
+    // (one code path with tested stores: a second, untested copy costs a CTA per SM in registers)
+    conv_fwd_tokens<T, kHeadLanes, true>(col, orow, (size_t)p.slab, w, active, normed, p.eps, nvalid);
+    __syncthreads();  // the buffer is staged again two tiles later
   }
 }
 
 template <typename T, int kHeadLanes>
-__global__ void __launch_bounds__(conv::kThreads)
+__global__ void __launch_bounds__(conv::kThreads, 2)
 pkda_qkv_conv_bwd_kernel(const ConvParams p) {
   using namespace conv;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  T* sx = reinterpret_cast<T*>(smem_raw);                      // tokens t0-3 .. t0+34
-  T* sd = sx + (kBwdTokens + 2 * kHalo) * kTileCh;             // tokens t0 .. t0+34
-  float* sdy = reinterpret_cast<float*>(sd + kBwdDyRows * kTileCh);  // tokens t0 .. t0+34; later the dw exchange
+  // two stages of {x rows t0-3 .. t0+34, gradient rows t0 .. t0+34}, then the fp32 dy tile
+  float* sdy = reinterpret_cast<float*>(smem_raw + 2 * bwd_stage<T>());
   const int b = blockIdx.y / p.spans_per_row;
   const int span0 = (blockIdx.y - b * p.spans_per_row) * (kBwdTokens * kBwdTiles);
   const int cb = blockIdx.x * kTileCh;
@@ -199,105 +352,76 @@ pkda_qkv_conv_bwd_kernel(const ConvParams p) {
   const bool active = c < p.channels;
   const int cc = active ? c : 0;
   const bool normed = active && c < p.norm_channels;
-  float w[4][4], dwacc[4][4];
-  load_taps(p, c, active, w);
-#pragma unroll
-  for (int i = 0; i < 4; ++i)
-#pragma unroll
-    for (int j = 0; j < 4; ++j) dwacc[i][j] = 0.f;
   const T* xrow = static_cast<const T*>(p.x) + (size_t)b * p.seq_len * p.channels;
   const size_t doff = (size_t)b * p.seq_len * p.slab;
   const T *dq = static_cast<const T*>(p.dq) + doff, *dk = static_cast<const T*>(p.dk) + doff,
           *dv = static_cast<const T*>(p.dv) + doff;
   T* dxrow = static_cast<T*>(p.dx) + (size_t)b * p.seq_len * p.channels + cc;
-  for (int tile = 0; tile < kBwdTiles; ++tile) {
+  const int ntiles = min(kBwdTiles, (p.seq_len - span0 + kBwdTokens - 1) / kBwdTokens);
+  auto stage_tile = [&](int tile) {
+    T* sx = reinterpret_cast<T*>(smem_raw + (tile & 1) * bwd_stage<T>());
+    T* sd = sx + (kBwdTokens + 2 * kHalo) * kTileCh;
     const int t0 = span0 + tile * kBwdTokens;
-    if (t0 >= p.seq_len) break;
     stage_rows(sx, xrow, t0 - kHalo, kBwdTokens + 2 * kHalo, p.seq_len, cb, p.channels);
     stage_grad_rows(sd, dq, dk, dv, t0, kBwdDyRows, p.seq_len, cb, p.channels, p.slab);
     cp_async_commit();
-    cp_async_wait<0>();
-    __syncthreads();
-    // ---- phase A: gradient of the pre-activation for tokens t0 .. t0+34
-    {
-      const int i0 = kBwdDyPerGroup * grp;
-      const T* xc = sx + kVec * lane;
-      float win[3][4];
+  };
+  stage_tile(0);
+  float2 w[2][4], dwacc[2][4];
+  load_taps(p, c, active, w);
 #pragma unroll
-      for (int j = 0; j < 3; ++j) Vec4<T>::load(xc + (i0 + j) * kTileCh, win[j]);
+  for (int pr = 0; pr < 2; ++pr)
 #pragma unroll
-      for (int u = 0; u < kBwdDyPerGroup; ++u) {
-        const int i = i0 + u;  // token t0 + i; its filter window is rows i .. i+3 of sx
-        if (i < kBwdDyRows) {
-          float xa[4], da[4], y[4], sg[4], s[4], ss = 0.f, sdot = 0.f;
-          Vec4<T>::load(xc + (i + kHalo) * kTileCh, xa);
-          Vec4<T>::load(sd + i * kTileCh + kVec * lane, da);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            y[e] = w[e][0] * win[0][e] + w[e][1] * win[1][e] + w[e][2] * win[2][e] + w[e][3] * xa[e];
-            sg[e] = Vec4<T>::sigmoid(y[e]);
-            s[e] = y[e] * sg[e];
-            ss += s[e] * s[e];
-            sdot += s[e] * da[e];
-            win[0][e] = win[1][e]; win[1][e] = win[2][e]; win[2][e] = xa[e];
-          }
-          ss = head_sum<kHeadLanes>(ss);
-          sdot = head_sum<kHeadLanes>(sdot);
-          const float r = normed ? rsqrtf(ss + p.eps) : 1.f;
-          const float back = normed ? r * r * r * sdot : 0.f;
-          float dy[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float ds = r * da[e] - s[e] * back;
-            dy[e] = ds * (sg[e] + s[e] * (1.f - sg[e]));  // silu'(y) = sig + y sig (1 - sig)
-          }
-          *reinterpret_cast<float4*>(sdy + i * kTileCh + kVec * lane) = make_float4(dy[0], dy[1], dy[2], dy[3]);
-        }
-      }
+    for (int j = 0; j < 4; ++j) dwacc[pr][j] = f2(0.f, 0.f);
+  for (int tile = 0; tile < ntiles; ++tile) {
+    const int t0 = span0 + tile * kBwdTokens;
+    if (tile + 1 < ntiles) {
+      stage_tile(tile + 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
     }
     __syncthreads();
-    // ---- phase B: dx and the weight gradient for the tile's own 32 tokens
+    const T* sx = reinterpret_cast<const T*>(smem_raw + (tile & 1) * bwd_stage<T>());
+    const T* sd = sx + (kBwdTokens + 2 * kHalo) * kTileCh;
+    // ---- phase A: gradient of the pre-activation for tokens t0 .. t0+34 and the weight gradient of
+    // the tile's own 32 tokens.  Groups 0-2 take 9 own tokens each, group 3 five own tokens and the
+    // three look-ahead rows.
+    {
+      const int i0 = kBwdDyPerGroup * grp;
+      const T* xc = sx + kVec * lane + i0 * kTileCh;
+      const T* dc = sd + kVec * lane + i0 * kTileCh;
+      float* yc = sdy + kVec * lane + i0 * kTileCh;
+      if (grp < kGroups - 1)
+        conv_bwd_phase_a<T, kHeadLanes, kBwdDyPerGroup, kBwdDyPerGroup>(xc, dc, yc, w, dwacc, normed, p.eps,
+                                                                         threadIdx.x & 31);
+      else
+        conv_bwd_phase_a<T, kHeadLanes, kBwdDyRows - (kGroups - 1) * kBwdDyPerGroup,
+                         kBwdTokens - (kGroups - 1) * kBwdDyPerGroup>(xc, dc, yc, w, dwacc, normed, p.eps,
+                                                                       threadIdx.x & 31);
+    }
+    __syncthreads();
+    // ---- phase B: dx for the tile's own 32 tokens
     {
       constexpr int kPer = kBwdTokens / kGroups;  // 8
       const int j0 = kPer * grp;
-      const T* xc = sx + kVec * lane;
-      const float* dc = sdy + kVec * lane;
-      float xw[3][4], dw3[3][4];  // x rows j..j+2 (tokens t-3..t-1), dy rows j..j+2 (tokens t..t+2)
-#pragma unroll
-      for (int j = 0; j < 3; ++j) {
-        Vec4<T>::load(xc + (j0 + j) * kTileCh, xw[j]);
-        const float4 d4 = *reinterpret_cast<const float4*>(dc + (j0 + j) * kTileCh);
-        dw3[j][0] = d4.x; dw3[j][1] = d4.y; dw3[j][2] = d4.z; dw3[j][3] = d4.w;
-      }
-#pragma unroll
-      for (int u = 0; u < kPer; ++u) {
-        const int j = j0 + u, t = t0 + j;
-        float xa[4], dn[4], dxv[4];
-        Vec4<T>::load(xc + (j + kHalo) * kTileCh, xa);  // x[t]
-        const float4 d4 = *reinterpret_cast<const float4*>(dc + (j + kHalo) * kTileCh);  // dy[t+3]
-        dn[0] = d4.x; dn[1] = d4.y; dn[2] = d4.z; dn[3] = d4.w;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float dyt = dw3[0][e];
-          dxv[e] = w[e][3] * dyt + w[e][2] * dw3[1][e] + w[e][1] * dw3[2][e] + w[e][0] * dn[e];
-          dwacc[e][0] += dyt * xw[0][e];
-          dwacc[e][1] += dyt * xw[1][e];
-          dwacc[e][2] += dyt * xw[2][e];
-          dwacc[e][3] += dyt * xa[e];
-          xw[0][e] = xw[1][e]; xw[1][e] = xw[2][e]; xw[2][e] = xa[e];
-          dw3[0][e] = dw3[1][e]; dw3[1][e] = dw3[2][e]; dw3[2][e] = dn[e];
-        }
-        if (active && t < p.seq_len) Vec4<T>::store(dxrow + (size_t)t * p.channels, dxv);
-      }
+      const float* dc = sdy + kVec * lane + j0 * kTileCh;
+      T* drow = dxrow + (size_t)(t0 + j0) * p.channels;
+      const int nvalid = p.seq_len - (t0 + j0);
+      if (nvalid >= kPer) conv_bwd_phase_b<T, false>(dc, drow, (size_t)p.channels, w, active, nvalid);
+      else conv_bwd_phase_b<T, true>(dc, drow, (size_t)p.channels, w, active, nvalid);
     }
     __syncthreads();
   }
   // ---- weight gradient: the four token groups in a fixed order, one partial per CTA
-  float* sPart = sdy;  // [kGroups][kLanes][16]
+  float* sPart = sdy;  // [kGroups][kLanes][16]; entry 4 * channel + padded tap
 #pragma unroll
-  for (int i = 0; i < 4; ++i)
+  for (int pr = 0; pr < 2; ++pr)
 #pragma unroll
-    for (int j = 0; j < 4; ++j) sPart[(grp * kLanes + lane) * 16 + 4 * i + j] = dwacc[i][j];
+    for (int j = 0; j < 4; ++j) {
+      sPart[(grp * kLanes + lane) * 16 + 4 * (2 * pr) + j] = dwacc[pr][j].x;
+      sPart[(grp * kLanes + lane) * 16 + 4 * (2 * pr + 1) + j] = dwacc[pr][j].y;
+    }
   __syncthreads();
   if (grp == 0 && active) {
 #pragma unroll
@@ -382,7 +506,7 @@ int qkv_conv_fwd(const pkda_qkv_conv_args* a, cudaStream_t st) {
   if (a->batch == 0 || a->seq_len == 0) return PKDA_OK;
   if (!a->x || !a->weight || !a->q || !a->k || !a->v) return PKDA_ERR_NULL;
   if (!aligned16(a->x) || !aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v)) return PKDA_ERR_ALIGN;
-  const dim3 grid = conv_grid(p, conv::kFwdTokens);
+  const dim3 grid = conv_grid(p, conv::kFwdTokens * conv::kFwdTiles);
   int rc = PKDA_OK;
   if (a->dtype == PKDA_BF16) { PKDA_CONV_DISPATCH(launch_conv_fwd, bf16) } else { PKDA_CONV_DISPATCH(launch_conv_fwd, float) }
   if (rc != PKDA_OK) return rc;

@@ -218,5 +218,56 @@ def _norm_gate_backward(ctx, dy, _drstd):
 
 pkda_norm_gate.register_autograd(_norm_gate_backward, setup_context=_norm_gate_setup_context)
 
-__all__ = ["pkda_qkv_conv", "pkda_norm_gate", "qkv_conv_forward", "qkv_conv_backward",
+# ----------------------------------------------------------------- decode step
+def pkda_decode_step(qkv: Tensor, conv_state, conv_weight: Tensor, g: Tensor, g_atk: Tensor,
+                     beta_atk: Tensor, beta: Tensor, A_log: Tensor, dt_bias: Tensor,
+                     log_atk_scale: Tensor, state: Tensor, a_state: Tensor, gate, norm_weight,
+                     head_dim: int, scale=None, squash_x: float = 1.5, squash_eps: float = 1e-6,
+                     qk_eps: float = 1e-6, norm_eps: float = 1e-6) -> Tensor:
+    """One cached decoding step of the layer's token mixer in one launch: the
+    history-prefixed Q|K|V convolution, one recurrence step and the RMS-norm gate
+    (reference: ``pkda.py:239-288, 473-474, 539-541`` and the cache update of
+    ``model.py:775-787``).  ``conv_state`` (three ``[B, W, taps-1]`` tensors), ``state``
+    (``[B,H,D,D]`` fp32) and ``a_state`` (``[B,H,D]`` fp32) are the decode cache and are
+    UPDATED IN PLACE.  ``qkv`` is the new projection row ``[B, 3W]``; ``g`` the raw decay
+    ``[B,H,D]``; ``g_atk`` (fp32), ``beta_atk``, ``beta`` are ``[B,H]``; ``gate`` the
+    output-gate logits ``[B,H,D]`` or None (the result is then the recurrence output).
+    Returns ``[B,H,D]``."""
+    ops._require_cuda(qkv, conv_weight, g, g_atk, beta_atk, beta, state, a_state)
+    lib = _lib.load()
+    B, C3 = qkv.shape
+    W = C3 // 3
+    H = W // head_dim
+    taps = conv_weight.shape[1]
+    act = qkv.dtype
+    cache = [state, a_state, *conv_state]
+    if state.dtype != torch.float32 or a_state.dtype != torch.float32 or not all(t.is_contiguous() for t in cache):
+        raise RuntimeError("the decode cache (state, a_state fp32; conv histories) must be contiguous: "
+                           "it is updated in place")
+    if any(c.dtype != act or tuple(c.shape) != (B, W, taps - 1) for c in conv_state):
+        raise RuntimeError("conv_state must be three [B, W, taps-1] tensors of the activation dtype")
+    a = _lib.DecodeStepArgs()
+    a.batch, a.heads, a.head_dim, a.taps = B, H, int(head_dim), int(taps)
+    a.dtype = _dtype_code(qkv)
+    a.scale = float(head_dim ** -0.5 if scale is None else scale)
+    a.squash_x, a.squash_eps, a.qk_eps, a.norm_eps = float(squash_x), float(squash_eps), float(qk_eps), float(norm_eps)
+    keep = [qkv.contiguous(), conv_weight.detach().float().contiguous(), g.to(act).contiguous(),
+            g_atk.float().contiguous(), beta_atk.to(act).contiguous(), beta.to(act).contiguous(),
+            A_log.detach().float().contiguous(), dt_bias.detach().float().contiguous(),
+            log_atk_scale.detach().float().contiguous()]
+    (a.qkv, a.conv_weight, a.g, a.g_atk, a.beta_atk, a.beta, a.A_log, a.dt_bias,
+     a.log_atk_scale) = [t.data_ptr() for t in keep]
+    a.conv_q, a.conv_k, a.conv_v = [c.data_ptr() for c in conv_state]
+    a.state, a.a_state = state.data_ptr(), a_state.data_ptr()
+    out = torch.empty((B, H, head_dim), device=qkv.device, dtype=act)
+    if gate is not None:
+        keep += [gate.to(act).contiguous(), norm_weight.detach().float().contiguous()]
+        a.gate, a.norm_weight = keep[-2].data_ptr(), keep[-1].data_ptr()
+    a.out = out.data_ptr()
+    _lib.check(lib.pkda_decode_step(C.byref(a), _lib.current_stream()), "pkda_decode_step")
+    ops._count(lib)
+    return out
+
+
+__all__ = ["pkda_decode_step", "pkda_qkv_conv", "pkda_norm_gate", "qkv_conv_forward", "qkv_conv_backward",
            "norm_gate_forward", "norm_gate_backward"]

@@ -298,6 +298,45 @@ int pkda_norm_gate_fwd(const pkda_norm_gate_args* args, void* cuda_stream);
 size_t pkda_norm_gate_bwd_workspace_bytes(const pkda_norm_gate_args* args);
 int pkda_norm_gate_bwd(const pkda_norm_gate_args* args, void* cuda_stream);
 
+/*
+ * pkda_decode_step: one cached decoding step (one new token per row) of the
+ * layer's token mixer in a single launch -- the reference's sequence
+ * pkda_qkv_conv on the history-prefixed rows (delta_feedback_experiment/pkda.py:239-288),
+ * fused_recurrent_precond_kda (pkda.py:473-474), pkda_norm_gate (pkda.py:539-541)
+ * and the cache update around them (model.py:428-468, 775-787).  The three
+ * convolution histories, the matrix state and the preconditioner state are
+ * updated IN PLACE (they are the decode cache).
+ *   qkv          [batch][3 * W]            new Q|K|V projection row, W = heads * head_dim
+ *   conv_q/k/v   [batch][W][taps - 1]      previous projections, oldest first (the
+ *                                          reference's conv_state layout, pkda.py:253-260)
+ *   conv_weight  [3 * W][taps] fp32
+ *   g            [batch][heads][head_dim]  raw decay;  g_atk fp32, beta_atk, beta [batch][heads]
+ *   state        [batch][heads][D][D] fp32, a_state [batch][heads][D] fp32
+ *   gate         [batch][heads][D] output-gate logits, or NULL: `out` is then the
+ *                recurrence output o without the RMS-norm gate
+ *   norm_weight  [D] fp32;  out [batch][heads][D]
+ * head_dim in {8, 16, 32, 64, 128}; taps 1..4.
+ */
+typedef struct pkda_decode_step_args {
+  int batch, heads, head_dim, taps;
+  int dtype;
+  float scale, squash_x, squash_eps, qk_eps, norm_eps;
+  const void* qkv;
+  void *conv_q, *conv_k, *conv_v;
+  const float* conv_weight;
+  const void* g;
+  const float* g_atk;
+  const void *beta_atk, *beta;
+  const float *A_log, *dt_bias, *log_atk_scale;
+  float *state, *a_state;
+  const void* gate;
+  const float* norm_weight;
+  void* out;
+} pkda_decode_step_args;
+
+int pkda_decode_step(const pkda_decode_step_args* args, void* cuda_stream);
+size_t pkda_sizeof_decode_step_args(void);
+
 size_t pkda_sizeof_qkv_conv_args(void);
 size_t pkda_sizeof_norm_gate_args(void);
 

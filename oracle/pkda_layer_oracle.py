@@ -52,3 +52,39 @@ def norm_gate_oracle(x: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, 
     rstd = torch.rsqrt(x.square().mean(-1, keepdim=True) + eps)
     y = x * rstd * weight * torch.sigmoid(gate)
     return y, rstd.reshape(-1)
+
+
+def decode_step_oracle(qkv, conv_state, conv_weight, g, g_atk, beta_atk, beta, A_log, dt_bias,
+                       log_atk_scale, state, a_state, gate, norm_weight, head_dim: int,
+                       squash_x: float = 1.5, squash_eps: float = 1e-6, qk_eps: float = 1e-6,
+                       norm_eps: float = 1e-6, dtype: torch.dtype = torch.float32):
+    """One cached decoding step, composed from the three oracles the way the
+    reference's layer composes its operators (``pkda.py:239-288, 473-474, 539-547``
+    and the cache update of ``model.py:775-787``).
+
+    qkv [B,3W]; conv_state: three [B,W,taps-1] histories (oldest first); g [B,H,D];
+    g_atk, beta_atk, beta [B,H]; state [B,H,D,D]; a_state [B,H,D]; gate [B,H,D] or None.
+    Returns ``(out [B,H,D], new_state, new_a_state, new_conv_state)``.
+    """
+    from oracle.pkda_oracle import pkda_recurrent_oracle
+
+    B, C3 = qkv.shape
+    W = C3 // 3
+    H = W // head_dim
+    prefix = torch.cat([s.to(dtype) for s in conv_state], dim=1).transpose(1, 2)   # [B, taps-1, 3W]
+    rows = torch.cat((prefix, qkv.to(dtype)[:, None, :]), dim=1)
+    q, k, v = qkv_conv_oracle(rows, conv_weight, head_dim, 2 * W, qk_eps, dtype)
+    hist = prefix.shape[1]
+    new_conv = tuple(part.transpose(1, 2).contiguous()
+                     for part in rows[:, rows.shape[1] - hist:].split(W, dim=-1)) if hist else conv_state
+    shape = (B, 1, H, head_dim)
+    o, S, A = pkda_recurrent_oracle(
+        q[:, -1:].reshape(shape), k[:, -1:].reshape(shape), v[:, -1:].reshape(shape),
+        g.reshape(shape), g_atk.reshape(B, 1, H), beta_atk.reshape(B, 1, H), beta.reshape(B, 1, H),
+        A_log, dt_bias, log_atk_scale, initial_state=state, initial_A_state=a_state,
+        squash_x=squash_x, squash_eps=squash_eps, dtype=dtype)
+    o = o.reshape(B, H, head_dim)
+    if gate is None:
+        return o, S, A, new_conv
+    y, _ = norm_gate_oracle(o, gate, norm_weight, norm_eps, dtype)
+    return y, S, A, new_conv

@@ -14,6 +14,9 @@ own code for the two operators next to the recurrence.
   that the layer output IS the result of the reference's inline RMS-norm / sigmoid
   gate code (``pkda.py:543-547``) on known inputs.
 
+* Decode cases call ``PreconditionedKDA.forward`` on CPU for consecutive cached
+  single-token steps (see ``run_decode``).
+
 Everything is float32; gradients come from torch autograd through the
 reference's code.
 """
@@ -131,6 +134,88 @@ def run_gate(ref_root: str, case: tuple) -> dict:
     }
 
 
+# name -> (B, H, D, taps, steps, seed)
+DECODE_CASES = {
+    "layer_decode_small": (2, 3, 16, 4, 3, 41),
+    "layer_decode_d128": (2, 2, 128, 4, 2, 42),
+    "layer_decode_taps2_d64": (3, 1, 64, 2, 2, 43),
+}
+
+
+def run_decode(ref_root: str, case: tuple) -> dict:
+    """Cached single-token steps through the reference's ``PreconditionedKDA.forward`` on CPU
+    (``state`` / ``a_state`` / ``conv_state`` given, ``output_final_state=True``): the real
+    ``_project`` (history-prefixed convolution, SiLU, L2 norm), the real recurrence and the real
+    norm-gate code run; the control projections and the gate up-projection return seeded tensors,
+    Q|K|V projections are channel selections and the output projection is the identity."""
+    sys.path.insert(0, ref_root)
+    import delta_feedback_experiment.pkda as ref_pkda
+    from delta_feedback_experiment.pkda import QK_NORM_EPS, PreconditionedKDA
+
+    B, H, D, taps, steps, seed = case
+    W = H * D
+    gen = torch.Generator().manual_seed(seed)
+    layer = PreconditionedKDA(3 * W, num_heads=H, head_dim=D, conv_size=taps)
+    eye, zero = torch.eye(W), torch.zeros(W, W)
+    with torch.no_grad():
+        layer.q_proj.weight.copy_(torch.cat((eye, zero, zero), dim=1))
+        layer.k_proj.weight.copy_(torch.cat((zero, eye, zero), dim=1))
+        layer.v_proj.weight.copy_(torch.cat((zero, zero, eye), dim=1))
+        for conv in (layer.q_conv, layer.k_conv, layer.v_conv):
+            conv.weight.copy_(torch.randn(conv.weight.shape, generator=gen) * 0.5)
+        layer.o_proj.weight.copy_(torch.cat((eye, zero, zero), dim=0))   # output = (mixed, 0, 0)
+        layer.output_norm.copy_(1.0 + 0.3 * torch.randn(D, generator=gen))
+        layer.A_log.copy_(torch.log(torch.empty(H).uniform_(1.0, 4.0, generator=gen)))
+        layer.dt_bias.copy_(0.1 * torch.randn(W, generator=gen))
+        layer.log_precond_center.copy_(-0.2 + 0.05 * torch.randn(H, generator=gen))
+    state = torch.randn(B, H, D, D, generator=gen) * 0.1
+    a_state = torch.rand(B, H, D, generator=gen) * 0.05
+    conv_state = tuple(torch.randn(B, W, taps - 1, generator=gen) for _ in range(3))
+    out = {
+        "conv_weight": torch.cat([c.weight.detach().squeeze(1) for c in (layer.q_conv, layer.k_conv, layer.v_conv)], 0).numpy(),
+        "A_log": layer.A_log.detach().numpy(), "dt_bias": layer.dt_bias.detach().numpy(),
+        "log_atk_scale": layer.log_precond_center.detach().numpy(), "norm_weight": layer.output_norm.detach().numpy(),
+        "head_dim": np.int64(D), "qk_eps": np.float64(QK_NORM_EPS), "norm_eps": np.float64(layer.norm_eps),
+        "squash_x": np.float64(layer.squash_x), "squash_eps": np.float64(layer.squash_eps),
+        "state0": state.numpy().copy(), "a_state0": a_state.numpy().copy(),
+        "steps": np.int64(steps),
+    }
+    for i, s in enumerate(conv_state):
+        out[f"conv0_{i}"] = s.numpy().copy()
+    real_F = ref_pkda.F
+    for t in range(steps):
+        x = torch.randn(B, 1, 3 * W, generator=gen)
+        raw = torch.randn(B, 1, H, D, generator=gen)
+        beta = torch.sigmoid(torch.randn(B, 1, H, generator=gen))
+        g_atk = -torch.nn.functional.softplus(torch.randn(B, 1, H, generator=gen))
+        beta_atk = torch.sigmoid(torch.randn(B, 1, H, generator=gen))
+        gate_logits = torch.randn(B, 1, W, generator=gen) * 2.0
+        hidden = torch.zeros(B, 1, D)
+        layer._controls = lambda _x, c=(raw, beta, g_atk, beta_atk, hidden): c
+        shim = types.SimpleNamespace(**{n: getattr(real_F, n) for n in dir(real_F) if not n.startswith("__")})
+        shim.linear = lambda inp, weight, bias=None, gl=gate_logits, hd=hidden: (
+            gl if inp is hd else real_F.linear(inp, weight, bias))
+        ref_pkda.F = shim
+        try:
+            with torch.no_grad():
+                mixed, state, a_state, conv_state = layer(x, state=state, a_state=a_state, conv_state=conv_state,
+                                                          output_final_state=True)
+        finally:
+            ref_pkda.F = real_F
+        out[f"qkv_{t}"] = x[:, 0].numpy()
+        out[f"g_{t}"] = raw[:, 0].numpy()
+        out[f"beta_{t}"] = beta[:, 0].numpy()
+        out[f"g_atk_{t}"] = g_atk[:, 0].numpy()
+        out[f"beta_atk_{t}"] = beta_atk[:, 0].numpy()
+        out[f"gate_{t}"] = gate_logits[:, 0].reshape(B, H, D).numpy()
+        out[f"out_{t}"] = mixed[:, 0, :W].reshape(B, H, D).numpy()
+        out[f"state_{t}"] = state.numpy().copy()
+        out[f"a_state_{t}"] = a_state.numpy().copy()
+        for i, s in enumerate(conv_state):
+            out[f"conv_{t}_{i}"] = s.numpy().copy()
+    return out
+
+
 def main() -> None:
     if len(sys.argv) != 2:
         raise SystemExit(__doc__)
@@ -140,6 +225,9 @@ def main() -> None:
         print("wrote", name)
     for name, case in GATE_CASES.items():
         np.savez_compressed(os.path.join(HERE, name + ".npz"), **run_gate(sys.argv[1], case))
+        print("wrote", name)
+    for name, case in DECODE_CASES.items():
+        np.savez_compressed(os.path.join(HERE, name + ".npz"), **run_decode(sys.argv[1], case))
         print("wrote", name)
 
 

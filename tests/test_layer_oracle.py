@@ -65,3 +65,34 @@ def test_conv_is_causal_and_row_independent():
     other = qkv_conv_oracle(x2, w, 8, 32, 1e-6)
     for a, b in zip(base, other):
         assert torch.equal(a[0, :7], b[0, :7])
+
+
+DECODE_CASES = ["layer_decode_small", "layer_decode_d128", "layer_decode_taps2_d64"]
+
+
+def decode_golden_steps(g):
+    """Yields per step (inputs dict, expected dict) of a decode golden file."""
+    for t in range(int(g["steps"])):
+        ins = {k: g[f"{k}_{t}"] for k in ("qkv", "g", "beta", "g_atk", "beta_atk", "gate")}
+        exp = {"out": g[f"out_{t}"], "state": g[f"state_{t}"], "a_state": g[f"a_state_{t}"],
+               "conv": [g[f"conv_{t}_{i}"] for i in range(3)]}
+        yield ins, exp
+
+
+@pytest.mark.parametrize("name", DECODE_CASES)
+def test_decode_step_oracle_matches_reference_golden(name):
+    from oracle.pkda_layer_oracle import decode_step_oracle
+    g = load_golden(name)
+    state, a_state = g["state0"], g["a_state0"]
+    conv = [g[f"conv0_{i}"] for i in range(3)]
+    for t, (ins, exp) in enumerate(decode_golden_steps(g)):
+        out, state, a_state, conv = decode_step_oracle(
+            ins["qkv"], conv, g["conv_weight"], ins["g"], ins["g_atk"], ins["beta_atk"], ins["beta"],
+            g["A_log"], g["dt_bias"], g["log_atk_scale"], state, a_state, ins["gate"], g["norm_weight"],
+            int(g["head_dim"]), float(g["squash_x"]), float(g["squash_eps"]), float(g["qk_eps"]),
+            float(g["norm_eps"]))
+        assert_close(out, exp["out"], 2e-5, f"{name}:out{t}")
+        assert_close(state, exp["state"], 2e-5, f"{name}:state{t}")
+        assert_close(a_state, exp["a_state"], 2e-5, f"{name}:a_state{t}")
+        for i in range(3):
+            assert torch.equal(conv[i], exp["conv"][i]), f"{name}:conv{t}_{i}"

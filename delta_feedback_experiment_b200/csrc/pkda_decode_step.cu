@@ -66,24 +66,62 @@ pkda_decode_step_kernel(const DecodeParams p) {
       S[r] = *reinterpret_cast<const float4*>(p.S + sbase + (size_t)(krow0 + r) * D + 4 * vq);
   }
 
-  // ---- convolution over the cached history, SiLU; the history moves up by one token
+  // ---- every other global read of the step is issued now as well, so that the step pays one
+  // memory round trip, not one per stage
   const T* qkv = static_cast<const T*>(p.qkv) + (size_t)n * 3 * W;
   const int hist = p.taps - 1;
-  for (int item = tid; item < 3 * D; item += kThreads) {
-    const int slab = item / D, d = item - slab * D;
-    const int cs = h * D + d;                 // channel inside the slab
-    const float* w = p.conv_w + (size_t)(slab * W + cs) * p.taps;
-    T* hs = static_cast<T*>(p.conv[slab]) + ((size_t)n * W + cs) * hist;
-    const T xn = qkv[slab * W + cs];
-    float y = w[hist] * to_f(xn);
-    T prev[3];
-    for (int j = 0; j < hist; ++j) {
-      prev[j] = hs[j];
-      y += w[j] * to_f(prev[j]);
+  constexpr int kItems = (3 * D + kThreads - 1) / kThreads;  // (slab, channel) items per thread
+  T xn[kItems], hv[kItems][3];
+  float wv[kItems][4];
+#pragma unroll
+  for (int it = 0; it < kItems; ++it) {
+    const int item = tid + it * kThreads;
+    if (item < 3 * D) {
+      const int slab = item / D, d = item - slab * D, cs = h * D + d;
+      const float* w = p.conv_w + (size_t)(slab * W + cs) * p.taps;
+      const T* hs = static_cast<const T*>(p.conv[slab]) + ((size_t)n * W + cs) * hist;
+      xn[it] = qkv[slab * W + cs];
+#pragma unroll
+      for (int j = 0; j < 3; ++j) {
+        if (j < hist) { hv[it][j] = hs[j]; wv[it][j] = w[j]; }
+      }
+      wv[it][3] = w[hist];
     }
-    for (int j = 0; j + 1 < hist; ++j) hs[j] = prev[j + 1];
-    if (hist > 0) hs[hist - 1] = xn;
-    s_qkv[slab][d] = y / (1.f + expf(-y));
+  }
+  const size_t sidx = (size_t)n * H + h;
+  const float ea = expf(p.A_log[h]);
+  const float centre = p.log_atk_scale[h];
+  float A = 0.f, r_pd = 0.f, r_ba = 0.f, r_b = 0.f, r_g = 0.f, r_bias = 0.f, r_gate = 0.f, r_nw = 0.f;
+  if (tid < D) {
+    A = p.A[sidx * D + tid];
+    r_pd = p.g_atk[sidx];
+    r_ba = to_f(static_cast<const T*>(p.beta_atk)[sidx]);
+    r_b = to_f(static_cast<const T*>(p.beta)[sidx]);
+    r_g = to_f(static_cast<const T*>(p.g)[sidx * D + tid]);
+    r_bias = p.dt_bias[h * D + tid];
+    if (p.gate) {
+      r_gate = to_f(static_cast<const T*>(p.gate)[sidx * D + tid]);
+      r_nw = p.norm_w[tid];
+    }
+  }
+
+  // ---- convolution over the cached history, SiLU; the history moves up by one token
+#pragma unroll
+  for (int it = 0; it < kItems; ++it) {
+    const int item = tid + it * kThreads;
+    if (item < 3 * D) {
+      const int slab = item / D, d = item - slab * D, cs = h * D + d;
+      T* hs = static_cast<T*>(p.conv[slab]) + ((size_t)n * W + cs) * hist;
+      float y = wv[it][3] * to_f(xn[it]);
+#pragma unroll
+      for (int j = 0; j < 3; ++j)
+        if (j < hist) y += wv[it][j] * to_f(hv[it][j]);
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+        if (j + 1 < hist) hs[j] = hv[it][j + 1];
+      if (hist > 0) hs[hist - 1] = xn[it];
+      s_qkv[slab][d] = y / (1.f + expf(-y));
+    }
   }
   __syncthreads();
   // ---- per-head L2 norm of q (warp 0) and k (warp 1); q, k, v rounded to the activation type,
@@ -97,22 +135,16 @@ pkda_decode_step_kernel(const DecodeParams p) {
   }
   __syncthreads();
 
-  float A = 0.f;
-  const float ea = expf(p.A_log[h]);
-  const float centre = p.log_atk_scale[h];
-  const size_t sidx = (size_t)n * H + h;
   if (tid < D) {
     const float qn = round_to<T>(s_qkv[0][tid] * s_stat[kWarps + 0]);
     const float kc = round_to<T>(s_qkv[1][tid] * s_stat[kWarps + 1]);
     const float vv = round_to<T>(s_qkv[2][tid]);
-    A = p.A[sidx * D + tid];
-    const float pd = expf(p.g_atk[sidx]);
-    A = pd * A + to_f(static_cast<const T*>(p.beta_atk)[sidx]) * kc * kc;
+    A = expf(r_pd) * A + r_ba * kc * kc;
     const float kw = kc * precond_factor(A, p.eps, centre, p.ln_x);
     s_k[tid] = kc;
-    s_wk[tid] = to_f(static_cast<const T*>(p.beta)[sidx]) * kw;
+    s_wk[tid] = r_b * kw;
     s_q[tid] = qn * p.scale;
-    s_al[tid] = expf(-ea * softplus_acc(to_f(static_cast<const T*>(p.g)[sidx * D + tid]) + p.dt_bias[h * D + tid]));
+    s_al[tid] = expf(-ea * softplus_acc(r_g + r_bias));
     s_v[tid] = vv;
   }
   __syncthreads();
@@ -169,8 +201,7 @@ pkda_decode_step_kernel(const DecodeParams p) {
 #pragma unroll
     for (int w = 0; w < kWarps; ++w) tot += s_stat[w];
     const float rstd = rsqrtf(tot / (float)D + p.norm_eps);
-    const float gl = to_f(static_cast<const T*>(p.gate)[sidx * D + tid]);
-    out[tid] = from_f<T>(o * rstd * p.norm_w[tid] / (1.f + expf(-gl)));
+    out[tid] = from_f<T>(o * rstd * r_nw / (1.f + expf(-r_gate)));
   }
 }
 

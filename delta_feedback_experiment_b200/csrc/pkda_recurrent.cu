@@ -117,11 +117,13 @@ pkda_recurrent_kernel(const RecParams p) {
         e.x -= pr.x; e.y -= pr.y; e.z -= pr.z; e.w -= pr.w;
       }
       acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      const bool last = p.ST && t == sq.len - 1;  // final state rows leave as soon as they are final
 #pragma unroll
       for (int r = 0; r < R; ++r) {
         const float wk = s_wk[krow0 + r], qq = s_q[krow0 + r];
         S[r].x += wk * e.x; S[r].y += wk * e.y; S[r].z += wk * e.z; S[r].w += wk * e.w;
         acc.x += S[r].x * qq; acc.y += S[r].y * qq; acc.z += S[r].z * qq; acc.w += S[r].w * qq;
+        if (last) *reinterpret_cast<float4*>(p.ST + sbase + (size_t)(krow0 + r) * D + 4 * vq) = S[r];
       }
       *reinterpret_cast<float4*>(&s_red[1][kq][4 * vq]) = acc;
     }
@@ -133,7 +135,7 @@ pkda_recurrent_kernel(const RecParams p) {
       o[sidx * D + tid] = from_f<T>(sum);
     }
   }
-  if (p.ST && active) {
+  if (p.ST && active && sq.len == 0) {  // no token: the state passes through
 #pragma unroll
     for (int r = 0; r < R; ++r)
       *reinterpret_cast<float4*>(p.ST + sbase + (size_t)(krow0 + r) * D + 4 * vq) = S[r];

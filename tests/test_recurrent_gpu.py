@@ -102,3 +102,27 @@ def test_run_twice_is_bitwise_identical():
     b = call(fused_recurrent_precond_kda, d)
     for x, y in zip(a, b):
         assert torch.equal(x, y)
+
+
+@pytest.mark.parametrize("dtype,inplace", [(torch.bfloat16, True), (torch.float32, False)])
+def test_large_decode_batch(dtype, inplace):
+    """Several (row, head) units per SM: two consecutive cached single-token steps, states
+    carried (in place or not), against the oracle."""
+    B, H, D, steps = 42, 16, 128, 2
+    d = make_inputs(B, steps, H, D, seed=77, dist="production", dtype=dtype, with_state=True)
+    ref_o, ref_S, ref_A = pkda_recurrent_oracle(*[d[n] for n in INPUT_NAMES],
+                                                initial_state=d["initial_state"],
+                                                initial_A_state=d["initial_A_state"])
+    t = {n: d[n].cuda() for n in INPUT_NAMES}
+    S, A = d["initial_state"].cuda(), d["initial_A_state"].cuda()
+    outs = []
+    for s in range(steps):
+        o, S, A = fused_recurrent_precond_kda(
+            **{n: t[n][:, s:s + 1].contiguous() for n in INPUT_NAMES[:7]}, A_log=t["A_log"],
+            dt_bias=t["dt_bias"], initial_state=S, initial_A_state=A, output_final_state=True,
+            log_atk_scale=t["log_atk_scale"], inplace_state=inplace)
+        outs.append(o)
+    rtol = 2e-2 if dtype == torch.bfloat16 else 1e-4
+    assert_close(torch.cat(outs, 1), ref_o, rtol, "o")
+    assert_close(S, ref_S, 1e-4, "S")
+    assert_close(A, ref_A, 1e-4, "A")

@@ -116,6 +116,25 @@ class DecodeStepArgs(C.Structure):
     ]
 
 
+class ControlsArgs(C.Structure):
+    _fields_ = [
+        ("rows", C.c_longlong), ("heads", C.c_int32), ("hidden", C.c_int32), ("dtype", C.c_int32),
+        ("packed", C.c_void_p), ("A_log_precond", C.c_void_p), ("dt_bias_precond", C.c_void_p),
+        ("beta", C.c_void_p), ("g_atk", C.c_void_p), ("beta_atk", C.c_void_p),
+        ("d_decay_hidden", C.c_void_p), ("d_beta", C.c_void_p), ("d_g_atk", C.c_void_p),
+        ("d_beta_atk", C.c_void_p), ("d_gate_hidden", C.c_void_p), ("d_packed", C.c_void_p),
+        ("dA_log_precond", C.c_void_p), ("ddt_bias_precond", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
+
+
+class PackControlArgs(C.Structure):
+    _fields_ = [
+        ("rows", C.c_longlong), ("sizes", C.c_int32 * 5), ("dtype", C.c_int32),
+        ("grads", C.c_void_p * 5), ("out", C.c_void_p),
+    ]
+
+
 EXPORTS = (
     "pkda_recurrent_fwd", "pkda_recurrent_bwd", "pkda_recurrent_bwd_workspace_bytes", "pkda_chunk_fwd_workspace_bytes", "pkda_chunk_fwd",
     "pkda_chunk_bwd_workspace_bytes", "pkda_chunk_bwd", "pkda_abi_version",
@@ -127,6 +146,8 @@ EXPORTS = (
     "pkda_norm_gate_fwd", "pkda_norm_gate_bwd_workspace_bytes", "pkda_norm_gate_bwd",
     "pkda_sizeof_qkv_conv_args", "pkda_sizeof_norm_gate_args",
     "pkda_decode_step", "pkda_sizeof_decode_step_args",
+    "pkda_controls_fwd", "pkda_controls_bwd_workspace_bytes", "pkda_controls_bwd",
+    "pkda_pack_control_gradients", "pkda_sizeof_controls_args", "pkda_sizeof_pack_control_args",
 )
 
 _lib: Optional[C.CDLL] = None
@@ -160,13 +181,21 @@ def _configure(lib: C.CDLL) -> None:
         getattr(lib, name + "_bwd_workspace_bytes").restype = C.c_size_t
     lib.pkda_decode_step.argtypes = [C.POINTER(DecodeStepArgs), C.c_void_p]
     lib.pkda_decode_step.restype = C.c_int
+    for name in ("pkda_controls_fwd", "pkda_controls_bwd"):
+        getattr(lib, name).argtypes = [C.POINTER(ControlsArgs), C.c_void_p]
+        getattr(lib, name).restype = C.c_int
+    lib.pkda_controls_bwd_workspace_bytes.argtypes = [C.POINTER(ControlsArgs)]
+    lib.pkda_controls_bwd_workspace_bytes.restype = C.c_size_t
+    lib.pkda_pack_control_gradients.argtypes = [C.POINTER(PackControlArgs), C.c_void_p]
+    lib.pkda_pack_control_gradients.restype = C.c_int
     lib.pkda_abi_version.restype = C.c_int
     lib.pkda_status_string.argtypes = [C.c_int]
     lib.pkda_status_string.restype = C.c_char_p
     for name in ("pkda_sizeof_problem", "pkda_sizeof_recurrent_args",
                  "pkda_sizeof_chunk_fwd_args", "pkda_sizeof_chunk_bwd_args",
                  "pkda_sizeof_qkv_conv_args", "pkda_sizeof_norm_gate_args",
-                 "pkda_sizeof_decode_step_args"):
+                 "pkda_sizeof_decode_step_args", "pkda_sizeof_controls_args",
+                 "pkda_sizeof_pack_control_args"):
         getattr(lib, name).restype = C.c_size_t
     lib.pkda_last_launch_count.restype = C.c_int
     lib.pkda_stage_count.restype = C.c_int
@@ -199,7 +228,9 @@ def load() -> C.CDLL:
                  (lib.pkda_sizeof_chunk_bwd_args(), ChunkBwdArgs),
                  (lib.pkda_sizeof_qkv_conv_args(), QkvConvArgs),
                  (lib.pkda_sizeof_norm_gate_args(), NormGateArgs),
-                 (lib.pkda_sizeof_decode_step_args(), DecodeStepArgs))
+                 (lib.pkda_sizeof_decode_step_args(), DecodeStepArgs),
+                 (lib.pkda_sizeof_controls_args(), ControlsArgs),
+                 (lib.pkda_sizeof_pack_control_args(), PackControlArgs))
         for size, struct in sizes:
             if size != C.sizeof(struct):
                 raise OSError(f"struct layout mismatch for {struct.__name__}")

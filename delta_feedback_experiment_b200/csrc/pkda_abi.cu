@@ -151,6 +151,28 @@ int pkda_decode_step(const pkda_decode_step_args* args, void* cuda_stream) {
   return pkda::decode_step(args, static_cast<cudaStream_t>(cuda_stream));
 }
 
+int pkda_controls_fwd(const pkda_controls_args* args, void* cuda_stream) {
+  if (!args) return PKDA_ERR_NULL;
+  pkda::reset_launch_count();
+  return pkda::controls_fwd(args, static_cast<cudaStream_t>(cuda_stream));
+}
+
+size_t pkda_controls_bwd_workspace_bytes(const pkda_controls_args* args) {
+  return args ? pkda::controls_bwd_workspace(*args) : 0;
+}
+
+int pkda_controls_bwd(const pkda_controls_args* args, void* cuda_stream) {
+  if (!args) return PKDA_ERR_NULL;
+  pkda::reset_launch_count();
+  return pkda::controls_bwd(args, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int pkda_pack_control_gradients(const pkda_pack_control_args* args, void* cuda_stream) {
+  if (!args) return PKDA_ERR_NULL;
+  pkda::reset_launch_count();
+  return pkda::pack_control_gradients(args, static_cast<cudaStream_t>(cuda_stream));
+}
+
 int pkda_abi_version(void) { return PKDA_ABI_VERSION; }
 
 const char* pkda_status_string(int status) {
@@ -174,6 +196,8 @@ size_t pkda_sizeof_chunk_bwd_args(void) { return sizeof(pkda_chunk_bwd_args); }
 size_t pkda_sizeof_qkv_conv_args(void) { return sizeof(pkda_qkv_conv_args); }
 size_t pkda_sizeof_norm_gate_args(void) { return sizeof(pkda_norm_gate_args); }
 size_t pkda_sizeof_decode_step_args(void) { return sizeof(pkda_decode_step_args); }
+size_t pkda_sizeof_controls_args(void) { return sizeof(pkda_controls_args); }
+size_t pkda_sizeof_pack_control_args(void) { return sizeof(pkda_pack_control_args); }
 int pkda_last_launch_count(void) { return pkda::g_launches; }
 
 int pkda_set_direct_block_cap(int cap) {
@@ -188,7 +212,7 @@ const char* pkda_stage_name(int stage) {
   static const char* names[] = {"chunk_offsets", "pack_beta", "atk_local", "atk_carry", "intra_fwd", "scan_fwd",
                                 "out_fwd", "scan_bwd", "intra_bwd", "atk_bwd_local", "atk_bwd_carry",
                                 "atk_bwd_final", "param_reduce", "recurrent", "qkv_conv_fwd", "qkv_conv_bwd",
-                                "qkv_conv_dw", "norm_gate_fwd", "norm_gate_bwd", "norm_gate_dw", "decode_step"};
+                                "qkv_conv_dw", "norm_gate_fwd", "norm_gate_bwd", "norm_gate_dw", "decode_step", "controls_fwd", "controls_bwd", "pack_control"};
   return (stage >= 0 && stage < pkda::kStageCount) ? names[stage] : "?";
 }
 

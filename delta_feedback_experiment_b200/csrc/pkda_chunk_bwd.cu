@@ -1032,29 +1032,43 @@ pkda_atk_bwd_carry_kernel(Geo geo, const float* c_loc, const float* sa, float* l
 }
 
 // Deterministic reduction of the per-chunk partial sums of the three per-head
-// parameter gradients.  grid (H), 128 threads.
-__global__ void __launch_bounds__(kD)
+// parameter gradients.  grid (H), 1024 threads: eight sub-ranges of the chunk axis are
+// summed side by side per channel and then added in order.
+constexpr int kReduceSubs = 8;
+__global__ void __launch_bounds__(kD * kReduceSubs)
 pkda_param_reduce_kernel(Geo geo, const float* partA, const float* partB, const float* partC, float* dA_log,
                          float* ddt_bias, float* dcentre) {
+  __shared__ float sSub[kReduceSubs][kD];
   __shared__ float sR[2][4];
-  const int h = blockIdx.x, H = geo.heads, c = threadIdx.x, warp = c >> 5, lane = c & 31;
+  const int h = blockIdx.x, H = geo.heads, tid = threadIdx.x, c = tid % kD, sub = tid / kD;
+  const int warp = tid >> 5, lane = tid & 31;
   const int nreal = geo.cu_seqlens ? geo.chunk_offsets[geo.n_seqs] : geo.total_chunks;
+  const int per = (nreal + kReduceSubs - 1) / kReduceSubs;
+  const int lo = sub * per, hi = min(nreal, lo + per);
   float b = 0.f;
-  for (int ch = 0; ch < nreal; ++ch) b += partB[((size_t)ch * H + h) * kD + c];
-  ddt_bias[h * kD + c] = b;
+  for (int ch = lo; ch < hi; ++ch) b += partB[((size_t)ch * H + h) * kD + c];
+  sSub[sub][c] = b;
   float a = 0.f, cc = 0.f;
-  for (int ch = c; ch < nreal; ch += kD) {
-    a += partA[(size_t)ch * H + h];
-    cc += partC[(size_t)ch * H + h];
-  }
+  if (tid < kD) {
+    for (int ch = c; ch < nreal; ch += kD) {
+      a += partA[(size_t)ch * H + h];
+      cc += partC[(size_t)ch * H + h];
+    }
 #pragma unroll
-  for (int o = 16; o >= 1; o >>= 1) {
-    a += __shfl_xor_sync(0xffffffffu, a, o);
-    cc += __shfl_xor_sync(0xffffffffu, cc, o);
+    for (int o = 16; o >= 1; o >>= 1) {
+      a += __shfl_xor_sync(0xffffffffu, a, o);
+      cc += __shfl_xor_sync(0xffffffffu, cc, o);
+    }
+    if (lane == 0) { sR[0][warp] = a; sR[1][warp] = cc; }
   }
-  if (lane == 0) { sR[0][warp] = a; sR[1][warp] = cc; }
   __syncthreads();
-  if (c == 0) {
+  if (tid < kD) {
+    float t = 0.f;
+#pragma unroll
+    for (int s2 = 0; s2 < kReduceSubs; ++s2) t += sSub[s2][c];
+    ddt_bias[h * kD + c] = t;
+  }
+  if (tid == 0) {
     dA_log[h] = sR[0][0] + sR[0][1] + sR[0][2] + sR[0][3];
     dcentre[h] = sR[1][0] + sR[1][1] + sR[1][2] + sR[1][3];
   }
@@ -1219,7 +1233,7 @@ int chunk_bwd(const pkda_chunk_bwd_args* a, cudaStream_t st) {
   pkda_atk_bwd_kernel<true><<<atk_grid, atkb::kThreads, atkb::smem_bytes<true>(), st>>>(ap, atk_tiles);
   PKDA_CHECK_LAUNCH();
   begin_stage(kStageParamReduce, st);
-  pkda_param_reduce_kernel<<<p.heads, kD, 0, st>>>(geo, ws.partA, ws.partB, ws.partC, a->dA_log, a->ddt_bias,
+  pkda_param_reduce_kernel<<<p.heads, kD * kReduceSubs, 0, st>>>(geo, ws.partA, ws.partB, ws.partC, a->dA_log, a->ddt_bias,
                                                    a->dlog_atk_scale);
   PKDA_CHECK_LAUNCH();
   return PKDA_OK;

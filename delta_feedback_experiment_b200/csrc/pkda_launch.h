@@ -13,7 +13,8 @@ enum Stage {
   kStageOffsets = 0, kStagePackBeta, kStageAtkLocal, kStageAtkCarry, kStageIntraFwd, kStageScanFwd,
   kStageOutFwd, kStageScanBwd, kStageIntraBwd, kStageAtkBwdLocal, kStageAtkBwdCarry, kStageAtkBwdFinal,
   kStageParamReduce, kStageRecurrent, kStageConvFwd, kStageConvBwd, kStageConvDw, kStageNormGateFwd,
-  kStageNormGateBwd, kStageNormGateDw, kStageDecodeStep, kStageCount
+  kStageNormGateBwd, kStageNormGateDw, kStageDecodeStep, kStageControlsFwd, kStageControlsBwd,
+  kStagePackControl, kStageCount
 };
 
 // begin_stage / end_stage bracket every kernel launch: they count launches and,
@@ -56,5 +57,9 @@ int norm_gate_fwd(const pkda_norm_gate_args* a, cudaStream_t st);
 int norm_gate_bwd(const pkda_norm_gate_args* a, cudaStream_t st);
 size_t norm_gate_bwd_workspace(const pkda_norm_gate_args& a);
 int decode_step(const pkda_decode_step_args* a, cudaStream_t st);
+int controls_fwd(const pkda_controls_args* a, cudaStream_t st);
+int controls_bwd(const pkda_controls_args* a, cudaStream_t st);
+size_t controls_bwd_workspace(const pkda_controls_args& a);
+int pack_control_gradients(const pkda_pack_control_args* a, cudaStream_t st);
 
 }  // namespace pkda

@@ -269,5 +269,115 @@ def pkda_decode_step(qkv: Tensor, conv_state, conv_weight: Tensor, g: Tensor, g_
     return out
 
 
-__all__ = ["pkda_decode_step", "pkda_qkv_conv", "pkda_norm_gate", "qkv_conv_forward", "qkv_conv_backward",
+# ------------------------------------------------------------ control epilogue
+def pack_control_gradients(gradients) -> Tensor:
+    """The reference's ``pack_control_gradients`` (``cuda_kernels.py:1529-1535``): five
+    contiguous slices with a common leading shape -> one row-major packed tensor."""
+    if len(gradients) != 5:
+        raise ValueError("PKDA has exactly five packed control gradients")
+    g0 = gradients[0]
+    ops._require_cuda(*gradients)
+    prefix = g0.shape[:-1]
+    if any(g.shape[:-1] != prefix or g.dtype != g0.dtype for g in gradients[1:]):
+        raise ValueError("control gradients must share their leading shape and dtype")
+    if any(not g.is_contiguous() for g in gradients):
+        raise ValueError("control gradients must be contiguous")
+    lib = _lib.load()
+    a = _lib.PackControlArgs()
+    a.rows = g0.numel() // max(g0.shape[-1], 1) if g0.shape[-1] else (gradients[1].numel() // max(gradients[1].shape[-1], 1))
+    total = 0
+    for i, g in enumerate(gradients):
+        a.sizes[i] = g.shape[-1]
+        a.grads[i] = g.data_ptr()
+        total += g.shape[-1]
+    a.dtype = _dtype_code(g0)
+    out = torch.empty((*prefix, total), device=g0.device, dtype=g0.dtype)
+    a.out = out.data_ptr()
+    _lib.check(lib.pkda_pack_control_gradients(C.byref(a), _lib.current_stream()), "pkda_pack_control_gradients")
+    ops._count(lib)
+    return out
+
+
+@torch.library.custom_op("delta_feedback::pack_control_gradients", mutates_args=(), device_types="cuda")
+def _pack_control_gradients_op(grad0: Tensor, grad1: Tensor, grad2: Tensor, grad3: Tensor,
+                               grad4: Tensor) -> Tensor:
+    """Name and signature of the reference's operator (``cuda_kernels.py:1493-1506``)."""
+    return pack_control_gradients((grad0, grad1, grad2, grad3, grad4))
+
+
+@_pack_control_gradients_op.register_fake
+def _pack_control_gradients_fake(grad0, grad1, grad2, grad3, grad4):
+    total = sum(g.shape[-1] for g in (grad0, grad1, grad2, grad3, grad4))
+    return torch.empty((*grad0.shape[:-1], total), device=grad0.device, dtype=grad0.dtype)
+
+
+def _controls_args(packed: Tensor, A_log_precond: Tensor, dt_bias_precond: Tensor, hidden: int):
+    H = A_log_precond.shape[0]
+    if packed.shape[-1] != 2 * hidden + 3 * H:
+        raise RuntimeError("packed control row must be [hidden | H | H | H | hidden]")
+    a = _lib.ControlsArgs()
+    a.rows = packed.numel() // packed.shape[-1]
+    a.heads, a.hidden, a.dtype = H, int(hidden), _dtype_code(packed)
+    return a
+
+
+class _Controls(torch.autograd.Function):
+    """Split of the packed control projection with the three per-head activations fused in
+    (forward) and the packed gradient written in one pass (backward)."""
+
+    @staticmethod
+    def forward(ctx, packed: Tensor, A_log_precond: Tensor, dt_bias_precond: Tensor, hidden: int):
+        ops._require_cuda(packed, A_log_precond, dt_bias_precond)
+        lib = _lib.load()
+        packed = packed.contiguous()
+        a32 = A_log_precond.detach().float().contiguous()
+        b32 = dt_bias_precond.detach().float().contiguous()
+        a = _controls_args(packed, a32, b32, hidden)
+        H = a.heads
+        lead = packed.shape[:-1]
+        beta = torch.empty((*lead, H), device=packed.device, dtype=packed.dtype)
+        beta_atk = torch.empty_like(beta)
+        g_atk = torch.empty((*lead, H), device=packed.device, dtype=torch.float32)
+        a.packed, a.A_log_precond, a.dt_bias_precond = packed.data_ptr(), a32.data_ptr(), b32.data_ptr()
+        a.beta, a.g_atk, a.beta_atk = beta.data_ptr(), g_atk.data_ptr(), beta_atk.data_ptr()
+        _lib.check(lib.pkda_controls_fwd(C.byref(a), _lib.current_stream()), "pkda_controls_fwd")
+        ops._count(lib)
+        ctx.save_for_backward(packed, A_log_precond, dt_bias_precond)
+        ctx.hidden = hidden
+        return packed[..., :hidden], beta, g_atk, beta_atk, packed[..., hidden + 3 * H:]
+
+    @staticmethod
+    def backward(ctx, d_h0, d_beta, d_g_atk, d_beta_atk, d_h1):
+        packed, A_log_precond, dt_bias_precond = ctx.saved_tensors
+        lib = _lib.load()
+        a32 = A_log_precond.detach().float().contiguous()
+        b32 = dt_bias_precond.detach().float().contiguous()
+        a = _controls_args(packed, a32, b32, ctx.hidden)
+        act = packed.dtype
+        keep = [None if g is None else g.to(torch.float32 if i == 2 else act).contiguous()
+                for i, g in enumerate((d_h0, d_beta, d_g_atk, d_beta_atk, d_h1))]
+        d_packed = torch.empty_like(packed)
+        dA = torch.empty_like(a32)
+        db = torch.empty_like(b32)
+        a.packed, a.A_log_precond, a.dt_bias_precond = packed.data_ptr(), a32.data_ptr(), b32.data_ptr()
+        (a.d_decay_hidden, a.d_beta, a.d_g_atk, a.d_beta_atk, a.d_gate_hidden) = [
+            None if t is None else t.data_ptr() for t in keep]
+        a.d_packed, a.dA_log_precond, a.ddt_bias_precond = d_packed.data_ptr(), dA.data_ptr(), db.data_ptr()
+        nbytes = lib.pkda_controls_bwd_workspace_bytes(C.byref(a))
+        ws = _workspace(nbytes, packed.device)
+        a.workspace, a.workspace_bytes = ws.data_ptr(), nbytes
+        _lib.check(lib.pkda_controls_bwd(C.byref(a), _lib.current_stream()), "pkda_controls_bwd")
+        ops._count(lib)
+        return d_packed, dA.to(A_log_precond.dtype), db.to(dt_bias_precond.dtype), None
+
+
+def pkda_controls(packed: Tensor, A_log_precond: Tensor, dt_bias_precond: Tensor, hidden: int):
+    """``(decay_hidden, beta, precond_decay, precond_beta, output_gate_hidden)`` from the packed
+    control projection ``[..., hidden + 3H + hidden]`` -- the middle of the reference's
+    ``PreconditionedKDA._controls`` (``pkda.py:318-353``) with its backward packing
+    (``pkda.py:56-74``).  The two hidden pieces are views of ``packed``."""
+    return _Controls.apply(packed, A_log_precond, dt_bias_precond, hidden)
+
+
+__all__ = ["pkda_controls", "pack_control_gradients", "pkda_decode_step", "pkda_qkv_conv", "pkda_norm_gate", "qkv_conv_forward", "qkv_conv_backward",
            "norm_gate_forward", "norm_gate_backward"]

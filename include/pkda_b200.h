@@ -337,6 +337,53 @@ typedef struct pkda_decode_step_args {
 int pkda_decode_step(const pkda_decode_step_args* args, void* cuda_stream);
 size_t pkda_sizeof_decode_step_args(void);
 
+/*
+ * Control epilogue of the layer (delta_feedback_experiment/pkda.py:318-353 and the
+ * gradient packer delta_feedback_experiment/cuda_kernels.py:1081-1172).  A packed
+ * control row is  [decay hidden (hidden) | beta logits (heads) | precond decay logits
+ * (heads) | precond beta logits (heads) | output-gate hidden (hidden)].
+ *   pkda_controls_fwd:  beta = sigmoid, beta_atk = sigmoid (activation dtype),
+ *                       g_atk = -exp(A_log_precond) * softplus(logit + dt_bias_precond) (fp32),
+ *                       each [rows][heads]; the two hidden slices are used in place by the caller.
+ *   pkda_controls_bwd:  from the gradients of the five pieces (any may be NULL = zero)
+ *                       writes the packed gradient row [rows][2*hidden + 3*heads] in one
+ *                       pass and the fp32 gradients of the two per-head parameters.
+ *   pkda_pack_control_gradients: the packer alone, out[r] = concat(grads[0][r] .. grads[4][r]).
+ */
+typedef struct pkda_controls_args {
+  long long rows;
+  int heads, hidden;
+  int dtype;
+  const void* packed;
+  const float *A_log_precond, *dt_bias_precond;
+  void* beta;
+  float* g_atk;
+  void* beta_atk;
+  const void *d_decay_hidden, *d_beta;
+  const float* d_g_atk;
+  const void *d_beta_atk, *d_gate_hidden;
+  void* d_packed;
+  float *dA_log_precond, *ddt_bias_precond;
+  void* workspace;
+  size_t workspace_bytes;
+} pkda_controls_args;
+
+int pkda_controls_fwd(const pkda_controls_args* args, void* cuda_stream);
+size_t pkda_controls_bwd_workspace_bytes(const pkda_controls_args* args);
+int pkda_controls_bwd(const pkda_controls_args* args, void* cuda_stream);
+
+typedef struct pkda_pack_control_args {
+  long long rows;
+  int sizes[5];
+  int dtype;
+  const void* grads[5];
+  void* out;
+} pkda_pack_control_args;
+
+int pkda_pack_control_gradients(const pkda_pack_control_args* args, void* cuda_stream);
+size_t pkda_sizeof_controls_args(void);
+size_t pkda_sizeof_pack_control_args(void);
+
 size_t pkda_sizeof_qkv_conv_args(void);
 size_t pkda_sizeof_norm_gate_args(void);
 

@@ -88,3 +88,14 @@ def decode_step_oracle(qkv, conv_state, conv_weight, g, g_atk, beta_atk, beta, A
         return o, S, A, new_conv
     y, _ = norm_gate_oracle(o, gate, norm_weight, norm_eps, dtype)
     return y, S, A, new_conv
+
+
+def controls_oracle(packed, A_log_precond, dt_bias_precond, hidden: int, dtype: torch.dtype = torch.float32):
+    """Packed control row -> (decay_hidden, beta, precond_decay, precond_beta, gate_hidden),
+    restating ``delta_feedback_experiment/pkda.py:325-346`` (split, sigmoid, softplus)."""
+    import torch.nn.functional as F
+    H = A_log_precond.shape[0]
+    x = packed.to(dtype)
+    h0, lb, ld, lp, h1 = x.split((hidden, H, H, H, hidden), dim=-1)
+    g_atk = -A_log_precond.to(dtype).exp() * F.softplus(ld + dt_bias_precond.to(dtype))
+    return h0, torch.sigmoid(lb), g_atk, torch.sigmoid(lp), h1

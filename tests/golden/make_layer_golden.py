@@ -14,6 +14,7 @@ own code for the two operators next to the recurrence.
   that the layer output IS the result of the reference's inline RMS-norm / sigmoid
   gate code (``pkda.py:543-547``) on known inputs.
 
+* Control cases call ``PreconditionedKDA._controls`` on CPU (see ``run_controls``).
 * Decode cases call ``PreconditionedKDA.forward`` on CPU for consecutive cached
   single-token steps (see ``run_decode``).
 
@@ -216,6 +217,46 @@ def run_decode(ref_root: str, case: tuple) -> dict:
     return out
 
 
+# name -> (B, T, H, D, seed)
+CONTROL_CASES = {
+    "layer_controls_small": (2, 7, 3, 16, 51),
+    "layer_controls_d128": (1, 5, 4, 128, 52),
+}
+
+
+def run_controls(ref_root: str, case: tuple) -> dict:
+    """``PreconditionedKDA._controls`` on CPU with an identity control projection (the layer
+    input IS the packed row) and a decay up-projection made of identity blocks (its output is
+    the decay hidden repeated per head), values and autograd gradients."""
+    sys.path.insert(0, ref_root)
+    from delta_feedback_experiment.pkda import PreconditionedKDA
+
+    B, T, H, D, seed = case
+    total = 2 * D + 3 * H
+    gen = torch.Generator().manual_seed(seed)
+    layer = PreconditionedKDA(total, num_heads=H, head_dim=D)
+    with torch.no_grad():
+        layer.control_proj.weight.copy_(torch.eye(total))
+        layer.decay_up.weight.copy_(torch.eye(D).repeat(H, 1))
+        layer.A_log_precond.copy_(torch.log(torch.empty(H).uniform_(1.0, 8.0, generator=gen)))
+        layer.dt_bias_precond.copy_(0.3 * torch.randn(H, generator=gen))
+    x = torch.randn(B, T, total, generator=gen).requires_grad_(True)
+    raw, beta, pd, pb, gate_hidden = layer._controls(x)
+    cot = [torch.randn(t.shape, generator=gen) for t in (raw, beta, pd, pb, gate_hidden)]
+    loss = sum((t * c).sum() for t, c in zip((raw, beta, pd, pb, gate_hidden), cot))
+    dx, dA, db = torch.autograd.grad(loss, [x, layer.A_log_precond, layer.dt_bias_precond])
+    return {
+        "packed": x.detach().numpy(), "A_log_precond": layer.A_log_precond.detach().numpy(),
+        "dt_bias_precond": layer.dt_bias_precond.detach().numpy(), "hidden": np.int64(D),
+        "decay_hidden": raw.detach()[..., 0, :].numpy(), "beta": beta.detach().numpy(),
+        "g_atk": pd.detach().numpy(), "beta_atk": pb.detach().numpy(),
+        "gate_hidden": gate_hidden.detach().numpy(),
+        "d_decay_hidden": cot[0].sum(-2).numpy(), "d_beta": cot[1].numpy(), "d_g_atk": cot[2].numpy(),
+        "d_beta_atk": cot[3].numpy(), "d_gate_hidden": cot[4].numpy(),
+        "d_packed": dx.numpy(), "dA_log_precond": dA.numpy(), "ddt_bias_precond": db.numpy(),
+    }
+
+
 def main() -> None:
     if len(sys.argv) != 2:
         raise SystemExit(__doc__)
@@ -225,6 +266,9 @@ def main() -> None:
         print("wrote", name)
     for name, case in GATE_CASES.items():
         np.savez_compressed(os.path.join(HERE, name + ".npz"), **run_gate(sys.argv[1], case))
+        print("wrote", name)
+    for name, case in CONTROL_CASES.items():
+        np.savez_compressed(os.path.join(HERE, name + ".npz"), **run_controls(sys.argv[1], case))
         print("wrote", name)
     for name, case in DECODE_CASES.items():
         np.savez_compressed(os.path.join(HERE, name + ".npz"), **run_decode(sys.argv[1], case))

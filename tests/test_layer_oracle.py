@@ -96,3 +96,24 @@ def test_decode_step_oracle_matches_reference_golden(name):
         assert_close(a_state, exp["a_state"], 2e-5, f"{name}:a_state{t}")
         for i in range(3):
             assert torch.equal(conv[i], exp["conv"][i]), f"{name}:conv{t}_{i}"
+
+
+CONTROL_CASES = ["layer_controls_small", "layer_controls_d128"]
+
+
+@pytest.mark.parametrize("name", CONTROL_CASES)
+def test_controls_oracle_matches_reference_golden(name):
+    from oracle.pkda_layer_oracle import controls_oracle
+    g = load_golden(name)
+    packed = g["packed"].clone().requires_grad_(True)
+    A = g["A_log_precond"].clone().requires_grad_(True)
+    b = g["dt_bias_precond"].clone().requires_grad_(True)
+    outs = controls_oracle(packed, A, b, int(g["hidden"]))
+    names = ("decay_hidden", "beta", "g_atk", "beta_atk", "gate_hidden")
+    for n, o in zip(names, outs):
+        assert_close(o, g[n], 2e-5, f"{name}:{n}")
+    loss = sum((o * g["d_" + n]).sum() for n, o in zip(names, outs))
+    dp, dA, db = torch.autograd.grad(loss, [packed, A, b])
+    assert_close(dp, g["d_packed"], 2e-4, f"{name}:d_packed")
+    assert_close(dA, g["dA_log_precond"], 2e-4, f"{name}:dA")
+    assert_close(db, g["ddt_bias_precond"], 2e-4, f"{name}:db")

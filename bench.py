@@ -273,6 +273,32 @@ def run_decode_fused(device, dev, S, A, B, H, D, steps, warmup, pk) -> dict:
             "finite": bool(torch.isfinite(out.float()).all().item())}
 
 
+def bind_to_gpu_cpus(index: int):
+    """Restricts this process to the CPU cores NVML reports as local to GPU `index` (same NUMA
+    node / PCIe root), so that the pinned host buffers of the end-to-end leg are allocated and
+    touched next to the GPU they feed.  Only this process's CPU affinity changes; returns the
+    number of cores kept, or None when NVML gives no answer."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        try:  # match the CUDA device by its PCI address (NVML numbering can differ from CUDA's)
+            pr = torch.cuda.get_device_properties(index)
+            handle = pynvml.nvmlDeviceGetHandleByPciBusId(
+                f"{pr.pci_domain_id:08x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0")
+        except Exception:
+            handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+        words = (os.cpu_count() + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(handle, words)
+        allowed = os.sched_getaffinity(0)
+        cpus = {64 * w + b for w, m in enumerate(mask) for b in range(64) if (m >> b) & 1} & allowed
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            return len(cpus)
+    except Exception:
+        pass
+    return None
+
+
 def run_layer_ops(device, B: int, T: int, H: int, D: int, steps: int, warmup: int, pk: dict) -> dict:
     """The two fused operators next to the recurrence on the headline shape: Q|K|V convolution
     (+SiLU +L2 norm) and RMS-norm x sigmoid gate, forward and backward, each against the HBM roofline
@@ -335,6 +361,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     _lib.load()
     device = torch.device("cuda", local_rank)
     torch.cuda.set_device(device)
+    numa = bind_to_gpu_cpus(local_rank)  # pinned host buffers then live next to this rank's GPU
     if world > 1:
         # keep NCCL's own banner off stdout: rank 0 prints exactly one JSON line there
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
@@ -470,6 +497,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
             "saving": "lean (recompute)" if lean else "full (retained intermediates)",
             "l2": "no flush: each of q,k,v,g,dO is larger than the 126 MB L2",
             "parallelism": f"{world} independent replica shard(s) by row x head, no collective",
+            "host_cores_bound_to_gpu": numa,
         },
         "roofline": roofline,
         "e2e": {"value": world * B * T / (e2e_ms * 1e-3), "unit": "tokens/s",

@@ -56,7 +56,7 @@ STAGE_FLOPS = {
     "scan_fwd": 2 * (2 * K * V),                                              # W*h, kg^T*F
     "out_fwd": 2 * K * V + 2 * C * V,                                         # qg*h, P*F
     "scan_bwd": 3 * (2 * K * V) + 2 * C * V,                                  # kg*dS, qg^T*dO, W^T*dE, P^T*dO
-    "intra_bwd": 3 * (2 * K * V) + 3 * (2 * C * V) + 4 * (2 * C * K),
+    "intra_bwd": 3 * (2 * K * V) + 3 * (2 * C * V) + 4 * (2 * C * K),         # dqg, dKd, dkg; dR, dM, dP; four gated pair products
 }
 # DRAM traffic per (token, head) of each kernel: dram__bytes_read.sum + dram__bytes_write.sum of one
 # ncu capture on the quarter-size workload (131,072 units), divided by its units; the traffic grows

@@ -1023,10 +1023,23 @@ pkda_atk_bwd_carry_kernel(Geo geo, const float* c_loc, const float* sa, float* l
   const int n = blockIdx.x, h = blockIdx.y, H = geo.heads, c = threadIdx.x;
   const SeqInfo sq = seq_info(geo, n);
   float lam = 0.f;
-  for (int i = sq.nchunks - 1; i >= 0; --i) {
-    const size_t ch = (size_t)(sq.chunk0 + i) * H + h;
-    lam_in[ch * kD + c] = lam;
-    lam = c_loc[ch * kD + c] + __expf(sa[ch]) * lam;
+  constexpr int kBatch = 16;  // loads of 16 chunks in flight before the dependent multiply-adds
+  for (int i0 = sq.nchunks - 1; i0 >= 0; i0 -= kBatch) {
+    float dec[kBatch], loc[kBatch];
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      const bool ok = i0 - j >= 0;
+      const size_t ch = (size_t)(sq.chunk0 + (ok ? i0 - j : 0)) * H + h;
+      dec[j] = ok ? sa[ch] : 0.f;
+      loc[j] = ok ? c_loc[ch * kD + c] : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      if (i0 - j >= 0) {
+        lam_in[((size_t)(sq.chunk0 + i0 - j) * H + h) * kD + c] = lam;
+        lam = loc[j] + __expf(dec[j]) * lam;
+      }
+    }
   }
   if (dA0) dA0[((size_t)n * H + h) * kD + c] = lam;
 }

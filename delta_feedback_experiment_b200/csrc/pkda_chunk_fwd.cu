@@ -83,10 +83,23 @@ pkda_atk_carry_kernel(Geo geo, const float* ac_local, const float* sa, const flo
   const int n = blockIdx.x, h = blockIdx.y, H = geo.heads, c = threadIdx.x;
   const SeqInfo sq = seq_info(geo, n);
   float A = A0 ? A0[((size_t)n * H + h) * kD + c] : 0.f;
-  for (int i = 0; i < sq.nchunks; ++i) {
-    const size_t ch = (size_t)(sq.chunk0 + i) * H + h;
-    a_start[ch * kD + c] = A;
-    A = __expf(sa[ch]) * A + ac_local[ch * kD + c];
+  constexpr int kBatch = 16;  // loads of 16 chunks in flight before the dependent multiply-adds
+  for (int i0 = 0; i0 < sq.nchunks; i0 += kBatch) {
+    float dec[kBatch], loc[kBatch];
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      const bool ok = i0 + j < sq.nchunks;
+      const size_t ch = (size_t)(sq.chunk0 + (ok ? i0 + j : 0)) * H + h;
+      dec[j] = ok ? sa[ch] : 0.f;
+      loc[j] = ok ? ac_local[ch * kD + c] : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      if (i0 + j < sq.nchunks) {
+        a_start[((size_t)(sq.chunk0 + i0 + j) * H + h) * kD + c] = A;
+        A = __expf(dec[j]) * A + loc[j];
+      }
+    }
   }
   if (AT) AT[((size_t)n * H + h) * kD + c] = A;
 }

@@ -46,34 +46,60 @@ __global__ void pkda_pack_beta_kernel(Geo geo, const bf16* beta, float* beta_c) 
 }
 
 // Chunk-local preconditioner scan from A = 0: loc[c] = sum_j (prod_{m>j} d_m) bP_j k_j[c]^2
-// and the chunk's summed log-decay.  grid (chunks, H), 128 threads (one per channel).
-__global__ void __launch_bounds__(kD)
-pkda_atk_local_kernel(Geo geo, const bf16* k, const float* g_atk, const bf16* beta_atk,
-                      float* ac_local, float* sa) {
+// and the chunk's summed log-decay; also the chunk-major fp32 copy of beta (when beta_c is
+// given), which saves a launch.  grid (chunks, H), 256 threads: warp w scans rows 8w..8w+7 with
+// lane l holding channels 4l..4l+3 (64-bit loads, one token row per warp request), then the
+// eight row blocks are chained in order through shared memory.
+__global__ void __launch_bounds__(256)
+pkda_atk_local_kernel(Geo geo, const bf16* k, const float* g_atk, const bf16* beta_atk, const bf16* beta,
+                      float* ac_local, float* sa, float* beta_c) {
+  __shared__ __align__(16) float sEnd[8][kD];
+  __shared__ float sDec[8], sSum[8];
   int n, tok0, valid;
   if (!chunk_lookup(geo, blockIdx.x, n, tok0, valid)) return;
-  const int h = blockIdx.y, H = geo.heads, c = threadIdx.x;
-  float A = 0.f, gsum = 0.f;
-  for (int r0 = 0; r0 < valid; r0 += 8) {
-    float kc[8], gp[8], bp[8];
+  const int h = blockIdx.y, H = geo.heads, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const size_t chh = (size_t)blockIdx.x * H + h;
+  const int c4 = lane << 2, r0 = warp * 8;
+  uint2 kraw[8];
+  float lg[8], bp[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int r = min(r0 + j, valid - 1);
-      const size_t s = (size_t)(tok0 + r) * H + h;
-      kc[j] = to_f(k[s * kD + c]);
-      gp[j] = g_atk[s];
-      bp[j] = to_f(beta_atk[s]);
-    }
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      if (r0 + j < valid) {
-        A = __expf(gp[j]) * A + bp[j] * kc[j] * kc[j];
-        gsum += gp[j];
-      }
-    }
+  for (int i = 0; i < 8; ++i) {  // all loads first
+    const int r = r0 + i;
+    const bool ok = r < valid;
+    const size_t s = (size_t)(tok0 + (ok ? r : 0)) * H + h;
+    kraw[i] = ok ? *reinterpret_cast<const uint2*>(k + s * kD + c4) : make_uint2(0, 0);
+    lg[i] = ok ? g_atk[s] : 0.f;
+    bp[i] = ok ? to_f(beta_atk[s]) : 0.f;
   }
-  ac_local[((size_t)blockIdx.x * H + h) * kD + c] = A;
-  if (c == 0) sa[(size_t)blockIdx.x * H + h] = gsum;
+  if (beta_c && tid < kChunk)
+    beta_c[chh * kChunk + tid] = tid < valid ? to_f(beta[(size_t)(tok0 + tid) * H + h]) : 0.f;
+  float a[4] = {0.f, 0.f, 0.f, 0.f}, dblk = 1.f, gsum = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float2 x = unpack_bf16(kraw[i].x), y = unpack_bf16(kraw[i].y);
+    const float pd = __expf(lg[i]);  // rows past the end: decay 1, beta 0
+    a[0] = pd * a[0] + bp[i] * x.x * x.x;
+    a[1] = pd * a[1] + bp[i] * x.y * x.y;
+    a[2] = pd * a[2] + bp[i] * y.x * y.x;
+    a[3] = pd * a[3] + bp[i] * y.y * y.y;
+    dblk *= pd;
+    gsum += lg[i];
+  }
+  *reinterpret_cast<float4*>(&sEnd[warp][c4]) = make_float4(a[0], a[1], a[2], a[3]);
+  if (lane == 0) { sDec[warp] = dblk; sSum[warp] = gsum; }
+  __syncthreads();
+  if (tid < kD) {
+    float acc = 0.f;
+#pragma unroll
+    for (int b = 0; b < 8; ++b) acc = sDec[b] * acc + sEnd[b][tid];
+    ac_local[chh * kD + tid] = acc;
+  }
+  if (tid == 0) {
+    float g = 0.f;
+#pragma unroll
+    for (int b = 0; b < 8; ++b) g += sSum[b];
+    sa[chh] = g;
+  }
 }
 
 // Sequential carry over the chunks of one (sequence, head): A at each chunk start.
@@ -764,15 +790,18 @@ int run_forward_stages(const pkda_problem& p, const Geo& geo, const float* beta_
 }
 
 int run_prologue(const pkda_problem& p, int* chunk_offsets, float* beta_c, Geo* geo, cudaStream_t st) {
+  // beta_c == nullptr: the caller fills the chunk-major beta itself (the forward does, in its first kernel)
   if (p.cu_seqlens) {
     begin_stage(kStageOffsets, st);
     pkda_chunk_offsets_kernel<<<1, 32, 0, st>>>(p.cu_seqlens, p.n_seqs, chunk_offsets);
     PKDA_CHECK_LAUNCH();
   }
   *geo = make_geo(p, chunk_offsets);
-  begin_stage(kStagePackBeta, st);
-  pkda_pack_beta_kernel<<<geo->total_chunks, 256, 0, st>>>(*geo, static_cast<const bf16*>(p.beta), beta_c);
-  PKDA_CHECK_LAUNCH();
+  if (beta_c) {
+    begin_stage(kStagePackBeta, st);
+    pkda_pack_beta_kernel<<<geo->total_chunks, 256, 0, st>>>(*geo, static_cast<const bf16*>(p.beta), beta_c);
+    PKDA_CHECK_LAUNCH();
+  }
   return PKDA_OK;
 }
 
@@ -787,13 +816,14 @@ int chunk_fwd(const pkda_chunk_fwd_args* a, cudaStream_t st) {
   if (!a->workspace || a->workspace_bytes < chunk_fwd_workspace(p)) return PKDA_ERR_WORKSPACE;
   FwdWorkspace ws = carve_fwd(p, a->workspace);
   Geo geo;
-  rc = run_prologue(p, ws.chunk_offsets, ws.beta_c, &geo, st);
+  rc = run_prologue(p, ws.chunk_offsets, nullptr, &geo, st);
   if (rc != PKDA_OK) return rc;
 
   dim3 gridc(geo.total_chunks, p.heads);
   begin_stage(kStageAtkLocal, st);
-  pkda_atk_local_kernel<<<gridc, kD, 0, st>>>(geo, static_cast<const bf16*>(p.k), p.g_atk,
-                                              static_cast<const bf16*>(p.beta_atk), a->ac_atk, a->sa_atk);
+  pkda_atk_local_kernel<<<gridc, 256, 0, st>>>(geo, static_cast<const bf16*>(p.k), p.g_atk,
+                                               static_cast<const bf16*>(p.beta_atk), static_cast<const bf16*>(p.beta),
+                                               a->ac_atk, a->sa_atk, ws.beta_c);
   PKDA_CHECK_LAUNCH();
   begin_stage(kStageAtkCarry, st);
   pkda_atk_carry_kernel<<<dim3(p.n_seqs, p.heads), kD, 0, st>>>(geo, a->ac_atk, a->sa_atk, p.initial_A_state,

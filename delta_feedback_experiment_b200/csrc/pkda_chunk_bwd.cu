@@ -682,8 +682,13 @@ pkda_intra_bwd_kernel(const IntraBwdParams p, const __grid_constant__ IntraBwdMa
         for (int j = 0; j < 4; ++j) {
           const float2 x = unpack_bf16(w[j]);
           const float z0 = x.x + sBias[c8 + 2 * j], z1 = x.y + sBias[c8 + 2 * j + 1];
-          const float dr0 = dgv[2 * j] * (-ea) * sigmoid_fast(z0), dr1 = dgv[2 * j + 1] * (-ea) * sigmoid_fast(z1);
-          pa += dgv[2 * j] * (-ea * softplus_fast(z0)) + dgv[2 * j + 1] * (-ea * softplus_fast(z1));
+          // sigmoid and softplus from one exp(-|z|): 1/(1+e) (or e/(1+e)) and max(z,0) - log(1/(1+e))
+          const float e0 = __expf(-fabsf(z0)), e1 = __expf(-fabsf(z1));
+          const float i0 = __fdividef(1.f, 1.f + e0), i1 = __fdividef(1.f, 1.f + e1);
+          const float sg0 = z0 >= 0.f ? i0 : e0 * i0, sg1 = z1 >= 0.f ? i1 : e1 * i1;
+          const float sp0 = fmaxf(z0, 0.f) - __logf(i0), sp1 = fmaxf(z1, 0.f) - __logf(i1);
+          const float dr0 = dgv[2 * j] * (-ea) * sg0, dr1 = dgv[2 * j + 1] * (-ea) * sg1;
+          pa += dgv[2 * j] * (-ea * sp0) + dgv[2 * j + 1] * (-ea * sp1);
           pb[2 * j] += dr0;
           pb[2 * j + 1] += dr1;
           o32[j] = pack_bf16(dr0, dr1);

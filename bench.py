@@ -562,7 +562,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         line["decode"] = run_decode(device, args.decode_steps, 16, pk)
     if not args.no_layer:
         line["layer_ops"] = run_layer_ops(device, B, T, H, D, 10, 3, pk)
-    if not args.no_cpu:
+    if not args.no_cpu and world == 1:  # the CPU baseline belongs to the single-GPU line
         cb = cpu_oracle_rate(T, H, D)
         line["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
     print(json.dumps(line), flush=True)

@@ -28,7 +28,9 @@ struct DecodeParams {
   const float* g_atk;
   const void *beta_atk, *beta;
   const float *A_log, *dt_bias, *log_atk_scale;
-  float *S, *A;
+  float *S, *A;          // states read here ...
+  float *S_out, *A_out;  // ... and written here (the same arrays when the cache is updated in place)
+  const void *q, *k, *v; // direct mode (qkv == nullptr): q, k, v [batch][heads][D] given, no convolution
   const void* gate;
   const float* norm_w;
   void* out;
@@ -70,13 +72,14 @@ pkda_decode_step_kernel(const DecodeParams p) {
   // memory round trip, not one per stage
   const T* qkv = static_cast<const T*>(p.qkv) + (size_t)n * 3 * W;
   const int hist = p.taps - 1;
+  const bool with_conv = p.qkv != nullptr;
   constexpr int kItems = (3 * D + kThreads - 1) / kThreads;  // (slab, channel) items per thread
   T xn[kItems], hv[kItems][3];
   float wv[kItems][4];
 #pragma unroll
   for (int it = 0; it < kItems; ++it) {
     const int item = tid + it * kThreads;
-    if (item < 3 * D) {
+    if (with_conv && item < 3 * D) {
       const int slab = item / D, d = item - slab * D, cs = h * D + d;
       const float* w = p.conv_w + (size_t)(slab * W + cs) * p.taps;
       const T* hs = static_cast<const T*>(p.conv[slab]) + ((size_t)n * W + cs) * hist;
@@ -92,8 +95,15 @@ pkda_decode_step_kernel(const DecodeParams p) {
   const float ea = expf(p.A_log[h]);
   const float centre = p.log_atk_scale[h];
   float A = 0.f, r_pd = 0.f, r_ba = 0.f, r_b = 0.f, r_g = 0.f, r_bias = 0.f, r_gate = 0.f, r_nw = 0.f;
+  float d_q = 0.f, d_k = 0.f, d_v = 0.f;
+  const bool direct = p.qkv == nullptr;
   if (tid < D) {
-    A = p.A[sidx * D + tid];
+    if (direct) {
+      d_q = to_f(static_cast<const T*>(p.q)[sidx * D + tid]);
+      d_k = to_f(static_cast<const T*>(p.k)[sidx * D + tid]);
+      d_v = to_f(static_cast<const T*>(p.v)[sidx * D + tid]);
+    }
+    A = p.A ? p.A[sidx * D + tid] : 0.f;
     r_pd = p.g_atk[sidx];
     r_ba = to_f(static_cast<const T*>(p.beta_atk)[sidx]);
     r_b = to_f(static_cast<const T*>(p.beta)[sidx]);
@@ -106,6 +116,7 @@ pkda_decode_step_kernel(const DecodeParams p) {
   }
 
   // ---- convolution over the cached history, SiLU; the history moves up by one token
+  if (with_conv) {
 #pragma unroll
   for (int it = 0; it < kItems; ++it) {
     const int item = tid + it * kThreads;
@@ -134,11 +145,12 @@ pkda_decode_step_kernel(const DecodeParams p) {
     if (lane == 0) s_stat[kWarps + warp] = rsqrtf(ss + p.qk_eps);
   }
   __syncthreads();
+  }  // with_conv
 
   if (tid < D) {
-    const float qn = round_to<T>(s_qkv[0][tid] * s_stat[kWarps + 0]);
-    const float kc = round_to<T>(s_qkv[1][tid] * s_stat[kWarps + 1]);
-    const float vv = round_to<T>(s_qkv[2][tid]);
+    const float qn = direct ? d_q : round_to<T>(s_qkv[0][tid] * s_stat[kWarps + 0]);
+    const float kc = direct ? d_k : round_to<T>(s_qkv[1][tid] * s_stat[kWarps + 1]);
+    const float vv = direct ? d_v : round_to<T>(s_qkv[2][tid]);
     A = expf(r_pd) * A + r_ba * kc * kc;
     const float kw = kc * precond_factor(A, p.eps, centre, p.ln_x);
     s_k[tid] = kc;
@@ -173,7 +185,7 @@ pkda_decode_step_kernel(const DecodeParams p) {
       const float wk = s_wk[krow0 + r], qq = s_q[krow0 + r];
       S[r].x += wk * e.x; S[r].y += wk * e.y; S[r].z += wk * e.z; S[r].w += wk * e.w;
       acc.x += S[r].x * qq; acc.y += S[r].y * qq; acc.z += S[r].z * qq; acc.w += S[r].w * qq;
-      *reinterpret_cast<float4*>(p.S + sbase + (size_t)(krow0 + r) * D + 4 * vq) = S[r];
+      *reinterpret_cast<float4*>(p.S_out + sbase + (size_t)(krow0 + r) * D + 4 * vq) = S[r];
     }
     *reinterpret_cast<float4*>(&s_red[1][kq][4 * vq]) = acc;
   }
@@ -184,7 +196,7 @@ pkda_decode_step_kernel(const DecodeParams p) {
 #pragma unroll
     for (int w = 0; w < KW; ++w) o += s_red[1][w][tid];
     o = round_to<T>(o);
-    p.A[sidx * D + tid] = A;
+    if (p.A_out) p.A_out[sidx * D + tid] = A;
   }
   T* out = static_cast<T*>(p.out) + sidx * D;
   if (!p.gate) {
@@ -206,21 +218,21 @@ pkda_decode_step_kernel(const DecodeParams p) {
 }
 
 template <int D, typename T>
-static int launch_decode(const DecodeParams& dp, cudaStream_t st) {
-  begin_stage(kStageDecodeStep, st);
+static int launch_decode(const DecodeParams& dp, int stage, cudaStream_t st) {
+  begin_stage(stage, st);
   pkda_decode_step_kernel<D, T><<<dp.batch * dp.heads, RecCfg<D>::kThreads, 0, st>>>(dp);
   end_stage(st);
   return cudaGetLastError() == cudaSuccess ? PKDA_OK : PKDA_ERR_LAUNCH;
 }
 
 template <typename T>
-static int dispatch_decode(int D, const DecodeParams& dp, cudaStream_t st) {
+static int dispatch_decode(int D, const DecodeParams& dp, int stage, cudaStream_t st) {
   switch (D) {
-    case 8: return launch_decode<8, T>(dp, st);
-    case 16: return launch_decode<16, T>(dp, st);
-    case 32: return launch_decode<32, T>(dp, st);
-    case 64: return launch_decode<64, T>(dp, st);
-    case 128: return launch_decode<128, T>(dp, st);
+    case 8: return launch_decode<8, T>(dp, stage, st);
+    case 16: return launch_decode<16, T>(dp, stage, st);
+    case 32: return launch_decode<32, T>(dp, stage, st);
+    case 64: return launch_decode<64, T>(dp, stage, st);
+    case 128: return launch_decode<128, T>(dp, stage, st);
     default: return PKDA_ERR_SHAPE;
   }
 }
@@ -242,9 +254,26 @@ int decode_step(const pkda_decode_step_args* a, cudaStream_t st) {
   dp.qkv = a->qkv; dp.conv[0] = a->conv_q; dp.conv[1] = a->conv_k; dp.conv[2] = a->conv_v;
   dp.conv_w = a->conv_weight; dp.g = a->g; dp.g_atk = a->g_atk; dp.beta_atk = a->beta_atk; dp.beta = a->beta;
   dp.A_log = a->A_log; dp.dt_bias = a->dt_bias; dp.log_atk_scale = a->log_atk_scale;
-  dp.S = a->state; dp.A = a->a_state; dp.gate = a->gate; dp.norm_w = a->norm_weight; dp.out = a->out;
-  if (a->dtype == PKDA_BF16) return dispatch_decode<bf16>(a->head_dim, dp, st);
-  return dispatch_decode<float>(a->head_dim, dp, st);
+  dp.S = a->state; dp.A = a->a_state; dp.S_out = a->state; dp.A_out = a->a_state;
+  dp.q = dp.k = dp.v = nullptr; dp.gate = a->gate; dp.norm_w = a->norm_weight; dp.out = a->out;
+  if (a->dtype == PKDA_BF16) return dispatch_decode<bf16>(a->head_dim, dp, kStageDecodeStep, st);
+  return dispatch_decode<float>(a->head_dim, dp, kStageDecodeStep, st);
+}
+
+// The plain single-token step of pkda_recurrent_fwd (q, k, v given, cached state in, new state
+// out) through the same kernel: no convolution, no norm gate.
+int decode_direct(const pkda_problem& p, void* o, float* final_state, float* final_A_state, cudaStream_t st) {
+  DecodeParams dp;
+  dp.batch = p.n_seqs; dp.heads = p.heads; dp.taps = 1;
+  dp.scale = p.scale; dp.ln_x = logf(p.squash_x); dp.eps = p.squash_eps; dp.qk_eps = 0.f; dp.norm_eps = 0.f;
+  dp.qkv = nullptr; dp.conv[0] = dp.conv[1] = dp.conv[2] = nullptr; dp.conv_w = nullptr;
+  dp.g = p.g; dp.g_atk = p.g_atk; dp.beta_atk = p.beta_atk; dp.beta = p.beta;
+  dp.A_log = p.A_log; dp.dt_bias = p.dt_bias; dp.log_atk_scale = p.log_atk_scale;
+  dp.S = const_cast<float*>(p.initial_state); dp.A = const_cast<float*>(p.initial_A_state);
+  dp.S_out = final_state; dp.A_out = final_A_state;
+  dp.q = p.q; dp.k = p.k; dp.v = p.v; dp.gate = nullptr; dp.norm_w = nullptr; dp.out = o;
+  if (p.dtype == PKDA_BF16) return dispatch_decode<bf16>(p.head_dim, dp, kStageRecurrent, st);
+  return dispatch_decode<float>(p.head_dim, dp, kStageRecurrent, st);
 }
 
 }  // namespace pkda

@@ -57,6 +57,7 @@ int norm_gate_fwd(const pkda_norm_gate_args* a, cudaStream_t st);
 int norm_gate_bwd(const pkda_norm_gate_args* a, cudaStream_t st);
 size_t norm_gate_bwd_workspace(const pkda_norm_gate_args& a);
 int decode_step(const pkda_decode_step_args* a, cudaStream_t st);
+int decode_direct(const pkda_problem& p, void* o, float* final_state, float* final_A_state, cudaStream_t st);
 int controls_fwd(const pkda_controls_args* a, cudaStream_t st);
 int controls_bwd(const pkda_controls_args* a, cudaStream_t st);
 size_t controls_bwd_workspace(const pkda_controls_args& a);

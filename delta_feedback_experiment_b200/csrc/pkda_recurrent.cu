@@ -172,6 +172,11 @@ int recurrent_fwd(const pkda_recurrent_args* a, cudaStream_t st) {
   if (rc != PKDA_OK) return rc;
   if (p.n_seqs == 0 || p.total_tokens == 0) return PKDA_OK;
   if (!a->o) return PKDA_ERR_NULL;
+  // One token per sequence on a cached state: the decode-step kernel (all loads of the step issued
+  // up front), without its convolution and gate stages.
+  if (!p.cu_seqlens && p.seq_len == 1 && p.initial_state && a->final_state &&
+      (p.dtype == PKDA_BF16 || p.dtype == PKDA_F32))
+    return decode_direct(p, a->o, a->final_state, a->final_A_state, st);
   RecParams rp;
   rp.geo = make_geo(p, nullptr);
   rp.q = p.q; rp.k = p.k; rp.v = p.v; rp.g = p.g; rp.g_atk = p.g_atk;

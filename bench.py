@@ -372,6 +372,10 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         dist.init_process_group("nccl", device_id=device)
     B, T, H, D = WORKLOADS[args.workload]
     pk = peaks()
+    if args.only_decode:  # profiling aid: the decode legs alone
+        print(json.dumps({"note": "profiling run (decode only): not a benchmark line",
+                          "decode": run_decode(device, args.decode_steps, 16, pk)}), flush=True)
+        return
     if args.only_layer:  # profiling aid: the convolution / norm-gate operators alone
         print(json.dumps({"note": "profiling run (layer operators only): not a benchmark line",
                           "layer_ops": run_layer_ops(device, B, T, H, D, args.steps, args.warmup, pk)}), flush=True)
@@ -585,6 +589,7 @@ def main() -> None:
     ap.add_argument("--no-layer", action="store_true", help="skip the convolution / norm-gate operators")
     ap.add_argument("--no-e2e", action="store_true", help="profiling aid: device-resident leg only")
     ap.add_argument("--only-layer", action="store_true", help="profiling aid: layer operators only")
+    ap.add_argument("--only-decode", action="store_true", help="profiling aid: decode legs only")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

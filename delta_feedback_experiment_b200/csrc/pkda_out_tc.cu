@@ -35,7 +35,7 @@ constexpr uint32_t kCols = 64;
 __global__ void __launch_bounds__(outtc::kThreads)
 pkda_out_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constant__ CUtensorMap tm_qg,
                        const __grid_constant__ CUtensorMap tm_e, const __grid_constant__ CUtensorMap tm_p,
-                       const OutTcParams p) {
+                       const __grid_constant__ CUtensorMap tm_o, const OutTcParams p) {
   using namespace outtc;
   extern __shared__ unsigned char smem_raw[];
   int n, tok0, valid;
@@ -110,6 +110,9 @@ pkda_out_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_co
   if (ok) ok = tc::mbar_wait(bar_mma, 0);
   tc::tc_fence_after();
 
+  // Full chunks leave through a swizzled shared-memory tile (the dead h tile) and two TMA stores;
+  // ragged chunks store their valid tokens directly.
+  const bool by_tma = valid == kChunk;
   if (ok) {
     const int v = 32 * warp + lane;  // this thread's accumulator row = value channel
 #pragma unroll
@@ -117,14 +120,30 @@ pkda_out_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_co
       float acc[32];
       tc::tmem_ld32(tmem + ((uint32_t)(32 * warp) << 16) + 32 * half, acc);
       tc::tmem_ld_wait();
+      if (by_tma) {
 #pragma unroll
-      for (int t = 0; t < 32; ++t) {
-        const int tok = 32 * half + t;
-        if (tok < valid) p.o[((size_t)(tok0 + tok) * H + h) * kD + v] = __float2bfloat16(acc[t]);
+        for (int t = 0; t < 32; ++t)
+          *reinterpret_cast<bf16*>(tiles + oH + sw128_offset(32 * half + t, v, 8192)) = __float2bfloat16(acc[t]);
+      } else {
+#pragma unroll
+        for (int t = 0; t < 32; ++t) {
+          const int tok = 32 * half + t;
+          if (tok < valid) p.o[((size_t)(tok0 + tok) * H + h) * kD + v] = __float2bfloat16(acc[t]);
+        }
       }
     }
   } else if (tid == 0) {
     atomicExch(p.status, 1);
+  }
+  if (by_tma) {  // uniform over the CTA
+    tc::fence_proxy_async();
+    __syncthreads();
+    if (tid == 0 && ok) {
+      tc::tma_store_3d(&tm_o, base + oH, 0, h, tok0);
+      tc::tma_store_3d(&tm_o, base + oH + 8192, 64, h, tok0);
+      tc::bulk_commit();
+      tc::bulk_wait_read();  // the tile must stay in place until the copies have read it
+    }
   }
   tc::tc_fence_before();
   __syncthreads();
@@ -169,7 +188,7 @@ bool encode_bf16_map(CUtensorMap* map, const void* base, int rank, const uint64_
 int launch_out_fwd_tc(const Geo& geo, int total_tokens, const bf16* qg, const bf16* h, const bf16* Aqk,
                       const bf16* v_new, const float* beta_c, bf16* o, int* status, cudaStream_t st) {
   const uint64_t H = geo.heads, chunks = geo.total_chunks, tok = total_tokens;
-  CUtensorMap tm_h, tm_qg, tm_e, tm_p;
+  CUtensorMap tm_h, tm_qg, tm_e, tm_p, tm_o;
   {
     const uint64_t dims[2] = {kD, chunks * H * kD}, str[1] = {kD * 2};
     const uint32_t box[2] = {64, 128};
@@ -180,6 +199,7 @@ int launch_out_fwd_tc(const Geo& geo, int total_tokens, const bf16* qg, const bf
     const uint32_t box[3] = {64, 1, 64};
     if (!encode_bf16_map(&tm_qg, qg, 3, dims, str, box)) return PKDA_ERR_LAUNCH;
     if (!encode_bf16_map(&tm_e, v_new, 3, dims, str, box)) return PKDA_ERR_LAUNCH;
+    if (!encode_bf16_map(&tm_o, o, 3, dims, str, box)) return PKDA_ERR_LAUNCH;
   }
   {
     const uint64_t dims[3] = {kChunk, H, tok}, str[2] = {kChunk * 2, H * kChunk * 2};
@@ -193,7 +213,7 @@ int launch_out_fwd_tc(const Geo& geo, int total_tokens, const bf16* qg, const bf
     return PKDA_ERR_LAUNCH;
   begin_stage(kStageOutFwd, st);
   pkda_out_fwd_tc_kernel<<<dim3(geo.total_chunks, geo.heads), outtc::kThreads, outtc::kSmem, st>>>(tm_h, tm_qg, tm_e,
-                                                                                                   tm_p, op);
+                                                                                                   tm_p, tm_o, op);
   end_stage(st);
   return cudaGetLastError() == cudaSuccess ? PKDA_OK : PKDA_ERR_LAUNCH;
 }

@@ -210,6 +210,7 @@ struct IntraBwdParams {
   float scale;
   int direct_cap;
   int use_tma;   // the five phase-A tiles of full chunks arrive by TMA (tensor maps valid)
+  int out_tma;   // dq, dk_read and dkt of full chunks leave by TMA from padded shared-memory tiles
   int* status;   // set to 1 if a bounded wait gives up
 };
 
@@ -217,8 +218,12 @@ struct IntraBwdParams {
 // or 72 columns for 128 or 64) so that the rows land in shared memory with the
 // padded pitch the ldmatrix reads want; the surplus columns are the neighbouring
 // head's data or, past the end of a row, zero fill.
+// The three output maps are [token][head][channel] with a box of one head and 136
+// columns: a store clips the eight columns past the head, so the padded pitch of
+// the shared-memory tile never reaches the neighbouring head.
 struct IntraBwdMaps {
   CUtensorMap d_o, dF, h, dh, Akk;
+  CUtensorMap dq, dk_read, dkt;
 };
 
 namespace ib {
@@ -616,22 +621,56 @@ pkda_intra_bwd_kernel(const IntraBwdParams p, const __grid_constant__ IntraBwdMa
     v += __shfl_xor_sync(0xffffffffu, v, 2);
     if (tq == 0) sRb[cq * kChunk + 16 * I + gq + 8 * half] = v;
   }
-  // outputs of this stage; dG goes through shared memory for the reverse cumulative sum
+  // outputs of this stage; dG goes through shared memory for the reverse cumulative sum.
+  // Full chunks send dq, dk_read and dkt through padded tiles in dead regions (q, k|kt and the
+  // decay tile) and TMA stores; the scattered fragment stores of the direct path cost more
+  // issue slots than the rest of this phase together.
   float* sdG = reinterpret_cast<float*>(smem + oStage);
+  const bool out_tma = by_tma && p.out_tma;
+  if (out_tma) {
+    float* sOutKt = sG;  // the decay tile is dead after the level loop
 #pragma unroll
-  for (int nt = 0; nt < 4; ++nt)
+    for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      const int i = 16 * I + gq + 8 * half, c = 32 * cq + 8 * nt + 2 * tq;
-      if (i < valid) {
-        const size_t off = row0 + (size_t)i * gld + c;
-        *reinterpret_cast<uint32_t*>(p.dq + off) = pack_bf16(dQ[0][nt][2 * half], dQ[0][nt][2 * half + 1]);
-        *reinterpret_cast<float2*>(p.dk_read + off) = make_float2(dK[0][nt][2 * half], dK[0][nt][2 * half + 1]);
-        *reinterpret_cast<float2*>(p.dkt + off) = make_float2(dKt[0][nt][2 * half], dKt[0][nt][2 * half + 1]);
+      for (int half = 0; half < 2; ++half) {
+        const int i = 16 * I + gq + 8 * half, c = 32 * cq + 8 * nt + 2 * tq;
+        *reinterpret_cast<float2*>(sOutKt + i * kLdG + c) = make_float2(dKt[0][nt][2 * half], dKt[0][nt][2 * half + 1]);
+        *reinterpret_cast<float2*>(sdG + i * kLdG + c) = make_float2(dG[0][nt][2 * half], dG[0][nt][2 * half + 1]);
       }
-      *reinterpret_cast<float2*>(sdG + i * kLdG + c) = make_float2(dG[0][nt][2 * half], dG[0][nt][2 * half + 1]);
-    }
+    tc::fence_proxy_async();
+  } else {
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int i = 16 * I + gq + 8 * half, c = 32 * cq + 8 * nt + 2 * tq;
+        if (i < valid) {
+          const size_t off = row0 + (size_t)i * gld + c;
+          *reinterpret_cast<uint32_t*>(p.dq + off) = pack_bf16(dQ[0][nt][2 * half], dQ[0][nt][2 * half + 1]);
+          *reinterpret_cast<float2*>(p.dk_read + off) = make_float2(dK[0][nt][2 * half], dK[0][nt][2 * half + 1]);
+          *reinterpret_cast<float2*>(p.dkt + off) = make_float2(dKt[0][nt][2 * half], dKt[0][nt][2 * half + 1]);
+        }
+        *reinterpret_cast<float2*>(sdG + i * kLdG + c) = make_float2(dG[0][nt][2 * half], dG[0][nt][2 * half + 1]);
+      }
+  }
   __syncthreads(); PKDA_PHASE(14);
+  if (out_tma) {
+    // every warp is past its reads of q and kt: their tiles take dq and dk_read
+    if (tid == 0) {
+      tc::tma_store_3d(&maps.dkt, smem_u32(sG), 0, h, tok0);
+      tc::bulk_commit();
+    }
+    float* sOutK = reinterpret_cast<float*>(smem + oA1);
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int i = 16 * I + gq + 8 * half, c = 32 * cq + 8 * nt + 2 * tq;
+        *reinterpret_cast<uint32_t*>(sQ + i * kLdD + c) = pack_bf16(dQ[0][nt][2 * half], dQ[0][nt][2 * half + 1]);
+        *reinterpret_cast<float2*>(sOutK + i * kLdG + c) = make_float2(dK[0][nt][2 * half], dK[0][nt][2 * half + 1]);
+      }
+    tc::fence_proxy_async();
+  }
   if (tid < kChunk && tid < valid) {
     const float b = sBeta[tid];
     const float s = sRb[tid] + sRb[kChunk + tid] + sRb[2 * kChunk + tid] + sRb[3 * kChunk + tid];
@@ -649,6 +688,11 @@ pkda_intra_bwd_kernel(const IntraBwdParams p, const __grid_constant__ IntraBwdMa
     }
   }
   __syncthreads(); PKDA_PHASE(15);
+  if (out_tma && tid == 0) {
+    tc::tma_store_3d(&maps.dq, smem_u32(sQ), 0, h, tok0);
+    tc::tma_store_3d(&maps.dk_read, smem_u32(smem + oA1), 0, h, tok0);
+    tc::bulk_commit();
+  }
   // ... then the gate's own backward, elementwise over the tile with all threads:
   //   g = -exp(A_log) softplus(raw + bias);  draw = dg * (-exp(A_log)) sigmoid(raw + bias)
   // Per-thread partial sums (dA_log: scalar; ddt_bias: per channel) are reduced in a fixed order.
@@ -715,6 +759,7 @@ pkda_intra_bwd_kernel(const IntraBwdParams p, const __grid_constant__ IntraBwdMa
 #pragma unroll
     for (int w = 0; w < kThreads / 32; ++w) acc += sRed[w];
     p.partA[chh] = acc;
+    if (out_tma) tc::bulk_wait_read();  // the tiles stay in place until the stores have read them
   }
   PKDA_PHASE(17);
 }
@@ -1221,6 +1266,11 @@ int chunk_bwd(const pkda_chunk_bwd_args* a, cudaStream_t st) {
                  encode_bf16_map(&maps.h, ip.h, 2, st_dims, st_str, st_box, false) &&
                  encode_bf16_map(&maps.dh, ip.dh, 2, st_dims, st_str, st_box, false) &&
                  encode_bf16_map(&maps.Akk, ip.Akk, 2, pr_dims, pr_str, pr_box, false);
+    const uint64_t o_dims[3] = {kD, H, tok}, o_str2[2] = {kD * 2, H * kD * 2}, o_str4[2] = {kD * 4, H * kD * 4};
+    const uint32_t o_box[3] = {kLdD, 1, kChunk};
+    ip.out_tma = ip.use_tma && encode_bf16_map(&maps.dq, ip.dq, 3, o_dims, o_str2, o_box, false) &&
+                 encode_f32_map(&maps.dk_read, ip.dk_read, 3, o_dims, o_str4, o_box) &&
+                 encode_f32_map(&maps.dkt, ip.dkt, 3, o_dims, o_str4, o_box);
     ip.status = ws.status;
   }
   if (!set_smem(pkda_intra_bwd_kernel, ib::kSmem)) return PKDA_ERR_LAUNCH;

@@ -167,8 +167,8 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-bool encode_bf16_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides,
-                     const uint32_t* box, bool swizzle128) {
+static bool encode_map(CUtensorMap* map, CUtensorMapDataType type, CUtensorMapSwizzle swizzle, const void* base,
+                       int rank, const uint64_t* dims, const uint64_t* strides, const uint32_t* box) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   cuuint64_t gdim[5], gstr[5];
@@ -179,10 +179,19 @@ bool encode_bf16_map(CUtensorMap* map, const void* base, int rank, const uint64_
     estr[i] = 1;
     if (i > 0) gstr[i - 1] = strides[i - 1];
   }
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), gdim, gstr, bdim, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
-            CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  return fn(map, type, (cuuint32_t)rank, const_cast<void*>(base), gdim, gstr, bdim, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool encode_bf16_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides,
+                     const uint32_t* box, bool swizzle128) {
+  return encode_map(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                    swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, base, rank, dims, strides, box);
+}
+
+bool encode_f32_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides,
+                    const uint32_t* box) {
+  return encode_map(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, CU_TENSOR_MAP_SWIZZLE_NONE, base, rank, dims, strides, box);
 }
 
 int launch_out_fwd_tc(const Geo& geo, int total_tokens, const bf16* qg, const bf16* h, const bf16* Aqk,

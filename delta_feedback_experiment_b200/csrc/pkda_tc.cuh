@@ -161,6 +161,9 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 // Returns false if the driver entry point is unavailable or the encode fails.
 bool encode_bf16_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides,
                      const uint32_t* box, bool swizzle128 = true);
+// The same for fp32 elements, rows laid out plainly (no swizzle).
+bool encode_f32_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides,
+                    const uint32_t* box);
 
 // Byte offset of element (row, col) in a 128-byte-swizzled tile made of blocks of
 // [rows][64 bf16]: block = col / 64, 16-byte piece (col % 64) / 8 XOR-ed with row % 8.

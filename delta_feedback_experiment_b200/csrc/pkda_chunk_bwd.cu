@@ -210,7 +210,7 @@ struct IntraBwdParams {
   float scale;
   int direct_cap;
   int use_tma;   // the five phase-A tiles of full chunks arrive by TMA (tensor maps valid)
-  int out_tma;   // dq, dk_read and dkt of full chunks leave by TMA from padded shared-memory tiles
+  int out_tma;   // dq, dv, dk_read and dkt of full chunks leave by TMA from padded shared-memory tiles
   int* status;   // set to 1 if a bounded wait gives up
 };
 
@@ -218,12 +218,12 @@ struct IntraBwdParams {
 // or 72 columns for 128 or 64) so that the rows land in shared memory with the
 // padded pitch the ldmatrix reads want; the surplus columns are the neighbouring
 // head's data or, past the end of a row, zero fill.
-// The three output maps are [token][head][channel] with a box of one head and 136
+// The four output maps are [token][head][channel] with a box of one head and 136
 // columns: a store clips the eight columns past the head, so the padded pitch of
 // the shared-memory tile never reaches the neighbouring head.
 struct IntraBwdMaps {
   CUtensorMap d_o, dF, h, dh, Akk;
-  CUtensorMap dq, dk_read, dkt;
+  CUtensorMap dq, dv, dk_read, dkt;
 };
 
 namespace ib {
@@ -321,6 +321,7 @@ pkda_intra_bwd_kernel(const IntraBwdParams p, const __grid_constant__ IntraBwdMa
   // gate computation while they land.  Ragged chunks (rows past the sequence end must
   // read as zero) take 16-byte cp.async copies.
   const bool by_tma = p.use_tma && valid == kChunk;
+  const bool out_tma = by_tma && p.out_tma;  // gradients of full chunks leave by TMA from padded tiles
   const uint32_t bar = smem_u32(smem + oBar);
   if (by_tma) {
     if (tid == 0) {
@@ -416,10 +417,15 @@ pkda_intra_bwd_kernel(const IntraBwdParams p, const __grid_constant__ IntraBwdMa
     for (int half = 0; half < 2; ++half) {
       const int r = 16 * I + gq + 8 * half, c = 32 * cq + 8 * nt + 2 * tq;
       const uint32_t pk = pack_bf16(t[0][nt][2 * half], t[0][nt][2 * half + 1]);
-      if (r < valid) *reinterpret_cast<uint32_t*>(p.dv + row0 + (size_t)r * gld + c) = pk;
+      if (!out_tma && r < valid) *reinterpret_cast<uint32_t*>(p.dv + row0 + (size_t)r * gld + c) = pk;
       *reinterpret_cast<uint32_t*>(sdR + r * kLdD + c) = pk;
     }
+  if (out_tma) tc::fence_proxy_async();
   __syncthreads(); PKDA_PHASE(4);
+  if (out_tma && tid == 0) {  // dv is the dR tile as it stands
+    tc::tma_store_3d(&maps.dv, smem_u32(sdR), 0, h, tok0);
+    tc::bulk_commit();
+  }
   // dKd = -dR S0^T  ->  dk_a = Gam * dKd
   zero_acc(t);
   warp_gemm<1, 4, false, false>(t, sdR, kLdD, 16 * I, sS0, kLdD, 32 * cq, 0, kD);
@@ -498,6 +504,7 @@ pkda_intra_bwd_kernel(const IntraBwdParams p, const __grid_constant__ IntraBwdMa
         *reinterpret_cast<uint32_t*>(sdP + i * kLdC + j) = pack_bf16(p0, p1);
       }
   }
+  if (out_tma && tid == 0) tc::bulk_wait_read();  // the dv store has read the dR tile
   __syncthreads(); PKDA_PHASE(7);  // dO, dR, E no longer needed
   // dkg = F dS1^T  ->  dkt_a = exp(G_last - G) * dkg
   PKDA_PHASE(8);
@@ -626,7 +633,6 @@ pkda_intra_bwd_kernel(const IntraBwdParams p, const __grid_constant__ IntraBwdMa
   // decay tile) and TMA stores; the scattered fragment stores of the direct path cost more
   // issue slots than the rest of this phase together.
   float* sdG = reinterpret_cast<float*>(smem + oStage);
-  const bool out_tma = by_tma && p.out_tma;
   if (out_tma) {
     float* sOutKt = sG;  // the decay tile is dead after the level loop
 #pragma unroll
@@ -1269,6 +1275,7 @@ int chunk_bwd(const pkda_chunk_bwd_args* a, cudaStream_t st) {
     const uint64_t o_dims[3] = {kD, H, tok}, o_str2[2] = {kD * 2, H * kD * 2}, o_str4[2] = {kD * 4, H * kD * 4};
     const uint32_t o_box[3] = {kLdD, 1, kChunk};
     ip.out_tma = ip.use_tma && encode_bf16_map(&maps.dq, ip.dq, 3, o_dims, o_str2, o_box, false) &&
+                 encode_bf16_map(&maps.dv, ip.dv, 3, o_dims, o_str2, o_box, false) &&
                  encode_f32_map(&maps.dk_read, ip.dk_read, 3, o_dims, o_str4, o_box) &&
                  encode_f32_map(&maps.dkt, ip.dkt, 3, o_dims, o_str4, o_box);
     ip.status = ws.status;

@@ -361,6 +361,11 @@ int launch_scan_fwd_tc(const Geo& geo, int total_tokens, int units, const bf16* 
                        const float* beta_c, const float* gc, const float* S0, bf16* h, bf16* v_new, float* ST,
                        int* status, bool recompute, cudaStream_t st);
 
+// tcgen05 / TMA reverse state scan of the backward (pkda_scan_bwd_tc.cu): one CTA per (sequence, head).
+int launch_scan_bwd_tc(const Geo& geo, int total_tokens, int units, const bf16* kg, const bf16* w, const bf16* qg,
+                       const bf16* d_o, const bf16* Aqk, const float* beta_c, const float* gc, const float* dST,
+                       bf16* dh, bf16* dF, float* dS0, int* status, cudaStream_t st);
+
 // Host-side pieces defined in pkda_chunk_fwd.cu and reused by the backward.
 int check_chunk_problem(const pkda_problem& p);
 int run_prologue(const pkda_problem& p, int* chunk_offsets, float* beta_c, Geo* geo, cudaStream_t st);

@@ -1240,8 +1240,16 @@ int chunk_bwd(const pkda_chunk_bwd_args* a, cudaStream_t st) {
   {
     const int units = p.n_seqs * p.heads;
     const int vb = units >= 120 ? 128 : (units >= 60 ? 64 : 32);
+    // Full-width slices run on tcgen05 / TMEM / TMA; PKDA_SCAN_IMPL=mma keeps the mma.sync kernel (A/B runs).
+    static const bool scan_mma = [] {
+      const char* e = getenv("PKDA_SCAN_IMPL");
+      return e && e[0] == 'm';
+    }();
     begin_stage(kStageScanBwd, st);
-    if (vb == 128) rc = launch_scan_bwd<128>(sp, units, st);
+    if (vb == 128 && !scan_mma)
+      rc = launch_scan_bwd_tc(geo, p.total_tokens, units, kg, w, qg, sp.d_o, Aqk, ws.beta_c, gc, a->d_final_state,
+                              ws.dh, ws.dF, a->d_initial_state, ws.status, st);
+    else if (vb == 128) rc = launch_scan_bwd<128>(sp, units, st);
     else if (vb == 64) rc = launch_scan_bwd<64>(sp, units, st);
     else rc = launch_scan_bwd<32>(sp, units, st);
     end_stage(st);

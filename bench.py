@@ -65,8 +65,8 @@ STAGE_FLOPS = {
 # DRAM traffic per (token, head) of each kernel: dram__bytes_read.sum + dram__bytes_write.sum of one
 # ncu capture on the quarter-size workload (131,072 units), divided by its units; the traffic grows
 # in proportion to the units, so a launch of any size moves this many bytes per unit.
-STAGE_TRAFFIC_PER_UNIT = {"intra_fwd": 2215, "scan_fwd": 1242, "out_fwd": 1297, "scan_bwd": 1732,
-                          "intra_bwd": 4511}
+STAGE_TRAFFIC_PER_UNIT = {"intra_fwd": 2212, "scan_fwd": 1251, "out_fwd": 1307, "scan_bwd": 1667,
+                          "intra_bwd": 4503}
 DECODE_BYTES_PER_UNIT = 2 * 4 * 128 * 128 + 2 * 4 * 128 + 4 * 2 * 128 + 8 + 2 * 128   # 133,384
 
 

@@ -24,7 +24,7 @@ SOURCES = ["pkda_abi.cu", "pkda_recurrent.cu", "pkda_chunk_fwd.cu", "pkda_chunk_
            "pkda_static_scratch.cu", "pkda_out_tc.cu", "pkda_scan_tc.cu", "pkda_scan_bwd_tc.cu",
            "pkda_recurrent_bwd.cu", "pkda_qkv_conv.cu", "pkda_norm_gate.cu", "pkda_decode_step.cu", "pkda_controls.cu"]
 NVCC_FLAGS = [
-    "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
+    "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17", "-ftz=true",
     "-Xcompiler", "-fPIC", "-Xptxas", "-v",
 ]
 
@@ -37,7 +37,7 @@ def _nvcc() -> str:
 
 
 def _deps() -> list[str]:
-    out = [os.path.join(INCLUDE, "pkda_b200.h")]
+    out = [os.path.join(INCLUDE, "pkda_b200.h"), os.path.abspath(__file__)]  # the flags live in this file
     for name in os.listdir(CSRC):
         out.append(os.path.join(CSRC, name))
     return out

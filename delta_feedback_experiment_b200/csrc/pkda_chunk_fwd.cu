@@ -213,6 +213,12 @@ pkda_intra_fwd_kernel(const IntraParams p) {
   // ---- 1. tiles and per-row scalars (the raw gate first: it is needed first)
   GateRaw<kThreads> graw;
   gate_load(graw, p.g + row0, gld, valid, tid);
+  // Scalars of later phases are fetched here: a global load issued where it is used costs
+  // that phase a full memory round trip with nothing to overlap it.
+  const float a_log = p.A_log[h];
+  const float centre = kRecompute ? 0.f : p.log_atk_scale[h];
+  float a_first = 0.f;
+  if (!kRecompute && tid >= kD && tid < 2 * kD) a_first = p.a_start[chh * kD + tid - kD];
   tile_load_async(sQ, kLdD, p.q + row0, gld, kChunk, kD, valid, kThreads);
   tile_load_async(sK, kLdD, p.k + row0, gld, kChunk, kD, valid, kThreads);
   if (kRecompute) tile_load_async(sKt, kLdD, p.kt + row0, gld, kChunk, kD, valid, kThreads);
@@ -232,7 +238,7 @@ pkda_intra_fwd_kernel(const IntraParams p) {
 
   // ---- 2. decay gate (elementwise, all threads; the q and k tiles are still landing), then
   // the two per-channel sequential passes side by side: cumulative sum | preconditioner recurrence A_t
-  gate_apply(graw, sG, valid, sBias, __expf(p.A_log[h]) * kLog2e, tid);
+  gate_apply(graw, sG, valid, sBias, __expf(a_log) * kLog2e, tid);
   cp_async_wait<0>();
   __syncthreads(); PKDA_PHASE(2);
   if (tid < kD) {
@@ -247,7 +253,7 @@ pkda_intra_fwd_kernel(const IntraParams p) {
     }
   } else if (!kRecompute && tid < 2 * kD) {
     const int c = tid - kD;
-    float A = p.a_start[chh * kD + c];
+    float A = a_first;
 #pragma unroll 8
     for (int r = 0; r < kChunk; ++r) {
       const float kc = to_f(sK[r * kLdD + c]);
@@ -258,7 +264,6 @@ pkda_intra_fwd_kernel(const IntraParams p) {
   __syncthreads(); PKDA_PHASE(3);
   if (!kRecompute) {
     // write keys kt = k * exp(-ln(x) * dev / (1 + |dev|)), dev = log(A + eps) - centre
-    const float centre = p.log_atk_scale[h];
     for (int idx = tid; idx < kChunk * kD / 8; idx += kThreads) {
       const int r = idx >> 4, c8 = (idx & 15) << 3;
       const float4 A0 = *reinterpret_cast<const float4*>(sAt + r * kLdG + c8);

@@ -229,10 +229,10 @@ struct IntraBwdMaps {
 namespace ib {
 constexpr int kThreads = 512;
 constexpr int oA0 = 0;                        // dO          | later q
-constexpr int oA1 = kTileBytes;               // S0 [128][136] | E, F | later k, kt
+constexpr int oA1 = kTileBytes;               // S0 [128][136] | E | later k, kt
 constexpr int oG = oA1 + 2 * kTileBytes;      // f32 [64][kLdG] log2-domain cumulative decay
 constexpr int oTm = oG + kChunk * kLdG * 4;   // bf16 [64][72]
-constexpr int oDE = oTm + kChunk * kLdC * 2;  // dE | later dS1 [128][136] together with oDR
+constexpr int oDE = oTm + kChunk * kLdC * 2;  // dE | later F = beta E
 constexpr int oDR = oDE + kTileBytes;
 constexpr int oStage = oTm;                   // three gated operand tiles | later dG f32 [64][128]
 constexpr int oDP = oStage + 3 * kTileBytes;  // bf16 [64][72]
@@ -282,7 +282,7 @@ pkda_intra_bwd_kernel(const IntraBwdParams p, const __grid_constant__ IntraBwdMa
   bf16* sdO = reinterpret_cast<bf16*>(smem + oA0);
   bf16* sS0 = reinterpret_cast<bf16*>(smem + oA1);
   bf16* sE = reinterpret_cast<bf16*>(smem + oA1);
-  bf16* sF = reinterpret_cast<bf16*>(smem + oA1 + kTileBytes);
+  bf16* sF = reinterpret_cast<bf16*>(smem + oDE);  // F = beta E takes the dE tile once that is dead
   float* sG = reinterpret_cast<float*>(smem + oG);
   bf16* sTm = reinterpret_cast<bf16*>(smem + oTm);
   bf16* sdE = reinterpret_cast<bf16*>(smem + oDE);
@@ -508,9 +508,10 @@ pkda_intra_bwd_kernel(const IntraBwdParams p, const __grid_constant__ IntraBwdMa
   __syncthreads(); PKDA_PHASE(7);  // dO, dR, E no longer needed
   // dkg = F dS1^T  ->  dkt_a = exp(G_last - G) * dkg
   PKDA_PHASE(8);
-  // q and k tiles of the pair-product phase land while the dkg product runs
+  // q, k and kt tiles of the pair-product phase land while the dkg product runs
   tile_load_async(reinterpret_cast<bf16*>(smem + oA0), kLdD, p.q + row0, gld, kChunk, kD, valid, kThreads);
   tile_load_async(reinterpret_cast<bf16*>(smem + oA1), kLdD, p.k + row0, gld, kChunk, kD, valid, kThreads);
+  tile_load_async(reinterpret_cast<bf16*>(smem + oA1 + kTileBytes), kLdD, p.kt + row0, gld, kChunk, kD, valid, kThreads);
   cp_async_commit();
   zero_acc(t);
   warp_gemm<1, 4, false, false>(t, sF, kLdD, 16 * I, sdSC, kLdD, 32 * cq, 0, kD);
@@ -530,8 +531,6 @@ pkda_intra_bwd_kernel(const IntraBwdParams p, const __grid_constant__ IntraBwdMa
   bf16* sXq = reinterpret_cast<bf16*>(smem + oStage);
   bf16* sXk = sXq + kChunk * kLdD;
   bf16* sY = sXk + kChunk * kLdD;
-  tile_load_async(sKt, kLdD, p.kt + row0, gld, kChunk, kD, valid, kThreads);
-  cp_async_commit();
   cp_async_wait<0>();
   __syncthreads(); PKDA_PHASE(10);
   {
@@ -677,6 +676,17 @@ pkda_intra_bwd_kernel(const IntraBwdParams p, const __grid_constant__ IntraBwdMa
       }
     tc::fence_proxy_async();
   }
+  // The raw gate of the tail phase is requested here, with the accumulators gone and the
+  // reverse cumulative sum still to run: loaded where it is used, it cost the tail a full
+  // memory round trip.
+  constexpr int kIter = kChunk * kD / 8 / kThreads;
+  uint4 raws[kIter];
+#pragma unroll
+  for (int it = 0; it < kIter; ++it) {
+    const int r = (tid + it * kThreads) >> 4;
+    raws[it] = make_uint4(0, 0, 0, 0);
+    if (r < valid) raws[it] = *reinterpret_cast<const uint4*>(p.g + row0 + (size_t)r * gld + ((tid & 15) << 3));
+  }
   if (tid < kChunk && tid < valid) {
     const float b = sBeta[tid];
     const float s = sRb[tid] + sRb[kChunk + tid] + sRb[2 * kChunk + tid] + sRb[3 * kChunk + tid];
@@ -710,14 +720,6 @@ pkda_intra_bwd_kernel(const IntraBwdParams p, const __grid_constant__ IntraBwdMa
 #pragma unroll
     for (int j = 0; j < 8; ++j) pb[j] = 0.f;
     const int c8 = (tid & 15) << 3;
-    constexpr int kIter = kChunk * kD / 8 / kThreads;
-    uint4 raws[kIter];
-#pragma unroll
-    for (int it = 0; it < kIter; ++it) {
-      const int r = (tid + it * kThreads) >> 4;
-      raws[it] = make_uint4(0, 0, 0, 0);
-      if (r < valid) raws[it] = *reinterpret_cast<const uint4*>(p.g + row0 + (size_t)r * gld + c8);
-    }
 #pragma unroll
     for (int it = 0; it < kIter; ++it) {
       const int r = (tid + it * kThreads) >> 4;

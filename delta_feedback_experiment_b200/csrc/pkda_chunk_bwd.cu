@@ -313,7 +313,12 @@ pkda_intra_bwd_kernel(const IntraBwdParams p, const __grid_constant__ IntraBwdMa
   const long cld = (long)H * kChunk;
 
   // ================= phase A: state-coupled terms =================
-  GateRaw<kThreads> graw;  // the raw gate is needed first: fetch it first
+  // The per-row scalars the first barrier waits for are requested before everything else.
+  float s_small = 0.f;
+  if (tid < kChunk) s_small = p.beta_c[chh * kChunk + tid];
+  else if (tid >= 2 * kD && tid < 3 * kD) s_small = p.gc[chh * kD + tid - 2 * kD];
+  else if (tid >= kD && tid < 2 * kD) s_small = p.dt_bias[h * kD + tid - kD];
+  GateRaw<kThreads> graw;  // the raw gate is needed next
   gate_load(graw, p.g + row0, gld, valid, tid);
   // dS1 waits in the (not yet used) level-factor array until the dkg product
   bf16* sdSC = reinterpret_cast<bf16*>(smem + oFac);
@@ -342,9 +347,9 @@ pkda_intra_bwd_kernel(const IntraBwdParams p, const __grid_constant__ IntraBwdMa
     tile_load_async(sdSC, kLdD, p.dh + chh * kD * kD, kD, kD, kD, kD, kThreads);
     cp_async_commit();
   }
-  if (tid < kChunk) sBeta[tid] = p.beta_c[chh * kChunk + tid];
-  if (tid < kD) sGcv[tid] = p.gc[chh * kD + tid];
-  else if (tid < 2 * kD) sBias[tid - kD] = p.dt_bias[h * kD + tid - kD];
+  if (tid < kChunk) sBeta[tid] = s_small;
+  else if (tid >= 2 * kD && tid < 3 * kD) sGcv[tid - 2 * kD] = s_small;
+  else if (tid >= kD && tid < 2 * kD) sBias[tid - kD] = s_small;
   __syncthreads(); PKDA_PHASE(1);
   // log2-domain cumulative log-decay, exactly as the forward computes it
   gate_apply(graw, sG, valid, sBias, __expf(p.A_log[h]) * kLog2e, tid);

@@ -210,7 +210,18 @@ pkda_intra_fwd_kernel(const IntraParams p) {
   const size_t row0 = ((size_t)tok0 * H + h) * kD;  // element offset of (tok0, h, 0)
   const long gld = (long)H * kD;
 
-  // ---- 1. tiles and per-row scalars (the raw gate first: it is needed first)
+  // ---- 1. tiles and per-row scalars.  The per-row scalars are requested first (the first barrier
+  // waits for them and they would otherwise queue behind the 48 KB of tile traffic), then the raw
+  // gate (needed next), then the q and k tiles.
+  float s_beta = 0.f, s_pd = 0.f, s_bp = 0.f, s_bias = 0.f;
+  if (tid < kChunk) {
+    const size_t s = (size_t)(tok0 + min(tid, valid - 1)) * H + h;
+    s_beta = p.beta_c[chh * kChunk + tid];
+    s_pd = p.g_atk[s];
+    s_bp = to_f(p.beta_atk[s]);
+  } else if (tid < kChunk + kD) {
+    s_bias = p.dt_bias[h * kD + tid - kChunk];
+  }
   GateRaw<kThreads> graw;
   gate_load(graw, p.g + row0, gld, valid, tid);
   // Scalars of later phases are fetched here: a global load issued where it is used costs
@@ -225,12 +236,11 @@ pkda_intra_fwd_kernel(const IntraParams p) {
   cp_async_commit();
   if (tid < kChunk) {
     const bool ok = tid < valid;
-    const size_t s = (size_t)(tok0 + tid) * H + h;
-    sBeta[tid] = p.beta_c[chh * kChunk + tid];
-    sPd[tid] = ok ? __expf(p.g_atk[s]) : 1.f;
-    sBp[tid] = ok ? to_f(p.beta_atk[s]) : 0.f;
+    sBeta[tid] = s_beta;
+    sPd[tid] = ok ? __expf(s_pd) : 1.f;
+    sBp[tid] = ok ? s_bp : 0.f;
   } else if (tid < kChunk + kD) {
-    sBias[tid - kChunk] = p.dt_bias[h * kD + tid - kChunk];
+    sBias[tid - kChunk] = s_bias;
   }
   // zero the P staging tile (upper triangle must read as zero)
   for (int i = tid; i < kChunk * kLdC / 8; i += kThreads) reinterpret_cast<uint4*>(sTmb)[i] = make_uint4(0, 0, 0, 0);

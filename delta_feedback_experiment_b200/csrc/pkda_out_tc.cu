@@ -49,18 +49,13 @@ pkda_out_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_co
   const uint32_t bar_full = base + oBar, bar_mma = base + oBar + 8, tmem_slot = base + oBar + 16;
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(tiles + oBar + 16);
 
+  // The tile copies start before the tensor-memory allocation and the CTA-wide barrier: one
+  // thread of the second warp sets up the mbarriers and issues them while warp 0 allocates.
   if (warp == 0) tc::tmem_alloc(tmem_slot, kCols);
-  if (tid == 0) {
+  if (tid == 32) {
     tc::mbar_init(bar_full, 1);
     tc::mbar_init(bar_mma, 1);
     tc::fence_barrier_init();
-  }
-  tc::tc_fence_before();
-  __syncthreads();
-  tc::tc_fence_after();
-  const uint32_t tmem = *tmem_slot_ptr;
-
-  if (tid == 0) {
     tc::mbar_expect_tx(bar_full, kTxBytes);
     const int hrow = (int)(chh * kD);
     tc::tma_load_2d(base + oH, &tm_h, bar_full, 0, hrow);
@@ -71,6 +66,15 @@ pkda_out_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_co
     tc::tma_load_3d(base + oE + 8192, &tm_e, bar_full, 64, h, tok0);
     tc::tma_load_3d(base + oP, &tm_p, bar_full, 0, h, tok0);
   }
+  // beta of this thread's eight columns of P (the same columns in every row it scales), requested
+  // now so that it is back when the tiles are
+  const float4 b0 = *reinterpret_cast<const float4*>(p.beta_c + chh * kChunk + 8 * (tid & 7));
+  const float4 b1 = *reinterpret_cast<const float4*>(p.beta_c + chh * kChunk + 8 * (tid & 7) + 4);
+  tc::tc_fence_before();
+  __syncthreads();
+  tc::tc_fence_after();
+  const uint32_t tmem = *tmem_slot_ptr;
+
   bool ok = tc::mbar_wait(bar_full, 0);
 
   // P[tok][j] *= beta[j], in place in the swizzled tile: 16-byte piece jc of row i
@@ -79,8 +83,6 @@ pkda_out_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_co
     for (int idx = tid; idx < kChunk * 8; idx += kThreads) {
       const int i = idx >> 3, jc = idx & 7;
       uint4* piece = reinterpret_cast<uint4*>(tiles + oP + i * 128 + ((jc ^ (i & 7)) << 4));
-      const float4 b0 = *reinterpret_cast<const float4*>(p.beta_c + chh * kChunk + 8 * jc);
-      const float4 b1 = *reinterpret_cast<const float4*>(p.beta_c + chh * kChunk + 8 * jc + 4);
       const float f[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
       uint4 x = *piece;
       scale8(x, f);

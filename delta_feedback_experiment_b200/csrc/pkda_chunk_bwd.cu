@@ -869,7 +869,11 @@ pkda_atk_bwd_kernel(const AtkBwdParams p, int n_tiles) {
   // The next tile's data is requested before the current tile is computed.
   int tok0_n = 0, valid_n = 0;
   bool live_n = false;
-  uint32_t bpraw_n[kRows / 2];  // the next tile's beta_atk (bf16 pairs), by plain loads
+  // The next tile's beta_atk (lane i of a warp holds the bf16 bits of the warp's row i) and centre,
+  // by plain loads that nothing consumes before the next iteration.
+  uint32_t bpraw_n = 0;
+  float centre_n = 0.f;
+  static_assert(kRows <= 32 && (kRows & (kRows - 1)) == 0, "one lane per row");
   auto request = [&](int tile) {
     live_n = false;
     if (tile < n_tiles) {
@@ -891,9 +895,13 @@ pkda_atk_bwd_kernel(const AtkBwdParams p, int n_tiles) {
         cp_async16(sDkt + i * kThreads + tid, p.dkt + off, ok);
         if (kFinal) cp_async16(sDkr + i * kThreads + tid, p.dk_read + off, ok);
         cp_async4(sLg + i * kThreads + tid, p.g_atk + s, ok);
-        const float bpv = ok ? to_f(p.beta_atk[s]) : 0.f;
-        if (i & 1) bpraw_n[i >> 1] = pack_bf16(__uint_as_float(bpraw_n[i >> 1]), bpv);
-        else bpraw_n[i >> 1] = __float_as_uint(bpv);
+      }
+      {
+        const int r = r0 + (lane & (kRows - 1));
+        bpraw_n = 0;
+        if (r < valid_n)
+          bpraw_n = *reinterpret_cast<const unsigned short*>(p.beta_atk + (size_t)(tok0_n + r) * H + hh);
+        centre_n = p.log_atk_scale[hh];
       }
       cp_async16(sA0 + tid, p.a_start + (size_t)tile * kD + c4, true);
       if (kFinal) cp_async16(sLin + tid, p.lam_in + (size_t)tile * kD + c4, true);
@@ -917,15 +925,14 @@ pkda_atk_bwd_kernel(const AtkBwdParams p, int n_tiles) {
     dkt[i] = sDkt[i * kThreads + tid];
     dkr[i] = kFinal ? sDkr[i * kThreads + tid] : make_float4(0.f, 0.f, 0.f, 0.f);
     pd[i] = sLg[i * kThreads + tid];  // the log-decay for now (zero fill past the end: decay 1)
-    const float2 b2 = unpack_bf16(bpraw_n[i >> 1]);
-    bp[i] = (i & 1) ? b2.y : b2.x;
+    bp[i] = __uint_as_float(__shfl_sync(0xffffffffu, bpraw_n, i) << 16);
   }
   const float4 a0 = sA0[tid];
   float4 lin = make_float4(0.f, 0.f, 0.f, 0.f);
   if (kFinal) lin = sLin[tid];
+  const float centre = centre_n;
   request(tile + gridDim.x);  // the slots are free again: next tile's copies fly during the computation
   if (!live) continue;        // (uniform) index past the last real chunk of a packed batch
-  const float centre = p.log_atk_scale[h];
   float dblk = 1.f;
 #pragma unroll
   for (int i = 0; i < kRows; ++i) {

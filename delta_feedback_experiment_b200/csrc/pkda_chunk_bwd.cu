@@ -222,7 +222,7 @@ struct IntraBwdParams {
 // columns: a store clips the eight columns past the head, so the padded pitch of
 // the shared-memory tile never reaches the neighbouring head.
 struct IntraBwdMaps {
-  CUtensorMap d_o, dF, h, dh, Akk;
+  CUtensorMap d_o, dF, h, dh, Akk, E;
   CUtensorMap dq, dv, dk_read, dkt;
 };
 
@@ -243,8 +243,8 @@ constexpr int oSmall = oFac + kChunk * kLdG * 4;
 constexpr int kSmallFloats = 64 + 64 + 128 + 128 + 512 + 256 + 16 + 128 + 24;
 constexpr int oBar = oSmall + kSmallFloats * 4;  // one mbarrier
 constexpr int kSmem = oBar + 16;
-constexpr uint32_t kTmaBytes = (3 * kChunk + 2 * kD) * kLdD * 2 - kChunk * kLdD * 2 + kChunk * kLdC * 2;
-static_assert(kTmaBytes == (2 * kChunk + 2 * kD) * kLdD * 2 + kChunk * kLdC * 2, "dO, dF, S0, dS1 and Tm tiles");
+constexpr uint32_t kTmaBytes = (3 * kChunk + 2 * kD) * kLdD * 2 + kChunk * kLdC * 2;  // dO, dF, E, S0, dS1 and Tm tiles
+static_assert(2 * kChunk * kLdC * 2 >= kTileBytes && oDP % 128 == 0, "E waits in the pair-gradient tiles");
 static_assert(oBar % 8 == 0 && oA1 % 128 == 0 && oTm % 128 == 0 && oDE % 128 == 0 && oFac % 128 == 0,
               "TMA destinations and the mbarrier must be aligned");
 static_assert(oDR + kTileBytes <= oDP, "phase-A tiles must not reach the pair-gradient tiles");
@@ -320,8 +320,10 @@ pkda_intra_bwd_kernel(const IntraBwdParams p, const __grid_constant__ IntraBwdMa
   else if (tid >= kD && tid < 2 * kD) s_small = p.dt_bias[h * kD + tid - kD];
   GateRaw<kThreads> graw;  // the raw gate is needed next
   gate_load(graw, p.g + row0, gld, valid, tid);
-  // dS1 waits in the (not yet used) level-factor array until the dkg product
+  // dS1 waits in the (not yet used) level-factor array until the dkg product, E in the (not yet
+  // used) pair-gradient tiles until S0 has left the tile E belongs in
   bf16* sdSC = reinterpret_cast<bf16*>(smem + oFac);
+  bf16* sEarly = reinterpret_cast<bf16*>(smem + oDP);
   // Full chunks: one thread starts five TMA tile copies and everybody goes on to the
   // gate computation while they land.  Ragged chunks (rows past the sequence end must
   // read as zero) take 16-byte cp.async copies.
@@ -338,6 +340,7 @@ pkda_intra_bwd_kernel(const IntraBwdParams p, const __grid_constant__ IntraBwdMa
       tc::tma_load_2d(smem_u32(sTm), &maps.Akk, bar, h * kChunk, tok0);
       tc::tma_load_2d(smem_u32(sdE), &maps.dF, bar, h * kD, tok0);  // raw dF; scaled by beta below
       tc::tma_load_2d(smem_u32(sdSC), &maps.dh, bar, 0, (int)(chh * kD));
+      tc::tma_load_2d(smem_u32(sEarly), &maps.E, bar, h * kD, tok0);
     }
   } else {
     tile_load_async(sdO, kLdD, p.d_o + row0, gld, kChunk, kD, valid, kThreads);
@@ -345,6 +348,7 @@ pkda_intra_bwd_kernel(const IntraBwdParams p, const __grid_constant__ IntraBwdMa
     tile_load_async(sTm, kLdC, p.Akk + crow0, cld, kChunk, kChunk, valid, kThreads);
     tile_load_async(sdE, kLdD, p.dF + row0, gld, kChunk, kD, valid, kThreads);
     tile_load_async(sdSC, kLdD, p.dh + chh * kD * kD, kD, kD, kD, kD, kThreads);
+    tile_load_async(sEarly, kLdD, p.v_new + row0, gld, kChunk, kD, valid, kThreads);
     cp_async_commit();
   }
   if (tid < kChunk) sBeta[tid] = s_small;
@@ -371,12 +375,27 @@ pkda_intra_bwd_kernel(const IntraBwdParams p, const __grid_constant__ IntraBwdMa
     cp_async_wait<0>();
   }
   __syncthreads(); PKDA_PHASE(3);
-  // dE = beta * dF in place;  hdh[k] = sum_v S0[k][v] dS1[k][v] (four threads per state row)
+  // the direct part of dbeta, rowsum(dF * E), while dF is still unscaled; dE = beta * dF in place;
+  // hdh[k] = sum_v S0[k][v] dS1[k][v] (four threads per state row)
   for (int i = tid; i < kChunk * kD / 8; i += kThreads) {
     const int r = i >> 4, c = (i & 15) << 3;
     const float b = sBeta[r];
     const float f[8] = {b, b, b, b, b, b, b, b};
     uint4 x = *reinterpret_cast<const uint4*>(sdE + r * kLdD + c);
+    const uint4 ev = *reinterpret_cast<const uint4*>(sEarly + r * kLdD + c);
+    const uint32_t* e32 = reinterpret_cast<const uint32_t*>(&ev);
+    const uint32_t* f32 = reinterpret_cast<const uint32_t*>(&x);
+    float part = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 xe = unpack_bf16(e32[j]), y = unpack_bf16(f32[j]);
+      part += xe.x * y.x + xe.y * y.y;
+    }
+    part += __shfl_xor_sync(0xffffffffu, part, 8);
+    part += __shfl_xor_sync(0xffffffffu, part, 4);
+    part += __shfl_xor_sync(0xffffffffu, part, 2);
+    part += __shfl_xor_sync(0xffffffffu, part, 1);
+    if ((i & 15) == 0) sDb[r] = part;
     scale8(x, f);
     *reinterpret_cast<uint4*>(sdE + r * kLdD + c) = x;
   }
@@ -442,44 +461,21 @@ pkda_intra_bwd_kernel(const IntraBwdParams p, const __grid_constant__ IntraBwdMa
       dK[0][nt][e] = -t[0][nt][e] * ex2(sG[i * kLdG + c]);
     }
   __syncthreads(); PKDA_PHASE(5);  // S0 no longer needed
-  // E, F = beta E, and the direct part of dbeta: rowsum(dF * E)
-  {
-    constexpr int kIter = kChunk * kD / 8 / kThreads;
-    uint4 evs[kIter], fvs[kIter];
+  // E moves into its operand tile (S0 has left it) and F = beta E into the dead dE tile
+  for (int i = tid; i < kChunk * kD / 8; i += kThreads) {
+    const int r = i >> 4, c = (i & 15) << 3;
+    const uint4 ev = *reinterpret_cast<const uint4*>(sEarly + r * kLdD + c);
+    const float b = sBeta[r];
+    const uint32_t* e32 = reinterpret_cast<const uint32_t*>(&ev);
+    uint4 bf;
+    uint32_t* bf32 = reinterpret_cast<uint32_t*>(&bf);
 #pragma unroll
-    for (int it = 0; it < kIter; ++it) {  // all global loads in flight before any use
-      const int i = tid + it * kThreads, r = i >> 4, c = (i & 15) << 3;
-      evs[it] = fvs[it] = make_uint4(0, 0, 0, 0);
-      if (r < valid) {
-        evs[it] = *reinterpret_cast<const uint4*>(p.v_new + row0 + (size_t)r * gld + c);
-        fvs[it] = *reinterpret_cast<const uint4*>(p.dF + row0 + (size_t)r * gld + c);
-      }
+    for (int j = 0; j < 4; ++j) {
+      const float2 x = unpack_bf16(e32[j]);
+      bf32[j] = pack_bf16(b * x.x, b * x.y);
     }
-#pragma unroll
-    for (int it = 0; it < kIter; ++it) {
-      const int i = tid + it * kThreads, r = i >> 4, c = (i & 15) << 3;
-      uint4 ev = evs[it];
-      const uint4 fv = fvs[it];
-      const float b = sBeta[r];
-      uint32_t* e32 = reinterpret_cast<uint32_t*>(&ev);
-      const uint32_t* f32 = reinterpret_cast<const uint32_t*>(&fv);
-      uint4 bf;
-      uint32_t* bf32 = reinterpret_cast<uint32_t*>(&bf);
-      float part = 0.f;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 x = unpack_bf16(e32[j]), y = unpack_bf16(f32[j]);
-        part += x.x * y.x + x.y * y.y;
-        bf32[j] = pack_bf16(b * x.x, b * x.y);
-      }
-      *reinterpret_cast<uint4*>(sE + r * kLdD + c) = ev;
-      *reinterpret_cast<uint4*>(sF + r * kLdD + c) = bf;
-      part += __shfl_xor_sync(0xffffffffu, part, 8);
-      part += __shfl_xor_sync(0xffffffffu, part, 4);
-      part += __shfl_xor_sync(0xffffffffu, part, 2);
-      part += __shfl_xor_sync(0xffffffffu, part, 1);
-      if ((i & 15) == 0) sDb[r] = part;
-    }
+    *reinterpret_cast<uint4*>(sE + r * kLdD + c) = ev;
+    *reinterpret_cast<uint4*>(sF + r * kLdD + c) = bf;
   }
   __syncthreads(); PKDA_PHASE(6);
   // pair-weight gradients: dM = -tril(dR E^T, -1) diag(beta),  dP = scale tril(dO F^T)
@@ -1291,6 +1287,7 @@ int chunk_bwd(const pkda_chunk_bwd_args* a, cudaStream_t st) {
     const uint32_t pr_box[2] = {kLdC, kChunk};
     ip.use_tma = tok >= kChunk && encode_bf16_map(&maps.d_o, ip.d_o, 2, act_dims, act_str, act_box, false) &&
                  encode_bf16_map(&maps.dF, ip.dF, 2, act_dims, act_str, act_box, false) &&
+                 encode_bf16_map(&maps.E, ip.v_new, 2, act_dims, act_str, act_box, false) &&
                  encode_bf16_map(&maps.h, ip.h, 2, st_dims, st_str, st_box, false) &&
                  encode_bf16_map(&maps.dh, ip.dh, 2, st_dims, st_str, st_box, false) &&
                  encode_bf16_map(&maps.Akk, ip.Akk, 2, pr_dims, pr_str, pr_box, false);

@@ -133,6 +133,28 @@ def test_packed_variable_length_gradients():
     check(res, ref, "packed")
 
 
+def test_packed_ragged_sequences_on_the_tensor_memory_scans():
+    """Eight ragged sequences x sixteen heads = 128 (sequence, head) units: enough for the
+    forward and backward state scans to take their tcgen05 / tensor-memory kernels (one CTA
+    per unit, all 128 value columns).  Ragged last chunks, a one-token sequence and a
+    cotangent on the final state, against the float64 oracle."""
+    lens = [130, 64, 1, 77, 200, 65, 127, 190]
+    offs = [0]
+    for n in lens:
+        offs.append(offs[-1] + n)
+    H, D = 16, 128
+    d = make_inputs(1, offs[-1], H, D, seed=85, dist="unit", dtype=torch.bfloat16,
+                    with_state=True, n_states=len(lens))
+    dS = torch.randn(len(lens), H, D, D, generator=torch.Generator().manual_seed(9)) * 0.1
+    ref = pkda_oracle_with_grads([d[n] for n in INPUT_NAMES], d["do"],
+                                 initial_state=d["initial_state"],
+                                 initial_A_state=d["initial_A_state"], cu_seqlens=offs,
+                                 d_final_state=dS, dtype=torch.float64)
+    res = run(d, cu=offs, dS=dS)
+    assert rel_rms(res["o"], ref["o"]) < 0.005
+    check(res, ref, "packed-128-units")
+
+
 def test_backward_twice_is_bitwise_identical():
     d = make_inputs(2, 150, 2, 128, seed=83, dist="production", dtype=torch.bfloat16, with_state=True)
     a, b = run(d), run(d)

@@ -142,6 +142,8 @@ EXPORTS = (
     "pkda_sizeof_chunk_fwd_args", "pkda_sizeof_chunk_bwd_args", "pkda_last_launch_count",
     "pkda_stage_count", "pkda_stage_name", "pkda_stage_timing", "pkda_stage_timing_read",
     "pkda_static_scratch_bytes", "pkda_chunk_fwd_static", "pkda_set_direct_block_cap",
+    "pkda_chunk_fwd_status_offset", "pkda_chunk_bwd_status_offset", "pkda_static_status_ptr",
+    "pkda_set_variant",
     "pkda_qkv_conv_fwd", "pkda_qkv_conv_bwd_workspace_bytes", "pkda_qkv_conv_bwd",
     "pkda_norm_gate_fwd", "pkda_norm_gate_bwd_workspace_bytes", "pkda_norm_gate_bwd",
     "pkda_sizeof_qkv_conv_args", "pkda_sizeof_norm_gate_args",
@@ -168,9 +170,14 @@ def _configure(lib: C.CDLL) -> None:
     lib.pkda_static_scratch_bytes.restype = C.c_size_t
     lib.pkda_set_direct_block_cap.argtypes = [C.c_int]
     lib.pkda_set_direct_block_cap.restype = C.c_int
+    lib.pkda_set_variant.argtypes = [C.c_char_p, C.c_int]
+    lib.pkda_set_variant.restype = C.c_int
+    lib.pkda_static_status_ptr.argtypes = [C.POINTER(Problem), C.POINTER(C.c_void_p)]
+    lib.pkda_static_status_ptr.restype = C.c_int
     lib.pkda_chunk_bwd.argtypes = [C.POINTER(ChunkBwdArgs), C.c_void_p]
     lib.pkda_chunk_bwd.restype = C.c_int
-    for name in ("pkda_chunk_fwd_workspace_bytes", "pkda_chunk_bwd_workspace_bytes"):
+    for name in ("pkda_chunk_fwd_workspace_bytes", "pkda_chunk_bwd_workspace_bytes",
+                 "pkda_chunk_fwd_status_offset", "pkda_chunk_bwd_status_offset"):
         getattr(lib, name).argtypes = [C.POINTER(Problem)]
         getattr(lib, name).restype = C.c_size_t
     for name, struct in (("pkda_qkv_conv", QkvConvArgs), ("pkda_norm_gate", NormGateArgs)):
@@ -259,8 +266,9 @@ def ptr(t: Optional[torch.Tensor]) -> Optional[int]:
     return None if t is None else t.data_ptr()
 
 
-def current_stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+def current_stream(device=None) -> int:
+    """Raw handle of torch's current stream on ``device`` (default: the current device)."""
+    return torch.cuda.current_stream(device).cuda_stream
 
 
 def last_launch_count() -> int:
@@ -284,3 +292,9 @@ def stage_timing_read() -> dict:
 def set_direct_block_cap(cap: int) -> None:
     """Testing aid: caps the kernels' direct block size (64 = data-driven default)."""
     check(load().pkda_set_direct_block_cap(int(cap)), "pkda_set_direct_block_cap")
+
+
+def set_variant(stage: str, legacy: bool) -> None:
+    """Testing aid: pins the older mma.sync kernel of a stage (``"intra_fwd"``,
+    ``"scan_fwd"``, ``"out_fwd"``, ``"scan_bwd"``, ``"intra_bwd"``) or restores the default."""
+    check(load().pkda_set_variant(stage.encode(), 1 if legacy else 0), "pkda_set_variant")

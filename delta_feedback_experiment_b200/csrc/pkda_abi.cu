@@ -1,4 +1,5 @@
 // extern "C" surface of libpkda_b200.so (declared in include/pkda_b200.h).
+#include <cstring>
 #include <vector>
 
 #include "pkda_launch.h"
@@ -10,6 +11,27 @@ void reset_launch_count() { g_launches = 0; }
 
 static int g_direct_cap = 64;
 int direct_block_cap() { return g_direct_cap; }
+
+static int g_variant[kStageCount] = {};
+int stage_variant(int stage) { return (stage >= 0 && stage < kStageCount) ? g_variant[stage] : 0; }
+
+__global__ void pkda_status_guard_kernel(const int* status, bf16* out0, bf16* out1, bf16* out2, size_t n) {
+  if (*status == 0) return;
+  const bf16 nan = __float2bfloat16(__int_as_float(0x7fc00000));
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    if (out0) out0[i] = nan;
+    if (out1) out1[i] = nan;
+    if (out2) out2[i] = nan;
+  }
+}
+
+int launch_status_guard(const int* status, void* out0, void* out1, void* out2, size_t n, cudaStream_t st) {
+  begin_stage(kStageStatusGuard, st);
+  pkda_status_guard_kernel<<<4, 256, 0, st>>>(status, static_cast<bf16*>(out0), static_cast<bf16*>(out1),
+                                              static_cast<bf16*>(out2), n);
+  end_stage(st);
+  return cudaGetLastError() == cudaSuccess ? PKDA_OK : PKDA_ERR_LAUNCH;
+}
 
 // Optional per-stage timing (used by the benchmark): one event pair per launch,
 // taken from a pool that grows only while timing is enabled.
@@ -106,6 +128,9 @@ int pkda_chunk_fwd(const pkda_chunk_fwd_args* args, void* cuda_stream) {
 size_t pkda_chunk_bwd_workspace_bytes(const pkda_problem* p) {
   return p ? pkda::chunk_bwd_workspace(*p) : 0;
 }
+
+size_t pkda_chunk_fwd_status_offset(const pkda_problem* p) { return p ? pkda::chunk_fwd_status_offset(*p) : 0; }
+size_t pkda_chunk_bwd_status_offset(const pkda_problem* p) { return p ? pkda::chunk_bwd_status_offset(*p) : 0; }
 
 int pkda_chunk_bwd(const pkda_chunk_bwd_args* args, void* cuda_stream) {
   if (!args) return PKDA_ERR_NULL;
@@ -208,11 +233,24 @@ int pkda_set_direct_block_cap(int cap) {
 
 int pkda_stage_count(void) { return pkda::kStageCount; }
 
+int pkda_set_variant(const char* stage, int variant) {
+  if (!stage) return PKDA_ERR_NULL;
+  const int two_impl[] = {pkda::kStageIntraFwd, pkda::kStageScanFwd, pkda::kStageOutFwd, pkda::kStageScanBwd,
+                          pkda::kStageIntraBwd};
+  for (int s : two_impl)
+    if (std::strcmp(stage, pkda_stage_name(s)) == 0) {
+      pkda::g_variant[s] = variant ? 1 : 0;
+      return PKDA_OK;
+    }
+  return PKDA_ERR_SHAPE;
+}
+
 const char* pkda_stage_name(int stage) {
   static const char* names[] = {"chunk_offsets", "pack_beta", "atk_local", "atk_carry", "intra_fwd", "scan_fwd",
                                 "out_fwd", "scan_bwd", "intra_bwd", "atk_bwd_local", "atk_bwd_carry",
                                 "atk_bwd_final", "param_reduce", "recurrent", "qkv_conv_fwd", "qkv_conv_bwd",
-                                "qkv_conv_dw", "norm_gate_fwd", "norm_gate_bwd", "norm_gate_dw", "decode_step", "controls_fwd", "controls_bwd", "pack_control"};
+                                "qkv_conv_dw", "norm_gate_fwd", "norm_gate_bwd", "norm_gate_dw", "decode_step", "controls_fwd", "controls_bwd", "pack_control",
+                                "status_guard"};
   return (stage >= 0 && stage < pkda::kStageCount) ? names[stage] : "?";
 }
 

@@ -13,6 +13,8 @@
 // Pipeline:  [recompute forward stages]  scan_bwd (sequential over chunks)
 //   -> intra_bwd (per chunk) -> atk_bwd local / carry / final (preconditioner
 //   reverse scan, chunk-parallel) -> param_reduce.
+#include <algorithm>
+
 #include "pkda_chunk.cuh"
 #include "pkda_tc.cuh"
 
@@ -1191,6 +1193,9 @@ static BwdWorkspace carve_bwd(const pkda_problem& p, void* base) {
 }
 
 size_t chunk_bwd_workspace(const pkda_problem& p) { return carve_bwd(p, nullptr).bytes; }
+size_t chunk_bwd_status_offset(const pkda_problem& p) {
+  return (size_t)(reinterpret_cast<unsigned char*>(carve_bwd(p, nullptr).status) - static_cast<unsigned char*>(nullptr));
+}
 
 #define PKDA_CHECK_LAUNCH()                                        \
   do {                                                             \
@@ -1250,11 +1255,8 @@ int chunk_bwd(const pkda_chunk_bwd_args* a, cudaStream_t st) {
   {
     const int units = p.n_seqs * p.heads;
     const int vb = units >= 120 ? 128 : (units >= 60 ? 64 : 32);
-    // Full-width slices run on tcgen05 / TMEM / TMA; PKDA_SCAN_IMPL=mma keeps the mma.sync kernel (A/B runs).
-    static const bool scan_mma = [] {
-      const char* e = getenv("PKDA_SCAN_IMPL");
-      return e && e[0] == 'm';
-    }();
+    // Full-width slices run on tcgen05 / TMEM / TMA unless the mma.sync kernel is pinned (pkda_set_variant).
+    const bool scan_mma = stage_variant(kStageScanBwd) != 0;
     begin_stage(kStageScanBwd, st);
     if (vb == 128 && !scan_mma)
       rc = launch_scan_bwd_tc(geo, p.total_tokens, units, kg, w, qg, sp.d_o, Aqk, ws.beta_c, gc, a->d_final_state,
@@ -1330,7 +1332,8 @@ int chunk_bwd(const pkda_chunk_bwd_args* a, cudaStream_t st) {
   pkda_param_reduce_kernel<<<p.heads, kD * kReduceSubs, 0, st>>>(geo, ws.partA, ws.partB, ws.partC, a->dA_log, a->ddt_bias,
                                                    a->dlog_atk_scale);
   PKDA_CHECK_LAUNCH();
-  return PKDA_OK;
+  const size_t guard_n = std::min<size_t>((size_t)p.total_tokens * p.heads * kD, 4096);
+  return launch_status_guard(ws.status, a->dq, a->dk, a->dv, guard_n, st);
 }
 
 }  // namespace pkda

@@ -16,7 +16,7 @@
 // (overflow after a few tokens); level L of the hierarchy pairs rows whose index
 // has bit L set with rows of the same 2L-block whose bit L is clear, both
 // expressed relative to the first row of the upper half, so every factor is <= 1.
-#include <cstdlib>
+#include <algorithm>
 
 #include "pkda_chunk.cuh"
 
@@ -723,6 +723,9 @@ static FwdWorkspace carve_fwd(const pkda_problem& p, void* base) {
 }
 
 size_t chunk_fwd_workspace(const pkda_problem& p) { return carve_fwd(p, nullptr).bytes; }
+size_t chunk_fwd_status_offset(const pkda_problem& p) {
+  return (size_t)(reinterpret_cast<unsigned char*>(carve_fwd(p, nullptr).status) - static_cast<unsigned char*>(nullptr));
+}
 
 template <typename K>
 static bool set_smem(K kernel, int bytes) {
@@ -787,11 +790,8 @@ int run_forward_stages(const pkda_problem& p, const Geo& geo, const float* beta_
   const int units = p.n_seqs * p.heads;
   const int vb = units >= 120 ? 128 : (units >= 60 ? 64 : 32);
   int rc = PKDA_ERR_LAUNCH;
-  // Full-width slices run on tcgen05 / TMEM / TMA; PKDA_SCAN_IMPL=mma keeps the mma.sync kernel (A/B runs).
-  static const bool scan_mma = [] {
-    const char* e = getenv("PKDA_SCAN_IMPL");
-    return e && e[0] == 'm';
-  }();
+  // Full-width slices run on tcgen05 / TMEM / TMA unless the mma.sync kernel is pinned (pkda_set_variant).
+  const bool scan_mma = stage_variant(kStageScanFwd) != 0;
   begin_stage(kStageScanFwd, st);
   if (vb == 128 && status && !scan_mma)
     rc = launch_scan_fwd_tc(geo, p.total_tokens, units, w, kg, u_ws, beta_c, gc, p.initial_state, h, v_new, ST,
@@ -852,15 +852,14 @@ int chunk_fwd(const pkda_chunk_fwd_args* a, cudaStream_t st) {
                           static_cast<bf16*>(a->qg), a->final_state, false, ws.status, st);
   if (rc != PKDA_OK) return rc;
 
-  // Output stage: tcgen05 + TMA by default; PKDA_OUT_IMPL=mma selects the mma.sync kernel (A/B runs).
-  static const bool use_mma = [] {
-    const char* e = getenv("PKDA_OUT_IMPL");
-    return e && e[0] == 'm';
-  }();
-  if (!use_mma) {
-    return launch_out_fwd_tc(geo, p.total_tokens, static_cast<const bf16*>(a->qg), static_cast<const bf16*>(a->h),
-                             static_cast<const bf16*>(a->Aqk), static_cast<const bf16*>(a->v_new), ws.beta_c,
-                             static_cast<bf16*>(a->o), ws.status, st);
+  // Output stage: tcgen05 + TMA unless the mma.sync kernel is pinned (pkda_set_variant).
+  const size_t guard_n = std::min<size_t>((size_t)p.total_tokens * p.heads * kD, 4096);
+  if (stage_variant(kStageOutFwd) == 0) {
+    rc = launch_out_fwd_tc(geo, p.total_tokens, static_cast<const bf16*>(a->qg), static_cast<const bf16*>(a->h),
+                           static_cast<const bf16*>(a->Aqk), static_cast<const bf16*>(a->v_new), ws.beta_c,
+                           static_cast<bf16*>(a->o), ws.status, st);
+    if (rc != PKDA_OK) return rc;
+    return launch_status_guard(ws.status, a->o, nullptr, nullptr, guard_n, st);
   }
   OutParams op;
   op.geo = geo;
@@ -871,7 +870,7 @@ int chunk_fwd(const pkda_chunk_fwd_args* a, cudaStream_t st) {
   begin_stage(kStageOutFwd, st);
   pkda_out_fwd_kernel<<<gridc, outk::kThreads, outk::kSmem, st>>>(op);
   PKDA_CHECK_LAUNCH();
-  return PKDA_OK;
+  return launch_status_guard(ws.status, a->o, nullptr, nullptr, guard_n, st);
 }
 
 }  // namespace pkda

@@ -14,7 +14,7 @@ enum Stage {
   kStageOutFwd, kStageScanBwd, kStageIntraBwd, kStageAtkBwdLocal, kStageAtkBwdCarry, kStageAtkBwdFinal,
   kStageParamReduce, kStageRecurrent, kStageConvFwd, kStageConvBwd, kStageConvDw, kStageNormGateFwd,
   kStageNormGateBwd, kStageNormGateDw, kStageDecodeStep, kStageControlsFwd, kStageControlsBwd,
-  kStagePackControl, kStageCount
+  kStagePackControl, kStageStatusGuard, kStageCount
 };
 
 // begin_stage / end_stage bracket every kernel launch: they count launches and,
@@ -22,6 +22,14 @@ enum Stage {
 void begin_stage(int stage, cudaStream_t st);
 void end_stage(cudaStream_t st);
 void reset_launch_count();
+
+// Testing aid behind pkda_set_variant: nonzero pins the older mma.sync kernel of a stage.
+int stage_variant(int stage);
+
+// Last launch of a chunked call: if the call's device status word is set (a bounded
+// wait inside a kernel gave up), the first `n` elements of each given bf16 output are
+// overwritten with NaN so that the failure reaches the caller's non-finite check.
+int launch_status_guard(const int* status, void* out0, void* out1, void* out2, size_t n, cudaStream_t st);
 
 // Upper limit for the kernels' direct block size (64 unless lowered through
 // pkda_set_direct_block_cap, a testing aid).
@@ -50,6 +58,9 @@ int recurrent_fwd_checkpointed(const pkda_problem& p, const int* chunk_offsets, 
                                float* Ab, cudaStream_t st);
 size_t chunk_fwd_workspace(const pkda_problem& p);
 size_t chunk_bwd_workspace(const pkda_problem& p);
+size_t chunk_fwd_status_offset(const pkda_problem& p);
+size_t chunk_bwd_status_offset(const pkda_problem& p);
+int check_chunk_problem(const pkda_problem& p);
 int qkv_conv_fwd(const pkda_qkv_conv_args* a, cudaStream_t st);
 int qkv_conv_bwd(const pkda_qkv_conv_args* a, cudaStream_t st);
 size_t qkv_conv_bwd_workspace(const pkda_qkv_conv_args& a);

@@ -21,7 +21,13 @@ static std::mutex g_scratch_mutex;
 // first call per device, with that device current).
 static int static_scratch_address(void** out) {
   int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return PKDA_ERR_LAUNCH;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) return PKDA_ERR_LAUNCH;
+  if (dev >= kMaxDevices) {  // beyond the cache: look the address up on every call
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || !ptr) return PKDA_ERR_LAUNCH;
+    *out = ptr;
+    return PKDA_OK;
+  }
   std::lock_guard<std::mutex> lock(g_scratch_mutex);
   if (!g_scratch_addr[dev]) {
     void* ptr = nullptr;
@@ -41,6 +47,8 @@ size_t pkda_static_scratch_bytes(void) { return pkda::kStaticScratchBytes; }
 int pkda_chunk_fwd_static(const pkda_chunk_fwd_args* args, void* cuda_stream) {
   if (!args) return PKDA_ERR_NULL;
   pkda::reset_launch_count();
+  int rc0 = pkda::check_chunk_problem(args->p);  // geometry errors are reported as such, not as a size problem
+  if (rc0 != PKDA_OK) return rc0;
   const size_t need = pkda::chunk_fwd_workspace(args->p);
   if (need > pkda::kStaticScratchBytes) return PKDA_ERR_STATIC_LIMIT;
   void* scratch = nullptr;
@@ -50,6 +58,19 @@ int pkda_chunk_fwd_static(const pkda_chunk_fwd_args* args, void* cuda_stream) {
   local.workspace = scratch;
   local.workspace_bytes = pkda::kStaticScratchBytes;
   return pkda::chunk_fwd(&local, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int pkda_static_status_ptr(const pkda_problem* p, const int32_t** device_ptr) {
+  if (!p || !device_ptr) return PKDA_ERR_NULL;
+  int rc = pkda::check_chunk_problem(*p);
+  if (rc != PKDA_OK) return rc;
+  if (pkda::chunk_fwd_workspace(*p) > pkda::kStaticScratchBytes) return PKDA_ERR_STATIC_LIMIT;
+  void* scratch = nullptr;
+  rc = pkda::static_scratch_address(&scratch);
+  if (rc != PKDA_OK) return rc;
+  *device_ptr = reinterpret_cast<const int32_t*>(static_cast<unsigned char*>(scratch) +
+                                                 pkda::chunk_fwd_status_offset(*p));
+  return PKDA_OK;
 }
 
 }  // extern "C"

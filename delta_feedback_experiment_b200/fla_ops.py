@@ -71,7 +71,9 @@ def pkda_recurrence(
     o, _, _ = ops.recurrent_forward(
         q, k, v, g, g_atk, beta_atk, beta, A_log, dt_bias, log_atk_scale,
         scale, squash_x, squash_eps, output_final_state=False)
-    saved = [torch.zeros(shape, device=q.device, dtype=dt)
+    # The exact backward needs none of the intermediates; the list only keeps the
+    # operator's output contract (names, shapes, dtypes), so it is left unwritten.
+    saved = [torch.empty(shape, device=q.device, dtype=dt)
              for shape, dt in _intermediate_meta(q, v, lean)]
     return o, saved
 
@@ -120,7 +122,8 @@ def _pkda_recurrence_backward(
 def _pkda_recurrence_backward_fake(q, k, v, g, g_atk, beta_atk, beta, A_log, dt_bias,
                                    log_atk_scale, saved, do, scale, squash_x, squash_eps,
                                    autocast_dtype, lean):
-    return [torch.empty_like(t) for t in
+    # the real operator returns fresh contiguous tensors whatever the inputs' strides
+    return [t.new_empty(t.shape) for t in
             (q, k, v, g, g_atk, beta_atk, beta, A_log, dt_bias, log_atk_scale)]
 
 

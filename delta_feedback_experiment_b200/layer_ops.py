@@ -49,6 +49,7 @@ def _conv_args(x: Tensor, weight: Tensor, head_dim: int, norm_channels: int, eps
     return a
 
 
+@ops._on_tensor_device
 def qkv_conv_forward(x: Tensor, weight: Tensor, head_dim: int, norm_channels: int, eps: float):
     ops._require_cuda(x, weight)
     lib = _lib.load()
@@ -64,6 +65,7 @@ def qkv_conv_forward(x: Tensor, weight: Tensor, head_dim: int, norm_channels: in
     return q, k, v
 
 
+@ops._on_tensor_device
 def qkv_conv_backward(x: Tensor, weight: Tensor, dq: Tensor, dk: Tensor, dv: Tensor, head_dim: int,
                       norm_channels: int, eps: float):
     ops._require_cuda(x, weight, dq, dk, dv)
@@ -108,7 +110,8 @@ def _pkda_qkv_conv_backward(x: Tensor, weight: Tensor, dq: Tensor, dk: Tensor, d
 
 @_pkda_qkv_conv_backward.register_fake
 def _pkda_qkv_conv_backward_fake(x, weight, dq, dk, dv, head_dim, norm_channels, eps):
-    return torch.empty_like(x), torch.empty_like(weight)
+    # the real operators return contiguous tensors whatever the inputs' strides
+    return x.new_empty(x.shape), weight.new_empty(weight.shape)
 
 
 def _conv_setup_context(ctx, inputs, output) -> None:
@@ -139,6 +142,7 @@ def _ng_args(x: Tensor, gate: Tensor, weight: Tensor, eps: float):
     return a
 
 
+@ops._on_tensor_device
 def norm_gate_forward(x: Tensor, gate: Tensor, weight: Tensor, eps: float):
     ops._require_cuda(x, gate, weight)
     lib = _lib.load()
@@ -155,6 +159,7 @@ def norm_gate_forward(x: Tensor, gate: Tensor, weight: Tensor, eps: float):
     return y, rstd
 
 
+@ops._on_tensor_device
 def norm_gate_backward(x: Tensor, gate: Tensor, weight: Tensor, rstd: Tensor, dy: Tensor, eps: float):
     ops._require_cuda(x, gate, weight, rstd, dy)
     lib = _lib.load()
@@ -187,7 +192,7 @@ def pkda_norm_gate(x: Tensor, gate: Tensor, weight: Tensor, eps: float) -> tuple
 @pkda_norm_gate.register_fake
 def _pkda_norm_gate_fake(x, gate, weight, eps):
     rows = x.numel() // x.shape[-1]
-    return torch.empty_like(x), torch.empty((rows,), device=x.device, dtype=torch.float32)
+    return x.new_empty(x.shape), torch.empty((rows,), device=x.device, dtype=torch.float32)
 
 
 @torch.library.custom_op("delta_feedback::pkda_norm_gate_backward", mutates_args=(),
@@ -199,7 +204,7 @@ def _pkda_norm_gate_backward(x: Tensor, gate: Tensor, weight: Tensor, rstd: Tens
 
 @_pkda_norm_gate_backward.register_fake
 def _pkda_norm_gate_backward_fake(x, gate, weight, rstd, dy, eps):
-    return torch.empty_like(x), torch.empty_like(gate), torch.empty_like(weight)
+    return x.new_empty(x.shape), gate.new_empty(gate.shape), weight.new_empty(weight.shape)
 
 
 def _norm_gate_setup_context(ctx, inputs, output) -> None:
@@ -219,6 +224,7 @@ def _norm_gate_backward(ctx, dy, _drstd):
 pkda_norm_gate.register_autograd(_norm_gate_backward, setup_context=_norm_gate_setup_context)
 
 # ----------------------------------------------------------------- decode step
+@ops._on_tensor_device
 def pkda_decode_step(qkv: Tensor, conv_state, conv_weight: Tensor, g: Tensor, g_atk: Tensor,
                      beta_atk: Tensor, beta: Tensor, A_log: Tensor, dt_bias: Tensor,
                      log_atk_scale: Tensor, state: Tensor, a_state: Tensor, gate, norm_weight,
@@ -233,7 +239,8 @@ def pkda_decode_step(qkv: Tensor, conv_state, conv_weight: Tensor, g: Tensor, g_
     ``[B,H,D]``; ``g_atk`` (fp32), ``beta_atk``, ``beta`` are ``[B,H]``; ``gate`` the
     output-gate logits ``[B,H,D]`` or None (the result is then the recurrence output).
     Returns ``[B,H,D]``."""
-    ops._require_cuda(qkv, conv_weight, g, g_atk, beta_atk, beta, state, a_state)
+    ops._require_cuda(qkv, conv_weight, g, g_atk, beta_atk, beta, state, a_state, *conv_state, A_log, dt_bias,
+                      log_atk_scale, gate, norm_weight)
     lib = _lib.load()
     B, C3 = qkv.shape
     W = C3 // 3
@@ -283,6 +290,11 @@ def pack_control_gradients(gradients) -> Tensor:
     if any(not g.is_contiguous() for g in gradients):
         raise ValueError("control gradients must be contiguous")
     lib = _lib.load()
+    return _pack_on_device(g0, lib, gradients, prefix)
+
+
+@ops._on_tensor_device
+def _pack_on_device(g0, lib, gradients, prefix) -> Tensor:
     a = _lib.PackControlArgs()
     a.rows = g0.numel() // max(g0.shape[-1], 1) if g0.shape[-1] else (gradients[1].numel() // max(gradients[1].shape[-1], 1))
     total = 0
@@ -328,6 +340,11 @@ class _Controls(torch.autograd.Function):
     @staticmethod
     def forward(ctx, packed: Tensor, A_log_precond: Tensor, dt_bias_precond: Tensor, hidden: int):
         ops._require_cuda(packed, A_log_precond, dt_bias_precond)
+        with torch.cuda.device(packed.device):
+            return _Controls._forward(ctx, packed, A_log_precond, dt_bias_precond, hidden)
+
+    @staticmethod
+    def _forward(ctx, packed, A_log_precond, dt_bias_precond, hidden):
         lib = _lib.load()
         packed = packed.contiguous()
         a32 = A_log_precond.detach().float().contiguous()
@@ -348,7 +365,13 @@ class _Controls(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, d_h0, d_beta, d_g_atk, d_beta_atk, d_h1):
-        packed, A_log_precond, dt_bias_precond = ctx.saved_tensors
+        saved = ctx.saved_tensors  # unpacked exactly once (checkpoint replays allow no more)
+        with torch.cuda.device(saved[0].device):
+            return _Controls._backward(ctx, saved, d_h0, d_beta, d_g_atk, d_beta_atk, d_h1)
+
+    @staticmethod
+    def _backward(ctx, saved, d_h0, d_beta, d_g_atk, d_beta_atk, d_h1):
+        packed, A_log_precond, dt_bias_precond = saved
         lib = _lib.load()
         a32 = A_log_precond.detach().float().contiguous()
         b32 = dt_bias_precond.detach().float().contiguous()

@@ -5,6 +5,7 @@ the C ABI on the current CUDA stream.  No arithmetic happens in Python.
 from __future__ import annotations
 
 import ctypes as C
+import functools
 from typing import Optional, Sequence
 
 import torch
@@ -18,14 +19,26 @@ LAUNCHES = 0
 """Kernels enqueued through this module since import (launch accounting)."""
 
 
+_TRACK_STATUS = False
 _LAST_STATUS = None
 _LAST_BWD_STATUS = None
+
+
+def track_device_status(enable: bool) -> None:
+    """Debugging aid.  While enabled, every chunked forward / backward copies its
+    device status word (4 bytes, one extra copy on the launch stream) into a tensor
+    of its own that ``last_device_status`` / ``last_backward_status`` read.  Off by
+    default: production callers learn of a device-side failure through the NaN the
+    library writes over the head of the outputs, without any read-back."""
+    global _TRACK_STATUS, _LAST_STATUS, _LAST_BWD_STATUS
+    _TRACK_STATUS = bool(enable)
+    _LAST_STATUS = _LAST_BWD_STATUS = None
 
 
 def last_device_status() -> int:
     """Status word the most recent chunked forward's kernels left on the device
     (0 = ok, 1 = a bounded wait inside a kernel gave up and its CTA skipped its
-    stores).  Synchronises; meant for tests and debugging."""
+    stores); 0 when tracking is off.  Synchronises; meant for tests and debugging."""
     if _LAST_STATUS is None:
         return 0
     return int(_LAST_STATUS.view(torch.int32).item())
@@ -39,6 +52,14 @@ def last_backward_status() -> int:
     return int(_LAST_BWD_STATUS.view(torch.int32).item())
 
 
+def _status_copy(ws: Tensor, offset: int) -> Optional[Tensor]:
+    """A 4-byte copy of the status word (so that the workspace itself can go back
+    to the allocator when the call returns)."""
+    if not _TRACK_STATUS:
+        return None
+    return ws[offset:offset + 4].clone()
+
+
 def _count(lib) -> None:
     global LAUNCHES
     LAUNCHES += int(lib.pkda_last_launch_count())
@@ -48,9 +69,33 @@ _DTYPES = {torch.bfloat16: _lib.PKDA_BF16, torch.float32: _lib.PKDA_F32}
 
 
 def _require_cuda(*tensors: Optional[Tensor]) -> None:
+    """Every given tensor must live on one and the same CUDA device (the kernels
+    run on a single device and dereference every pointer there)."""
+    device = None
     for t in tensors:
-        if t is not None and not t.is_cuda:
+        if t is None:
+            continue
+        if not t.is_cuda:
             raise RuntimeError("PKDA CUDA operators need CUDA tensors; there is no CPU path")
+        if device is None:
+            device = t.device
+        elif t.device != device:
+            raise RuntimeError(
+                f"PKDA operator arguments live on different devices ({device} and {t.device})")
+
+
+def _on_tensor_device(fn):
+    """Runs a launcher with its first tensor's device current, so that the library
+    launches (and encodes its tensor maps) on the device that owns the data and
+    torch's current stream of THAT device is the one used, whatever device the
+    caller had current (the reference's kernels guard the same way)."""
+    @functools.wraps(fn)
+    def wrapper(first, *args, **kwargs):
+        if not getattr(first, "is_cuda", False):
+            raise RuntimeError("PKDA CUDA operators need CUDA tensors; there is no CPU path")
+        with torch.cuda.device(first.device):
+            return fn(first, *args, **kwargs)
+    return wrapper
 
 
 def _problem(q, k, v, g, g_atk, beta_atk, beta, A_log, dt_bias, log_atk_scale, scale, x, eps,
@@ -61,6 +106,8 @@ def _problem(q, k, v, g, g_atk, beta_atk, beta, A_log, dt_bias, log_atk_scale, s
     if q.dtype not in _DTYPES:
         raise RuntimeError(f"PKDA supports bf16 and fp32 activations, not {q.dtype}")
     act = q.dtype
+    _require_cuda(q, k, v, g, g_atk, beta_atk, beta, A_log, dt_bias, log_atk_scale,
+                  initial_state, initial_A_state)
 
     def act_c(t, shape):
         if tuple(t.shape) != tuple(shape):
@@ -118,6 +165,7 @@ def n_chunks(B: int, T: int, cu_seqlens: Optional[Tensor]) -> int:
     return (B * T) // CHUNK_SIZE + (cu_seqlens.numel() - 1)
 
 
+@_on_tensor_device
 def recurrent_forward(q, k, v, g, g_atk, beta_atk, beta, A_log, dt_bias, log_atk_scale, scale,
                       x, eps, initial_state=None, initial_A_state=None, cu_seqlens=None,
                       output_final_state=True, inplace_state=False):
@@ -170,6 +218,7 @@ def intermediate_meta(q: Tensor, v: Tensor, lean: bool, chunks_flat: Optional[in
     return tuple(meta)
 
 
+@_on_tensor_device
 def chunk_forward(q, k, v, g, g_atk, beta_atk, beta, A_log, dt_bias, log_atk_scale, scale, x,
                   eps, initial_state=None, initial_A_state=None, cu_seqlens=None,
                   output_final_state=False):
@@ -203,17 +252,18 @@ def chunk_forward(q, k, v, g, g_atk, beta_atk, beta, A_log, dt_bias, log_atk_sca
     _lib.check(lib.pkda_chunk_fwd(C.byref(args), _lib.current_stream()), "pkda_chunk_fwd")
     _count(lib)
     global _LAST_STATUS
-    _LAST_STATUS = ws[nbytes - 256:nbytes - 252] if nbytes >= 256 else None
+    _LAST_STATUS = _status_copy(ws, int(lib.pkda_chunk_fwd_status_offset(C.byref(p))))
     return o, S, A, saved
 
 
+@_on_tensor_device
 def chunk_backward(q, k, v, g, g_atk, beta_atk, beta, A_log, dt_bias, log_atk_scale, scale, x,
                    eps, saved: Sequence[Tensor], do, initial_state=None, initial_A_state=None,
                    cu_seqlens=None, d_final_state=None, lean=False, want_state_grads=False):
     """Chunked backward.  ``saved`` holds the six always-kept intermediates and,
     unless ``lean``, the five retained ones.  Returns the ten gradients (plus
     ``dS0, dA0`` when ``want_state_grads``)."""
-    _require_cuda(q, k, v, g, g_atk, beta_atk, beta, do)
+    _require_cuda(q, k, v, g, g_atk, beta_atk, beta, do, d_final_state)
     lib = _lib.load()
     keep: list = []
     p = _problem(q, k, v, g, g_atk, beta_atk, beta, A_log, dt_bias, log_atk_scale, scale, x, eps,
@@ -261,18 +311,19 @@ def chunk_backward(q, k, v, g, g_atk, beta_atk, beta, A_log, dt_bias, log_atk_sc
     _lib.check(lib.pkda_chunk_bwd(C.byref(args), _lib.current_stream()), "pkda_chunk_bwd")
     _count(lib)
     global _LAST_BWD_STATUS
-    _LAST_BWD_STATUS = ws[nbytes - 256:nbytes - 252] if nbytes >= 256 else None
+    _LAST_BWD_STATUS = _status_copy(ws, int(lib.pkda_chunk_bwd_status_offset(C.byref(p))))
     grads = [dq, dk, dv, dg, dg_atk, dbeta_atk, dbeta, dA_log, ddt_bias, dcentre]
     return grads, dS0, dA0
 
 
+@_on_tensor_device
 def recurrent_backward(q, k, v, g, g_atk, beta_atk, beta, A_log, dt_bias, log_atk_scale, scale, x,
                        eps, do, initial_state=None, initial_A_state=None, cu_seqlens=None,
                        d_final_state=None, want_state_grads=False):
     """Exact fp32 backward of the recurrence (any supported head width, bf16 or
     fp32 activations); needs no saved intermediates.  Returns the ten gradients
     (plus ``dS0, dA0`` when ``want_state_grads``)."""
-    _require_cuda(q, k, v, g, g_atk, beta_atk, beta, do)
+    _require_cuda(q, k, v, g, g_atk, beta_atk, beta, do, d_final_state)
     lib = _lib.load()
     keep: list = []
     p = _problem(q, k, v, g, g_atk, beta_atk, beta, A_log, dt_bias, log_atk_scale, scale, x, eps,
@@ -317,6 +368,7 @@ def static_scratch_bytes() -> int:
     return int(_lib.load().pkda_static_scratch_bytes())
 
 
+@_on_tensor_device
 def chunk_forward_static(q, k, v, g, g_atk, beta_atk, beta, A_log, dt_bias, log_atk_scale, scale,
                          x, eps, o, saved, initial_state=None, initial_A_state=None,
                          final_state=None, final_A_state=None):
@@ -350,4 +402,24 @@ def chunk_forward_static(q, k, v, g, g_atk, beta_atk, beta, A_log, dt_bias, log_
     _lib.check(lib.pkda_chunk_fwd_static(C.byref(args), _lib.current_stream()),
                "pkda_chunk_fwd_static")
     _count(lib)
+    if _TRACK_STATUS:
+        global _LAST_STATUS
+        _LAST_STATUS = _static_status_view(lib, p)
     return o
+
+
+class _DeviceWord:
+    """Wraps a raw device address as a one-element int32 array for
+    ``torch.as_tensor`` (no copy, no allocation)."""
+
+    def __init__(self, address: int):
+        self.__cuda_array_interface__ = {
+            "shape": (1,), "typestr": "<i4", "data": (int(address), False), "version": 2}
+
+
+def _static_status_view(lib, p) -> Tensor:
+    """The static-scratch forward's status word, as a tensor that aliases the
+    library's own array (read it before the next such call overwrites it)."""
+    addr = C.c_void_p()
+    _lib.check(lib.pkda_static_status_ptr(C.byref(p), C.byref(addr)), "pkda_static_status_ptr")
+    return torch.as_tensor(_DeviceWord(addr.value), device=torch.device("cuda", torch.cuda.current_device()))

@@ -3,10 +3,22 @@
  *
  * Every entry point takes plain device pointers and sizes, launches on the
  * stream it is given, never synchronises, never allocates and returns an int
- * status (0 = ok).  All scratch memory is supplied by the caller, sized by the
- * *_workspace_bytes functions.  The Python host code in
+ * status (0 = ok).  Scratch memory is supplied by the caller, sized by the
+ * *_workspace_bytes functions (the one exception is pkda_chunk_fwd_static, whose
+ * scratch is an array inside the library).  The Python host code in
  * delta_feedback_experiment_b200/ binds these through ctypes; any other host
- * language binds them the same way.
+ * language binds them the same way.  Kernels run on the device that is current
+ * when an entry point is called: the caller makes the tensors' device current.
+ *
+ * Device-side failures.  The tensor-core kernels wait on hardware barriers with
+ * a bounded number of polls.  If such a wait ever gives up, the kernel records 1
+ * in a 32-bit status word at the end of the call's workspace
+ * (pkda_chunk_fwd_status_offset / pkda_chunk_bwd_status_offset bytes from its
+ * start; pkda_static_status_ptr for the static-scratch entry point), and the
+ * last launch of the call overwrites the head of the call's outputs (o; dq, dk,
+ * dv) with NaN, so that a failed call cannot pass for a result: it reaches the
+ * caller's non-finite check.  The return value of the entry point itself only
+ * reports host-side errors (the call does not synchronise).
  *
  * Tensor conventions (identical to the reference operator boundary,
  * delta_feedback_experiment/fla_ops.py:255-349 and pkda.py:450-475):
@@ -141,6 +153,8 @@ typedef struct pkda_chunk_fwd_args {
 
 size_t pkda_chunk_fwd_workspace_bytes(const pkda_problem* p);
 int pkda_chunk_fwd(const pkda_chunk_fwd_args* args, void* cuda_stream);
+/* Byte offset of the 32-bit device status word inside the forward workspace. */
+size_t pkda_chunk_fwd_status_offset(const pkda_problem* p);
 
 /*
  * pkda_chunk_fwd for hosts that cannot hand over scratch memory.  (No
@@ -170,6 +184,12 @@ int pkda_chunk_fwd(const pkda_chunk_fwd_args* args, void* cuda_stream);
 #define PKDA_STATIC_SCRATCH_BYTES (16u << 20)
 size_t pkda_static_scratch_bytes(void);
 int pkda_chunk_fwd_static(const pkda_chunk_fwd_args* args, void* cuda_stream);
+/*
+ * Device address (on the current device) of the status word the last
+ * pkda_chunk_fwd_static call for problem p used.  Allocates nothing; like the
+ * entry point itself, the first call on a device belongs outside stream capture.
+ */
+int pkda_static_status_ptr(const pkda_problem* p, const int32_t** device_ptr);
 
 /*
  * Chunked backward.  Replaces kda_gate_chunk_cumsum + chunk_precond_kda_bwd +
@@ -200,6 +220,8 @@ typedef struct pkda_chunk_bwd_args {
 
 size_t pkda_chunk_bwd_workspace_bytes(const pkda_problem* p);
 int pkda_chunk_bwd(const pkda_chunk_bwd_args* args, void* cuda_stream);
+/* Byte offset of the 32-bit device status word inside the backward workspace. */
+size_t pkda_chunk_bwd_status_offset(const pkda_problem* p);
 
 /* Introspection used by the bindings' self-checks. */
 int pkda_abi_version(void);
@@ -219,6 +241,17 @@ int pkda_last_launch_count(void);
  * 1 = hierarchy only) so that tests can exercise every variant on the same input.
  */
 int pkda_set_direct_block_cap(int cap);
+
+/*
+ * Testing aid.  Several stages exist in two implementations: the tcgen05 /
+ * tensor-memory kernel that runs by default and an older mma.sync kernel that is
+ * kept as a cross-check (and for shapes the default does not cover).
+ * pkda_set_variant(stage name as pkda_stage_name reports it, 1) pins the older
+ * kernel for that stage, (.., 0) restores the default.  Stages with two
+ * implementations: "intra_fwd", "scan_fwd", "out_fwd", "scan_bwd", "intra_bwd".
+ * Returns PKDA_ERR_SHAPE for any other name.  Process-wide; not thread-safe.
+ */
+int pkda_set_variant(const char* stage, int variant);
 
 /*
  * Optional per-kernel timing for benchmarks.  pkda_stage_timing(1) makes every

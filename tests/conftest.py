@@ -27,6 +27,15 @@ def pytest_collection_modifyitems(config, items):
             item.add_marker(skip)
 
 
+@pytest.fixture(autouse=True, scope="session")
+def _track_device_status():
+    """GPU tests read the kernels' device status word after their calls."""
+    if torch.cuda.is_available():
+        from delta_feedback_experiment_b200 import ops
+        ops.track_device_status(True)
+    yield
+
+
 def load_golden(name: str) -> dict:
     with np.load(os.path.join(GOLDEN_DIR, name + ".npz")) as z:
         return {k: torch.from_numpy(z[k].copy()) for k in z.files}

@@ -67,3 +67,43 @@ def test_operators_refuse_cpu_tensors():
     with pytest.raises(RuntimeError, match="no CPU path"):
         fused_recurrent_precond_kda(t, t, t, t, s, s, s, torch.zeros(1), torch.zeros(8),
                                     log_atk_scale=torch.zeros(1))
+
+
+def test_variant_switch_and_status_offsets(lib):
+    """The testing switch accepts exactly the stages that have two implementations, and
+    the status word sits inside the workspace the size query reports."""
+    for name in (b"intra_fwd", b"scan_fwd", b"out_fwd", b"scan_bwd", b"intra_bwd"):
+        assert lib.pkda_set_variant(name, 1) == 0
+        assert lib.pkda_set_variant(name, 0) == 0
+    assert lib.pkda_set_variant(b"atk_local", 1) == 2
+    assert lib.pkda_set_variant(None, 1) == 1
+    p = _lib.Problem()
+    p.n_seqs, p.seq_len, p.total_tokens, p.heads, p.head_dim = 2, 130, 260, 3, 128
+    for size, off in ((lib.pkda_chunk_fwd_workspace_bytes, lib.pkda_chunk_fwd_status_offset),
+                      (lib.pkda_chunk_bwd_workspace_bytes, lib.pkda_chunk_bwd_status_offset)):
+        total, where = size(C.byref(p)), off(C.byref(p))
+        assert 0 < where and where + 4 <= total and where % 256 == 0
+
+
+class _FakeTensor:
+    """Stands in for a CUDA tensor where there is no GPU: only the attributes the
+    device checks read."""
+
+    def __init__(self, device):
+        import torch
+        self.is_cuda = device is not None
+        self.device = torch.device("cuda", device) if device is not None else torch.device("cpu")
+
+
+def test_arguments_on_different_devices_are_rejected_before_any_launch():
+    from delta_feedback_experiment_b200 import ops
+    ops._require_cuda(_FakeTensor(1), None, _FakeTensor(1))
+    with pytest.raises(RuntimeError, match="different devices"):
+        ops._require_cuda(_FakeTensor(0), _FakeTensor(1))
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        ops._require_cuda(_FakeTensor(0), _FakeTensor(None))
+    calls = []
+    guarded = ops._on_tensor_device(lambda first: calls.append(first))
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        guarded(_FakeTensor(None))
+    assert not calls

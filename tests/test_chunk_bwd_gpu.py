@@ -184,10 +184,16 @@ def test_direct_block_variants(cap, dist):
 
 @pytest.mark.parametrize("B", [4, 8])
 def test_wide_state_slices_match_narrow_ones(B):
-    """The state-scan kernels split the value axis across CTAs according to how
-    many (row, head) units there are (32, 64 or all 128 columns per CTA).  Rows are
-    independent, so a batch large enough to select the wide variants must agree
-    bitwise with the same rows run one at a time (narrow variant)."""
+    """The state scans run as tcgen05 / tensor-memory kernels (one CTA per (row, head), all
+    128 value columns) when there are at least 120 (row, head) units -- B = 8 here -- and as
+    mma.sync kernels on 32- or 64-column slices below that.  Rows are independent, so a row of
+    the big batch must agree with the same row run alone through the other implementation.
+    Both feed the same bf16 operands to the tensor cores in the same order; on this short input
+    every result is equal bit for bit, which this test pins.  That is a property of the input,
+    not a guarantee: the tcgen05 scan adds U inside the fp32 accumulator while the mma.sync
+    scan subtracts in a register, and on long inputs a few outputs differ by one bf16 unit in
+    the last place (T = 1024: max |delta o| = 3.8e-6 with every gradient and the final state
+    still equal), which is why the full-size tests compare within tolerance."""
     H, T = 16, 130
     d = make_inputs(B, T, H, 128, seed=97, dist="production", dtype=torch.bfloat16, with_state=True)
     dS = torch.randn(B, H, 128, 128, generator=torch.Generator().manual_seed(6)) * 0.1

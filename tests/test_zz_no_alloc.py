@@ -36,6 +36,8 @@ def _run_both(seed, B, T, H):
     ops.chunk_forward_static(*t, 128 ** -0.5, 1.5, 1e-6, o, saved, S0, A0, S, A)
     assert torch.cuda.memory_allocated() == allocated  # nothing allocated through torch either
     torch.cuda.synchronize()
+    assert ops.last_device_status() == 0   # read from the library's own array, still nothing allocated
+    assert torch.cuda.memory_allocated() == allocated
     assert torch.equal(o, o_ref) and torch.equal(S, S_ref) and torch.equal(A, A_ref)
     for a, b in zip(saved, saved_ref):
         assert torch.equal(a, b)

@@ -352,6 +352,48 @@ __device__ __forceinline__ void unit_lower_inverse_64(const float* sL, float* sT
   inverse_merge_tc<32>(sL, sT, sY2, ld, tid);
 }
 
+// Sums each of v[0..7] over the 32 lanes.  On return lane l holds in v[0] the
+// total of entry ((l >> 4) & 1) * 4 + ((l >> 3) & 1) * 2 + ((l >> 2) & 1).
+__device__ __forceinline__ void row_sums8(float (&v)[8], int lane) {
+  const bool hi16 = lane & 16, hi8 = lane & 8, hi4 = lane & 4;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float keep = hi16 ? v[j + 4] : v[j], send = hi16 ? v[j] : v[j + 4];
+    v[j] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+  }
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const float keep = hi8 ? v[j + 2] : v[j], send = hi8 ? v[j] : v[j + 2];
+    v[j] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+  }
+  {
+    const float keep = hi4 ? v[1] : v[0], send = hi4 ? v[0] : v[1];
+    v[0] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+  }
+  v[0] += __shfl_xor_sync(0xffffffffu, v[0], 2);
+  v[0] += __shfl_xor_sync(0xffffffffu, v[0], 1);
+}
+
+// Arguments of the intra-chunk forward stage (both implementations).
+struct IntraParams {
+  Geo geo;
+  const bf16 *q, *k, *v, *g;
+  const float* g_atk;
+  const bf16* beta_atk;
+  const float *A_log, *dt_bias, *log_atk_scale;
+  const float* beta_c;
+  const float* a_start;
+  bf16 *Aqk, *Akk, *kt;
+  float* gc;  // [chunks][H][D] exp of the chunk's total log-decay
+  bf16 *w, *u, *kg, *qg;
+  float scale, ln_x, eps;
+  int direct_cap;  // upper limit for the direct block size (64 = no limit, 1 = hierarchy only)
+  int* status;     // device status word (tcgen05 kernel): set to 1 when a bounded wait gives up
+};
+
+// tcgen05 / tensor-memory intra-chunk forward stage (pkda_intra_fwd_tc.cu).
+int launch_intra_fwd_tc(const IntraParams& ip, bool recompute, cudaStream_t st);
+
 // tcgen05 / TMA output stage (pkda_out_tc.cu).
 int launch_out_fwd_tc(const Geo& geo, int total_tokens, const bf16* qg, const bf16* h, const bf16* Aqk,
                       const bf16* v_new, const float* beta_c, bf16* o, int* status, cudaStream_t st);

@@ -811,28 +811,6 @@ constexpr int kThreads = 256;
 constexpr int kRows = 8;  // rows per warp
 }  // namespace atkb
 
-// Sums each of v[0..7] over the 32 lanes.  On return lane l holds in v[0] the
-// total of entry ((l >> 4) & 1) * 4 + ((l >> 3) & 1) * 2 + ((l >> 2) & 1).
-__device__ __forceinline__ void row_sums8(float (&v)[8], int lane) {
-  const bool hi16 = lane & 16, hi8 = lane & 8, hi4 = lane & 4;
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const float keep = hi16 ? v[j + 4] : v[j], send = hi16 ? v[j] : v[j + 4];
-    v[j] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
-  }
-#pragma unroll
-  for (int j = 0; j < 2; ++j) {
-    const float keep = hi8 ? v[j + 2] : v[j], send = hi8 ? v[j] : v[j + 2];
-    v[j] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
-  }
-  {
-    const float keep = hi4 ? v[1] : v[0], send = hi4 ? v[0] : v[1];
-    v[0] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
-  }
-  v[0] += __shfl_xor_sync(0xffffffffu, v[0], 2);
-  v[0] += __shfl_xor_sync(0xffffffffu, v[0], 1);
-}
-
 // Thread-private prefetch slots in dynamic shared memory (a thread only reads back
 // what it copied itself, so they need no barrier): per row k (8 B), dkt (16 B),
 // dk_read (16 B, final pass only), the row's log-decay (4 B); per tile the chunk's

@@ -131,21 +131,6 @@ pkda_atk_carry_kernel(Geo geo, const float* ac_local, const float* sa, const flo
 }
 
 // ------------------------------------------------------------------ intra-chunk kernel
-struct IntraParams {
-  Geo geo;
-  const bf16 *q, *k, *v, *g;
-  const float* g_atk;
-  const bf16* beta_atk;
-  const float *A_log, *dt_bias, *log_atk_scale;
-  const float* beta_c;
-  const float* a_start;
-  bf16 *Aqk, *Akk, *kt;
-  float* gc;  // [chunks][H][D] exp of the chunk's total log-decay
-  bf16 *w, *u, *kg, *qg;
-  float scale, ln_x, eps;
-  int direct_cap;  // upper limit for the direct block size (64 = no limit, 1 = hierarchy only)
-};
-
 namespace intra {
 constexpr int kThreads = 512;
 constexpr int oQ = 0;
@@ -770,8 +755,13 @@ int run_forward_stages(const pkda_problem& p, const Geo& geo, const float* beta_
   ip.w = w; ip.u = u_ws; ip.kg = kg; ip.qg = qg;
   ip.scale = p.scale; ip.ln_x = logf(p.squash_x); ip.eps = p.squash_eps;
   ip.direct_cap = direct_block_cap();
+  ip.status = status;
   dim3 gridc(chunks, p.heads);
-  if (recompute) {
+  if (status && stage_variant(kStageIntraFwd) == 0) {  // tcgen05 / tensor-memory kernel (default)
+    begin_stage(kStageIntraFwd, st);
+    const int rc_tc = launch_intra_fwd_tc(ip, recompute, st);
+    if (rc_tc != PKDA_OK) return rc_tc;
+  } else if (recompute) {
     if (!set_smem(pkda_intra_fwd_kernel<true>, intra::kSmem)) return PKDA_ERR_LAUNCH;
     begin_stage(kStageIntraFwd, st);
     pkda_intra_fwd_kernel<true><<<gridc, intra::kThreads, intra::kSmem, st>>>(ip);

@@ -41,6 +41,10 @@ def last_device_status() -> int:
     stores); 0 when tracking is off.  Synchronises; meant for tests and debugging."""
     if _LAST_STATUS is None:
         return 0
+    if isinstance(_LAST_STATUS, tuple):   # (device address inside the library's static array, device)
+        address, device = _LAST_STATUS
+        with torch.cuda.device(device):
+            return int(torch.as_tensor(_DeviceWord(address), device=device).item())
     return int(_LAST_STATUS.view(torch.int32).item())
 
 
@@ -409,17 +413,19 @@ def chunk_forward_static(q, k, v, g, g_atk, beta_atk, beta, A_log, dt_bias, log_
 
 
 class _DeviceWord:
-    """Wraps a raw device address as a one-element int32 array for
-    ``torch.as_tensor`` (no copy, no allocation)."""
+    """Presents a raw device address as a one-element int32 array to
+    ``torch.as_tensor``."""
 
     def __init__(self, address: int):
         self.__cuda_array_interface__ = {
             "shape": (1,), "typestr": "<i4", "data": (int(address), False), "version": 2}
 
 
-def _static_status_view(lib, p) -> Tensor:
-    """The static-scratch forward's status word, as a tensor that aliases the
-    library's own array (read it before the next such call overwrites it)."""
+def _static_status_view(lib, p):
+    """Where the static-scratch forward keeps its status word: the device address
+    inside the library's own array and the device (nothing is allocated or copied
+    here; ``last_device_status`` reads the word, before the next such call
+    overwrites it)."""
     addr = C.c_void_p()
     _lib.check(lib.pkda_static_status_ptr(C.byref(p), C.byref(addr)), "pkda_static_status_ptr")
-    return torch.as_tensor(_DeviceWord(addr.value), device=torch.device("cuda", torch.cuda.current_device()))
+    return int(addr.value), torch.device("cuda", torch.cuda.current_device())

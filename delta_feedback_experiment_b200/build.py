@@ -21,7 +21,7 @@ LIB_PATH = os.path.join(HERE, "libpkda_b200.so")
 OBJ_DIR = os.path.join(HERE, "build")
 
 SOURCES = ["pkda_abi.cu", "pkda_recurrent.cu", "pkda_chunk_fwd.cu", "pkda_chunk_bwd.cu",
-           "pkda_static_scratch.cu", "pkda_intra_fwd_tc.cu", "pkda_out_tc.cu", "pkda_scan_tc.cu", "pkda_scan_bwd_tc.cu",
+           "pkda_static_scratch.cu", "pkda_intra_fwd_tc.cu", "pkda_intra_bwd_tc.cu", "pkda_out_tc.cu", "pkda_scan_tc.cu", "pkda_scan_bwd_tc.cu",
            "pkda_recurrent_bwd.cu", "pkda_qkv_conv.cu", "pkda_norm_gate.cu", "pkda_decode_step.cu", "pkda_controls.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17", "-ftz=true",

@@ -26,7 +26,7 @@ constexpr int kLdG = kD + 8;                  // smem row stride of a [64][128] 
 // picks the largest b whose worst block decay is below kDirectLimit (log2 units)
 // and covers the remaining pairs with hierarchy levels >= b.  lvl == 0 denotes the
 // direct level everywhere below.
-constexpr float kDirectLimit = 96.f;
+constexpr float kDirectLimit = 104.f;
 
 __device__ __forceinline__ bool pair_ok(int i, int j, int lvl, int b) {
   if (lvl) return level_pair_ok(i, j, lvl);
@@ -393,6 +393,29 @@ struct IntraParams {
 
 // tcgen05 / tensor-memory intra-chunk forward stage (pkda_intra_fwd_tc.cu).
 int launch_intra_fwd_tc(const IntraParams& ip, bool recompute, cudaStream_t st);
+
+// Arguments of the chunk-parallel backward stage (both implementations).
+struct IntraBwdParams {
+  Geo geo;
+  const bf16 *q, *k, *kt, *g;
+  const float *A_log, *dt_bias;
+  const float *beta_c, *gc;
+  const bf16 *Akk, *v_new, *h, *dh, *dF, *d_o;
+  bf16 *dq, *dv, *dg, *dbeta;
+  float *dk_read, *dkt;
+  float *partA, *partB;
+  float scale;
+  int direct_cap;
+  int use_tma;   // the five phase-A tiles of full chunks arrive by TMA (tensor maps valid)
+  int out_tma;   // dq, dv, dk_read and dkt of full chunks leave by TMA from padded shared-memory tiles
+  int* status;   // set to 1 if a bounded wait gives up
+  // Per (chunk, head) byte: the tcgen05 kernel writes 1 for every chunk it leaves to the mma.sync
+  // kernel and 0 for those it has done; the mma.sync kernel skips the zeros (NULL: it takes all).
+  unsigned char* flags;
+};
+
+// tcgen05 / tensor-memory chunk-parallel backward stage (pkda_intra_bwd_tc.cu).
+int launch_intra_bwd_tc(const IntraBwdParams& ip, cudaStream_t st);
 
 // tcgen05 / TMA output stage (pkda_out_tc.cu).
 int launch_out_fwd_tc(const Geo& geo, int total_tokens, const bf16* qg, const bf16* h, const bf16* Aqk,

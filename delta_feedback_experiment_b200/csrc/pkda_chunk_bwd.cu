@@ -200,22 +200,6 @@ pkda_scan_bwd_kernel(const ScanBwdParams p) {
 }
 
 // ------------------------------------------------------------------ chunk-parallel backward
-struct IntraBwdParams {
-  Geo geo;
-  const bf16 *q, *k, *kt, *g;
-  const float *A_log, *dt_bias;
-  const float *beta_c, *gc;
-  const bf16 *Akk, *v_new, *h, *dh, *dF, *d_o;
-  bf16 *dq, *dv, *dg, *dbeta;
-  float *dk_read, *dkt;
-  float *partA, *partB;
-  float scale;
-  int direct_cap;
-  int use_tma;   // the five phase-A tiles of full chunks arrive by TMA (tensor maps valid)
-  int out_tma;   // dq, dv, dk_read and dkt of full chunks leave by TMA from padded shared-memory tiles
-  int* status;   // set to 1 if a bounded wait gives up
-};
-
 // Tensor maps of the phase-A tiles.  Each box is wider than the data it needs (136
 // or 72 columns for 128 or 64) so that the rows land in shared memory with the
 // padded pitch the ldmatrix reads want; the surplus columns are the neighbouring
@@ -309,6 +293,7 @@ pkda_intra_bwd_kernel(const IntraBwdParams p, const __grid_constant__ IntraBwdMa
   const int gq = lane >> 2, tq = lane & 3;
   const int I = warp & 3, cq = warp >> 2;
   const size_t chh = (size_t)blockIdx.x * H + h;
+  if (p.flags && !p.flags[chh]) return;  // the tcgen05 kernel has done this chunk
   const size_t row0 = ((size_t)tok0 * H + h) * kD;
   const long gld = (long)H * kD;
   const size_t crow0 = ((size_t)tok0 * H + h) * kChunk;
@@ -1139,6 +1124,7 @@ struct BwdWorkspace {
   float* beta_c;
   bf16 *u, *dF, *dh;
   float *dk_read, *dkt, *partA, *partB, *partC, *c_loc, *lam_in;
+  unsigned char* flags;
   int* status;
   size_t bytes;
 };
@@ -1165,6 +1151,7 @@ static BwdWorkspace carve_bwd(const pkda_problem& p, void* base) {
   w.partC = static_cast<float*>(take(chunks * H * 4));
   w.c_loc = static_cast<float*>(take(chunks * H * kD * 4));
   w.lam_in = static_cast<float*>(take(chunks * H * kD * 4));
+  w.flags = static_cast<unsigned char*>(take(chunks * H));
   w.status = static_cast<int*>(take(sizeof(int)));
   w.bytes = off;
   return w;
@@ -1278,6 +1265,16 @@ int chunk_bwd(const pkda_chunk_bwd_args* a, cudaStream_t st) {
                  encode_f32_map(&maps.dk_read, ip.dk_read, 3, o_dims, o_str4, o_box) &&
                  encode_f32_map(&maps.dkt, ip.dkt, 3, o_dims, o_str4, o_box);
     ip.status = ws.status;
+  }
+  // Full chunks that are one direct block run on tcgen05 / tensor memory; that kernel flags the
+  // others for the mma.sync kernel behind it (which takes every chunk when it is pinned).
+  ip.flags = nullptr;
+  if (stage_variant(kStageIntraBwd) == 0) {
+    ip.flags = ws.flags;
+    begin_stage(kStageIntraBwd, st);
+    rc = launch_intra_bwd_tc(ip, st);
+    end_stage(st);
+    if (rc != PKDA_OK) return rc;
   }
   if (!set_smem(pkda_intra_bwd_kernel, ib::kSmem)) return PKDA_ERR_LAUNCH;
   begin_stage(kStageIntraBwd, st);

@@ -1,0 +1,486 @@
+// Chunk-parallel stage of the chunked backward on tcgen05 / tensor memory (D = 128, chunk 64).
+//
+// One CTA of 512 threads per (chunk, head); all operand tiles of the chunk (about 216 KB) sit in
+// shared memory at once, every one of them placed by TMA in the 128-byte-swizzled layout the
+// tensor core reads, and every dense product is a tcgen05.mma chain into tensor memory.  The
+// kernel takes the chunks that are full (64 tokens) and whose decay lets the whole chunk be ONE
+// direct block (pkda_chunk.cuh): there the gated operands are q 2^G, k 2^G and kt 2^-G with G the
+// cumulative log2-decay from the chunk start, one set for all pairs.  Every other chunk (a ragged
+// last chunk, a chunk that decays by more than kDirectLimit, a capped direct block) is flagged
+// and left to the mma.sync kernel of pkda_chunk_bwd.cu, which runs right after this one and
+// handles flagged chunks only.
+//
+// Accumulators are laid out with one value / key channel per tensor-memory lane and tokens along
+// the columns (M = 128 channels everywhere, N = 64 tokens), so a thread owns one channel and 16
+// consecutive tokens for all elementwise work: the gate and its cumulative sum, the gating of the
+// operands (in place in the tiles), the gradient epilogue, the reverse cumulative sum of the
+// log-decay gradient and the gate's own backward need no transposition, only one exchange
+// between the four token slices of a channel.
+//
+//   (1) dR^T  = dF^T (diag(beta) T)                      K = 64    -> dv, and rows 0..63 of the stack
+//   (2) [dR; dO] E^T                                     K = 128   -> dM = -tril(.,-1) diag(beta),
+//                                                                     dP = scale tril(.) diag(beta)
+//       Qs = S0 dO^T, Ks = -S0 dR^T, Kts = dS1 E^T       K = 128   (state-coupled parts)
+//   (3) Qp = Y^T dP^T, Kp = Y^T dM^T, KtM = Xk^T dM, KtP = Xq^T dP   K = 64 (pair parts)
+//   dq  = 2^G (scale Qs + Qp)      dk_read = 2^G (Ks + Kp)
+//   dkt = 2^-G (2^G_last beta Kts + KtM + KtP)
+//   dG  = Xq (scale Qs + Qp) + Xk (Ks + Kp) - Y (2^G_last beta Kts + KtM + KtP)
+// with Xq = bf16(q 2^G), Xk = bf16(k 2^G), Y = bf16(kt 2^-G) the very operands of the products, so
+// that the two sides of every pair cancel under the reverse cumulative sum.
+//
+// Every mbarrier wait is bounded; a CTA whose wait gives up sets the status word.
+#include "pkda_chunk.cuh"
+#include "pkda_tc.cuh"
+
+namespace pkda {
+
+namespace ibtc {
+constexpr int kThreads = 512;
+constexpr int oS0 = 0;                  // [128 c][128 v] chunk-entry state           (K-major A)
+constexpr int oDS = oS0 + 32768;        // [128 c][128 v] cotangent of the exit state (K-major A)
+constexpr int oStk = oDS + 32768;       // [128][128 v]: rows 0..63 dR, rows 64..127 dO (K-major A, and K-major B by halves)
+constexpr int oDF = oStk + 32768;       // [64 j][128 v] dF                            (MN-major A)
+constexpr int oE = oDF + 16384;         // [64 j][128 v] E                             (K-major B)
+constexpr int oQ = oE + 16384;          // [64 i][128 c] q, then Xq                    (MN-major A)
+constexpr int oK = oQ + 16384;          // [64 i][128 c] k, then Xk                    (MN-major A)
+constexpr int oKt = oK + 16384;         // [64 j][128 c] kt, then Y                    (MN-major A)
+constexpr int oG = oKt + 16384;         // [64][128 c] raw gate
+constexpr int oTm = oG + 16384;         // [64 j][64 i] T, then diag(beta) T           (MN-major B)
+constexpr int oDM = oTm + 8192;         // [64 i][64 j] dM                             (K-major / MN-major B)
+constexpr int oDP = oDM + 8192;         // [64 i][64 j] dP
+constexpr int oSmall = oDP + 8192;      // f32: beta[64] | x1[4][128] | x2[4][128] | red[16]
+constexpr int oBar = oSmall + 256 + 2048 + 2048 + 64;  // barriers A, B, C, m1, m2, m3 and the tensor-memory address
+constexpr int kSmem = oBar + 64 + 1024;
+static_assert(kSmem <= 232448, "shared memory of one SM");
+// after the last product: exchange arrays in the (dead) pair-gradient tiles
+constexpr int oX3 = oDM;                // f32 [4][128] slice sums of dG
+constexpr int oX4 = oDM + 2048;         // f32 [4][128] slice sums of kt dkt (state part)
+constexpr int oX5 = oDM + 4096;         // f32 [4][128] slice sums of the raw-gate gradient
+constexpr int oDb = oDM + 6144;         // f32 [4][64] per lane-quarter partial sums of dbeta
+constexpr uint32_t kCols = 512;
+constexpr uint32_t cR = 0, cStk = 64, cQs = 128, cKs = 192, cKts = 256, cKtM = 320, cKtP = 384;  // cR / cStk later Qp / Kp
+}  // namespace ibtc
+
+// Sums each of v[0..15] over the 32 lanes.  On return lane l holds in v[0] the total of entry
+// ((l >> 4) & 1) * 8 + ((l >> 3) & 1) * 4 + ((l >> 2) & 1) * 2 + ((l >> 1) & 1).
+__device__ __forceinline__ void row_sums16(float (&v)[16], int lane) {
+  const bool b16 = lane & 16, b8 = lane & 8, b4 = lane & 4, b2 = lane & 2;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float keep = b16 ? v[j + 8] : v[j], send = b16 ? v[j] : v[j + 8];
+    v[j] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float keep = b8 ? v[j + 4] : v[j], send = b8 ? v[j] : v[j + 4];
+    v[j] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+  }
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const float keep = b4 ? v[j + 2] : v[j], send = b4 ? v[j] : v[j + 2];
+    v[j] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+  }
+  {
+    const float keep = b2 ? v[1] : v[0], send = b2 ? v[0] : v[1];
+    v[0] = keep + __shfl_xor_sync(0xffffffffu, send, 2);
+  }
+  v[0] += __shfl_xor_sync(0xffffffffu, v[0], 1);
+}
+
+struct IntraBwdTcMaps {
+  CUtensorMap h, dh, d_o, dF, E, q, k, kt, g, Akk, dv;
+};
+
+__global__ void __launch_bounds__(ibtc::kThreads, 1)
+pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBwdTcMaps maps) {
+  using namespace ibtc;
+  extern __shared__ unsigned char smem_raw[];
+  int n, tok0, valid;
+  if (!chunk_lookup(p.geo, blockIdx.x, n, tok0, valid)) return;
+  PKDA_PHASE(0);
+  const int h = blockIdx.y, H = p.geo.heads;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const size_t chh = (size_t)blockIdx.x * H + h;
+  const int q4 = warp & 3, sl = warp >> 2;      // lane quarter of tensor memory; token slice
+  const int c = 32 * q4 + lane;                 // this thread's channel (= tensor-memory lane)
+  const int j0 = 16 * sl;                       // first of its 16 tokens
+  const uint32_t lane_addr = (uint32_t)(32 * q4) << 16;
+
+  // ---- which kernel takes this chunk
+  const float gl = p.gc[chh * kD + c];          // 2^G_last of this channel
+  {
+    const bool bad = valid != kChunk || p.direct_cap < 64 || !(gl > 0.f) || -__log2f(gl) > kDirectLimit;
+    const bool decline = __syncthreads_or(bad);
+    if (tid == 0) p.flags[chh] = decline ? 1 : 0;
+    if (decline) return;
+  }
+
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char* tiles = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t barA = base + oBar, barB = barA + 8, barC = barA + 16, barM = barA + 24, tmem_slot = barA + 48;
+  float* sBeta = reinterpret_cast<float*>(tiles + oSmall);
+  float* sX1 = sBeta + 64;     // [4][128] slice totals of the gate
+  float* sX2 = sX1 + 512;      // [4][128] slice partials of sum_v S0 dS1
+  float* sRed = sX2 + 512;     // [16]
+
+  // ---- 0. all tiles by TMA, in the order they are needed
+  if (tid == 0) {
+    tc::mbar_init(barA, 1);
+    tc::mbar_init(barB, 1);
+    tc::mbar_init(barC, 1);
+    tc::mbar_init(barM, 1);
+    tc::fence_barrier_init();
+    const int srow = (int)(chh * kD);
+    tc::mbar_expect_tx(barB, 8192 + 3 * 16384);
+    tc::tma_load_3d(base + oTm, &maps.Akk, barB, 0, h, tok0);
+    for (int kb = 0; kb < 2; ++kb) {
+      tc::tma_load_3d(base + oDF + kb * 8192, &maps.dF, barB, 64 * kb, h, tok0);
+      tc::tma_load_3d(base + oE + kb * 8192, &maps.E, barB, 64 * kb, h, tok0);
+      tc::tma_load_3d(base + oStk + kb * 16384 + 8192, &maps.d_o, barB, 64 * kb, h, tok0);
+    }
+    tc::mbar_expect_tx(barA, 4 * 16384);
+    for (int kb = 0; kb < 2; ++kb) {
+      tc::tma_load_3d(base + oG + kb * 8192, &maps.g, barA, 64 * kb, h, tok0);
+      tc::tma_load_3d(base + oQ + kb * 8192, &maps.q, barA, 64 * kb, h, tok0);
+      tc::tma_load_3d(base + oK + kb * 8192, &maps.k, barA, 64 * kb, h, tok0);
+      tc::tma_load_3d(base + oKt + kb * 8192, &maps.kt, barA, 64 * kb, h, tok0);
+    }
+    tc::mbar_expect_tx(barC, 2 * 32768);
+    for (int kb = 0; kb < 2; ++kb) {
+      tc::tma_load_2d(base + oS0 + kb * 16384, &maps.h, barC, 64 * kb, srow);
+      tc::tma_load_2d(base + oDS + kb * 16384, &maps.dh, barC, 64 * kb, srow);
+    }
+  }
+  if (warp == 1) tc::tmem_alloc(tmem_slot, kCols);
+  if (tid < kChunk) sBeta[tid] = p.beta_c[chh * kChunk + tid];
+  const float bias = p.dt_bias[h * kD + c];
+  const float ea = __expf(p.A_log[h]);
+  tc::tc_fence_before();
+  __syncthreads(); PKDA_PHASE(1);
+  tc::tc_fence_after();
+  const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(tiles + oBar + 48);
+  bool ok = true;
+  uint32_t m_phase = 0;
+
+  // ---- 1. T <- diag(beta) T (row j scaled by beta_j: the beta of dE = beta dF moves onto T), then dR^T
+  ok = tc::mbar_wait(barB, 0) && ok;
+  {
+    const int j = tid >> 3, pc = tid & 7;
+    uint4* piece = reinterpret_cast<uint4*>(tiles + oTm + j * 128 + (pc << 4));  // a whole row takes one factor
+    const float b = sBeta[j];
+    const float f[8] = {b, b, b, b, b, b, b, b};
+    uint4 x = *piece;
+    scale8(x, f);
+    *piece = x;
+  }
+  tc::fence_proxy_async();
+  __syncthreads(); PKDA_PHASE(2);
+  if (tid == 0) {
+    tc::tc_fence_after();
+    constexpr uint32_t idesc = tc::idesc_bf16(128, 64, true, true);
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk)
+      tc::umma_bf16(tmem + cR, tc::desc_mnmajor(base + oDF + kk * 2048, 8192), tc::desc_mnmajor(base + oTm + kk * 2048, 8192),
+                    idesc, kk > 0);
+    tc::umma_commit(barM);
+  }
+
+  // ---- 2. while that runs: the gate, its cumulative sum over the tokens, the operands gated in place
+  ok = tc::mbar_wait(barA, 0) && ok;
+  float G[16];
+  {
+    const float ea2 = ea * kLog2e;
+    float run = 0.f;
+#pragma unroll
+    for (int t = 0; t < 16; ++t) {
+      const float raw = to_f(*reinterpret_cast<const bf16*>(tiles + oG + sw128_offset(j0 + t, c, 8192)));
+      run += -ea2 * softplus_fast(raw + bias);
+      G[t] = run;
+    }
+    sX1[sl * kD + c] = run;
+  }
+  __syncthreads(); PKDA_PHASE(3);
+  {
+    float pre = 0.f;
+#pragma unroll
+    for (int s = 0; s < 3; ++s) pre += (s < sl) ? sX1[s * kD + c] : 0.f;
+#pragma unroll
+    for (int t = 0; t < 16; ++t) {
+      G[t] += pre;
+      const float e = ex2(G[t]), ei = __fdividef(1.f, e);
+      const uint32_t off = sw128_offset(j0 + t, c, 8192);
+      bf16* xq = reinterpret_cast<bf16*>(tiles + oQ + off);
+      bf16* xk = reinterpret_cast<bf16*>(tiles + oK + off);
+      bf16* y = reinterpret_cast<bf16*>(tiles + oKt + off);
+      *xq = __float2bfloat16(to_f(*xq) * e);
+      *xk = __float2bfloat16(to_f(*xk) * e);
+      *y = __float2bfloat16(to_f(*y) * ei);
+    }
+  }
+  // the state-coupled products that need nothing but landed tiles; sum_v S0 dS1 per channel
+  ok = tc::mbar_wait(barC, 0) && ok;
+  if (tid == 0) {
+    tc::tc_fence_after();
+    constexpr uint32_t idesc = tc::idesc_bf16(128, 64, false, false);
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+      const uint32_t ko = (kk >> 2) * 16384 + (kk & 3) * 32;
+      tc::umma_bf16(tmem + cQs, tc::desc_kmajor(base + oS0 + ko), tc::desc_kmajor(base + oStk + 8192 + ko), idesc, kk > 0);
+    }
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+      const uint32_t ko = (kk >> 2) * 16384 + (kk & 3) * 32, ke = (kk >> 2) * 8192 + (kk & 3) * 32;
+      tc::umma_bf16(tmem + cKts, tc::desc_kmajor(base + oDS + ko), tc::desc_kmajor(base + oE + ke), idesc, kk > 0);
+    }
+  }
+  {
+    // channel c's row of both state tiles, values 32 sl .. 32 sl + 31 (four 16-byte pieces of one K block)
+    const unsigned char* rs = tiles + oS0 + (sl >> 1) * 16384 + c * 128;
+    const unsigned char* rd = tiles + oDS + (sl >> 1) * 16384 + c * 128;
+    float acc = 0.f;
+#pragma unroll
+    for (int pc = 0; pc < 4; ++pc) {
+      const int po = (((4 * (sl & 1) + pc) ^ (c & 7)) << 4);
+      const uint4 a = *reinterpret_cast<const uint4*>(rs + po), b = *reinterpret_cast<const uint4*>(rd + po);
+      const uint32_t* a32 = reinterpret_cast<const uint32_t*>(&a);
+      const uint32_t* b32 = reinterpret_cast<const uint32_t*>(&b);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 x = unpack_bf16(a32[e]), y = unpack_bf16(b32[e]);
+        acc += x.x * y.x + x.y * y.y;
+      }
+    }
+    sX2[sl * kD + c] = acc;
+  }
+
+  // ---- 3. dR^T -> bf16 -> rows 0..63 of the stack (it is dv as it stands)
+  ok = tc::mbar_wait(barM, m_phase) && ok;
+  m_phase ^= 1;
+  tc::tc_fence_after();
+  PKDA_PHASE(4);
+  {
+    float acc[16];
+    tc::tmem_ld16(tmem + lane_addr + cR + j0, acc);
+    tc::tmem_ld_wait();
+#pragma unroll
+    for (int t = 0; t < 16; ++t)
+      *reinterpret_cast<bf16*>(tiles + oStk + (c >> 6) * 16384 + (j0 + t) * 128 + ((((c & 63) >> 3) ^ ((j0 + t) & 7)) << 4) +
+                               (c & 7) * 2) = __float2bfloat16(acc[t]);
+  }
+  tc::fence_proxy_async();
+  tc::tc_fence_before();
+  __syncthreads(); PKDA_PHASE(5);
+  if (tid == 0) {
+    tc::tc_fence_after();
+    tc::tma_store_3d(&maps.dv, base + oStk, 0, h, tok0);
+    tc::tma_store_3d(&maps.dv, base + oStk + 16384, 64, h, tok0);
+    tc::bulk_commit();
+    constexpr uint32_t idesc = tc::idesc_bf16(128, 64, false, false);
+    constexpr uint32_t idesc_neg = idesc | (1u << 13);  // A negated
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {  // [dR; dO] E^T
+      const uint32_t ko = (kk >> 2) * 16384 + (kk & 3) * 32, ke = (kk >> 2) * 8192 + (kk & 3) * 32;
+      tc::umma_bf16(tmem + cStk, tc::desc_kmajor(base + oStk + ko), tc::desc_kmajor(base + oE + ke), idesc, kk > 0);
+    }
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {  // -S0 dR^T
+      const uint32_t ko = (kk >> 2) * 16384 + (kk & 3) * 32;
+      tc::umma_bf16(tmem + cKs, tc::desc_kmajor(base + oS0 + ko), tc::desc_kmajor(base + oStk + ko), idesc_neg, kk > 0);
+    }
+    tc::umma_commit(barM);
+  }
+
+  // ---- 4. pair-weight gradients: row i of dM = -tril(dR E^T, -1) diag(beta), of dP = scale tril(dO E^T) diag(beta)
+  ok = tc::mbar_wait(barM, m_phase) && ok;
+  m_phase ^= 1;
+  tc::tc_fence_after();
+  PKDA_PHASE(6);
+  {
+    float acc[16];
+    tc::tmem_ld16(tmem + lane_addr + cStk + j0, acc);
+    tc::tmem_ld_wait();
+    const bool isP = c >= 64;
+    const int i = c & 63;
+    float x[16];
+#pragma unroll
+    for (int t = 0; t < 16; ++t) {
+      const int j = j0 + t;
+      const float b = sBeta[j];
+      x[t] = isP ? (j <= i ? acc[t] * b * p.scale : 0.f) : (j < i ? -acc[t] * b : 0.f);
+    }
+    unsigned char* row = tiles + (isP ? oDP : oDM) + i * 128;
+    *reinterpret_cast<uint4*>(row + (((2 * sl) ^ (i & 7)) << 4)) =
+        make_uint4(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]), pack_bf16(x[4], x[5]), pack_bf16(x[6], x[7]));
+    *reinterpret_cast<uint4*>(row + (((2 * sl + 1) ^ (i & 7)) << 4)) =
+        make_uint4(pack_bf16(x[8], x[9]), pack_bf16(x[10], x[11]), pack_bf16(x[12], x[13]), pack_bf16(x[14], x[15]));
+  }
+  tc::fence_proxy_async();  // also covers the gated operands written in step 2
+  tc::tc_fence_before();
+  __syncthreads(); PKDA_PHASE(7);
+  if (tid == 0) {
+    tc::tc_fence_after();
+    constexpr uint32_t idesc_k = tc::idesc_bf16(128, 64, true, false);  // B = pair gradient as [i][j], K = j
+    constexpr uint32_t idesc_m = tc::idesc_bf16(128, 64, true, true);   // B = pair gradient read as [j][i], K = i
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+      const uint64_t ay = tc::desc_mnmajor(base + oKt + kk * 2048, 8192);
+      tc::umma_bf16(tmem + cR, ay, tc::desc_kmajor(base + oDP + kk * 32), idesc_k, kk > 0);    // Qp = Y^T dP^T
+      tc::umma_bf16(tmem + cStk, ay, tc::desc_kmajor(base + oDM + kk * 32), idesc_k, kk > 0);  // Kp = Y^T dM^T
+    }
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+      tc::umma_bf16(tmem + cKtM, tc::desc_mnmajor(base + oK + kk * 2048, 8192), tc::desc_mnmajor(base + oDM + kk * 2048, 8192),
+                    idesc_m, kk > 0);  // Xk^T dM
+      tc::umma_bf16(tmem + cKtP, tc::desc_mnmajor(base + oQ + kk * 2048, 8192), tc::desc_mnmajor(base + oDP + kk * 2048, 8192),
+                    idesc_m, kk > 0);  // Xq^T dP
+    }
+    tc::umma_commit(barM);
+  }
+  ok = tc::mbar_wait(barM, m_phase) && ok;
+  tc::tc_fence_after();
+  PKDA_PHASE(8);
+
+  // ---- 5. gradients of this thread's channel and 16 tokens
+  const size_t gld = (size_t)H * kD;
+  const size_t out0 = ((size_t)(tok0 + j0) * H + h) * kD + c;  // element (first token of the slice, h, c)
+  float dGv[16], dbv[16], kdsum = 0.f;
+  {
+    float a[16], b[16];
+    tc::tmem_ld16(tmem + lane_addr + cQs + j0, a);
+    tc::tmem_ld16(tmem + lane_addr + cR + j0, b);
+    tc::tmem_ld_wait();
+#pragma unroll
+    for (int t = 0; t < 16; ++t) {
+      const float tot = p.scale * a[t] + b[t];
+      const float xq = to_f(*reinterpret_cast<const bf16*>(tiles + oQ + sw128_offset(j0 + t, c, 8192)));
+      p.dq[out0 + t * gld] = __float2bfloat16(ex2(G[t]) * tot);
+      dGv[t] = xq * tot;
+    }
+    tc::tmem_ld16(tmem + lane_addr + cKs + j0, a);
+    tc::tmem_ld16(tmem + lane_addr + cStk + j0, b);
+    tc::tmem_ld_wait();
+#pragma unroll
+    for (int t = 0; t < 16; ++t) {
+      const float tot = a[t] + b[t];
+      const float xk = to_f(*reinterpret_cast<const bf16*>(tiles + oK + sw128_offset(j0 + t, c, 8192)));
+      p.dk_read[out0 + t * gld] = ex2(G[t]) * tot;
+      dGv[t] += xk * tot;
+    }
+    float m[16];
+    tc::tmem_ld16(tmem + lane_addr + cKts + j0, a);
+    tc::tmem_ld16(tmem + lane_addr + cKtM + j0, m);
+    tc::tmem_ld16(tmem + lane_addr + cKtP + j0, b);
+    tc::tmem_ld_wait();
+#pragma unroll
+    for (int t = 0; t < 16; ++t) {
+      const float bj = sBeta[j0 + t];
+      const uint32_t off = sw128_offset(j0 + t, c, 8192);
+      const float y = to_f(*reinterpret_cast<const bf16*>(tiles + oKt + off));
+      const float st = gl * bj * a[t], pr = m[t] + b[t];
+      p.dkt[out0 + t * gld] = ex2(-G[t]) * (st + pr);
+      const float kd = y * st;
+      dGv[t] -= y * pr + kd;
+      kdsum += kd;
+      const float df = to_f(*reinterpret_cast<const bf16*>(tiles + oDF + off));
+      const float ev = to_f(*reinterpret_cast<const bf16*>(tiles + oE + off));
+      dbv[t] = df * ev + (bj != 0.f ? __fdividef(y * m[t], bj) : 0.f);
+    }
+  }
+  tc::tc_fence_before();
+  float* sX3 = reinterpret_cast<float*>(tiles + oX3);
+  float* sX4 = reinterpret_cast<float*>(tiles + oX4);
+  float* sX5 = reinterpret_cast<float*>(tiles + oX5);
+  float* sDb = reinterpret_cast<float*>(tiles + oDb);
+  {
+    float tot = 0.f;
+#pragma unroll
+    for (int t = 0; t < 16; ++t) tot += dGv[t];
+    sX3[sl * kD + c] = tot;     // the pair-gradient tiles are dead: every product has finished
+    sX4[sl * kD + c] = kdsum;
+    row_sums16(dbv, lane);
+    if ((lane & 1) == 0)
+      sDb[q4 * kChunk + j0 + ((lane >> 4) & 1) * 8 + ((lane >> 3) & 1) * 4 + ((lane >> 2) & 1) * 2 + ((lane >> 1) & 1)] = dbv[0];
+  }
+  __syncthreads(); PKDA_PHASE(9);
+  // reverse cumulative sum over the tokens (the chunk's last row also takes the decay-total terms),
+  // then the gate's own backward:  g = -exp(A_log) softplus(raw + bias)
+  {
+    float run = gl * (sX2[c] + sX2[kD + c] + sX2[2 * kD + c] + sX2[3 * kD + c]) + sX4[c] + sX4[kD + c] + sX4[2 * kD + c] +
+                sX4[3 * kD + c];
+#pragma unroll
+    for (int s = 1; s < 4; ++s) run += (s > sl) ? sX3[s * kD + c] : 0.f;
+    float pa = 0.f, pb = 0.f;
+#pragma unroll
+    for (int t = 15; t >= 0; --t) {
+      run += dGv[t];
+      const float raw = to_f(*reinterpret_cast<const bf16*>(tiles + oG + sw128_offset(j0 + t, c, 8192)));
+      const float z = raw + bias;
+      const float e0 = __expf(-fabsf(z)), i0 = __fdividef(1.f, 1.f + e0);
+      const float sg = z >= 0.f ? i0 : e0 * i0;
+      const float sp = fmaxf(z, 0.f) - __logf(i0);
+      const float dr = run * (-ea) * sg;
+      pa += run * (-ea * sp);
+      pb += dr;
+      p.dg[out0 + t * gld] = __float2bfloat16(dr);
+    }
+    sX5[sl * kD + c] = pb;
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) pa += __shfl_xor_sync(0xffffffffu, pa, o);
+    if (lane == 0) sRed[warp] = pa;
+  }
+  if (tid < kChunk)
+    p.dbeta[(size_t)(tok0 + tid) * H + h] =
+        __float2bfloat16(sDb[tid] + sDb[kChunk + tid] + sDb[2 * kChunk + tid] + sDb[3 * kChunk + tid]);
+  const bool all_ok = !__syncthreads_or(!ok);
+  PKDA_PHASE(10);
+  if (tid < kD) p.partB[chh * kD + tid] = sX5[tid] + sX5[kD + tid] + sX5[2 * kD + tid] + sX5[3 * kD + tid];
+  if (tid == 0) {
+    float acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < kThreads / 32; ++w) acc += sRed[w];
+    p.partA[chh] = acc;
+    if (!all_ok) atomicExch(p.status, 1);
+    tc::bulk_wait_read();  // the dv store has read the stack
+  }
+  if (warp == 1) tc::tmem_dealloc(tmem, kCols);
+  PKDA_PHASE(11);
+}
+
+// ------------------------------------------------------------------ host side
+int launch_intra_bwd_tc(const IntraBwdParams& ip, cudaStream_t st) {
+  const uint64_t H = ip.geo.heads, tok = ip.geo.total_tokens, rows = (uint64_t)ip.geo.total_chunks * H * kD;
+  IntraBwdTcMaps maps;
+  {
+    const uint64_t dims[3] = {kD, H, tok}, str[2] = {kD * 2, H * kD * 2};
+    const uint32_t box[3] = {64, 1, 64};
+    if (!encode_bf16_map(&maps.d_o, ip.d_o, 3, dims, str, box) || !encode_bf16_map(&maps.dF, ip.dF, 3, dims, str, box) ||
+        !encode_bf16_map(&maps.E, ip.v_new, 3, dims, str, box) || !encode_bf16_map(&maps.q, ip.q, 3, dims, str, box) ||
+        !encode_bf16_map(&maps.k, ip.k, 3, dims, str, box) || !encode_bf16_map(&maps.kt, ip.kt, 3, dims, str, box) ||
+        !encode_bf16_map(&maps.g, ip.g, 3, dims, str, box) || !encode_bf16_map(&maps.dv, ip.dv, 3, dims, str, box))
+      return PKDA_ERR_LAUNCH;
+  }
+  {
+    const uint64_t dims[3] = {kChunk, H, tok}, str[2] = {kChunk * 2, H * kChunk * 2};
+    const uint32_t box[3] = {64, 1, 64};
+    if (!encode_bf16_map(&maps.Akk, ip.Akk, 3, dims, str, box)) return PKDA_ERR_LAUNCH;
+  }
+  {
+    const uint64_t dims[2] = {kD, rows}, str[1] = {kD * 2};
+    const uint32_t box[2] = {64, 128};
+    if (!encode_bf16_map(&maps.h, ip.h, 2, dims, str, box) || !encode_bf16_map(&maps.dh, ip.dh, 2, dims, str, box))
+      return PKDA_ERR_LAUNCH;
+  }
+  if (cudaFuncSetAttribute(pkda_intra_bwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ibtc::kSmem) !=
+      cudaSuccess)
+    return PKDA_ERR_LAUNCH;
+  pkda_intra_bwd_tc_kernel<<<dim3(ip.geo.total_chunks, ip.geo.heads), ibtc::kThreads, ibtc::kSmem, st>>>(ip, maps);
+  return cudaGetLastError() == cudaSuccess ? PKDA_OK : PKDA_ERR_LAUNCH;
+}
+
+}  // namespace pkda
+
+#ifdef PKDA_PHASE_PROFILE
+extern "C" int pkda_phase_prof_ibtc(long long* out) {
+  return cudaMemcpyFromSymbol(out, g_phase_prof, sizeof(long long) * 64) == cudaSuccess ? 0 : 1;
+}
+#endif

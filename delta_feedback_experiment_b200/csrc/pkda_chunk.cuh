@@ -409,9 +409,11 @@ struct IntraBwdParams {
   int use_tma;   // the five phase-A tiles of full chunks arrive by TMA (tensor maps valid)
   int out_tma;   // dq, dv, dk_read and dkt of full chunks leave by TMA from padded shared-memory tiles
   int* status;   // set to 1 if a bounded wait gives up
-  // Per (chunk, head) byte: the tcgen05 kernel writes 1 for every chunk it leaves to the mma.sync
-  // kernel and 0 for those it has done; the mma.sync kernel skips the zeros (NULL: it takes all).
-  unsigned char* flags;
+  // Work lists of (chunk * heads + head) items written by pkda_bwd_classify_kernel: fast_list for the
+  // tensor-memory kernel, slow_list for the mma.sync kernel; fast_count[0] / fast_count[1] are their
+  // lengths (zeroed before every call).  slow_list == NULL: the mma.sync kernel takes every chunk,
+  // one CTA per (chunk, head).
+  int *fast_list, *slow_list, *fast_count;
 };
 
 // tcgen05 / tensor-memory chunk-parallel backward stage (pkda_intra_bwd_tc.cu).

@@ -260,8 +260,8 @@ __device__ __forceinline__ void epi_add(float (&acc)[1][4][4], float (&dG)[1][4]
     }
 }
 
-__global__ void __launch_bounds__(ib::kThreads, 1)
-pkda_intra_bwd_kernel(const IntraBwdParams p, const __grid_constant__ IntraBwdMaps maps) {
+// One (chunk bx, head by) item; every thread of the CTA takes part.
+__device__ __forceinline__ void intra_bwd_item(const IntraBwdParams& p, const IntraBwdMaps& maps, int bx, int by) {
   using namespace ib;
   extern __shared__ __align__(128) unsigned char smem[];
   PKDA_PHASE(0);
@@ -287,13 +287,12 @@ pkda_intra_bwd_kernel(const IntraBwdParams p, const __grid_constant__ IntraBwdMa
   float* sWarpMax = sBias + 128;  // [4][6]
 
   int n, tok0, valid;
-  if (!chunk_lookup(p.geo, blockIdx.x, n, tok0, valid)) return;
-  const int h = blockIdx.y, H = p.geo.heads;
+  if (!chunk_lookup(p.geo, bx, n, tok0, valid)) return;
+  const int h = by, H = p.geo.heads;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int gq = lane >> 2, tq = lane & 3;
   const int I = warp & 3, cq = warp >> 2;
-  const size_t chh = (size_t)blockIdx.x * H + h;
-  if (p.flags && !p.flags[chh]) return;  // the tcgen05 kernel has done this chunk
+  const size_t chh = (size_t)bx * H + h;
   const size_t row0 = ((size_t)tok0 * H + h) * kD;
   const long gld = (long)H * kD;
   const size_t crow0 = ((size_t)tok0 * H + h) * kChunk;
@@ -756,8 +755,24 @@ pkda_intra_bwd_kernel(const IntraBwdParams p, const __grid_constant__ IntraBwdMa
     for (int w = 0; w < kThreads / 32; ++w) acc += sRed[w];
     p.partA[chh] = acc;
     if (out_tma) tc::bulk_wait_read();  // the tiles stay in place until the stores have read them
+    if (by_tma) tc::mbar_inval(bar);    // a CTA that walks a work list sets the barrier up anew per item
   }
   PKDA_PHASE(17);
+}
+
+// grid (chunks, heads): one item per CTA; or, with a work list, a few persistent CTAs that walk it.
+__global__ void __launch_bounds__(ib::kThreads, 1)
+pkda_intra_bwd_kernel(const IntraBwdParams p, const __grid_constant__ IntraBwdMaps maps) {
+  if (!p.slow_list) {
+    intra_bwd_item(p, maps, blockIdx.x, blockIdx.y);
+    return;
+  }
+  const int n_items = p.fast_count[1], H = p.geo.heads;
+  for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+    const int chh = p.slow_list[item];
+    intra_bwd_item(p, maps, chh / H, chh % H);
+    __syncthreads();  // the next item reuses every shared-memory region
+  }
 }
 
 // ------------------------------------------------------------------ preconditioner backward
@@ -1124,7 +1139,7 @@ struct BwdWorkspace {
   float* beta_c;
   bf16 *u, *dF, *dh;
   float *dk_read, *dkt, *partA, *partB, *partC, *c_loc, *lam_in;
-  unsigned char* flags;
+  int *fast_list, *slow_list, *counts;
   int* status;
   size_t bytes;
 };
@@ -1151,8 +1166,10 @@ static BwdWorkspace carve_bwd(const pkda_problem& p, void* base) {
   w.partC = static_cast<float*>(take(chunks * H * 4));
   w.c_loc = static_cast<float*>(take(chunks * H * kD * 4));
   w.lam_in = static_cast<float*>(take(chunks * H * kD * 4));
-  w.flags = static_cast<unsigned char*>(take(chunks * H));
-  w.status = static_cast<int*>(take(sizeof(int)));
+  w.fast_list = static_cast<int*>(take(chunks * H * sizeof(int)));
+  w.slow_list = static_cast<int*>(take(chunks * H * sizeof(int)));
+  w.status = static_cast<int*>(take(4 * sizeof(int)));  // status word, then the two work-list lengths
+  w.counts = w.status + 1;
   w.bytes = off;
   return w;
 }
@@ -1204,7 +1221,7 @@ int chunk_bwd(const pkda_chunk_bwd_args* a, cudaStream_t st) {
   bf16* v_new = static_cast<bf16*>(a->v_new);
   bf16* h = static_cast<bf16*>(a->h);
   bf16* qg = static_cast<bf16*>(a->qg);
-  if (cudaMemsetAsync(ws.status, 0, sizeof(int), st) != cudaSuccess) return PKDA_ERR_LAUNCH;
+  if (cudaMemsetAsync(ws.status, 0, 4 * sizeof(int), st) != cudaSuccess) return PKDA_ERR_LAUNCH;
   if (a->recompute) {
     // The recompute kernels only read the products, write keys and decay totals.
     rc = run_forward_stages(p, geo, ws.beta_c, ws.u, const_cast<bf16*>(Aqk), const_cast<bf16*>(Akk),
@@ -1266,18 +1283,21 @@ int chunk_bwd(const pkda_chunk_bwd_args* a, cudaStream_t st) {
                  encode_f32_map(&maps.dkt, ip.dkt, 3, o_dims, o_str4, o_box);
     ip.status = ws.status;
   }
-  // Full chunks that are one direct block run on tcgen05 / tensor memory; that kernel flags the
-  // others for the mma.sync kernel behind it (which takes every chunk when it is pinned).
-  ip.flags = nullptr;
+  // Full chunks that are one direct block run on tcgen05 / tensor memory; a classifier in front sorts
+  // the chunks into two work lists and the mma.sync kernel works off the second one (every chunk, one
+  // CTA each, when it is pinned).
+  ip.fast_list = ip.slow_list = ip.fast_count = nullptr;
+  int sms = 148, dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (stage_variant(kStageIntraBwd) == 0) {
-    ip.flags = ws.flags;
-    begin_stage(kStageIntraBwd, st);
+    ip.fast_list = ws.fast_list; ip.slow_list = ws.slow_list; ip.fast_count = ws.counts;
     rc = launch_intra_bwd_tc(ip, st);
-    end_stage(st);
     if (rc != PKDA_OK) return rc;
+    const int items = geo.total_chunks * p.heads;
+    gridc = dim3(items < sms ? items : sms, 1);
   }
   if (!set_smem(pkda_intra_bwd_kernel, ib::kSmem)) return PKDA_ERR_LAUNCH;
-  begin_stage(kStageIntraBwd, st);
+  begin_stage(ip.slow_list ? kStageIntraBwdRest : kStageIntraBwd, st);
   pkda_intra_bwd_kernel<<<gridc, ib::kThreads, ib::kSmem, st>>>(ip, maps);
   PKDA_CHECK_LAUNCH();
 
@@ -1289,8 +1309,6 @@ int chunk_bwd(const pkda_chunk_bwd_args* a, cudaStream_t st) {
   ap.partC = ws.partC; ap.ln_x = logf(p.squash_x); ap.eps = p.squash_eps;
   begin_stage(kStageAtkBwdLocal, st);
   const int atk_tiles = geo.total_chunks * p.heads;
-  int sms = 148, dev = 0;
-  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int atk_grid = atk_tiles < 2 * sms ? atk_tiles : 2 * sms;  // persistent: two CTAs per SM
   if (!set_smem(pkda_atk_bwd_kernel<false>, atkb::smem_bytes<false>())) return PKDA_ERR_LAUNCH;
   pkda_atk_bwd_kernel<false><<<atk_grid, atkb::kThreads, atkb::smem_bytes<false>(), st>>>(ap, atk_tiles);

@@ -1,14 +1,16 @@
 // Chunk-parallel stage of the chunked backward on tcgen05 / tensor memory (D = 128, chunk 64).
 //
-// One CTA of 512 threads per (chunk, head); all operand tiles of the chunk (about 216 KB) sit in
-// shared memory at once, every one of them placed by TMA in the 128-byte-swizzled layout the
-// tensor core reads, and every dense product is a tcgen05.mma chain into tensor memory.  The
-// kernel takes the chunks that are full (64 tokens) and whose decay lets the whole chunk be ONE
+// Persistent CTAs of 512 threads (one per SM) walk a list of (chunk, head) items; all operand
+// tiles of an item (about 216 KB) sit in shared memory at once, every one of them placed by TMA
+// in the 128-byte-swizzled layout the tensor core reads, and every dense product is a
+// tcgen05.mma chain into tensor memory.  The tiles of the next item are requested as soon as the
+// current item's last read of them is over, so they land while the gate's backward runs.  The
+// list holds the chunks that are full (64 tokens) and whose decay lets the whole chunk be ONE
 // direct block (pkda_chunk.cuh): there the gated operands are q 2^G, k 2^G and kt 2^-G with G the
-// cumulative log2-decay from the chunk start, one set for all pairs.  Every other chunk (a ragged
-// last chunk, a chunk that decays by more than kDirectLimit, a capped direct block) is flagged
-// and left to the mma.sync kernel of pkda_chunk_bwd.cu, which runs right after this one and
-// handles flagged chunks only.
+// cumulative log2-decay from the chunk start, one set for all pairs.  A small kernel in front
+// (pkda_bwd_classify_kernel) sorts the chunks: every other chunk (a ragged last chunk, a chunk
+// that decays by more than kDirectLimit, a capped direct block) goes on a second list, which the
+// mma.sync kernel of pkda_chunk_bwd.cu works off right after this one.
 //
 // Accumulators are laid out with one value / key channel per tensor-memory lane and tokens along
 // the columns (M = 128 channels everywhere, N = 64 tokens), so a thread owns one channel and 16
@@ -31,6 +33,14 @@
 // Every mbarrier wait is bounded; a CTA whose wait gives up sets the status word.
 #include "pkda_chunk.cuh"
 #include "pkda_tc.cuh"
+
+#ifdef PKDA_PHASE_PROFILE
+#undef PKDA_PHASE
+#define PKDA_PHASE(k)                                                                             \
+  do {                                                                                            \
+    if (threadIdx.x == 0 && blockIdx.x == 37 && item == 37 + 10 * (int)gridDim.x) g_phase_prof[k] = clock64(); \
+  } while (0)
+#endif
 
 namespace pkda {
 
@@ -87,83 +97,170 @@ __device__ __forceinline__ void row_sums16(float (&v)[16], int lane) {
   v[0] += __shfl_xor_sync(0xffffffffu, v[0], 1);
 }
 
+// One bf16 element of shared memory by its 32-bit shared address (register + immediate addressing).
+__device__ __forceinline__ float lds_bf16(uint32_t addr) {
+  unsigned short u;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(u) : "r"(addr));
+  return __uint_as_float((uint32_t)u << 16);
+}
+__device__ __forceinline__ void sts_bf16(uint32_t addr, float x) {
+  const bf16 b = __float2bfloat16(x);
+  asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"(*reinterpret_cast<const unsigned short*>(&b)) : "memory");
+}
+
 struct IntraBwdTcMaps {
   CUtensorMap h, dh, d_o, dF, E, q, k, kt, g, Akk, dv;
 };
+
+// Sorts the (chunk, head) items of a backward call into the two work lists.  One warp per item
+// reads the chunk's decay totals (128 floats); a CTA appends its items with one atomic per list.
+__global__ void __launch_bounds__(256)
+pkda_bwd_classify_kernel(Geo geo, const float* gc, int direct_cap, int* fast_list, int* slow_list, int* counts) {
+  __shared__ int sKind[64];
+  __shared__ int sBase[2];
+  const int H = geo.heads, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int items = geo.total_chunks * H;
+  for (int k = 0; k < 8; ++k) {
+    const int local = warp * 8 + k, chh = blockIdx.x * 64 + local;
+    int kind = -1;  // -1: not an item, 0: tensor-memory kernel, 1: mma.sync kernel
+    if (chh < items) {
+      int n, tok0, valid;
+      if (chunk_lookup(geo, chh / H, n, tok0, valid)) {
+        const float4 x = *reinterpret_cast<const float4*>(gc + (size_t)chh * kD + 4 * lane);
+        float m = fminf(fminf(x.x, x.y), fminf(x.z, x.w));
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) m = fminf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        const bool fast = valid == kChunk && direct_cap >= 64 && m > 0.f && -__log2f(m) <= kDirectLimit;
+        kind = fast ? 0 : 1;
+      }
+    }
+    if (lane == 0) sKind[local] = kind;
+  }
+  __syncthreads();
+  if (tid < 2) {
+    int cnt = 0;
+    for (int i = 0; i < 64; ++i) cnt += sKind[i] == tid;
+    sBase[tid] = cnt ? atomicAdd(counts + tid, cnt) : 0;
+  }
+  __syncthreads();
+  if (tid < 2) {
+    int* list = tid ? slow_list : fast_list;
+    int pos = sBase[tid];
+    for (int i = 0; i < 64; ++i)
+      if (sKind[i] == tid) list[pos++] = blockIdx.x * 64 + i;
+  }
+}
 
 __global__ void __launch_bounds__(ibtc::kThreads, 1)
 pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBwdTcMaps maps) {
   using namespace ibtc;
   extern __shared__ unsigned char smem_raw[];
-  int n, tok0, valid;
-  if (!chunk_lookup(p.geo, blockIdx.x, n, tok0, valid)) return;
-  PKDA_PHASE(0);
-  const int h = blockIdx.y, H = p.geo.heads;
+  const int n_items = *p.fast_count;
+  if ((int)blockIdx.x >= n_items) return;
+  const int H = p.geo.heads;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const size_t chh = (size_t)blockIdx.x * H + h;
   const int q4 = warp & 3, sl = warp >> 2;      // lane quarter of tensor memory; token slice
   const int c = 32 * q4 + lane;                 // this thread's channel (= tensor-memory lane)
   const int j0 = 16 * sl;                       // first of its 16 tokens
   const uint32_t lane_addr = (uint32_t)(32 * q4) << 16;
-
-  // ---- which kernel takes this chunk
-  const float gl = p.gc[chh * kD + c];          // 2^G_last of this channel
-  {
-    const bool bad = valid != kChunk || p.direct_cap < 64 || !(gl > 0.f) || -__log2f(gl) > kDirectLimit;
-    const bool decline = __syncthreads_or(bad);
-    if (tid == 0) p.flags[chh] = decline ? 1 : 0;
-    if (decline) return;
-  }
+  const size_t gld = (size_t)H * kD;
 
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char* tiles = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t barA = base + oBar, barB = barA + 8, barC = barA + 16, barM = barA + 24, tmem_slot = barA + 48;
+  // Shared address of element (token j0 + t, channel c) of a [64][128] tile at offset o: sa[t & 7] + o + 128 t
+  // (the 16-byte pieces of a row are permuted by the row index modulo 8).
+  uint32_t sa[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) sa[k] = base + sw128_offset(k, c, 8192) - 128 * k + j0 * 128;
   float* sBeta = reinterpret_cast<float*>(tiles + oSmall);
   float* sX1 = sBeta + 64;     // [4][128] slice totals of the gate
   float* sX2 = sX1 + 512;      // [4][128] slice partials of sum_v S0 dS1
   float* sRed = sX2 + 512;     // [16]
+  float* sX3 = reinterpret_cast<float*>(tiles + oX3);
+  float* sX4 = reinterpret_cast<float*>(tiles + oX4);
+  float* sX5 = reinterpret_cast<float*>(tiles + oX5);
+  float* sDb = reinterpret_cast<float*>(tiles + oDb);
 
-  // ---- 0. all tiles by TMA, in the order they are needed
+  // All tiles of one item by TMA.  Thread 0 arms the three barriers with the byte counts (arm), a
+  // CTA-wide barrier later the 20 copies are issued by the first lanes of the 16 warps (request), so
+  // that no single thread spends a thousand cycles issuing them.
+  auto arm = [&]() {
+    tc::mbar_expect_tx(barB, 8192 + 3 * 16384 + 256);
+    tc::mbar_expect_tx(barA, 4 * 16384);
+    tc::mbar_expect_tx(barC, 2 * 32768);
+  };
+  auto request = [&](int item) {
+    if (lane != 0) return;  // (the barriers were armed by arm() before the preceding CTA-wide barrier)
+    const int chh = p.fast_list[item];
+    const int h = chh % H;
+    int n, tok0, valid;
+    chunk_lookup(p.geo, chh / H, n, tok0, valid);
+    const int srow = chh * kD;
+    if (warp == 0) {
+      tc::tma_load_3d(base + oTm, &maps.Akk, barB, 0, h, tok0);
+      tc::bulk_load(base + oSmall, p.beta_c + (size_t)chh * kChunk, 256, barB);
+    }
+    const int kb = warp & 1;
+    switch (warp >> 1) {
+      case 0: tc::tma_load_3d(base + oDF + kb * 8192, &maps.dF, barB, 64 * kb, h, tok0); break;
+      case 1: tc::tma_load_3d(base + oE + kb * 8192, &maps.E, barB, 64 * kb, h, tok0); break;
+      case 2: tc::tma_load_3d(base + oStk + kb * 16384 + 8192, &maps.d_o, barB, 64 * kb, h, tok0); break;
+      case 3: tc::tma_load_3d(base + oG + kb * 8192, &maps.g, barA, 64 * kb, h, tok0); break;
+      case 4: tc::tma_load_3d(base + oQ + kb * 8192, &maps.q, barA, 64 * kb, h, tok0); break;
+      case 5: tc::tma_load_3d(base + oK + kb * 8192, &maps.k, barA, 64 * kb, h, tok0); break;
+      case 6: tc::tma_load_3d(base + oKt + kb * 8192, &maps.kt, barA, 64 * kb, h, tok0); break;
+      default:
+        tc::tma_load_2d(base + oS0 + kb * 16384, &maps.h, barC, 64 * kb, srow);
+        tc::tma_load_2d(base + oDS + kb * 16384, &maps.dh, barC, 64 * kb, srow);
+        break;
+    }
+  };
+
   if (tid == 0) {
     tc::mbar_init(barA, 1);
     tc::mbar_init(barB, 1);
     tc::mbar_init(barC, 1);
     tc::mbar_init(barM, 1);
     tc::fence_barrier_init();
-    const int srow = (int)(chh * kD);
-    tc::mbar_expect_tx(barB, 8192 + 3 * 16384);
-    tc::tma_load_3d(base + oTm, &maps.Akk, barB, 0, h, tok0);
-    for (int kb = 0; kb < 2; ++kb) {
-      tc::tma_load_3d(base + oDF + kb * 8192, &maps.dF, barB, 64 * kb, h, tok0);
-      tc::tma_load_3d(base + oE + kb * 8192, &maps.E, barB, 64 * kb, h, tok0);
-      tc::tma_load_3d(base + oStk + kb * 16384 + 8192, &maps.d_o, barB, 64 * kb, h, tok0);
-    }
-    tc::mbar_expect_tx(barA, 4 * 16384);
-    for (int kb = 0; kb < 2; ++kb) {
-      tc::tma_load_3d(base + oG + kb * 8192, &maps.g, barA, 64 * kb, h, tok0);
-      tc::tma_load_3d(base + oQ + kb * 8192, &maps.q, barA, 64 * kb, h, tok0);
-      tc::tma_load_3d(base + oK + kb * 8192, &maps.k, barA, 64 * kb, h, tok0);
-      tc::tma_load_3d(base + oKt + kb * 8192, &maps.kt, barA, 64 * kb, h, tok0);
-    }
-    tc::mbar_expect_tx(barC, 2 * 32768);
-    for (int kb = 0; kb < 2; ++kb) {
-      tc::tma_load_2d(base + oS0 + kb * 16384, &maps.h, barC, 64 * kb, srow);
-      tc::tma_load_2d(base + oDS + kb * 16384, &maps.dh, barC, 64 * kb, srow);
-    }
+    arm();
   }
   if (warp == 1) tc::tmem_alloc(tmem_slot, kCols);
-  if (tid < kChunk) sBeta[tid] = p.beta_c[chh * kChunk + tid];
-  const float bias = p.dt_bias[h * kD + c];
-  const float ea = __expf(p.A_log[h]);
   tc::tc_fence_before();
-  __syncthreads(); PKDA_PHASE(1);
+  __syncthreads();
   tc::tc_fence_after();
+  request(blockIdx.x);
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(tiles + oBar + 48);
   bool ok = true;
-  uint32_t m_phase = 0;
+  uint32_t m_phase = 0, ld_phase = 0;
+  // per-item scalars of this thread, fetched one item ahead: 2^G_last of its channel, the gate bias, A_log
+  float gl_n, bias_n, alog_n;
+  int chh_n;
+  auto fetch_scalars = [&](int item) {
+    const int chh = p.fast_list[item], h = chh % H;
+    chh_n = chh;
+    gl_n = p.gc[(size_t)chh * kD + c];
+    bias_n = p.dt_bias[h * kD + c];
+    alog_n = p.A_log[h];
+  };
+  fetch_scalars(blockIdx.x);
+
+#pragma unroll 1
+  for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+  PKDA_PHASE(0);
+  const int chh = chh_n;
+  const int h = chh % H;
+  int n, tok0, valid;
+  chunk_lookup(p.geo, chh / H, n, tok0, valid);  // a full chunk (the classifier checked)
+  const float gl = gl_n, bias = bias_n, ea = __expf(alog_n);
+  // The operand descriptors are functions of the tile base only; keeping the base opaque per item
+  // stops the compiler from computing all sixty of them ahead of the loop and holding them in registers.
+  uint32_t dbase = base;
+  asm volatile("" : "+r"(dbase));
+  PKDA_PHASE(1);
 
   // ---- 1. T <- diag(beta) T (row j scaled by beta_j: the beta of dE = beta dF moves onto T), then dR^T
-  ok = tc::mbar_wait(barB, 0) && ok;
+  ok = tc::mbar_wait(barB, ld_phase) && ok;
   {
     const int j = tid >> 3, pc = tid & 7;
     uint4* piece = reinterpret_cast<uint4*>(tiles + oTm + j * 128 + (pc << 4));  // a whole row takes one factor
@@ -180,22 +277,27 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
     constexpr uint32_t idesc = tc::idesc_bf16(128, 64, true, true);
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk)
-      tc::umma_bf16(tmem + cR, tc::desc_mnmajor(base + oDF + kk * 2048, 8192), tc::desc_mnmajor(base + oTm + kk * 2048, 8192),
+      tc::umma_bf16(tmem + cR, tc::desc_mnmajor(dbase + oDF + kk * 2048, 8192), tc::desc_mnmajor(dbase + oTm + kk * 2048, 8192),
                     idesc, kk > 0);
     tc::umma_commit(barM);
   }
 
   // ---- 2. while that runs: the gate, its cumulative sum over the tokens, the operands gated in place
-  ok = tc::mbar_wait(barA, 0) && ok;
+  ok = tc::mbar_wait(barA, ld_phase) && ok;
   float G[16];
+  uint32_t zraw[8];  // raw gate + bias of the 16 tokens, kept (as bf16 pairs) for the gate's backward
   {
     const float ea2 = ea * kLog2e;
     float run = 0.f;
 #pragma unroll
-    for (int t = 0; t < 16; ++t) {
-      const float raw = to_f(*reinterpret_cast<const bf16*>(tiles + oG + sw128_offset(j0 + t, c, 8192)));
-      run += -ea2 * softplus_fast(raw + bias);
+    for (int t = 0; t < 16; t += 2) {
+      const float r0 = lds_bf16(sa[t & 7] + oG + 128 * t);
+      const float r1 = lds_bf16(sa[(t + 1) & 7] + oG + 128 * (t + 1));
+      zraw[t >> 1] = pack_bf16(r0, r1);
+      run += -ea2 * softplus_fast(r0 + bias);
       G[t] = run;
+      run += -ea2 * softplus_fast(r1 + bias);
+      G[t + 1] = run;
     }
     sX1[sl * kD + c] = run;
   }
@@ -205,35 +307,71 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
 #pragma unroll
     for (int s = 0; s < 3; ++s) pre += (s < sl) ? sX1[s * kD + c] : 0.f;
 #pragma unroll
-    for (int t = 0; t < 16; ++t) {
-      G[t] += pre;
-      const float e = ex2(G[t]), ei = __fdividef(1.f, e);
-      const uint32_t off = sw128_offset(j0 + t, c, 8192);
-      bf16* xq = reinterpret_cast<bf16*>(tiles + oQ + off);
-      bf16* xk = reinterpret_cast<bf16*>(tiles + oK + off);
-      bf16* y = reinterpret_cast<bf16*>(tiles + oKt + off);
-      *xq = __float2bfloat16(to_f(*xq) * e);
-      *xk = __float2bfloat16(to_f(*xk) * e);
-      *y = __float2bfloat16(to_f(*y) * ei);
-    }
+    for (int t = 0; t < 16; ++t) G[t] += pre;
   }
-  // the state-coupled products that need nothing but landed tiles; sum_v S0 dS1 per channel
-  ok = tc::mbar_wait(barC, 0) && ok;
+  // the state-coupled products that need nothing but landed tiles
+  ok = tc::mbar_wait(barC, ld_phase) && ok;
+  ld_phase ^= 1;
   if (tid == 0) {
     tc::tc_fence_after();
     constexpr uint32_t idesc = tc::idesc_bf16(128, 64, false, false);
 #pragma unroll
     for (int kk = 0; kk < 8; ++kk) {
       const uint32_t ko = (kk >> 2) * 16384 + (kk & 3) * 32;
-      tc::umma_bf16(tmem + cQs, tc::desc_kmajor(base + oS0 + ko), tc::desc_kmajor(base + oStk + 8192 + ko), idesc, kk > 0);
+      tc::umma_bf16(tmem + cQs, tc::desc_kmajor(dbase + oS0 + ko), tc::desc_kmajor(dbase + oStk + 8192 + ko), idesc, kk > 0);
     }
 #pragma unroll
     for (int kk = 0; kk < 8; ++kk) {
       const uint32_t ko = (kk >> 2) * 16384 + (kk & 3) * 32, ke = (kk >> 2) * 8192 + (kk & 3) * 32;
-      tc::umma_bf16(tmem + cKts, tc::desc_kmajor(base + oDS + ko), tc::desc_kmajor(base + oE + ke), idesc, kk > 0);
+      tc::umma_bf16(tmem + cKts, tc::desc_kmajor(dbase + oDS + ko), tc::desc_kmajor(dbase + oE + ke), idesc, kk > 0);
     }
   }
+
+  // ---- 3. dR^T -> bf16 -> rows 0..63 of the stack (it is dv as it stands)
+  ok = tc::mbar_wait(barM, m_phase) && ok;
+  m_phase ^= 1;
+  tc::tc_fence_after();
+  PKDA_PHASE(4);
   {
+    float acc[16];
+    tc::tmem_ld16(tmem + lane_addr + cR + j0, acc);
+    tc::tmem_ld_wait();
+#pragma unroll
+    for (int t = 0; t < 16; ++t) sts_bf16(sa[t & 7] + oStk + (c >> 6) * 8192 + 128 * t, acc[t]);  // K blocks 16 KB apart
+  }
+  tc::fence_proxy_async();
+  tc::tc_fence_before();
+  __syncthreads(); PKDA_PHASE(5);
+  if (tid == 0) {
+    tc::tc_fence_after();
+    tc::tma_store_3d(&maps.dv, base + oStk, 0, h, tok0);
+    tc::tma_store_3d(&maps.dv, base + oStk + 16384, 64, h, tok0);
+    tc::bulk_commit();
+    constexpr uint32_t idesc = tc::idesc_bf16(128, 64, false, false);
+    constexpr uint32_t idesc_neg = idesc | (1u << 13);  // A negated
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {  // [dR; dO] E^T
+      const uint32_t ko = (kk >> 2) * 16384 + (kk & 3) * 32, ke = (kk >> 2) * 8192 + (kk & 3) * 32;
+      tc::umma_bf16(tmem + cStk, tc::desc_kmajor(dbase + oStk + ko), tc::desc_kmajor(dbase + oE + ke), idesc, kk > 0);
+    }
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {  // -S0 dR^T
+      const uint32_t ko = (kk >> 2) * 16384 + (kk & 3) * 32;
+      tc::umma_bf16(tmem + cKs, tc::desc_kmajor(dbase + oS0 + ko), tc::desc_kmajor(dbase + oStk + ko), idesc_neg, kk > 0);
+    }
+    tc::umma_commit(barM);
+  }
+
+  // ---- 3b. while those run: the operands gated in place; sum_v S0 dS1 per channel
+  {
+#pragma unroll
+    for (int t = 0; t < 16; ++t) {
+      const float e = ex2(G[t]), ei = __fdividef(1.f, e);
+      const uint32_t a0 = sa[t & 7] + 128 * t;
+      sts_bf16(a0 + oQ, lds_bf16(a0 + oQ) * e);
+      sts_bf16(a0 + oK, lds_bf16(a0 + oK) * e);
+      sts_bf16(a0 + oKt, lds_bf16(a0 + oKt) * ei);
+    }
     // channel c's row of both state tiles, values 32 sl .. 32 sl + 31 (four 16-byte pieces of one K block)
     const unsigned char* rs = tiles + oS0 + (sl >> 1) * 16384 + c * 128;
     const unsigned char* rd = tiles + oDS + (sl >> 1) * 16384 + c * 128;
@@ -251,43 +389,6 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
       }
     }
     sX2[sl * kD + c] = acc;
-  }
-
-  // ---- 3. dR^T -> bf16 -> rows 0..63 of the stack (it is dv as it stands)
-  ok = tc::mbar_wait(barM, m_phase) && ok;
-  m_phase ^= 1;
-  tc::tc_fence_after();
-  PKDA_PHASE(4);
-  {
-    float acc[16];
-    tc::tmem_ld16(tmem + lane_addr + cR + j0, acc);
-    tc::tmem_ld_wait();
-#pragma unroll
-    for (int t = 0; t < 16; ++t)
-      *reinterpret_cast<bf16*>(tiles + oStk + (c >> 6) * 16384 + (j0 + t) * 128 + ((((c & 63) >> 3) ^ ((j0 + t) & 7)) << 4) +
-                               (c & 7) * 2) = __float2bfloat16(acc[t]);
-  }
-  tc::fence_proxy_async();
-  tc::tc_fence_before();
-  __syncthreads(); PKDA_PHASE(5);
-  if (tid == 0) {
-    tc::tc_fence_after();
-    tc::tma_store_3d(&maps.dv, base + oStk, 0, h, tok0);
-    tc::tma_store_3d(&maps.dv, base + oStk + 16384, 64, h, tok0);
-    tc::bulk_commit();
-    constexpr uint32_t idesc = tc::idesc_bf16(128, 64, false, false);
-    constexpr uint32_t idesc_neg = idesc | (1u << 13);  // A negated
-#pragma unroll
-    for (int kk = 0; kk < 8; ++kk) {  // [dR; dO] E^T
-      const uint32_t ko = (kk >> 2) * 16384 + (kk & 3) * 32, ke = (kk >> 2) * 8192 + (kk & 3) * 32;
-      tc::umma_bf16(tmem + cStk, tc::desc_kmajor(base + oStk + ko), tc::desc_kmajor(base + oE + ke), idesc, kk > 0);
-    }
-#pragma unroll
-    for (int kk = 0; kk < 8; ++kk) {  // -S0 dR^T
-      const uint32_t ko = (kk >> 2) * 16384 + (kk & 3) * 32;
-      tc::umma_bf16(tmem + cKs, tc::desc_kmajor(base + oS0 + ko), tc::desc_kmajor(base + oStk + ko), idesc_neg, kk > 0);
-    }
-    tc::umma_commit(barM);
   }
 
   // ---- 4. pair-weight gradients: row i of dM = -tril(dR E^T, -1) diag(beta), of dP = scale tril(dO E^T) diag(beta)
@@ -323,85 +424,119 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
     constexpr uint32_t idesc_m = tc::idesc_bf16(128, 64, true, true);   // B = pair gradient read as [j][i], K = i
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) {
-      const uint64_t ay = tc::desc_mnmajor(base + oKt + kk * 2048, 8192);
-      tc::umma_bf16(tmem + cR, ay, tc::desc_kmajor(base + oDP + kk * 32), idesc_k, kk > 0);    // Qp = Y^T dP^T
-      tc::umma_bf16(tmem + cStk, ay, tc::desc_kmajor(base + oDM + kk * 32), idesc_k, kk > 0);  // Kp = Y^T dM^T
+      const uint64_t ay = tc::desc_mnmajor(dbase + oKt + kk * 2048, 8192);
+      tc::umma_bf16(tmem + cR, ay, tc::desc_kmajor(dbase + oDP + kk * 32), idesc_k, kk > 0);    // Qp = Y^T dP^T
+      tc::umma_bf16(tmem + cStk, ay, tc::desc_kmajor(dbase + oDM + kk * 32), idesc_k, kk > 0);  // Kp = Y^T dM^T
     }
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) {
-      tc::umma_bf16(tmem + cKtM, tc::desc_mnmajor(base + oK + kk * 2048, 8192), tc::desc_mnmajor(base + oDM + kk * 2048, 8192),
+      tc::umma_bf16(tmem + cKtM, tc::desc_mnmajor(dbase + oK + kk * 2048, 8192), tc::desc_mnmajor(dbase + oDM + kk * 2048, 8192),
                     idesc_m, kk > 0);  // Xk^T dM
-      tc::umma_bf16(tmem + cKtP, tc::desc_mnmajor(base + oQ + kk * 2048, 8192), tc::desc_mnmajor(base + oDP + kk * 2048, 8192),
+      tc::umma_bf16(tmem + cKtP, tc::desc_mnmajor(dbase + oQ + kk * 2048, 8192), tc::desc_mnmajor(dbase + oDP + kk * 2048, 8192),
                     idesc_m, kk > 0);  // Xq^T dP
     }
     tc::umma_commit(barM);
   }
   ok = tc::mbar_wait(barM, m_phase) && ok;
+  m_phase ^= 1;
   tc::tc_fence_after();
   PKDA_PHASE(8);
 
   // ---- 5. gradients of this thread's channel and 16 tokens
-  const size_t gld = (size_t)H * kD;
   const size_t out0 = ((size_t)(tok0 + j0) * H + h) * kD + c;  // element (first token of the slice, h, c)
-  float dGv[16], dbv[16], kdsum = 0.f;
+  float dGv[16], kdsum = 0.f;
   {
-    float a[16], b[16];
-    tc::tmem_ld16(tmem + lane_addr + cQs + j0, a);
-    tc::tmem_ld16(tmem + lane_addr + cR + j0, b);
-    tc::tmem_ld_wait();
+    // eight tokens at a time: the accumulator pieces stay small next to the per-token state
+    bf16* pq = p.dq + out0;  // walked row by row (running pointers keep the row offsets out of registers)
+    float* pk = p.dk_read + out0;
+    float* pkt = p.dkt + out0;
 #pragma unroll
-    for (int t = 0; t < 16; ++t) {
-      const float tot = p.scale * a[t] + b[t];
-      const float xq = to_f(*reinterpret_cast<const bf16*>(tiles + oQ + sw128_offset(j0 + t, c, 8192)));
-      p.dq[out0 + t * gld] = __float2bfloat16(ex2(G[t]) * tot);
-      dGv[t] = xq * tot;
-    }
-    tc::tmem_ld16(tmem + lane_addr + cKs + j0, a);
-    tc::tmem_ld16(tmem + lane_addr + cStk + j0, b);
-    tc::tmem_ld_wait();
+    for (int hh = 0; hh < 2; ++hh) {
+      const uint32_t ta = tmem + lane_addr + j0 + 8 * hh;
+      float a[8], b[8];
+      tc::tmem_ld8(ta + cQs, a);
+      tc::tmem_ld8(ta + cR, b);
+      tc::tmem_ld_wait();
 #pragma unroll
-    for (int t = 0; t < 16; ++t) {
-      const float tot = a[t] + b[t];
-      const float xk = to_f(*reinterpret_cast<const bf16*>(tiles + oK + sw128_offset(j0 + t, c, 8192)));
-      p.dk_read[out0 + t * gld] = ex2(G[t]) * tot;
-      dGv[t] += xk * tot;
-    }
-    float m[16];
-    tc::tmem_ld16(tmem + lane_addr + cKts + j0, a);
-    tc::tmem_ld16(tmem + lane_addr + cKtM + j0, m);
-    tc::tmem_ld16(tmem + lane_addr + cKtP + j0, b);
-    tc::tmem_ld_wait();
+      for (int u = 0; u < 8; ++u) {
+        const int t = 8 * hh + u;
+        const float tot = p.scale * a[u] + b[u];
+        const float xq = lds_bf16(sa[t & 7] + oQ + 128 * t);
+        *pq = __float2bfloat16(ex2(G[t]) * tot);
+        pq += gld;
+        dGv[t] = xq * tot;
+      }
+      tc::tmem_ld8(ta + cKs, a);
+      tc::tmem_ld8(ta + cStk, b);
+      tc::tmem_ld_wait();
 #pragma unroll
-    for (int t = 0; t < 16; ++t) {
-      const float bj = sBeta[j0 + t];
-      const uint32_t off = sw128_offset(j0 + t, c, 8192);
-      const float y = to_f(*reinterpret_cast<const bf16*>(tiles + oKt + off));
-      const float st = gl * bj * a[t], pr = m[t] + b[t];
-      p.dkt[out0 + t * gld] = ex2(-G[t]) * (st + pr);
-      const float kd = y * st;
-      dGv[t] -= y * pr + kd;
-      kdsum += kd;
-      const float df = to_f(*reinterpret_cast<const bf16*>(tiles + oDF + off));
-      const float ev = to_f(*reinterpret_cast<const bf16*>(tiles + oE + off));
-      dbv[t] = df * ev + (bj != 0.f ? __fdividef(y * m[t], bj) : 0.f);
+      for (int u = 0; u < 8; ++u) {
+        const int t = 8 * hh + u;
+        const float tot = a[u] + b[u];
+        const float xk = lds_bf16(sa[t & 7] + oK + 128 * t);
+        *pk = ex2(G[t]) * tot;
+        pk += gld;
+        dGv[t] += xk * tot;
+      }
     }
-  }
-  tc::tc_fence_before();
-  float* sX3 = reinterpret_cast<float*>(tiles + oX3);
-  float* sX4 = reinterpret_cast<float*>(tiles + oX4);
-  float* sX5 = reinterpret_cast<float*>(tiles + oX5);
-  float* sDb = reinterpret_cast<float*>(tiles + oDb);
-  {
+    // write-key gradient: first the part of dbeta that flows through M (rows of KtM against Y)
+    {
+      float dbv[16];
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        float a[8];
+        tc::tmem_ld8(tmem + lane_addr + j0 + 8 * hh + cKtM, a);
+        tc::tmem_ld_wait();
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int t = 8 * hh + u;
+          const float bj = sBeta[j0 + t];
+          const float y = lds_bf16(sa[t & 7] + oKt + 128 * t);
+          const float df = lds_bf16(sa[t & 7] + oDF + 128 * t);
+          const float ev = lds_bf16(sa[t & 7] + oE + 128 * t);
+          dbv[t] = df * ev + (bj != 0.f ? __fdividef(y * a[u], bj) : 0.f);
+        }
+      }
+      row_sums16(dbv, lane);
+      if ((lane & 1) == 0)
+        sDb[q4 * kChunk + j0 + ((lane >> 4) & 1) * 8 + ((lane >> 3) & 1) * 4 + ((lane >> 2) & 1) * 2 + ((lane >> 1) & 1)] = dbv[0];
+    }
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      const uint32_t ta = tmem + lane_addr + j0 + 8 * hh;
+      float a[8], b[8], m[8];
+      tc::tmem_ld8(ta + cKtM, m);
+      tc::tmem_ld8(ta + cKtP, b);
+      tc::tmem_ld8(ta + cKts, a);
+      tc::tmem_ld_wait();
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int t = 8 * hh + u;
+        const float y = lds_bf16(sa[t & 7] + oKt + 128 * t);
+        const float st = gl * sBeta[j0 + t] * a[u], pr = m[u] + b[u];
+        *pkt = ex2(-G[t]) * (st + pr);
+        pkt += gld;
+        const float kd = y * st;
+        dGv[t] -= y * pr + kd;
+        kdsum += kd;
+      }
+    }
     float tot = 0.f;
 #pragma unroll
     for (int t = 0; t < 16; ++t) tot += dGv[t];
     sX3[sl * kD + c] = tot;     // the pair-gradient tiles are dead: every product has finished
     sX4[sl * kD + c] = kdsum;
-    row_sums16(dbv, lane);
-    if ((lane & 1) == 0)
-      sDb[q4 * kChunk + j0 + ((lane >> 4) & 1) * 8 + ((lane >> 3) & 1) * 4 + ((lane >> 2) & 1) * 2 + ((lane >> 1) & 1)] = dbv[0];
   }
+  tc::tc_fence_before();
+  tc::fence_proxy_async();  // this item's last reads of the operand tiles come before the next item's copies
+  if (tid == 0 && item + (int)gridDim.x < n_items) arm();
   __syncthreads(); PKDA_PHASE(9);
+  // every tile except the stack rows the dv store is reading is free: the next item's tiles start to
+  // arrive while the gate's backward runs
+  if (item + (int)gridDim.x < n_items) {
+    request(item + gridDim.x);
+    fetch_scalars(item + gridDim.x);
+  }
   // reverse cumulative sum over the tokens (the chunk's last row also takes the decay-total terms),
   // then the gate's own backward:  g = -exp(A_log) softplus(raw + bias)
   {
@@ -410,18 +545,20 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
 #pragma unroll
     for (int s = 1; s < 4; ++s) run += (s > sl) ? sX3[s * kD + c] : 0.f;
     float pa = 0.f, pb = 0.f;
+    bf16* pg = p.dg + out0 + 15 * gld;
 #pragma unroll
     for (int t = 15; t >= 0; --t) {
       run += dGv[t];
-      const float raw = to_f(*reinterpret_cast<const bf16*>(tiles + oG + sw128_offset(j0 + t, c, 8192)));
-      const float z = raw + bias;
+      const float2 zz = unpack_bf16(zraw[t >> 1]);
+      const float z = ((t & 1) ? zz.y : zz.x) + bias;
       const float e0 = __expf(-fabsf(z)), i0 = __fdividef(1.f, 1.f + e0);
       const float sg = z >= 0.f ? i0 : e0 * i0;
       const float sp = fmaxf(z, 0.f) - __logf(i0);
       const float dr = run * (-ea) * sg;
       pa += run * (-ea * sp);
       pb += dr;
-      p.dg[out0 + t * gld] = __float2bfloat16(dr);
+      *pg = __float2bfloat16(dr);
+      pg -= gld;
     }
     sX5[sl * kD + c] = pb;
 #pragma unroll
@@ -431,19 +568,22 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
   if (tid < kChunk)
     p.dbeta[(size_t)(tok0 + tid) * H + h] =
         __float2bfloat16(sDb[tid] + sDb[kChunk + tid] + sDb[2 * kChunk + tid] + sDb[3 * kChunk + tid]);
-  const bool all_ok = !__syncthreads_or(!ok);
-  PKDA_PHASE(10);
-  if (tid < kD) p.partB[chh * kD + tid] = sX5[tid] + sX5[kD + tid] + sX5[2 * kD + tid] + sX5[3 * kD + tid];
+  __syncthreads(); PKDA_PHASE(10);
+  if (tid < kD) p.partB[(size_t)chh * kD + tid] = sX5[tid] + sX5[kD + tid] + sX5[2 * kD + tid] + sX5[3 * kD + tid];
   if (tid == 0) {
     float acc = 0.f;
 #pragma unroll
     for (int w = 0; w < kThreads / 32; ++w) acc += sRed[w];
     p.partA[chh] = acc;
-    if (!all_ok) atomicExch(p.status, 1);
-    tc::bulk_wait_read();  // the dv store has read the stack
+    tc::bulk_wait_read();  // the dv store has read the stack rows the next item's dR overwrites
   }
-  if (warp == 1) tc::tmem_dealloc(tmem, kCols);
+  __syncthreads();  // the exchange arrays and beta are rewritten by the next item
   PKDA_PHASE(11);
+  }  // item loop
+  if (__syncthreads_or(!ok) && tid == 0) atomicExch(p.status, 1);
+  tc::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tc::tmem_dealloc(tmem, kCols);
 }
 
 // ------------------------------------------------------------------ host side
@@ -473,7 +613,17 @@ int launch_intra_bwd_tc(const IntraBwdParams& ip, cudaStream_t st) {
   if (cudaFuncSetAttribute(pkda_intra_bwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ibtc::kSmem) !=
       cudaSuccess)
     return PKDA_ERR_LAUNCH;
-  pkda_intra_bwd_tc_kernel<<<dim3(ip.geo.total_chunks, ip.geo.heads), ibtc::kThreads, ibtc::kSmem, st>>>(ip, maps);
+  const int items = ip.geo.total_chunks * ip.geo.heads;
+  begin_stage(kStageBwdClassify, st);
+  pkda_bwd_classify_kernel<<<(items + 63) / 64, 256, 0, st>>>(ip.geo, ip.gc, ip.direct_cap, ip.fast_list, ip.slow_list,
+                                                             ip.fast_count);
+  end_stage(st);
+  if (cudaGetLastError() != cudaSuccess) return PKDA_ERR_LAUNCH;
+  begin_stage(kStageIntraBwd, st);
+  int sms = 148, dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  pkda_intra_bwd_tc_kernel<<<items < sms ? items : sms, ibtc::kThreads, ibtc::kSmem, st>>>(ip, maps);
+  end_stage(st);
   return cudaGetLastError() == cudaSuccess ? PKDA_OK : PKDA_ERR_LAUNCH;
 }
 

@@ -512,7 +512,9 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
                           "layer_ops": run_layer_ops(device, B, T, H, D, args.steps, args.warmup, pk)}), flush=True)
         return
 
-    d = make_inputs(B, T, H, D, seed=1000 + rank, dist="unit", dtype=torch.bfloat16, with_state=True)
+    for stage in filter(None, args.legacy.split(",")):
+        _lib.set_variant(stage, True)
+    d = make_inputs(B, T, H, D, seed=1000 + rank, dist=args.dist, dtype=torch.bfloat16, with_state=True)
     host = {n: d[n].pin_memory() for n in (*INPUT_NAMES, "do", "initial_state", "initial_A_state")}
     dev = {n: t.to(device) for n, t in host.items()}
     lean = bool(args.lean)
@@ -624,7 +626,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
             dist.destroy_process_group()
         if rank == 0:
             print(json.dumps({"note": "profiling run (no e2e leg): not a benchmark line",
-                              "ms_per_step": ms_per_step,
+                              "ms_per_step": ms_per_step, "distribution": args.dist, "legacy_stages": args.legacy,
                               "stages_ms_per_step": {n: ms / args.steps for n, (ms, _) in stages.items()}}))
         return
     # The public call for host-resident data: HostStep streams row slices so that the copy in, the
@@ -693,6 +695,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         "config": {
             "workload": f"{args.workload}: B={B}/GPU T={T} H={H} d_k=d_v={D} chunk=64 bf16 fwd+bwd, "
                         "fp32 initial state, ten input gradients + initial-state gradients",
+            "distribution": args.dist, "legacy_stages": args.legacy,
             "saving": "lean (recompute)" if lean else "full (retained intermediates)",
             "l2": "no flush: each of q,k,v,g,dO is larger than the 126 MB L2",
             "parallelism": f"{world} independent replica shard(s) by row x head, no collective",
@@ -738,6 +741,10 @@ def main() -> None:
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--workload", choices=tuple(WORKLOADS), default="config1")
     ap.add_argument("--lean", type=int, default=0, help="1: recompute w,kg,v_new,h,qg in backward")
+    ap.add_argument("--dist", choices=("unit", "production"), default="unit",
+                    help="input distribution: the benchmark configurations' (unit) or the strong per-channel decay "
+                         "of the reference's own operator benchmark (production)")
+    ap.add_argument("--legacy", default="", help="comma-separated stages pinned to their mma.sync kernels (A/B runs)")
     ap.add_argument("--decode-steps", type=int, default=1024)
     ap.add_argument("--e2e-slices", type=int, default=8, help="row slices of the host-memory step")
     ap.add_argument("--no-decode", action="store_true")

@@ -250,7 +250,7 @@ const char* pkda_stage_name(int stage) {
                                 "out_fwd", "scan_bwd", "intra_bwd", "atk_bwd_local", "atk_bwd_carry",
                                 "atk_bwd_final", "param_reduce", "recurrent", "qkv_conv_fwd", "qkv_conv_bwd",
                                 "qkv_conv_dw", "norm_gate_fwd", "norm_gate_bwd", "norm_gate_dw", "decode_step", "controls_fwd", "controls_bwd", "pack_control",
-                                "status_guard", "bwd_classify", "intra_bwd_rest"};
+                                "status_guard", "bwd_classify", "intra_bwd_rest", "intra_fwd_rest"};
   return (stage >= 0 && stage < pkda::kStageCount) ? names[stage] : "?";
 }
 

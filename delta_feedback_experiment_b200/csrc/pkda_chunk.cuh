@@ -374,6 +374,26 @@ __device__ __forceinline__ void row_sums8(float (&v)[8], int lane) {
   v[0] += __shfl_xor_sync(0xffffffffu, v[0], 1);
 }
 
+// Tail of the classifier kernels: a CTA of 256 threads has put the kind of its 64 items into sKind
+// (-1: none, 0: tensor-memory kernel, 1: mma.sync kernel) and appends them to the two work lists with
+// one atomic per list, keeping their order.
+__device__ __forceinline__ void append_work_items(const int* sKind, int* sBase, int* fast_list, int* slow_list,
+                                                  int* counts, int first_item, int tid) {
+  __syncthreads();
+  if (tid < 2) {
+    int cnt = 0;
+    for (int i = 0; i < 64; ++i) cnt += sKind[i] == tid;
+    sBase[tid] = cnt ? atomicAdd(counts + tid, cnt) : 0;
+  }
+  __syncthreads();
+  if (tid < 2) {
+    int* list = tid ? slow_list : fast_list;
+    int pos = sBase[tid];
+    for (int i = 0; i < 64; ++i)
+      if (sKind[i] == tid) list[pos++] = first_item + i;
+  }
+}
+
 // Arguments of the intra-chunk forward stage (both implementations).
 struct IntraParams {
   Geo geo;
@@ -389,6 +409,10 @@ struct IntraParams {
   float scale, ln_x, eps;
   int direct_cap;  // upper limit for the direct block size (64 = no limit, 1 = hierarchy only)
   int* status;     // device status word (tcgen05 kernel): set to 1 when a bounded wait gives up
+  // Work list of (chunk * heads + head) items the tensor-memory kernel leaves to the mma.sync kernel;
+  // counts[1] is its length and counts[2] the cursor the mma.sync CTAs draw items with (both zeroed
+  // before every call).  slow_list == NULL: the mma.sync kernel takes every chunk, one CTA per item.
+  int *slow_list, *counts;
 };
 
 // tcgen05 / tensor-memory intra-chunk forward stage (pkda_intra_fwd_tc.cu).
@@ -411,8 +435,8 @@ struct IntraBwdParams {
   int* status;   // set to 1 if a bounded wait gives up
   // Work lists of (chunk * heads + head) items written by pkda_bwd_classify_kernel: fast_list for the
   // tensor-memory kernel, slow_list for the mma.sync kernel; fast_count[0] / fast_count[1] are their
-  // lengths (zeroed before every call).  slow_list == NULL: the mma.sync kernel takes every chunk,
-  // one CTA per (chunk, head).
+  // lengths and fast_count[2] the cursor the mma.sync CTAs draw items with (all zeroed before every
+  // call).  slow_list == NULL: the mma.sync kernel takes every chunk, one CTA per (chunk, head).
   int *fast_list, *slow_list, *fast_count;
 };
 
@@ -436,8 +460,10 @@ int launch_scan_bwd_tc(const Geo& geo, int total_tokens, int units, const bf16* 
 // Host-side pieces defined in pkda_chunk_fwd.cu and reused by the backward.
 int check_chunk_problem(const pkda_problem& p);
 int run_prologue(const pkda_problem& p, int* chunk_offsets, float* beta_c, Geo* geo, cudaStream_t st);
+// lists: room for chunks * heads ints (the forward's work list); counts: three zeroed ints.
 int run_forward_stages(const pkda_problem& p, const Geo& geo, const float* beta_c, bf16* u_ws, bf16* Aqk,
                        bf16* Akk, bf16* kt, float* gc, const float* a_start, bf16* w, bf16* kg, bf16* v_new,
-                       bf16* h, bf16* qg, float* ST, bool recompute, int* status, cudaStream_t st);
+                       bf16* h, bf16* qg, float* ST, bool recompute, int* status, int* lists, int* counts,
+                       cudaStream_t st);
 
 }  // namespace pkda

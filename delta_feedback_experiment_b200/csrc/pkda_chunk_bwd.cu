@@ -767,11 +767,17 @@ pkda_intra_bwd_kernel(const IntraBwdParams p, const __grid_constant__ IntraBwdMa
     intra_bwd_item(p, maps, blockIdx.x, blockIdx.y);
     return;
   }
+  // items differ in cost (the number of pairing levels follows the decay): CTAs draw them one at a time
+  __shared__ int s_item;
   const int n_items = p.fast_count[1], H = p.geo.heads;
-  for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+  for (;;) {
+    if (threadIdx.x == 0) s_item = atomicAdd(p.fast_count + 2, 1);
+    __syncthreads();
+    const int item = s_item;
+    if (item >= n_items) break;
     const int chh = p.slow_list[item];
     intra_bwd_item(p, maps, chh / H, chh % H);
-    __syncthreads();  // the next item reuses every shared-memory region
+    __syncthreads();  // the next item reuses every shared-memory region (and s_item)
   }
 }
 
@@ -1140,6 +1146,7 @@ struct BwdWorkspace {
   bf16 *u, *dF, *dh;
   float *dk_read, *dkt, *partA, *partB, *partC, *c_loc, *lam_in;
   int *fast_list, *slow_list, *counts;
+  int *fwd_lists, *fwd_counts;  // work lists of the recompute pass (lean backward)
   int* status;
   size_t bytes;
 };
@@ -1168,8 +1175,10 @@ static BwdWorkspace carve_bwd(const pkda_problem& p, void* base) {
   w.lam_in = static_cast<float*>(take(chunks * H * kD * 4));
   w.fast_list = static_cast<int*>(take(chunks * H * sizeof(int)));
   w.slow_list = static_cast<int*>(take(chunks * H * sizeof(int)));
-  w.status = static_cast<int*>(take(4 * sizeof(int)));  // status word, then the two work-list lengths
-  w.counts = w.status + 1;
+  w.fwd_lists = static_cast<int*>(take(chunks * H * sizeof(int)));
+  w.status = static_cast<int*>(take(16 * sizeof(int)));  // status word, then lengths and cursors of the work lists
+  w.counts = w.status + 1;       // [0] fast, [1] slow, [2] cursor
+  w.fwd_counts = w.status + 5;   // [1] slow, [2] cursor
   w.bytes = off;
   return w;
 }
@@ -1221,12 +1230,12 @@ int chunk_bwd(const pkda_chunk_bwd_args* a, cudaStream_t st) {
   bf16* v_new = static_cast<bf16*>(a->v_new);
   bf16* h = static_cast<bf16*>(a->h);
   bf16* qg = static_cast<bf16*>(a->qg);
-  if (cudaMemsetAsync(ws.status, 0, 4 * sizeof(int), st) != cudaSuccess) return PKDA_ERR_LAUNCH;
+  if (cudaMemsetAsync(ws.status, 0, 16 * sizeof(int), st) != cudaSuccess) return PKDA_ERR_LAUNCH;
   if (a->recompute) {
     // The recompute kernels only read the products, write keys and decay totals.
     rc = run_forward_stages(p, geo, ws.beta_c, ws.u, const_cast<bf16*>(Aqk), const_cast<bf16*>(Akk),
                             const_cast<bf16*>(kt), const_cast<float*>(gc), a->a_atk, w, kg, v_new, h, qg,
-                            nullptr, true, ws.status, st);
+                            nullptr, true, ws.status, ws.fwd_lists, ws.fwd_counts, st);
     if (rc != PKDA_OK) return rc;
   }
 

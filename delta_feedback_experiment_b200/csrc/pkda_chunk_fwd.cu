@@ -162,9 +162,9 @@ __device__ __forceinline__ void for_tile(const float (&t)[2][4], int i0, int j0,
 
 // kRecompute: rebuild w,u,kg,qg only (backward's lean mode); the products, the
 // write keys and the decay totals already exist and are left untouched.
+// One (chunk bx, head by) item; every thread of the CTA takes part.
 template <bool kRecompute>
-__global__ void __launch_bounds__(intra::kThreads, 1)
-pkda_intra_fwd_kernel(const IntraParams p) {
+__device__ __forceinline__ void intra_fwd_item(const IntraParams& p, int bx, int by) {
   using namespace intra;
   extern __shared__ __align__(128) unsigned char smem[];
   PKDA_PHASE(0);
@@ -187,11 +187,11 @@ pkda_intra_fwd_kernel(const IntraParams p) {
   float* sY2 = reinterpret_cast<float*>(smem + oY2);
 
   int n, tok0, valid;
-  if (!chunk_lookup(p.geo, blockIdx.x, n, tok0, valid)) return;
-  const int h = blockIdx.y, H = p.geo.heads;
+  if (!chunk_lookup(p.geo, bx, n, tok0, valid)) return;
+  const int h = by, H = p.geo.heads;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int gq = lane >> 2, tq = lane & 3;
-  const size_t chh = (size_t)blockIdx.x * H + h;
+  const size_t chh = (size_t)bx * H + h;
   const size_t row0 = ((size_t)tok0 * H + h) * kD;  // element offset of (tok0, h, 0)
   const long gld = (long)H * kD;
 
@@ -446,6 +446,28 @@ pkda_intra_fwd_kernel(const IntraParams p) {
   PKDA_PHASE(11);
 }
 
+// grid (chunks, heads): one item per CTA; or, with a work list, a few persistent CTAs that walk it.
+template <bool kRecompute>
+__global__ void __launch_bounds__(intra::kThreads, 1)
+pkda_intra_fwd_kernel(const IntraParams p) {
+  if (!p.slow_list) {
+    intra_fwd_item<kRecompute>(p, blockIdx.x, blockIdx.y);
+    return;
+  }
+  // items differ in cost (the number of pairing levels follows the decay): CTAs draw them one at a time
+  __shared__ int s_item;
+  const int n_items = p.counts[1], H = p.geo.heads;
+  for (;;) {
+    if (threadIdx.x == 0) s_item = atomicAdd(p.counts + 2, 1);
+    __syncthreads();
+    const int item = s_item;
+    if (item >= n_items) break;
+    const int chh = p.slow_list[item];
+    intra_fwd_item<kRecompute>(p, chh / H, chh % H);
+    __syncthreads();  // the next item reuses every shared-memory region (and s_item)
+  }
+}
+
 // ------------------------------------------------------------------ forward state scan
 struct ScanParams {
   Geo geo;
@@ -686,7 +708,8 @@ struct FwdWorkspace {
   int* chunk_offsets;
   float* beta_c;
   bf16* u;
-  int* status;  // device status word: 0 = ok, 1 = a bounded wait in a kernel gave up
+  int* lists;   // work list of the intra-chunk stage (chunks * heads ints)
+  int* status;  // device status word: 0 = ok, 1 = a bounded wait in a kernel gave up; then the list lengths
   size_t bytes;
 };
 
@@ -701,8 +724,10 @@ static FwdWorkspace carve_fwd(const pkda_problem& p, void* base) {
   off += align_up(chunks * p.heads * kChunk * sizeof(float));
   w.u = reinterpret_cast<bf16*>(b + off);
   off += align_up((size_t)p.total_tokens * p.heads * kD * sizeof(bf16));
+  w.lists = reinterpret_cast<int*>(b + off);
+  off += align_up(chunks * p.heads * sizeof(int));
   w.status = reinterpret_cast<int*>(b + off);
-  off += align_up(sizeof(int));
+  off += align_up(8 * sizeof(int));
   w.bytes = off;
   return w;
 }
@@ -742,7 +767,7 @@ static int launch_scan_fwd(const ScanParams& sp, int units, cudaStream_t st) {
 int run_forward_stages(const pkda_problem& p, const Geo& geo, const float* beta_c, bf16* u_ws,
                        bf16* Aqk, bf16* Akk, bf16* kt, float* gc, const float* a_start,
                        bf16* w, bf16* kg, bf16* v_new, bf16* h, bf16* qg, float* ST,
-                       bool recompute, int* status, cudaStream_t st) {
+                       bool recompute, int* status, int* lists, int* counts, cudaStream_t st) {
   const int chunks = geo.total_chunks;
   IntraParams ip;
   ip.geo = geo;
@@ -756,18 +781,31 @@ int run_forward_stages(const pkda_problem& p, const Geo& geo, const float* beta_
   ip.scale = p.scale; ip.ln_x = logf(p.squash_x); ip.eps = p.squash_eps;
   ip.direct_cap = direct_block_cap();
   ip.status = status;
+  ip.slow_list = ip.counts = nullptr;
   dim3 gridc(chunks, p.heads);
-  if (status && stage_variant(kStageIntraFwd) == 0) {  // tcgen05 / tensor-memory kernel (default)
+  // Chunks that are one direct block run on tcgen05 / tensor memory; that kernel lists the others and
+  // the mma.sync kernel works the list off (it takes every chunk, one CTA each, when it is pinned or the
+  // direct block is capped).  The recompute pass of a lean backward decides the same way, from the same
+  // inputs, so that every chunk is rebuilt by the kernel that built it.
+  if (status && lists && stage_variant(kStageIntraFwd) == 0 && ip.direct_cap >= 64) {
+    const int items = chunks * p.heads;
+    ip.slow_list = lists; ip.counts = counts;
     begin_stage(kStageIntraFwd, st);
     const int rc_tc = launch_intra_fwd_tc(ip, recompute, st);
+    end_stage(st);
     if (rc_tc != PKDA_OK) return rc_tc;
-  } else if (recompute) {
+    int sms = 148, dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    gridc = dim3(items < sms ? items : sms, 1);
+  }
+  const int rest_stage = ip.slow_list ? kStageIntraFwdRest : kStageIntraFwd;
+  if (recompute) {
     if (!set_smem(pkda_intra_fwd_kernel<true>, intra::kSmem)) return PKDA_ERR_LAUNCH;
-    begin_stage(kStageIntraFwd, st);
+    begin_stage(rest_stage, st);
     pkda_intra_fwd_kernel<true><<<gridc, intra::kThreads, intra::kSmem, st>>>(ip);
   } else {
     if (!set_smem(pkda_intra_fwd_kernel<false>, intra::kSmem)) return PKDA_ERR_LAUNCH;
-    begin_stage(kStageIntraFwd, st);
+    begin_stage(rest_stage, st);
     pkda_intra_fwd_kernel<false><<<gridc, intra::kThreads, intra::kSmem, st>>>(ip);
   }
   PKDA_CHECK_LAUNCH();
@@ -835,11 +873,11 @@ int chunk_fwd(const pkda_chunk_fwd_args* a, cudaStream_t st) {
                                                                a->a_atk, a->final_A_state);
   PKDA_CHECK_LAUNCH();
 
-  if (cudaMemsetAsync(ws.status, 0, sizeof(int), st) != cudaSuccess) return PKDA_ERR_LAUNCH;
+  if (cudaMemsetAsync(ws.status, 0, 8 * sizeof(int), st) != cudaSuccess) return PKDA_ERR_LAUNCH;
   rc = run_forward_stages(p, geo, ws.beta_c, ws.u, static_cast<bf16*>(a->Aqk), static_cast<bf16*>(a->Akk),
                           static_cast<bf16*>(a->k_precond), a->ac_atk, a->a_atk, static_cast<bf16*>(a->w),
                           static_cast<bf16*>(a->kg), static_cast<bf16*>(a->v_new), static_cast<bf16*>(a->h),
-                          static_cast<bf16*>(a->qg), a->final_state, false, ws.status, st);
+                          static_cast<bf16*>(a->qg), a->final_state, false, ws.status, ws.lists, ws.status + 1, st);
   if (rc != PKDA_OK) return rc;
 
   // Output stage: tcgen05 + TMA unless the mma.sync kernel is pinned (pkda_set_variant).

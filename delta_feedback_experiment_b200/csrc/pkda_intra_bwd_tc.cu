@@ -136,19 +136,7 @@ pkda_bwd_classify_kernel(Geo geo, const float* gc, int direct_cap, int* fast_lis
     }
     if (lane == 0) sKind[local] = kind;
   }
-  __syncthreads();
-  if (tid < 2) {
-    int cnt = 0;
-    for (int i = 0; i < 64; ++i) cnt += sKind[i] == tid;
-    sBase[tid] = cnt ? atomicAdd(counts + tid, cnt) : 0;
-  }
-  __syncthreads();
-  if (tid < 2) {
-    int* list = tid ? slow_list : fast_list;
-    int pos = sBase[tid];
-    for (int i = 0; i < 64; ++i)
-      if (sKind[i] == tid) list[pos++] = blockIdx.x * 64 + i;
-  }
+  append_work_items(sKind, sBase, fast_list, slow_list, counts, blockIdx.x * 64, tid);
 }
 
 __global__ void __launch_bounds__(ibtc::kThreads, 1)

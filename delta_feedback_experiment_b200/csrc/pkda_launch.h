@@ -14,7 +14,7 @@ enum Stage {
   kStageOutFwd, kStageScanBwd, kStageIntraBwd, kStageAtkBwdLocal, kStageAtkBwdCarry, kStageAtkBwdFinal,
   kStageParamReduce, kStageRecurrent, kStageConvFwd, kStageConvBwd, kStageConvDw, kStageNormGateFwd,
   kStageNormGateBwd, kStageNormGateDw, kStageDecodeStep, kStageControlsFwd, kStageControlsBwd,
-  kStagePackControl, kStageStatusGuard, kStageBwdClassify, kStageIntraBwdRest, kStageCount
+  kStagePackControl, kStageStatusGuard, kStageBwdClassify, kStageIntraBwdRest, kStageIntraFwdRest, kStageCount
 };
 
 // begin_stage / end_stage bracket every kernel launch: they count launches and,

@@ -26,7 +26,12 @@ constexpr int kLdG = kD + 8;                  // smem row stride of a [64][128] 
 // picks the largest b whose worst block decay is below kDirectLimit (log2 units)
 // and covers the remaining pairs with hierarchy levels >= b.  lvl == 0 denotes the
 // direct level everywhere below.
-constexpr float kDirectLimit = 104.f;
+// With the limit at 112 the column operand kt 2^112 (|kt| <= 1.5 |k|) and the fp32 sums of up to 128
+// masked products of that size stay below 2^127, and the row operand k 2^-112 only loses (to the
+// flush of denormals) channels with |k| < 2^-14, whose products are below the bf16 rounding of the
+// others; chunks of the benchmark's gate distribution (about 75 +- 6 log2 units of decay per 64
+// tokens) then practically always form one block.
+constexpr float kDirectLimit = 112.f;
 
 __device__ __forceinline__ bool pair_ok(int i, int j, int lvl, int b) {
   if (lvl) return level_pair_ok(i, j, lvl);
@@ -410,8 +415,8 @@ struct IntraParams {
   int direct_cap;  // upper limit for the direct block size (64 = no limit, 1 = hierarchy only)
   int* status;     // device status word (tcgen05 kernel): set to 1 when a bounded wait gives up
   // Work list of (chunk * heads + head) items the tensor-memory kernel leaves to the mma.sync kernel;
-  // counts[1] is its length and counts[2] the cursor the mma.sync CTAs draw items with (both zeroed
-  // before every call).  slow_list == NULL: the mma.sync kernel takes every chunk, one CTA per item.
+  // counts[1] is its length, counts[0] and counts[2] the cursors the CTAs of the two kernels draw their
+  // items with (all zeroed before every call).  slow_list == NULL: the mma.sync kernel takes every chunk, one CTA per item.
   int *slow_list, *counts;
 };
 
@@ -433,6 +438,16 @@ struct IntraBwdParams {
   int use_tma;   // the five phase-A tiles of full chunks arrive by TMA (tensor maps valid)
   int out_tma;   // dq, dv, dk_read and dkt of full chunks leave by TMA from padded shared-memory tiles
   int* status;   // set to 1 if a bounded wait gives up
+  // The local part of the preconditioner's backward runs inside the tensor-memory kernel (the mma.sync
+  // kernel leaves it to pkda_atk_bwd_kernel<false>): with B the write-key factor kt = k B(A_t),
+  //   dkt buffer <- dA_local = d(loss)/dA_t through B alone,  dk_read buffer <- dk_read + dkt B,
+  //   c_loc[chunk] = sum_r (prod_{j<=r} decay_j) dA_local_r,  partC[chunk] = d(loss)/d(centre).
+  const float* g_atk;
+  const bf16* beta_atk;
+  const float* log_atk_scale;
+  const float* a_start;
+  float *c_loc, *partC;
+  float ln_x, eps;
   // Work lists of (chunk * heads + head) items written by pkda_bwd_classify_kernel: fast_list for the
   // tensor-memory kernel, slow_list for the mma.sync kernel; fast_count[0] / fast_count[1] are their
   // lengths and fast_count[2] the cursor the mma.sync CTAs draw items with (all zeroed before every

@@ -789,8 +789,8 @@ struct AtkBwdParams {
   const bf16* beta_atk;
   const float* log_atk_scale;
   const float* a_start;
-  const float* dkt;
-  const float* dk_read;
+  float* dkt;      // in: d(loss)/d(kt); after the local pass: dA_local
+  float* dk_read;  // in: d(loss)/dk through the read path; after the local pass: + dkt B
   const float* lam_in;
   float* c_loc;
   bf16* dk;
@@ -798,6 +798,9 @@ struct AtkBwdParams {
   bf16* dbeta_atk;
   float* partC;
   float ln_x, eps;
+  // local pass only: the (chunk * heads + head) items it works on and their number (NULL: every tile)
+  const int* tile_list;
+  const int* tile_count;
 };
 
 // One (chunk, head) per CTA, 256 threads, everything in registers.  Warp w owns
@@ -810,8 +813,13 @@ struct AtkBwdParams {
 // memory, and each block continues from the carry it is owed -- every factor is a
 // product of decays <= 1, so nothing overflows.  The per-row channel sums are
 // transposed butterfly reductions (9 shuffles for 8 rows).
-//   kFinal = false: zero incoming carry, only the outgoing carry is produced.
-//   kFinal = true : incoming carry given, all gradients written.
+//   kFinal = false (local pass): everything that needs the write-key factor B(A_t) -- it turns the
+//                   gradient buffers into dA_local (in the dkt buffer) and dk_read + dkt B, and leaves
+//                   the chunk's outgoing carry and its share of the centre gradient.  Runs on the
+//                   chunks the mma.sync chunk kernel handled; the tensor-memory kernel does the same
+//                   for its chunks itself.
+//   kFinal = true : incoming carry given; reverse scan of dA_local and all gradients.  No
+//                   transcendental per element: the states A_t are rebuilt with multiply-adds.
 namespace atkb {
 constexpr int kThreads = 256;
 constexpr int kRows = 8;  // rows per warp
@@ -823,7 +831,7 @@ constexpr int kRows = 8;  // rows per warp
 // entry state and incoming carry (16 B each).
 namespace atkb {
 template <bool kFinal> __host__ __device__ constexpr int slot_bytes() {
-  return kRows * (8 + 16 + (kFinal ? 16 : 0) + 4) + 16 + (kFinal ? 16 : 0);
+  return kRows * (8 + 16 + 16 + 4) + 16 + (kFinal ? 16 : 0);
 }
 template <bool kFinal> __host__ __device__ constexpr int smem_bytes() { return kThreads * slot_bytes<kFinal>(); }
 }  // namespace atkb
@@ -843,7 +851,7 @@ pkda_atk_bwd_kernel(const AtkBwdParams p, int n_tiles) {
   uint2* sK = reinterpret_cast<uint2*>(slots);
   float4* sDkt = reinterpret_cast<float4*>(slots + kThreads * kRows * 8);
   float4* sDkr = sDkt + kThreads * kRows;
-  float* sLg = reinterpret_cast<float*>(sDkr + (kFinal ? kThreads * kRows : 0));
+  float* sLg = reinterpret_cast<float*>(sDkr + kThreads * kRows);
   float4* sA0 = reinterpret_cast<float4*>(sLg + kThreads * kRows);
   float4* sLin = sA0 + kThreads;
 
@@ -856,12 +864,17 @@ pkda_atk_bwd_kernel(const AtkBwdParams p, int n_tiles) {
   uint32_t bpraw_n = 0;
   float centre_n = 0.f;
   static_assert(kRows <= 32 && (kRows & (kRows - 1)) == 0, "one lane per row");
-  auto request = [&](int tile) {
+  if (!kFinal && p.tile_list) n_tiles = *p.tile_count;
+  int tile_n = 0;  // the (chunk * heads + head) item behind the next position of the walk
+  auto request = [&](int pos) {
     live_n = false;
-    if (tile < n_tiles) {
+    int tile = 0;
+    if (pos < n_tiles) {
+      tile = (!kFinal && p.tile_list) ? p.tile_list[pos] : pos;
       int n;
       live_n = chunk_lookup(p.geo, tile / H, n, tok0_n, valid_n);
     }
+    tile_n = tile;
     if (live_n) {
       const int hh = tile % H;
       const size_t col0 = ((size_t)tok0_n * H + hh) * kD + c4;
@@ -875,7 +888,7 @@ pkda_atk_bwd_kernel(const AtkBwdParams p, int n_tiles) {
         asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;\n" ::"r"(smem_u32(sK + i * kThreads + tid)),
                      "l"(p.k + off), "r"(ok ? 8 : 0));
         cp_async16(sDkt + i * kThreads + tid, p.dkt + off, ok);
-        if (kFinal) cp_async16(sDkr + i * kThreads + tid, p.dk_read + off, ok);
+        cp_async16(sDkr + i * kThreads + tid, p.dk_read + off, ok);
         cp_async4(sLg + i * kThreads + tid, p.g_atk + s, ok);
       }
       {
@@ -891,21 +904,24 @@ pkda_atk_bwd_kernel(const AtkBwdParams p, int n_tiles) {
     cp_async_commit();
   };
   request(blockIdx.x);
-  for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+  for (int pos = blockIdx.x; pos < n_tiles; pos += gridDim.x) {
   const bool live = live_n;
+  const int tile = tile_n;
   const int tok0 = tok0_n, valid = valid_n, h = tile % H;
   const size_t chh = (size_t)tile;
   const size_t col0 = ((size_t)tok0 * H + h) * kD + c4;
   cp_async_wait<0>();
   // ---- this tile's data: shared-memory slots -> registers
   uint2 kraw[kRows];
-  float4 dkt[kRows], dkr[kRows];
+  float4 dkt[kFinal ? kRows : 1], dkr[kFinal ? kRows : 1];  // the local pass takes these from its slots row by row
   float pd[kRows], bp[kRows];
 #pragma unroll
   for (int i = 0; i < kRows; ++i) {
     kraw[i] = sK[i * kThreads + tid];
-    dkt[i] = sDkt[i * kThreads + tid];
-    dkr[i] = kFinal ? sDkr[i * kThreads + tid] : make_float4(0.f, 0.f, 0.f, 0.f);
+    if (kFinal) {
+      dkt[i] = sDkt[i * kThreads + tid];
+      dkr[i] = sDkr[i * kThreads + tid];
+    }
     pd[i] = sLg[i * kThreads + tid];  // the log-decay for now (zero fill past the end: decay 1)
     bp[i] = __uint_as_float(__shfl_sync(0xffffffffu, bpraw_n, i) << 16);
   }
@@ -913,8 +929,13 @@ pkda_atk_bwd_kernel(const AtkBwdParams p, int n_tiles) {
   float4 lin = make_float4(0.f, 0.f, 0.f, 0.f);
   if (kFinal) lin = sLin[tid];
   const float centre = centre_n;
-  request(tile + gridDim.x);  // the slots are free again: next tile's copies fly during the computation
-  if (!live) continue;        // (uniform) index past the last real chunk of a packed batch
+  // final pass: the slots are free again, the next tile's copies fly during the computation; the local
+  // pass still reads its gradient rows from the slots and asks for the next tile after that
+  if (kFinal) request(pos + gridDim.x);
+  if (!live) {               // (uniform) index past the last real chunk of a packed batch
+    if (!kFinal) request(pos + gridDim.x);
+    continue;
+  }
   float dblk = 1.f;
 #pragma unroll
   for (int i = 0; i < kRows; ++i) {
@@ -942,39 +963,40 @@ pkda_atk_bwd_kernel(const AtkBwdParams p, int n_tiles) {
     A[0] = d * A[0] + e4.x; A[1] = d * A[1] + e4.y; A[2] = d * A[2] + e4.z; A[3] = d * A[3] + e4.w;
   }
   const float Ain[4] = {A[0], A[1], A[2], A[3]};
-  // ---- pass 2: true states; dA_local into dkt, the lam-free part of dk into dkr
+  // ---- pass 2 (local pass only): true states; dA_local replaces dkt, dk_read takes the lam-free part
+  // of dk; the block's share of the outgoing carry = sum_r (prod_{j<=r} decay_j) dA_local_r
   float dcacc = 0.f;
-#pragma unroll
-  for (int i = 0; i < kRows; ++i) {
-    const bool ok = r0 + i < valid;
-    const float2 x = unpack_bf16(kraw[i].x), y = unpack_bf16(kraw[i].y);
-    const float kc[4] = {x.x, x.y, y.x, y.y};
-    float* dk_t = reinterpret_cast<float*>(&dkt[i]);
-    float* dk_r = reinterpret_cast<float*>(&dkr[i]);
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const float An = pd[i] * A[e] + bp[i] * kc[e] * kc[e];
-      const float dev = __logf(An + p.eps) - centre;
-      const float den = 1.f + fabsf(dev);
-      const float rden = __fdividef(1.f, den);
-      const float Bf = __expf(-p.ln_x * dev * rden);
-      const float ddev = -p.ln_x * dk_t[e] * kc[e] * Bf * rden * rden;
-      if (kFinal) dk_r[e] += dk_t[e] * Bf;
-      dk_t[e] = ok ? __fdividef(ddev, An + p.eps) : 0.f;
-      if (ok) dcacc -= ddev;
-      A[e] = An;
-    }
-  }
   if (!kFinal) {
-    // outgoing carry = sum_r (prod_{j<=r} decay_j) dA_local_r : block partial, then blocks in order
     float w = 1.f, part[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int i = 0; i < kRows; ++i) {
+      const bool ok = r0 + i < valid;
+      const float2 x = unpack_bf16(kraw[i].x), y = unpack_bf16(kraw[i].y);
+      const float kc[4] = {x.x, x.y, y.x, y.y};
+      float4 dkt_i = sDkt[i * kThreads + tid], dkr_i = sDkr[i * kThreads + tid];
+      float* dk_t = reinterpret_cast<float*>(&dkt_i);
+      float* dk_r = reinterpret_cast<float*>(&dkr_i);
       w *= pd[i];
-      const float* d = reinterpret_cast<const float*>(&dkt[i]);
 #pragma unroll
-      for (int e = 0; e < 4; ++e) part[e] += w * d[e];
+      for (int e = 0; e < 4; ++e) {
+        const float An = pd[i] * A[e] + bp[i] * kc[e] * kc[e];
+        const float dev = __logf(An + p.eps) - centre;
+        const float den = 1.f + fabsf(dev);
+        const float rden = __fdividef(1.f, den);
+        const float Bf = __expf(-p.ln_x * dev * rden);
+        const float ddev = -p.ln_x * dk_t[e] * kc[e] * Bf * rden * rden;
+        dk_r[e] += dk_t[e] * Bf;
+        dk_t[e] = ok ? __fdividef(ddev, An + p.eps) : 0.f;
+        if (ok) dcacc -= ddev;
+        part[e] += w * dk_t[e];
+        A[e] = An;
+      }
+      if (ok) {  // the gradient buffers now hold what the final pass reads
+        *reinterpret_cast<float4*>(p.dkt + col0 + (size_t)(r0 + i) * gld) = dkt_i;
+        *reinterpret_cast<float4*>(p.dk_read + col0 + (size_t)(r0 + i) * gld) = dkr_i;
+      }
     }
+    request(pos + gridDim.x);  // the slots are free now
     __syncthreads();  // every warp has read the forward end values
     *reinterpret_cast<float4*>(&sEnd[warp][c4]) = make_float4(part[0], part[1], part[2], part[3]);
     __syncthreads();
@@ -986,6 +1008,16 @@ pkda_atk_bwd_kernel(const AtkBwdParams p, int n_tiles) {
         w2 *= sDec[b];
       }
       p.c_loc[chh * kD + tid] = acc;
+    }
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) dcacc += __shfl_xor_sync(0xffffffffu, dcacc, o);
+    if (lane == 0) sRed[warp] = dcacc;
+    __syncthreads();
+    if (tid == 0) {
+      float acc = 0.f;
+#pragma unroll
+      for (int w = 0; w < kThreads / 32; ++w) acc += sRed[w];
+      p.partC[chh] = acc;
     }
     __syncthreads();  // the exchange arrays are reused by the next tile
     continue;
@@ -1053,16 +1085,6 @@ pkda_atk_bwd_kernel(const AtkBwdParams p, int n_tiles) {
       p.dbeta_atk[s] = __float2bfloat16(x1[0]);
       p.dg_atk[s] = x2[0];
     }
-  }
-#pragma unroll
-  for (int o = 16; o >= 1; o >>= 1) dcacc += __shfl_xor_sync(0xffffffffu, dcacc, o);
-  if (lane == 0) sRed[warp] = dcacc;
-  __syncthreads();
-  if (tid == 0) {
-    float acc = 0.f;
-#pragma unroll
-    for (int w = 0; w < kThreads / 32; ++w) acc += sRed[w];
-    p.partC[chh] = acc;
   }
   __syncthreads();  // the exchange arrays are reused by the next tile
   }  // tile loop
@@ -1269,6 +1291,9 @@ int chunk_bwd(const pkda_chunk_bwd_args* a, cudaStream_t st) {
   ip.dq = static_cast<bf16*>(a->dq); ip.dk_read = ws.dk_read; ip.dv = static_cast<bf16*>(a->dv);
   ip.dg = static_cast<bf16*>(a->dg); ip.dbeta = static_cast<bf16*>(a->dbeta); ip.dkt = ws.dkt;
   ip.partA = ws.partA; ip.partB = ws.partB; ip.scale = p.scale; ip.direct_cap = direct_block_cap();
+  ip.g_atk = p.g_atk; ip.beta_atk = static_cast<const bf16*>(p.beta_atk); ip.log_atk_scale = p.log_atk_scale;
+  ip.a_start = a->a_atk; ip.c_loc = ws.c_loc; ip.partC = ws.partC;
+  ip.ln_x = logf(p.squash_x); ip.eps = p.squash_eps;
   IntraBwdMaps maps;
   {
     const uint64_t H = p.heads, tok = p.total_tokens, rows = (uint64_t)geo.total_chunks * H * kD;
@@ -1316,6 +1341,8 @@ int chunk_bwd(const pkda_chunk_bwd_args* a, cudaStream_t st) {
   ap.a_start = a->a_atk; ap.dkt = ws.dkt; ap.dk_read = ws.dk_read; ap.lam_in = ws.lam_in; ap.c_loc = ws.c_loc;
   ap.dk = static_cast<bf16*>(a->dk); ap.dg_atk = a->dg_atk; ap.dbeta_atk = static_cast<bf16*>(a->dbeta_atk);
   ap.partC = ws.partC; ap.ln_x = logf(p.squash_x); ap.eps = p.squash_eps;
+  // the tensor-memory chunk kernel has done the local pass of its own chunks
+  ap.tile_list = ip.slow_list; ap.tile_count = ip.slow_list ? ws.counts + 1 : nullptr;
   begin_stage(kStageAtkBwdLocal, st);
   const int atk_tiles = geo.total_chunks * p.heads;
   const int atk_grid = atk_tiles < 2 * sms ? atk_tiles : 2 * sms;  // persistent: two CTAs per SM

@@ -30,6 +30,12 @@
 // with Xq = bf16(q 2^G), Xk = bf16(k 2^G), Y = bf16(kt 2^-G) the very operands of the products, so
 // that the two sides of every pair cancel under the reverse cumulative sum.
 //
+// The kernel also takes the local part of the preconditioner's backward along (kt = k B(A_t) with the
+// diagonal state A_t = decay_t A_(t-1) + gain_t k_t^2): it has dkt in registers, reloads the raw k
+// tile into the dead state tile and recomputes A_t per channel, so the gradient buffers leave as
+// dA_local (in the dkt buffer) and dk_read + dkt B, and the chunk-parallel reverse scan that follows
+// (pkda_atk_bwd_kernel<true>) needs no transcendental.
+//
 // Every mbarrier wait is bounded; a CTA whose wait gives up sets the status word.
 #include "pkda_chunk.cuh"
 #include "pkda_tc.cuh"
@@ -58,8 +64,8 @@ constexpr int oG = oKt + 16384;         // [64][128 c] raw gate
 constexpr int oTm = oG + 16384;         // [64 j][64 i] T, then diag(beta) T           (MN-major B)
 constexpr int oDM = oTm + 8192;         // [64 i][64 j] dM                             (K-major / MN-major B)
 constexpr int oDP = oDM + 8192;         // [64 i][64 j] dP
-constexpr int oSmall = oDP + 8192;      // f32: beta[64] | x1[4][128] | x2[4][128] | red[16]
-constexpr int oBar = oSmall + 256 + 2048 + 2048 + 64;  // barriers A, B, C, m1, m2, m3 and the tensor-memory address
+constexpr int oSmall = oDP + 8192;      // f32: beta[64] | x1[4][128] | x2[4][128] | red[32] | pd[64] | bp[64]
+constexpr int oBar = oSmall + 256 + 2048 + 2048 + 128 + 512;  // barriers A, B, C, M, K and the tensor-memory address
 constexpr int kSmem = oBar + 64 + 1024;
 static_assert(kSmem <= 232448, "shared memory of one SM");
 // after the last product: exchange arrays in the (dead) pair-gradient tiles
@@ -67,6 +73,7 @@ constexpr int oX3 = oDM;                // f32 [4][128] slice sums of dG
 constexpr int oX4 = oDM + 2048;         // f32 [4][128] slice sums of kt dkt (state part)
 constexpr int oX5 = oDM + 4096;         // f32 [4][128] slice sums of the raw-gate gradient
 constexpr int oDb = oDM + 6144;         // f32 [4][64] per lane-quarter partial sums of dbeta
+constexpr int oX6 = oDP;                // f32 [4][128] slice sums of the preconditioner's outgoing carry
 constexpr uint32_t kCols = 512;
 constexpr uint32_t cR = 0, cStk = 64, cQs = 128, cKs = 192, cKts = 256, cKtM = 320, cKtP = 384;  // cR / cStk later Qp / Kp
 }  // namespace ibtc
@@ -155,7 +162,8 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
 
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char* tiles = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t barA = base + oBar, barB = barA + 8, barC = barA + 16, barM = barA + 24, tmem_slot = barA + 48;
+  const uint32_t barA = base + oBar, barB = barA + 8, barC = barA + 16, barM = barA + 24, barK = barA + 32;
+  const uint32_t tmem_slot = barA + 48;
   // Shared address of element (token j0 + t, channel c) of a [64][128] tile at offset o: sa[t & 7] + o + 128 t
   // (the 16-byte pieces of a row are permuted by the row index modulo 8).
   uint32_t sa[8];
@@ -164,11 +172,14 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
   float* sBeta = reinterpret_cast<float*>(tiles + oSmall);
   float* sX1 = sBeta + 64;     // [4][128] slice totals of the gate
   float* sX2 = sX1 + 512;      // [4][128] slice partials of sum_v S0 dS1
-  float* sRed = sX2 + 512;     // [16]
+  float* sRed = sX2 + 512;     // [32]: 16 warp sums of dA_log, 16 of the centre gradient
+  float* sPd = sRed + 32;      // [64] preconditioner decay exp(g_atk) per token
+  float* sBp = sPd + 64;       // [64] preconditioner gain beta_atk per token
   float* sX3 = reinterpret_cast<float*>(tiles + oX3);
   float* sX4 = reinterpret_cast<float*>(tiles + oX4);
   float* sX5 = reinterpret_cast<float*>(tiles + oX5);
   float* sDb = reinterpret_cast<float*>(tiles + oDb);
+  float* sX6 = reinterpret_cast<float*>(tiles + oX6);
 
   // All tiles of one item by TMA.  Thread 0 arms the three barriers with the byte counts (arm), a
   // CTA-wide barrier later the 20 copies are issued by the first lanes of the 16 warps (request), so
@@ -210,6 +221,7 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
     tc::mbar_init(barB, 1);
     tc::mbar_init(barC, 1);
     tc::mbar_init(barM, 1);
+    tc::mbar_init(barK, 1);
     tc::fence_barrier_init();
     arm();
   }
@@ -222,7 +234,7 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
   bool ok = true;
   uint32_t m_phase = 0, ld_phase = 0;
   // per-item scalars of this thread, fetched one item ahead: 2^G_last of its channel, the gate bias, A_log
-  float gl_n, bias_n, alog_n;
+  float gl_n, bias_n, alog_n, astart_n, centre_n, gatk_n = 0.f, batk_n = 0.f;
   int chh_n;
   auto fetch_scalars = [&](int item) {
     const int chh = p.fast_list[item], h = chh % H;
@@ -230,6 +242,15 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
     gl_n = p.gc[(size_t)chh * kD + c];
     bias_n = p.dt_bias[h * kD + c];
     alog_n = p.A_log[h];
+    astart_n = p.a_start[(size_t)chh * kD + c];
+    centre_n = p.log_atk_scale[h];
+    if (tid < kChunk) {  // the preconditioner's per-token controls
+      int n, tok0, valid;
+      chunk_lookup(p.geo, chh / H, n, tok0, valid);
+      const size_t s = (size_t)(tok0 + tid) * H + h;
+      gatk_n = p.g_atk[s];
+      batk_n = to_f(p.beta_atk[s]);
+    }
   };
   fetch_scalars(blockIdx.x);
 
@@ -240,7 +261,11 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
   const int h = chh % H;
   int n, tok0, valid;
   chunk_lookup(p.geo, chh / H, n, tok0, valid);  // a full chunk (the classifier checked)
-  const float gl = gl_n, bias = bias_n, ea = __expf(alog_n);
+  const float gl = gl_n, bias = bias_n, ea = __expf(alog_n), a_start = astart_n, centre = centre_n;
+  if (tid < kChunk) {
+    sPd[tid] = __expf(gatk_n);
+    sBp[tid] = batk_n;
+  }
   // The operand descriptors are functions of the tile base only; keeping the base opaque per item
   // stops the compiler from computing all sixty of them ahead of the loop and holding them in registers.
   uint32_t dbase = base;
@@ -408,6 +433,10 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
   __syncthreads(); PKDA_PHASE(7);
   if (tid == 0) {
     tc::tc_fence_after();
+    // the raw k tile comes back into the (dead) entry-state tile for the preconditioner's backward
+    tc::mbar_expect_tx(barK, 16384);
+    tc::tma_load_3d(base + oS0, &maps.k, barK, 0, h, tok0);
+    tc::tma_load_3d(base + oS0 + 8192, &maps.k, barK, 64, h, tok0);
     constexpr uint32_t idesc_k = tc::idesc_bf16(128, 64, true, false);  // B = pair gradient as [i][j], K = j
     constexpr uint32_t idesc_m = tc::idesc_bf16(128, 64, true, true);   // B = pair gradient read as [j][i], K = i
 #pragma unroll
@@ -430,18 +459,45 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
   tc::tc_fence_after();
   PKDA_PHASE(8);
 
-  // ---- 5. gradients of this thread's channel and 16 tokens
-  const size_t out0 = ((size_t)(tok0 + j0) * H + h) * kD + c;  // element (first token of the slice, h, c)
-  float dGv[16], kdsum = 0.f;
+  // ---- 5a. preconditioner state at the start of this thread's token slice: zero-start scan of the slice,
+  // one exchange, then the slices before it folded in (a slice's decay product is the same for all channels)
+  ok = tc::mbar_wait(barK, ld_phase ^ 1) && ok;  // (ld_phase was flipped after this item's tile waits)
+  float A_in, w_in = 1.f;  // state before the slice's first token; product of the decays before it
   {
-    // eight tokens at a time: the accumulator pieces stay small next to the per-token state
+    float a = 0.f;
+#pragma unroll
+    for (int t = 0; t < 16; ++t) {
+      const float kc = lds_bf16(sa[t & 7] + oS0 + 128 * t);
+      a = sPd[j0 + t] * a + sBp[j0 + t] * kc * kc;
+    }
+    sX1[sl * kD + c] = a;  // (the gate totals that lived here were consumed in step 2)
+    __syncthreads();
+    A_in = a_start;
+#pragma unroll
+    for (int s = 0; s < 3; ++s) {
+      float d = 1.f;
+#pragma unroll
+      for (int t = 0; t < 16; ++t) d *= sPd[16 * s + t];
+      if (s < sl) {
+        A_in = d * A_in + sX1[s * kD + c];
+        w_in *= d;
+      }
+    }
+  }
+
+  // ---- 5b. gradients of this thread's channel and 16 tokens, eight tokens at a time (the accumulator
+  // pieces stay small next to the per-token state)
+  const size_t out0 = ((size_t)(tok0 + j0) * H + h) * kD + c;  // element (first token of the slice, h, c)
+  float dGv[16], kdsum = 0.f, cloc = 0.f, dcen = 0.f;
+  {
     bf16* pq = p.dq + out0;  // walked row by row (running pointers keep the row offsets out of registers)
     float* pk = p.dk_read + out0;
     float* pkt = p.dkt + out0;
+    float A = A_in, w = w_in;
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
       const uint32_t ta = tmem + lane_addr + j0 + 8 * hh;
-      float a[8], b[8];
+      float a[8], b[8], dkr[8];
       tc::tmem_ld8(ta + cQs, a);
       tc::tmem_ld8(ta + cR, b);
       tc::tmem_ld_wait();
@@ -462,58 +518,59 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
         const int t = 8 * hh + u;
         const float tot = a[u] + b[u];
         const float xk = lds_bf16(sa[t & 7] + oK + 128 * t);
-        *pk = ex2(G[t]) * tot;
-        pk += gld;
+        dkr[u] = ex2(G[t]) * tot;
         dGv[t] += xk * tot;
       }
-    }
-    // write-key gradient: first the part of dbeta that flows through M (rows of KtM against Y)
-    {
-      float dbv[16];
-#pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
-        float a[8];
-        tc::tmem_ld8(tmem + lane_addr + j0 + 8 * hh + cKtM, a);
-        tc::tmem_ld_wait();
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          const int t = 8 * hh + u;
-          const float bj = sBeta[j0 + t];
-          const float y = lds_bf16(sa[t & 7] + oKt + 128 * t);
-          const float df = lds_bf16(sa[t & 7] + oDF + 128 * t);
-          const float ev = lds_bf16(sa[t & 7] + oE + 128 * t);
-          dbv[t] = df * ev + (bj != 0.f ? __fdividef(y * a[u], bj) : 0.f);
-        }
-      }
-      row_sums16(dbv, lane);
-      if ((lane & 1) == 0)
-        sDb[q4 * kChunk + j0 + ((lane >> 4) & 1) * 8 + ((lane >> 3) & 1) * 4 + ((lane >> 2) & 1) * 2 + ((lane >> 1) & 1)] = dbv[0];
-    }
-#pragma unroll
-    for (int hh = 0; hh < 2; ++hh) {
-      const uint32_t ta = tmem + lane_addr + j0 + 8 * hh;
-      float a[8], b[8], m[8];
+      // write-key gradient; the part of dbeta that flows through M (rows of KtM against Y)
+      float m[8];
       tc::tmem_ld8(ta + cKtM, m);
       tc::tmem_ld8(ta + cKtP, b);
       tc::tmem_ld8(ta + cKts, a);
       tc::tmem_ld_wait();
+      float dbv[8];
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
         const int t = 8 * hh + u;
+        const float bj = sBeta[j0 + t];
         const float y = lds_bf16(sa[t & 7] + oKt + 128 * t);
-        const float st = gl * sBeta[j0 + t] * a[u], pr = m[u] + b[u];
-        *pkt = ex2(-G[t]) * (st + pr);
-        pkt += gld;
+        const float df = lds_bf16(sa[t & 7] + oDF + 128 * t);
+        const float ev = lds_bf16(sa[t & 7] + oE + 128 * t);
+        dbv[u] = df * ev + (bj != 0.f ? __fdividef(y * m[u], bj) : 0.f);
+        const float st = gl * bj * a[u], pr = m[u] + b[u];
+        const float dkt = ex2(-G[t]) * (st + pr);
         const float kd = y * st;
         dGv[t] -= y * pr + kd;
         kdsum += kd;
+        // the preconditioner: A_t, the factor B(A_t) and its derivative (pkda_atk_bwd_kernel has the same math)
+        const float kc = lds_bf16(sa[t & 7] + oS0 + 128 * t);
+        const float pd = sPd[j0 + t];
+        A = pd * A + sBp[j0 + t] * kc * kc;
+        w *= pd;
+        const float dev = __logf(A + p.eps) - centre;
+        const float rden = __fdividef(1.f, 1.f + fabsf(dev));
+        const float Bf = __expf(-p.ln_x * dev * rden);
+        const float ddev = -p.ln_x * dkt * kc * Bf * rden * rden;
+        const float dA = __fdividef(ddev, A + p.eps);
+        *pkt = dA;
+        pkt += gld;
+        *pk = dkr[u] + dkt * Bf;
+        pk += gld;
+        dcen -= ddev;
+        cloc += w * dA;
       }
+      row_sums8(dbv, lane);
+      if ((lane & 3) == 0)
+        sDb[q4 * kChunk + j0 + 8 * hh + ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1)] = dbv[0];
     }
     float tot = 0.f;
 #pragma unroll
     for (int t = 0; t < 16; ++t) tot += dGv[t];
     sX3[sl * kD + c] = tot;     // the pair-gradient tiles are dead: every product has finished
     sX4[sl * kD + c] = kdsum;
+    sX6[sl * kD + c] = cloc;
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) dcen += __shfl_xor_sync(0xffffffffu, dcen, o);
+    if (lane == 0) sRed[16 + warp] = dcen;
   }
   tc::tc_fence_before();
   tc::fence_proxy_async();  // this item's last reads of the operand tiles come before the next item's copies
@@ -557,12 +614,19 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
     p.dbeta[(size_t)(tok0 + tid) * H + h] =
         __float2bfloat16(sDb[tid] + sDb[kChunk + tid] + sDb[2 * kChunk + tid] + sDb[3 * kChunk + tid]);
   __syncthreads(); PKDA_PHASE(10);
-  if (tid < kD) p.partB[(size_t)chh * kD + tid] = sX5[tid] + sX5[kD + tid] + sX5[2 * kD + tid] + sX5[3 * kD + tid];
+  if (tid < kD) {
+    p.partB[(size_t)chh * kD + tid] = sX5[tid] + sX5[kD + tid] + sX5[2 * kD + tid] + sX5[3 * kD + tid];
+    p.c_loc[(size_t)chh * kD + tid] = sX6[tid] + sX6[kD + tid] + sX6[2 * kD + tid] + sX6[3 * kD + tid];
+  }
   if (tid == 0) {
     float acc = 0.f;
 #pragma unroll
     for (int w = 0; w < kThreads / 32; ++w) acc += sRed[w];
     p.partA[chh] = acc;
+    float accc = 0.f;
+#pragma unroll
+    for (int w = 0; w < kThreads / 32; ++w) accc += sRed[16 + w];
+    p.partC[chh] = accc;
     tc::bulk_wait_read();  // the dv store has read the stack rows the next item's dR overwrites
   }
   __syncthreads();  // the exchange arrays and beta are rewritten by the next item

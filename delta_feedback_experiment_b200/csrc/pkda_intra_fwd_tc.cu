@@ -36,7 +36,7 @@
 #undef PKDA_PHASE
 #define PKDA_PHASE(k)                                                                             \
   do {                                                                                            \
-    if (threadIdx.x == 0 && blockIdx.x == 37 && item == 37 + 10 * (int)gridDim.x) g_phase_prof[k] = clock64(); \
+    if (threadIdx.x == 0 && item == 3000) g_phase_prof[k] = clock64();                               \
   } while (0)
 #endif
 
@@ -130,12 +130,18 @@ pkda_intra_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_
   const int ei = R & 63, j0 = 32 * (warp >> 2);
   const bool isP = (warp & 3) >= 2;
 
+  // Items differ in cost (a chunk that is handed over costs a fraction of one that is finished), so
+  // the CTAs draw them one at a time from a cursor instead of striding through them.
+  __shared__ int s_next;
+  if (tid == 0) s_next = atomicAdd(p.counts, 1);
+  __syncthreads();
+  int item = s_next;
 #pragma unroll 1
-  for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+  while (item < n_items) {
   PKDA_PHASE(0);
   const int h = item % H;
   int n, tok0, valid;
-  if (!chunk_lookup(p.geo, item / H, n, tok0, valid)) break;  // past the last real chunk of a packed batch
+  if (!chunk_lookup(p.geo, item / H, n, tok0, valid)) break;  // past the last real chunk of a packed batch (items ascend)
   const size_t chh = (size_t)item;
   const size_t row0 = ((size_t)tok0 * H + h) * kD;
   const bool full = valid == kChunk;
@@ -251,7 +257,9 @@ pkda_intra_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_
       if (tid == 0) p.slow_list[atomicAdd(p.counts + 1, 1)] = item;
       ok = tc::mbar_wait(bar_tma, tma_phase) && ok;  // the V tile in flight must land before the tile is reused
       tma_phase ^= 1;
+      if (tid == 0) s_next = atomicAdd(p.counts, 1);
       __syncthreads();
+      item = s_next;
       continue;
     }
   }
@@ -470,9 +478,11 @@ pkda_intra_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_
       tc::bulk_commit();
     }
     tc::bulk_wait_read();  // the tiles stay in place until every store of this item has read them
+    s_next = atomicAdd(p.counts, 1);
   }
   __syncthreads();  // the next item's copies overwrite the tiles
   PKDA_PHASE(11);
+  item = s_next;
   }  // item loop
   if (__syncthreads_or(!ok) && tid == 0) atomicExch(p.status, 1);
   tc::tc_fence_before();

@@ -633,7 +633,12 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     # kernels and the copy out overlap.  Every step moves all inputs in and all results out.
     from delta_feedback_experiment_b200.host_pipeline import HostStep
     e2e_steps = max(1, min(args.steps, 5))
-    host_step = HostStep(device, slices=args.e2e_slices, lean=lean)
+    e2e_plan = tuple(int(x) for x in str(args.e2e_slices).split(","))
+    if len(e2e_plan) == 1:
+        e2e_plan = e2e_plan[0]
+    elif sum(e2e_plan) != B:
+        e2e_plan = min(8, B)
+    host_step = HostStep(device, slices=e2e_plan, lean=lean)
     host_in = {n: host[n] for n in (*INPUT_NAMES, "initial_state", "initial_A_state")}
 
     def e2e_step():
@@ -706,7 +711,8 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
                 "steps": e2e_steps, "finite": e2e_finite, "copy_floor_ms": floor,
                 "call": f"host_pipeline.HostStep(slices={args.e2e_slices}): pinned host inputs -> forward+backward -> "
-                        "pinned host outputs, copies overlapped with the kernels by row slice"},
+                        "pinned host outputs, copies overlapped with the kernels by row slice; the kernels of a "
+                        "slice replay from a CUDA graph on fixed device buffers"},
         "gpu_launches": launches,
         "clocks": clocks.summary(),
         "stages_ms_per_step": {n: ms / args.steps for n, (ms, _) in stages.items()},
@@ -746,7 +752,8 @@ def main() -> None:
                          "of the reference's own operator benchmark (production)")
     ap.add_argument("--legacy", default="", help="comma-separated stages pinned to their mma.sync kernels (A/B runs)")
     ap.add_argument("--decode-steps", type=int, default=1024)
-    ap.add_argument("--e2e-slices", type=int, default=8, help="row slices of the host-memory step")
+    ap.add_argument("--e2e-slices", default="8",
+                    help="row slices of the host-memory step: a count of equal slices, or row counts separated by commas")
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-layer", action="store_true", help="skip the convolution / norm-gate operators")

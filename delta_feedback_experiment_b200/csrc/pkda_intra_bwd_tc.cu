@@ -64,8 +64,8 @@ constexpr int oG = oKt + 16384;         // [64][128 c] raw gate
 constexpr int oTm = oG + 16384;         // [64 j][64 i] T, then diag(beta) T           (MN-major B)
 constexpr int oDM = oTm + 8192;         // [64 i][64 j] dM                             (K-major / MN-major B)
 constexpr int oDP = oDM + 8192;         // [64 i][64 j] dP
-constexpr int oSmall = oDP + 8192;      // f32: beta[64] | x1[4][128] | x2[4][128] | red[32] | pd[64] | bp[64]
-constexpr int oBar = oSmall + 256 + 2048 + 2048 + 128 + 512;  // barriers A, B, C, M, K and the tensor-memory address
+constexpr int oSmall = oDP + 8192;      // f32: beta[64] | x1[4][128] | x2[4][128] | red[32] | pd[64] | bp[64] | 1/beta[64]
+constexpr int oBar = oSmall + 256 + 2048 + 2048 + 128 + 512 + 256;  // barriers A, B, C, M, K and the tensor-memory address
 constexpr int kSmem = oBar + 64 + 1024;
 static_assert(kSmem <= 232448, "shared memory of one SM");
 // after the last product: exchange arrays in the (dead) pair-gradient tiles
@@ -175,6 +175,7 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
   float* sRed = sX2 + 512;     // [32]: 16 warp sums of dA_log, 16 of the centre gradient
   float* sPd = sRed + 32;      // [64] preconditioner decay exp(g_atk) per token
   float* sBp = sPd + 64;       // [64] preconditioner gain beta_atk per token
+  float* sBinv = sBp + 64;     // [64] 1 / beta (0 where beta is 0)
   float* sX3 = reinterpret_cast<float*>(tiles + oX3);
   float* sX4 = reinterpret_cast<float*>(tiles + oX4);
   float* sX5 = reinterpret_cast<float*>(tiles + oX5);
@@ -274,6 +275,10 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
 
   // ---- 1. T <- diag(beta) T (row j scaled by beta_j: the beta of dE = beta dF moves onto T), then dR^T
   ok = tc::mbar_wait(barB, ld_phase) && ok;
+  if (tid < kChunk) {
+    const float b = sBeta[tid];
+    sBinv[tid] = b != 0.f ? __fdividef(1.f, b) : 0.f;
+  }
   {
     const int j = tid >> 3, pc = tid & 7;
     uint4* piece = reinterpret_cast<uint4*>(tiles + oTm + j * 128 + (pc << 4));  // a whole row takes one factor
@@ -297,20 +302,14 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
 
   // ---- 2. while that runs: the gate, its cumulative sum over the tokens, the operands gated in place
   ok = tc::mbar_wait(barA, ld_phase) && ok;
-  float G[16];
-  uint32_t zraw[8];  // raw gate + bias of the 16 tokens, kept (as bf16 pairs) for the gate's backward
+  float G[16], G_before;  // cumulative log2-decay of the 16 tokens, and of the token before them
   {
     const float ea2 = ea * kLog2e;
     float run = 0.f;
 #pragma unroll
-    for (int t = 0; t < 16; t += 2) {
-      const float r0 = lds_bf16(sa[t & 7] + oG + 128 * t);
-      const float r1 = lds_bf16(sa[(t + 1) & 7] + oG + 128 * (t + 1));
-      zraw[t >> 1] = pack_bf16(r0, r1);
-      run += -ea2 * softplus_fast(r0 + bias);
+    for (int t = 0; t < 16; ++t) {
+      run += -ea2 * softplus_fast(lds_bf16(sa[t & 7] + oG + 128 * t) + bias);
       G[t] = run;
-      run += -ea2 * softplus_fast(r1 + bias);
-      G[t + 1] = run;
     }
     sX1[sl * kD + c] = run;
   }
@@ -321,6 +320,7 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
     for (int s = 0; s < 3; ++s) pre += (s < sl) ? sX1[s * kD + c] : 0.f;
 #pragma unroll
     for (int t = 0; t < 16; ++t) G[t] += pre;
+    G_before = pre;
   }
   // the state-coupled products that need nothing but landed tiles
   ok = tc::mbar_wait(barC, ld_phase) && ok;
@@ -497,7 +497,7 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
       const uint32_t ta = tmem + lane_addr + j0 + 8 * hh;
-      float a[8], b[8], dkr[8];
+      float a[8], b[8], dkr[8], e8[8];
       tc::tmem_ld8(ta + cQs, a);
       tc::tmem_ld8(ta + cR, b);
       tc::tmem_ld_wait();
@@ -506,7 +506,8 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
         const int t = 8 * hh + u;
         const float tot = p.scale * a[u] + b[u];
         const float xq = lds_bf16(sa[t & 7] + oQ + 128 * t);
-        *pq = __float2bfloat16(ex2(G[t]) * tot);
+        e8[u] = ex2(G[t]);
+        *pq = __float2bfloat16(e8[u] * tot);
         pq += gld;
         dGv[t] = xq * tot;
       }
@@ -518,7 +519,7 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
         const int t = 8 * hh + u;
         const float tot = a[u] + b[u];
         const float xk = lds_bf16(sa[t & 7] + oK + 128 * t);
-        dkr[u] = ex2(G[t]) * tot;
+        dkr[u] = e8[u] * tot;
         dGv[t] += xk * tot;
       }
       // write-key gradient; the part of dbeta that flows through M (rows of KtM against Y)
@@ -535,9 +536,9 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
         const float y = lds_bf16(sa[t & 7] + oKt + 128 * t);
         const float df = lds_bf16(sa[t & 7] + oDF + 128 * t);
         const float ev = lds_bf16(sa[t & 7] + oE + 128 * t);
-        dbv[u] = df * ev + (bj != 0.f ? __fdividef(y * m[u], bj) : 0.f);
+        dbv[u] = df * ev + y * m[u] * sBinv[j0 + t];
         const float st = gl * bj * a[u], pr = m[u] + b[u];
-        const float dkt = ex2(-G[t]) * (st + pr);
+        const float dkt = __fdividef(st + pr, e8[u]);
         const float kd = y * st;
         dGv[t] -= y * pr + kd;
         kdsum += kd;
@@ -589,16 +590,17 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
                 sX4[3 * kD + c];
 #pragma unroll
     for (int s = 1; s < 4; ++s) run += (s > sl) ? sX3[s * kD + c] : 0.f;
+    // softplus and sigmoid of (raw + bias) come back from the per-token decay the forward part of this
+    // kernel summed up: G_t - G_(t-1) = -exp(A_log) log2(e) softplus, and sigmoid = 1 - exp(-softplus)
     float pa = 0.f, pb = 0.f;
     bf16* pg = p.dg + out0 + 15 * gld;
+    const float inv_ea = __fdividef(1.f, ea), inv_ea2 = inv_ea * kLn2;
 #pragma unroll
     for (int t = 15; t >= 0; --t) {
       run += dGv[t];
-      const float2 zz = unpack_bf16(zraw[t >> 1]);
-      const float z = ((t & 1) ? zz.y : zz.x) + bias;
-      const float e0 = __expf(-fabsf(z)), i0 = __fdividef(1.f, 1.f + e0);
-      const float sg = z >= 0.f ? i0 : e0 * i0;
-      const float sp = fmaxf(z, 0.f) - __logf(i0);
+      const float dlog2 = G[t] - (t ? G[t - 1] : G_before);  // <= 0
+      const float sp = -dlog2 * inv_ea2;
+      const float sg = 1.f - ex2(dlog2 * inv_ea);
       const float dr = run * (-ea) * sg;
       pa += run * (-ea * sp);
       pb += dr;

@@ -12,6 +12,14 @@ host-to-device copy of slice i+1, the kernels of slice i and the device-to-host
 copy of slice i-1 on three CUDA streams.  The result is what the un-sliced
 device call returns (per-row tensors exactly, per-head parameter gradients up to
 the order in which the slices are added).
+
+Launching the twenty-odd kernels of a slice from Python costs about as much host
+time as the slice's copies take on the bus, so with many slices the host becomes
+the bottleneck.  When the batch divides evenly into the slices, ``HostStep``
+therefore captures the forward+backward of one slice into a CUDA graph on fixed
+device buffers (three sets, used in turn, so that copy-in, kernels and copy-out of
+neighbouring slices overlap) and replays it per slice; the host then only enqueues
+the copies and one replay.
 """
 
 from __future__ import annotations
@@ -42,10 +50,18 @@ class HostStep:
     marks completion.
     """
 
-    def __init__(self, device, slices: int = 4, lean: bool = False):
+    def __init__(self, device, slices=4, lean: bool = False, graphs: bool = True):
+        """``slices``: how many equal row slices to cut the batch into, or a sequence of row
+        counts (summing to the batch), e.g. ``(1, 3, 3, 1)``: small slices at both ends keep the
+        un-overlapped first copy-in and last copy-out short, large ones in between keep the
+        number of copies that alternate on the bus low."""
         self.device = torch.device(device)
-        self.slices = int(slices)
+        self.plan = None if isinstance(slices, int) else tuple(int(x) for x in slices)
+        self.slices = int(slices) if isinstance(slices, int) else len(self.plan)
         self.lean = bool(lean)
+        self.graphs = bool(graphs)
+        self._slots = None      # graph mode: three sets of fixed device buffers with a captured step each
+        self._slot_key = None
         self.s_in = torch.cuda.Stream(self.device)
         self.s_comp = torch.cuda.Stream(self.device)
         self.s_out = torch.cuda.Stream(self.device)
@@ -63,6 +79,124 @@ class HostStep:
                 out["d" + n] = torch.empty(host[n].shape, dtype=torch.float32, pin_memory=True)
         return out
 
+    # ------------------------------------------------------------------ graph mode
+    def _step(self, rows, params, with_state):
+        """Forward + backward of one slice on device tensors; returns (o, grads)."""
+        # (detached views: the fixed buffers themselves stay plain tensors the copies can write into)
+        leaves = [rows[n].detach().requires_grad_(True) for n in ROW_INPUTS]
+        heads = [params[n].detach().requires_grad_(True) for n in HEAD_PARAMS]
+        kw = dict(zip(INPUT_NAMES, leaves + heads))
+        centre = kw.pop("log_atk_scale")
+        S0 = A0 = None
+        wrt = leaves + heads
+        if with_state:
+            S0 = rows["initial_state"].detach().requires_grad_(True)
+            A0 = rows["initial_A_state"].detach().requires_grad_(True)
+            wrt = wrt + [S0, A0]
+        o, _, _ = chunk_precond_kda(**kw, initial_state=S0, initial_A_state=A0,
+                                    output_final_state=False, log_atk_scale=centre,
+                                    disable_recompute=not self.lean)
+        grads = torch.autograd.grad(o, wrt, rows["do"])
+        return o.detach(), [g.detach() for g in grads]
+
+    def _build_slots(self, host, do, with_state, rows_per):
+        dev = self.device
+        names = list(ROW_INPUTS) + ["do"] + (["initial_state", "initial_A_state"] if with_state else [])
+        src = dict(host, do=do)
+        if getattr(self, "_params", None) is None:
+            self._params = {n: torch.empty(host[n].shape, dtype=host[n].dtype, device=dev) for n in HEAD_PARAMS}
+        # Every graph keeps a memory pool of its own: with a shared pool the temporaries of one graph's
+        # replay would land on the results of the graph captured after it, which are still being copied out.
+        slots = []
+        for k in range(3):
+            rows = {n: torch.zeros((rows_per, *src[n].shape[1:]), dtype=src[n].dtype, device=dev) for n in names}
+            with torch.cuda.stream(self.s_comp):
+                if k == 0:  # one eager pass first (lazy initialisation must not happen inside a capture)
+                    for n in HEAD_PARAMS:
+                        self._params[n].copy_(host[n], non_blocking=True)
+                    for n in names:
+                        rows[n].copy_(src[n][:rows_per], non_blocking=True)
+                    self._step(rows, self._params, with_state)
+            self.s_comp.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=self.s_comp):
+                o, grads = self._step(rows, self._params, with_state)
+            slots.append({"rows": rows, "graph": graph, "o": o, "grads": grads,
+                          "in_free": torch.cuda.Event(), "out_free": torch.cuda.Event(),
+                          "ready": torch.cuda.Event(), "done": torch.cuda.Event()})
+        for sl in slots:  # nothing pending on a fresh slot
+            sl["in_free"].record(self.s_comp)
+            sl["out_free"].record(self.s_out)
+        self._names = names
+        return slots
+
+    def _call_graphs(self, host, do, with_state, plan):
+        dev, out = self.device, self.out
+        key = (plan, with_state, tuple(do.shape), do.dtype)
+        if self._slots is None or self._slot_key != key:
+            self._params = None
+            # three buffer sets (and captured steps) per distinct slice size
+            self._slots = {r: self._build_slots(host, do, with_state, r) for r in sorted(set(plan))}
+            self._slot_key = key
+        used = {r: 0 for r in self._slots}
+        cur = torch.cuda.current_stream(dev)
+        for s in (self.s_in, self.s_comp, self.s_out):
+            s.wait_stream(cur)
+        self.h2d_bytes = self.d2h_bytes = 0
+        src = dict(host, do=do)
+        nbytes = lambda t: t.numel() * t.element_size()
+        with torch.cuda.stream(self.s_in):
+            for n in HEAD_PARAMS:
+                self._params[n].copy_(host[n], non_blocking=True)
+                self.h2d_bytes += nbytes(host[n])
+            params_ready = torch.cuda.Event()
+            params_ready.record(self.s_in)
+        acc = None
+        b1 = 0
+        for i, rows_per in enumerate(plan):
+            sl = self._slots[rows_per][used[rows_per] % 3]
+            used[rows_per] += 1
+            b0, b1 = b1, b1 + rows_per
+            with torch.cuda.stream(self.s_in):
+                self.s_in.wait_event(sl["in_free"])       # the replay that last read these inputs is over
+                for n in self._names:
+                    sl["rows"][n].copy_(src[n][b0:b1], non_blocking=True)
+                    self.h2d_bytes += nbytes(sl["rows"][n])
+                sl["ready"].record(self.s_in)
+            with torch.cuda.stream(self.s_comp):
+                if i == 0:
+                    self.s_comp.wait_event(params_ready)
+                self.s_comp.wait_event(sl["ready"])
+                self.s_comp.wait_event(sl["out_free"])    # the copies that last read these outputs are over
+                sl["graph"].replay()
+                head = sl["grads"][7:10]
+                if acc is None:
+                    acc = [g.float().clone() for g in head]
+                else:
+                    for a, g in zip(acc, head):
+                        a.add_(g)
+                sl["in_free"].record(self.s_comp)
+                sl["done"].record(self.s_comp)
+            with torch.cuda.stream(self.s_out):
+                self.s_out.wait_event(sl["done"])
+                pairs = [(out["o"][b0:b1], sl["o"])]
+                pairs += [(out["d" + n][b0:b1], g) for n, g in zip(ROW_INPUTS, sl["grads"][:7])]
+                if with_state:
+                    pairs += [(out["dinitial_state"][b0:b1], sl["grads"][10]),
+                              (out["dinitial_A_state"][b0:b1], sl["grads"][11])]
+                for dst, g in pairs:
+                    dst.copy_(g, non_blocking=True)
+                    self.d2h_bytes += nbytes(g)
+                sl["out_free"].record(self.s_out)
+        with torch.cuda.stream(self.s_out):
+            self.s_out.wait_stream(self.s_comp)
+            for n, g in zip(HEAD_PARAMS, acc):
+                g.record_stream(self.s_out)
+                out["d" + n].copy_(g, non_blocking=True)
+                self.d2h_bytes += nbytes(g)
+        cur.wait_stream(self.s_out)
+        return out
+
     def __call__(self, host: Dict[str, Tensor], do: Tensor) -> Dict[str, Tensor]:
         dev = self.device
         B = host["q"].shape[0]
@@ -71,7 +205,17 @@ class HostStep:
             self.out = self._alloc_out(host, do, with_state)
         out = self.out
         n_slices = max(1, min(self.slices, B))
+        plan = self.plan
+        if plan is not None and (sum(plan) != B or min(plan) < 1):
+            raise ValueError(f"the slice plan {plan} does not add up to the batch of {B} rows")
+        if plan is None and B % n_slices == 0:
+            plan = (B // n_slices,) * n_slices
+        if self.graphs and plan is not None:
+            return self._call_graphs(host, do, with_state, plan)
         bounds = [(B * i) // n_slices for i in range(n_slices + 1)]
+        if plan is not None:
+            bounds = [sum(plan[:i]) for i in range(len(plan) + 1)]
+            n_slices = len(plan)
         cur = torch.cuda.current_stream(dev)
         for s in (self.s_in, self.s_comp, self.s_out):
             s.wait_stream(cur)

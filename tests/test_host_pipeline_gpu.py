@@ -10,12 +10,16 @@ from delta_feedback_experiment_b200.synthetic import INPUT_NAMES, make_inputs
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("slices,with_state", [(2, True), (3, False), (8, True)])
-def test_streamed_step_matches_device_call(slices, with_state):
+@pytest.mark.parametrize("slices,with_state,B", [(2, True, 4), (3, False, 4), (8, True, 4), (8, True, 8),
+                                                 ((1, 3, 3, 1), True, 8)])
+def test_streamed_step_matches_device_call(slices, with_state, B):
+    """Slice counts that divide the batch replay a captured graph per slice (three buffer sets in turn:
+    with eight slices every set is used more than once); three slices of four rows take the eager path;
+    a plan of unequal slices keeps buffer sets and a captured step per slice size."""
     from delta_feedback_experiment_b200 import chunk_precond_kda
     from delta_feedback_experiment_b200.host_pipeline import HostStep
 
-    B, T, H, D = 4, 192, 2, 128
+    T, H, D = 192, 2, 128
     d = make_inputs(B, T, H, D, seed=91, dist="unit", dtype=torch.bfloat16, with_state=with_state)
     host = {n: d[n].pin_memory() for n in INPUT_NAMES}
     if with_state:

@@ -21,6 +21,13 @@ CUDA event pair around every kernel, and reported as ``eager_ms_per_step`` and
 ``cpu_baseline`` is the CPU oracle timed on this box's host cores on a bounded
 sample; ``decode`` reports the recurrent decode step (configuration 3) as
 achieved HBM GB/s.  ``--impl reference`` times the CPU implementation alone.
+The graph replays are repeated in rounds of K until the timed region is at least
+one second long (``consistency``).  Further legs of the line: ``e2e.copy_floor_ms``
+(the same pinned buffers copied with no kernels: each direction alone and both at
+once), ``small_batch`` (B=2 with 16 and 8 heads: the regime with fewer (row, head)
+units than SMs, where the state scans dominate), ``layer_ops`` (the operators next
+to the recurrence, an HBM roofline each) and, at N > 1, ``config4`` (benchmark
+configuration 4's per-GPU shape, B=16, T=8192, as max-over-ranks time).
 """
 
 from __future__ import annotations
@@ -65,8 +72,12 @@ STAGE_FLOPS = {
 # DRAM traffic per (token, head) of each kernel: dram__bytes_read.sum + dram__bytes_write.sum of one
 # ncu capture on the quarter-size workload (131,072 units), divided by its units; the traffic grows
 # in proportion to the units, so a launch of any size moves this many bytes per unit.
-STAGE_TRAFFIC_PER_UNIT = {"intra_fwd": 2212, "scan_fwd": 1251, "out_fwd": 1307, "scan_bwd": 1667,
-                          "intra_bwd": 4503}
+STAGE_TRAFFIC_PER_UNIT = {"intra_fwd": 2158, "scan_fwd": 1245, "out_fwd": 1280, "scan_bwd": 1661,
+                          "intra_bwd": 4496}
+# The kernel behind each stage name (tcgen05 / tensor-memory build; --legacy runs the mma.sync ones).
+STAGE_KERNEL = {"intra_fwd": "pkda_intra_fwd_tc_kernel", "scan_fwd": "pkda_scan_fwd_tc_kernel",
+                "out_fwd": "pkda_out_fwd_tc_kernel", "scan_bwd": "pkda_scan_bwd_tc_kernel",
+                "intra_bwd": "pkda_intra_bwd_tc_kernel"}
 DECODE_BYTES_PER_UNIT = 2 * 4 * 128 * 128 + 2 * 4 * 128 + 4 * 2 * 128 + 8 + 2 * 128   # 133,384
 
 
@@ -679,7 +690,8 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     achieved_tf = STAGE_FLOPS[top] * units / (top_ms * 1e-3) / 1e12
     peak_tf = pk["bf16_tflops_sustained"]
     roofline = {
-        "bound": "tensor", "kernel": f"pkda_{top}_kernel", "achieved": achieved_tf, "peak": peak_tf,
+        "bound": "tensor", "kernel": f"pkda_{top}_kernel" if top in args.legacy.split(",") else STAGE_KERNEL[top],
+        "achieved": achieved_tf, "peak": peak_tf,
         "unit": "TFLOP/s", "frac": achieved_tf / peak_tf,
         "traffic": STAGE_TRAFFIC_PER_UNIT[top] * units if D == 128 else None,
         "traffic_source": "ncu capture of a quarter-size launch, scaled by the units processed",

@@ -523,8 +523,9 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
                           "layer_ops": run_layer_ops(device, B, T, H, D, args.steps, args.warmup, pk)}), flush=True)
         return
 
-    for stage in filter(None, args.legacy.split(",")):
-        _lib.set_variant(stage, True)
+    for stage in filter(None, args.legacy.split(",")):  # "stage" (= the mma.sync kernel) or "stage=variant"
+        name, _, variant = stage.partition("=")
+        _lib.set_variant(name, int(variant) if variant else 1)
     d = make_inputs(B, T, H, D, seed=1000 + rank, dist=args.dist, dtype=torch.bfloat16, with_state=True)
     host = {n: d[n].pin_memory() for n in (*INPUT_NAMES, "do", "initial_state", "initial_A_state")}
     dev = {n: t.to(device) for n, t in host.items()}
@@ -685,6 +686,8 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     units = B * T * H  # (token, head) units one launch processes
     per_launch = {name: ms / n for name, (ms, n) in stages.items()}
     step_kernel_ms = sum(ms for ms, _ in stages.values()) / args.steps
+    if "out_fwd" not in stages:  # the state scan formed the output too: its products belong to that launch
+        STAGE_FLOPS["scan_fwd"] += STAGE_FLOPS["out_fwd"]
     top = max((n for n in stages if n in STAGE_FLOPS), key=lambda n: stages[n][0])
     top_ms = per_launch[top]
     achieved_tf = STAGE_FLOPS[top] * units / (top_ms * 1e-3) / 1e12

@@ -294,7 +294,9 @@ def set_direct_block_cap(cap: int) -> None:
     check(load().pkda_set_direct_block_cap(int(cap)), "pkda_set_direct_block_cap")
 
 
-def set_variant(stage: str, legacy: bool) -> None:
+def set_variant(stage: str, legacy) -> None:
     """Testing aid: pins the older mma.sync kernel of a stage (``"intra_fwd"``,
-    ``"scan_fwd"``, ``"out_fwd"``, ``"scan_bwd"``, ``"intra_bwd"``) or restores the default."""
-    check(load().pkda_set_variant(stage.encode(), 1 if legacy else 0), "pkda_set_variant")
+    ``"scan_fwd"``, ``"out_fwd"``, ``"scan_bwd"``, ``"intra_bwd"``) or restores the default.
+    ``set_variant("out_fwd", 2)`` runs the stand-alone tcgen05 output kernel instead of
+    letting the state scan produce the output."""
+    check(load().pkda_set_variant(stage.encode(), int(legacy)), "pkda_set_variant")

@@ -239,7 +239,7 @@ int pkda_set_variant(const char* stage, int variant) {
                           pkda::kStageIntraBwd};
   for (int s : two_impl)
     if (std::strcmp(stage, pkda_stage_name(s)) == 0) {
-      pkda::g_variant[s] = variant ? 1 : 0;
+      pkda::g_variant[s] = (s == pkda::kStageOutFwd && variant == 2) ? 2 : (variant ? 1 : 0);
       return PKDA_OK;
     }
   return PKDA_ERR_SHAPE;

@@ -465,7 +465,7 @@ int launch_out_fwd_tc(const Geo& geo, int total_tokens, const bf16* qg, const bf
 // tcgen05 / TMA forward state scan (pkda_scan_tc.cu): one CTA per (sequence, head).
 int launch_scan_fwd_tc(const Geo& geo, int total_tokens, int units, const bf16* w, const bf16* kg, const bf16* u,
                        const float* beta_c, const float* gc, const float* S0, bf16* h, bf16* v_new, float* ST,
-                       int* status, bool recompute, cudaStream_t st);
+                       int* status, bool recompute, const bf16* qg, const bf16* Aqk, bf16* o, cudaStream_t st);
 
 // tcgen05 / TMA reverse state scan of the backward (pkda_scan_bwd_tc.cu): one CTA per (sequence, head).
 int launch_scan_bwd_tc(const Geo& geo, int total_tokens, int units, const bf16* kg, const bf16* w, const bf16* qg,
@@ -476,9 +476,10 @@ int launch_scan_bwd_tc(const Geo& geo, int total_tokens, int units, const bf16* 
 int check_chunk_problem(const pkda_problem& p);
 int run_prologue(const pkda_problem& p, int* chunk_offsets, float* beta_c, Geo* geo, cudaStream_t st);
 // lists: room for chunks * heads ints (the forward's work list); counts: three zeroed ints.
+// o / o_done: the forward's output tensor; *o_done says whether the state scan has already written it.
 int run_forward_stages(const pkda_problem& p, const Geo& geo, const float* beta_c, bf16* u_ws, bf16* Aqk,
                        bf16* Akk, bf16* kt, float* gc, const float* a_start, bf16* w, bf16* kg, bf16* v_new,
                        bf16* h, bf16* qg, float* ST, bool recompute, int* status, int* lists, int* counts,
-                       cudaStream_t st);
+                       cudaStream_t st, bf16* o = nullptr, bool* o_done = nullptr);
 
 }  // namespace pkda

@@ -767,7 +767,8 @@ static int launch_scan_fwd(const ScanParams& sp, int units, cudaStream_t st) {
 int run_forward_stages(const pkda_problem& p, const Geo& geo, const float* beta_c, bf16* u_ws,
                        bf16* Aqk, bf16* Akk, bf16* kt, float* gc, const float* a_start,
                        bf16* w, bf16* kg, bf16* v_new, bf16* h, bf16* qg, float* ST,
-                       bool recompute, int* status, int* lists, int* counts, cudaStream_t st) {
+                       bool recompute, int* status, int* lists, int* counts, cudaStream_t st, bf16* o,
+                       bool* o_done) {
   const int chunks = geo.total_chunks;
   IntraParams ip;
   ip.geo = geo;
@@ -820,10 +821,16 @@ int run_forward_stages(const pkda_problem& p, const Geo& geo, const float* beta_
   int rc = PKDA_ERR_LAUNCH;
   // Full-width slices run on tcgen05 / TMEM / TMA unless the mma.sync kernel is pinned (pkda_set_variant).
   const bool scan_mma = stage_variant(kStageScanFwd) != 0;
+  // The tcgen05 scan also produces the output (it holds h and E of every chunk) unless a separate
+  // output kernel is asked for (pkda_set_variant("out_fwd", 1: mma.sync, 2: tcgen05)).
+  const bool fuse_out = o && !recompute && stage_variant(kStageOutFwd) == 0;
+  if (o_done) *o_done = false;
   begin_stage(kStageScanFwd, st);
-  if (vb == 128 && status && !scan_mma)
+  if (vb == 128 && status && !scan_mma) {
     rc = launch_scan_fwd_tc(geo, p.total_tokens, units, w, kg, u_ws, beta_c, gc, p.initial_state, h, v_new, ST,
-                            status, recompute, st);
+                            status, recompute, qg, Aqk, fuse_out ? o : nullptr, st);
+    if (o_done) *o_done = fuse_out;
+  }
   else if (vb == 128) rc = recompute ? launch_scan_fwd<128, true>(sp, units, st) : launch_scan_fwd<128, false>(sp, units, st);
   else if (vb == 64) rc = recompute ? launch_scan_fwd<64, true>(sp, units, st) : launch_scan_fwd<64, false>(sp, units, st);
   else rc = recompute ? launch_scan_fwd<32, true>(sp, units, st) : launch_scan_fwd<32, false>(sp, units, st);
@@ -874,15 +881,19 @@ int chunk_fwd(const pkda_chunk_fwd_args* a, cudaStream_t st) {
   PKDA_CHECK_LAUNCH();
 
   if (cudaMemsetAsync(ws.status, 0, 8 * sizeof(int), st) != cudaSuccess) return PKDA_ERR_LAUNCH;
+  bool o_done = false;
   rc = run_forward_stages(p, geo, ws.beta_c, ws.u, static_cast<bf16*>(a->Aqk), static_cast<bf16*>(a->Akk),
                           static_cast<bf16*>(a->k_precond), a->ac_atk, a->a_atk, static_cast<bf16*>(a->w),
                           static_cast<bf16*>(a->kg), static_cast<bf16*>(a->v_new), static_cast<bf16*>(a->h),
-                          static_cast<bf16*>(a->qg), a->final_state, false, ws.status, ws.lists, ws.status + 1, st);
+                          static_cast<bf16*>(a->qg), a->final_state, false, ws.status, ws.lists, ws.status + 1, st,
+                          static_cast<bf16*>(a->o), &o_done);
   if (rc != PKDA_OK) return rc;
 
-  // Output stage: tcgen05 + TMA unless the mma.sync kernel is pinned (pkda_set_variant).
+  // Output stage, when the scan has not produced o already: tcgen05 + TMA unless the mma.sync kernel is
+  // pinned (pkda_set_variant).
   const size_t guard_n = std::min<size_t>((size_t)p.total_tokens * p.heads * kD, 4096);
-  if (stage_variant(kStageOutFwd) == 0) {
+  if (o_done) return launch_status_guard(ws.status, a->o, nullptr, nullptr, guard_n, st);
+  if (stage_variant(kStageOutFwd) != 1) {
     rc = launch_out_fwd_tc(geo, p.total_tokens, static_cast<const bf16*>(a->qg), static_cast<const bf16*>(a->h),
                            static_cast<const bf16*>(a->Aqk), static_cast<const bf16*>(a->v_new), ws.beta_c,
                            static_cast<bf16*>(a->o), ws.status, st);

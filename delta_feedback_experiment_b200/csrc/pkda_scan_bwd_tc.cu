@@ -100,26 +100,32 @@ pkda_scan_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_kg, const __grid_
   tc::tmem_st_wait();
 
   const int last = sq.nchunks - 1;
-  auto prefetch = [&](int j) {  // thread 0 only; j counts processed chunks, chunk index = last - j
+  // A TMA instruction costs its thread about a hundred cycles and every thread is on the critical chain
+  // (the barriers wait for the slowest), so the copies of a chunk step are spread over the first lanes of
+  // the warps: eleven pieces of the next chunk's tiles (warps 5..7 take two), the halves of the d tile
+  // stored by warps 1, 2 and those of dF by warps 3, 4.  The bytes may land before thread 0 has armed the
+  // barrier: the phase cannot complete without its arrival.
+  auto prefetch_piece = [&](int j, int piece) {  // j counts processed chunks, chunk index = last - j
     const int i = last - j;
     const uint32_t st = base + (j % kStages) * kStage, bar = bar_full0 + 8 * (j % kStages);
     const int tok0 = sq.bos + i * kChunk;
     const size_t chh = (size_t)(sq.chunk0 + i) * H + h;
-    tc::mbar_expect_tx(bar, kTx);
-    tc::tma_load_3d(st + oKg, &tm_kg, bar, 0, h, tok0);
-    tc::tma_load_3d(st + oKg + 8192, &tm_kg, bar, 64, h, tok0);
-    tc::tma_load_3d(st + oDo, &tm_do, bar, 0, h, tok0);
-    tc::tma_load_3d(st + oDo + 8192, &tm_do, bar, 64, h, tok0);
-    tc::tma_load_3d(st + oP, &tm_p, bar, 0, h, tok0);
-    tc::tma_load_3d(st + oQg, &tm_qg, bar, 0, h, tok0);
-    tc::tma_load_3d(st + oQg + 8192, &tm_qg, bar, 64, h, tok0);
-    tc::tma_load_3d(st + oW, &tm_w, bar, 0, h, tok0);
-    tc::tma_load_3d(st + oW + 8192, &tm_w, bar, 64, h, tok0);
-    tc::bulk_load(st + oBeta, p.beta_c + chh * kChunk, 256, bar);
-    tc::bulk_load(st + oGc, p.gc + chh * kD, 512, bar);
+    switch (piece) {
+      case 0: tc::mbar_expect_tx(bar, kTx); tc::tma_load_3d(st + oKg, &tm_kg, bar, 0, h, tok0); break;
+      case 1: tc::tma_load_3d(st + oKg + 8192, &tm_kg, bar, 64, h, tok0); break;
+      case 2: tc::tma_load_3d(st + oDo, &tm_do, bar, 0, h, tok0); break;
+      case 3: tc::tma_load_3d(st + oDo + 8192, &tm_do, bar, 64, h, tok0); break;
+      case 4: tc::tma_load_3d(st + oP, &tm_p, bar, 0, h, tok0); break;
+      case 5: tc::tma_load_3d(st + oQg, &tm_qg, bar, 0, h, tok0);
+              tc::bulk_load(st + oBeta, p.beta_c + chh * kChunk, 256, bar); break;
+      case 6: tc::tma_load_3d(st + oQg + 8192, &tm_qg, bar, 64, h, tok0);
+              tc::bulk_load(st + oGc, p.gc + chh * kD, 512, bar); break;
+      default: tc::tma_load_3d(st + oW, &tm_w, bar, 0, h, tok0);
+               tc::tma_load_3d(st + oW + 8192, &tm_w, bar, 64, h, tok0); break;
+    }
   };
-  if (tid == 0) {
-    for (int j = 0; j < kStages - 1 && j < sq.nchunks; ++j) prefetch(j);
+  if (lane == 0) {
+    for (int j = 0; j < kStages - 1 && j < sq.nchunks; ++j) prefetch_piece(j, warp);
   }
 
   constexpr uint32_t idesc_dkg = tc::idesc_bf16(128, 64, true, false);    // d^T (MN) x kg (K)
@@ -135,12 +141,15 @@ pkda_scan_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_kg, const __grid_
     const int tok0 = sq.bos + i * kChunk;
     const int valid = min(kChunk, sq.len - i * kChunk);
     const size_t chh = (size_t)(sq.chunk0 + i) * H + h;
-    if (tid == 0) {
-      tc::bulk_wait_read();  // the previous chunk's stores have finished reading the d and dF tiles
-      if (j + kStages - 1 < sq.nchunks) prefetch(j + kStages - 1);  // into the stage the chunk before used
+    if (lane == 0) {
+      if (warp >= 1 && warp <= 4) tc::bulk_wait_read();  // this thread's store of the previous chunk has read its tile
+      if (j + kStages - 1 < sq.nchunks) prefetch_piece(j + kStages - 1, warp);  // into the stage the chunk before used
     }
-    ok = tc::mbar_wait(bar_full0 + 8 * stg, (j / kStages) & 1) && ok;
+    // (one warp polls each barrier, the others sleep in the barrier that follows: a polling warp takes
+    // issue slots and shared-memory bandwidth from whoever shares its scheduler)
+    if (warp == 0) ok = tc::mbar_wait(bar_full0 + 8 * stg, (j / kStages) & 1) && ok;
     if (__syncthreads_or(!ok)) { ok = false; break; }
+    tc::tc_fence_after();
     if (valid < kChunk) {  // ragged last chunk: no output cotangent past its end
       for (int idx = tid; idx < (kChunk - valid) * 16; idx += kThreads) {
         const int r = valid + (idx >> 4), pc = idx & 15;
@@ -174,12 +183,12 @@ pkda_scan_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_kg, const __grid_
     tc::fence_proxy_async();
     tc::tc_fence_before();
     __syncthreads();
+    if (lane == 0 && (warp == 1 || warp == 2)) {  // the d tile out, one half each
+      tc::tma_store_2d(&tm_dh, base + oD + (warp - 1) * 16384, 64 * (warp - 1), (int)(chh * kD));
+      tc::bulk_commit();
+    }
     if (tid == 0) {
       tc::tc_fence_after();
-      const int hrow = (int)(chh * kD);
-      tc::tma_store_2d(&tm_dh, base + oD, 0, hrow);
-      tc::tma_store_2d(&tm_dh, base + oD + 16384, 64, hrow);
-      tc::bulk_commit();
 #pragma unroll
       for (int kk = 0; kk < 8; ++kk) {  // d^T kg^T
         const uint64_t a = tc::desc_mnmajor(base + oD + kk * 2048, 16384);
@@ -200,9 +209,10 @@ pkda_scan_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_kg, const __grid_
         tc::umma_bf16(tmem, a, b, idesc_qdo, 1);
       }
     }
-    ok = tc::mbar_wait(bar_mma1, j & 1) && ok;
-    tc::tc_fence_after();
+    if (warp == 0) ok = tc::mbar_wait(bar_mma1, j & 1) && ok;
+    tc::tc_fence_before();
     if (__syncthreads_or(!ok)) { ok = false; break; }
+    tc::tc_fence_after();
 
     // b. dF^T sits in the accumulator (lane = value channel, column = token);  dE = -beta dF
     {
@@ -251,13 +261,12 @@ pkda_scan_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_kg, const __grid_
     tc::fence_proxy_async();
     tc::tc_fence_before();
     __syncthreads();
+    if (lane == 0 && (warp == 3 || warp == 4) && valid == kChunk) {
+      tc::tma_store_3d(&tm_df, base + oF + (warp - 3) * 8192, 64 * (warp - 3), h, tok0);
+      tc::bulk_commit();
+    }
     if (tid == 0) {
       tc::tc_fence_after();
-      if (valid == kChunk) {
-        tc::tma_store_3d(&tm_df, base + oF, 0, h, tok0);
-        tc::tma_store_3d(&tm_df, base + oF + 8192, 64, h, tok0);
-        tc::bulk_commit();
-      }
 #pragma unroll
       for (int kk = 0; kk < 4; ++kk) {  // dS += W^T dE
         const uint64_t a = tc::desc_mnmajor(st + oW + kk * 2048, 8192);
@@ -266,12 +275,13 @@ pkda_scan_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_kg, const __grid_
       }
       tc::umma_commit(bar_mma2);
     }
-    ok = tc::mbar_wait(bar_mma2, j & 1) && ok;
-    tc::tc_fence_after();
+    if (warp == 0) ok = tc::mbar_wait(bar_mma2, j & 1) && ok;
+    tc::tc_fence_before();  // (the barrier at the top of the next step, or the one after the loop, follows)
   }
   if (__syncthreads_or(!ok)) {
     if (tid == 0) atomicExch(p.status, 1);
   } else if (p.dS0) {
+    tc::tc_fence_after();
 #pragma unroll
     for (int jj = 0; jj < 2; ++jj) {
       float v[32];
@@ -283,7 +293,7 @@ pkda_scan_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_kg, const __grid_
             make_float4(v[e], v[e + 1], v[e + 2], v[e + 3]);
     }
   }
-  if (tid == 0) tc::bulk_wait_all();  // our stores must have left shared memory before the CTA exits
+  if (lane == 0 && warp >= 1 && warp <= 4) tc::bulk_wait_all();  // our stores must have left shared memory before the CTA exits
   tc::tc_fence_before();
   __syncthreads();
   if (warp == 0) tc::tmem_dealloc(tmem, kCols);

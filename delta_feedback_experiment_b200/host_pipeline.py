@@ -50,7 +50,7 @@ class HostStep:
     marks completion.
     """
 
-    def __init__(self, device, slices=4, lean: bool = False, graphs: bool = True):
+    def __init__(self, device, slices=4, lean: bool = False, graphs: bool = True, trace: bool = False):
         """``slices``: how many equal row slices to cut the batch into, or a sequence of row
         counts (summing to the batch), e.g. ``(1, 3, 3, 1)``: small slices at both ends keep the
         un-overlapped first copy-in and last copy-out short, large ones in between keep the
@@ -60,6 +60,8 @@ class HostStep:
         self.slices = int(slices) if isinstance(slices, int) else len(self.plan)
         self.lean = bool(lean)
         self.graphs = bool(graphs)
+        self.trace = bool(trace)  # graph mode: record events around every slice's three stages (see timeline())
+        self._marks = []
         self._slots = None      # graph mode: three sets of fixed device buffers with a captured step each
         self._slot_key = None
         self.s_in = torch.cuda.Stream(self.device)
@@ -153,21 +155,34 @@ class HostStep:
             params_ready.record(self.s_in)
         acc = None
         b1 = 0
+        self._marks = []
+
+        def mark(stream):
+            if not self.trace:
+                return None
+            e = torch.cuda.Event(enable_timing=True)
+            e.record(stream)
+            return e
+
+        t_origin = mark(cur)
         for i, rows_per in enumerate(plan):
             sl = self._slots[rows_per][used[rows_per] % 3]
             used[rows_per] += 1
             b0, b1 = b1, b1 + rows_per
             with torch.cuda.stream(self.s_in):
                 self.s_in.wait_event(sl["in_free"])       # the replay that last read these inputs is over
+                m0 = mark(self.s_in)
                 for n in self._names:
                     sl["rows"][n].copy_(src[n][b0:b1], non_blocking=True)
                     self.h2d_bytes += nbytes(sl["rows"][n])
                 sl["ready"].record(self.s_in)
+                m1 = mark(self.s_in)
             with torch.cuda.stream(self.s_comp):
                 if i == 0:
                     self.s_comp.wait_event(params_ready)
                 self.s_comp.wait_event(sl["ready"])
                 self.s_comp.wait_event(sl["out_free"])    # the copies that last read these outputs are over
+                m2 = mark(self.s_comp)
                 sl["graph"].replay()
                 head = sl["grads"][7:10]
                 if acc is None:
@@ -177,8 +192,10 @@ class HostStep:
                         a.add_(g)
                 sl["in_free"].record(self.s_comp)
                 sl["done"].record(self.s_comp)
+                m3 = mark(self.s_comp)
             with torch.cuda.stream(self.s_out):
                 self.s_out.wait_event(sl["done"])
+                m4 = mark(self.s_out)
                 pairs = [(out["o"][b0:b1], sl["o"])]
                 pairs += [(out["d" + n][b0:b1], g) for n, g in zip(ROW_INPUTS, sl["grads"][:7])]
                 if with_state:
@@ -188,6 +205,8 @@ class HostStep:
                     dst.copy_(g, non_blocking=True)
                     self.d2h_bytes += nbytes(g)
                 sl["out_free"].record(self.s_out)
+                if self.trace:
+                    self._marks.append((t_origin, m0, m1, m2, m3, m4, mark(self.s_out)))
         with torch.cuda.stream(self.s_out):
             self.s_out.wait_stream(self.s_comp)
             for n, g in zip(HEAD_PARAMS, acc):
@@ -196,6 +215,11 @@ class HostStep:
                 self.d2h_bytes += nbytes(g)
         cur.wait_stream(self.s_out)
         return out
+
+    def timeline(self):
+        """With ``trace=True``, after a synchronised call in graph mode: per slice the start and end
+        (ms after the call began) of its copy-in, its kernels and its copy-out, as six numbers."""
+        return [tuple(t0.elapsed_time(m) for m in rest) for t0, *rest in self._marks]
 
     def __call__(self, host: Dict[str, Tensor], do: Tensor) -> Dict[str, Tensor]:
         dev = self.device

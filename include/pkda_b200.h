@@ -249,6 +249,9 @@ int pkda_set_direct_block_cap(int cap);
  * pkda_set_variant(stage name as pkda_stage_name reports it, 1) pins the older
  * kernel for that stage, (.., 0) restores the default.  Stages with two
  * implementations: "intra_fwd", "scan_fwd", "out_fwd", "scan_bwd", "intra_bwd".
+ * "out_fwd" has three: by default the tcgen05 state scan produces the output
+ * itself (no output launch), 2 runs the stand-alone tcgen05 output kernel, 1 the
+ * mma.sync one.
  * Returns PKDA_ERR_SHAPE for any other name.  Process-wide; not thread-safe.
  */
 int pkda_set_variant(const char* stage, int variant);

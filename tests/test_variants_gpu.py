@@ -121,3 +121,38 @@ def test_mixed_chunks_take_their_own_kernel_bit_for_bit(legacy):
     assert rel_rms(first["o"], ref["o"]) < 0.005
     for n in ("q", "k", "v"):
         assert rel_rms(first["d" + n], ref["d" + n]) < RMS[n], n
+
+
+def test_output_from_the_scan_equals_the_stand_alone_output_kernel(legacy):
+    """By default the tcgen05 state scan also forms o (it holds the chunk-entry state and E of
+    every chunk); `set_variant("out_fwd", 2)` runs the stand-alone tcgen05 output kernel on
+    the h and v_new the scan stored.  Same operands, same products, same order: equal bits.
+    Ragged tails (T = 200) and packed sequences included."""
+    for B, T in ((8, 256), (8, 200)):
+        d, do, dS = _problem(B, T, 16, seed=47)
+        fused = _run(d, do, dS)
+        _lib.set_variant("out_fwd", 2)
+        split = _run(d, do, dS)
+        _lib.set_variant("out_fwd", 0)
+        for n in fused:
+            assert torch.equal(fused[n], split[n]), f"T={T} {n}"
+    # packed: 128 sequences x 1 head would be slow to build; 16 sequences x 8 heads = 128 units
+    from delta_feedback_experiment_b200.synthetic import packed_lengths
+    H = 8
+    offs = packed_lengths(16 * 150, 100, 200, seed=3)[:17]
+    total = offs[-1]
+    d = make_inputs(1, total, H, D, seed=49, dtype=torch.bfloat16, with_state=True, n_states=len(offs) - 1)
+    cu = torch.tensor(offs, dtype=torch.int32, device="cuda")
+
+    def run():
+        kw = {n: d[n].cuda() for n in INPUT_NAMES if n != "log_atk_scale"}
+        o, S, A = chunk_precond_kda(**kw, initial_state=d["initial_state"].cuda(),
+                                    initial_A_state=d["initial_A_state"].cuda(), output_final_state=True,
+                                    log_atk_scale=d["log_atk_scale"].cuda(), cu_seqlens=cu)
+        assert ops.last_device_status() == 0
+        return o, S
+    o1, S1 = run()
+    _lib.set_variant("out_fwd", 2)
+    o2, S2 = run()
+    _lib.set_variant("out_fwd", 0)
+    assert torch.equal(o1, o2) and torch.equal(S1, S2)

@@ -688,6 +688,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     step_kernel_ms = sum(ms for ms, _ in stages.values()) / args.steps
     if "out_fwd" not in stages:  # the state scan formed the output too: its products belong to that launch
         STAGE_FLOPS["scan_fwd"] += STAGE_FLOPS["out_fwd"]
+        STAGE_TRAFFIC_PER_UNIT["scan_fwd"] = 1898  # (ncu, same capture: 161.0 MB read + 87.8 MB written per 131,072 units)
     top = max((n for n in stages if n in STAGE_FLOPS), key=lambda n: stages[n][0])
     top_ms = per_launch[top]
     achieved_tf = STAGE_FLOPS[top] * units / (top_ms * 1e-3) / 1e12

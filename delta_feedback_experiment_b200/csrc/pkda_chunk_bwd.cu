@@ -1124,7 +1124,17 @@ pkda_atk_bwd_carry_kernel(Geo geo, const float* c_loc, const float* sa, float* l
 constexpr int kReduceSubs = 8;
 __global__ void __launch_bounds__(kD * kReduceSubs)
 pkda_param_reduce_kernel(Geo geo, const float* partA, const float* partB, const float* partC, float* dA_log,
-                         float* ddt_bias, float* dcentre) {
+                         float* ddt_bias, float* dcentre, const int* status, bf16* g0, bf16* g1, bf16* g2, size_t guard_n) {
+  // The backward's last kernel: if any kernel of the call gave up, the heads of dq, dk and dv become
+  // NaN, so that a caller who never reads the status word cannot take partial gradients for complete ones.
+  if (blockIdx.x == 0 && *status != 0) {
+    const bf16 nan = __float2bfloat16(__int_as_float(0x7fc00000));
+    for (size_t i = threadIdx.x; i < guard_n; i += blockDim.x) {
+      g0[i] = nan;
+      g1[i] = nan;
+      g2[i] = nan;
+    }
+  }
   __shared__ float sSub[kReduceSubs][kD];
   __shared__ float sR[2][4];
   const int h = blockIdx.x, H = geo.heads, tid = threadIdx.x, c = tid % kD, sub = tid / kD;
@@ -1358,11 +1368,12 @@ int chunk_bwd(const pkda_chunk_bwd_args* a, cudaStream_t st) {
   pkda_atk_bwd_kernel<true><<<atk_grid, atkb::kThreads, atkb::smem_bytes<true>(), st>>>(ap, atk_tiles);
   PKDA_CHECK_LAUNCH();
   begin_stage(kStageParamReduce, st);
-  pkda_param_reduce_kernel<<<p.heads, kD * kReduceSubs, 0, st>>>(geo, ws.partA, ws.partB, ws.partC, a->dA_log, a->ddt_bias,
-                                                   a->dlog_atk_scale);
-  PKDA_CHECK_LAUNCH();
   const size_t guard_n = std::min<size_t>((size_t)p.total_tokens * p.heads * kD, 4096);
-  return launch_status_guard(ws.status, a->dq, a->dk, a->dv, guard_n, st);
+  pkda_param_reduce_kernel<<<p.heads, kD * kReduceSubs, 0, st>>>(
+      geo, ws.partA, ws.partB, ws.partC, a->dA_log, a->ddt_bias, a->dlog_atk_scale, ws.status,
+      static_cast<bf16*>(a->dq), static_cast<bf16*>(a->dk), static_cast<bf16*>(a->dv), guard_n);
+  PKDA_CHECK_LAUNCH();
+  return PKDA_OK;
 }
 
 }  // namespace pkda

@@ -476,6 +476,14 @@ pkda_scan_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_c
   tc::tc_fence_before();
   __syncthreads();
   if (warp == 0) tc::tmem_dealloc(tmem, kCols);
+  // This is the forward's last kernel when it forms the output.  If any kernel of the call gave up
+  // (this CTA included), the first output row of this (sequence, head) becomes NaN, so that a caller
+  // who never reads the status word cannot take a partial result for a complete one.
+  if (kOut && warp == 1 && sq.len > 0 && *reinterpret_cast<volatile int*>(p.status) != 0) {
+    const bf16 nan = __float2bfloat16(__int_as_float(0x7fc00000));
+    bf16* row = p.o + ((size_t)sq.bos * H + h) * kD;
+    for (int c = lane; c < kD; c += 32) row[c] = nan;
+  }
 }
 
 int launch_scan_fwd_tc(const Geo& geo, int total_tokens, int units, const bf16* w, const bf16* kg, const bf16* u,

@@ -15,7 +15,7 @@
  * in a 32-bit status word at the end of the call's workspace
  * (pkda_chunk_fwd_status_offset / pkda_chunk_bwd_status_offset bytes from its
  * start; pkda_static_status_ptr for the static-scratch entry point), and the
- * last launch of the call overwrites the head of the call's outputs (o; dq, dk,
+ * last kernel of the call overwrites part of the call's outputs (o; dq, dk,
  * dv) with NaN, so that a failed call cannot pass for a result: it reaches the
  * caller's non-finite check.  The return value of the entry point itself only
  * reports host-side errors (the call does not synchronise).

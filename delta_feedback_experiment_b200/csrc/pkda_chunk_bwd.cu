@@ -264,7 +264,6 @@ __device__ __forceinline__ void epi_add(float (&acc)[1][4][4], float (&dG)[1][4]
 __device__ __forceinline__ void intra_bwd_item(const IntraBwdParams& p, const IntraBwdMaps& maps, int bx, int by) {
   using namespace ib;
   extern __shared__ __align__(128) unsigned char smem[];
-  PKDA_PHASE(0);
   bf16* sdO = reinterpret_cast<bf16*>(smem + oA0);
   bf16* sS0 = reinterpret_cast<bf16*>(smem + oA1);
   bf16* sE = reinterpret_cast<bf16*>(smem + oA1);
@@ -340,10 +339,10 @@ __device__ __forceinline__ void intra_bwd_item(const IntraBwdParams& p, const In
   if (tid < kChunk) sBeta[tid] = s_small;
   else if (tid >= 2 * kD && tid < 3 * kD) sGcv[tid - 2 * kD] = s_small;
   else if (tid >= kD && tid < 2 * kD) sBias[tid - kD] = s_small;
-  __syncthreads(); PKDA_PHASE(1);
+  __syncthreads();
   // log2-domain cumulative log-decay, exactly as the forward computes it
   gate_apply(graw, sG, valid, sBias, __expf(p.A_log[h]) * kLog2e, tid);
-  __syncthreads(); PKDA_PHASE(2);
+  __syncthreads();
   if (tid < kD) {
     gate_cumsum(sG, tid);
     float dmax[6];
@@ -360,7 +359,7 @@ __device__ __forceinline__ void intra_bwd_item(const IntraBwdParams& p, const In
   } else {
     cp_async_wait<0>();
   }
-  __syncthreads(); PKDA_PHASE(3);
+  __syncthreads();
   // the direct part of dbeta, rowsum(dF * E), while dF is still unscaled; dE = beta * dF in place;
   // hdh[k] = sum_v S0[k][v] dS1[k][v] (four threads per state row)
   for (int i = tid; i < kChunk * kD / 8; i += kThreads) {
@@ -404,7 +403,7 @@ __device__ __forceinline__ void intra_bwd_item(const IntraBwdParams& p, const In
     acc += __shfl_xor_sync(0xffffffffu, acc, 2);
     if (part == 0) sHdh[row] = acc;
   }
-  __syncthreads(); PKDA_PHASE(30);
+  __syncthreads();
 
   float dQ[1][4][4], dK[1][4][4], dKt[1][4][4], dG[1][4][4];
   float t[1][4][4];
@@ -431,7 +430,7 @@ __device__ __forceinline__ void intra_bwd_item(const IntraBwdParams& p, const In
       *reinterpret_cast<uint32_t*>(sdR + r * kLdD + c) = pk;
     }
   if (out_tma) tc::fence_proxy_async();
-  __syncthreads(); PKDA_PHASE(4);
+  __syncthreads();
   if (out_tma && tid == 0) {  // dv is the dR tile as it stands
     tc::tma_store_3d(&maps.dv, smem_u32(sdR), 0, h, tok0);
     tc::bulk_commit();
@@ -446,7 +445,7 @@ __device__ __forceinline__ void intra_bwd_item(const IntraBwdParams& p, const In
       const int i = 16 * I + gq + 8 * (e >> 1), c = 32 * cq + 8 * nt + 2 * tq + (e & 1);
       dK[0][nt][e] = -t[0][nt][e] * ex2(sG[i * kLdG + c]);
     }
-  __syncthreads(); PKDA_PHASE(5);  // S0 no longer needed
+  __syncthreads();  // S0 no longer needed
   // E moves into its operand tile (S0 has left it) and F = beta E into the dead dE tile
   for (int i = tid; i < kChunk * kD / 8; i += kThreads) {
     const int r = i >> 4, c = (i & 15) << 3;
@@ -463,7 +462,7 @@ __device__ __forceinline__ void intra_bwd_item(const IntraBwdParams& p, const In
     *reinterpret_cast<uint4*>(sE + r * kLdD + c) = ev;
     *reinterpret_cast<uint4*>(sF + r * kLdD + c) = bf;
   }
-  __syncthreads(); PKDA_PHASE(6);
+  __syncthreads();
   // pair-weight gradients: dM = -tril(dR E^T, -1) diag(beta),  dP = scale tril(dO F^T)
   {
     const int J = cq;
@@ -492,9 +491,8 @@ __device__ __forceinline__ void intra_bwd_item(const IntraBwdParams& p, const In
       }
   }
   if (out_tma && tid == 0) tc::bulk_wait_read();  // the dv store has read the dR tile
-  __syncthreads(); PKDA_PHASE(7);  // dO, dR, E no longer needed
+  __syncthreads();  // dO, dR, E no longer needed
   // dkg = F dS1^T  ->  dkt_a = exp(G_last - G) * dkg
-  PKDA_PHASE(8);
   // q, k and kt tiles of the pair-product phase land while the dkg product runs
   tile_load_async(reinterpret_cast<bf16*>(smem + oA0), kLdD, p.q + row0, gld, kChunk, kD, valid, kThreads);
   tile_load_async(reinterpret_cast<bf16*>(smem + oA1), kLdD, p.k + row0, gld, kChunk, kD, valid, kThreads);
@@ -509,7 +507,7 @@ __device__ __forceinline__ void intra_bwd_item(const IntraBwdParams& p, const In
       const int i = 16 * I + gq + 8 * (e >> 1), c = 32 * cq + 8 * nt + 2 * tq + (e & 1);
       dKt[0][nt][e] = t[0][nt][e] * ex2(sG[(kChunk - 1) * kLdG + c] - sG[i * kLdG + c]);
     }
-  __syncthreads(); PKDA_PHASE(9);
+  __syncthreads();
 
   // ================= phase B: gated pair products =================
   bf16* sQ = reinterpret_cast<bf16*>(smem + oA0);
@@ -519,7 +517,7 @@ __device__ __forceinline__ void intra_bwd_item(const IntraBwdParams& p, const In
   bf16* sXk = sXq + kChunk * kLdD;
   bf16* sY = sXk + kChunk * kLdD;
   cp_async_wait<0>();
-  __syncthreads(); PKDA_PHASE(10);
+  __syncthreads();
   {
     // dG starts from the state-coupled parts; column sums of kt * dkt_a feed the
     // chunk's last row (d/dG_last of exp(G_last - G_j)).
@@ -552,7 +550,7 @@ __device__ __forceinline__ void intra_bwd_item(const IntraBwdParams& p, const In
   // the staging tiles start from zeros rather than from whatever phase A left.
   for (int i = tid; i < 3 * kTileBytes / 16; i += kThreads)
     reinterpret_cast<uint4*>(smem + oStage)[i] = make_uint4(0, 0, 0, 0);
-  __syncthreads(); PKDA_PHASE(11);
+  __syncthreads();
   float rb[2] = {0.f, 0.f};
   // Direct level (lvl = 0) for pairs inside a b-block, hierarchy levels >= b for the rest.
   const int bdir = pick_direct_block(sWarpMax, 4, p.direct_cap);
@@ -561,7 +559,7 @@ __device__ __forceinline__ void intra_bwd_item(const IntraBwdParams& p, const In
     const int lvl = it ? (64 >> it) : 0;
     if (lvl && lvl < bdir) break;
     stage_level(sXq, sXk, sY, sQ, sK, sKt, sG, lvl, bdir, tid, kThreads, sFac);
-    __syncthreads(); PKDA_PHASE(12);
+    __syncthreads();
     const bool big = lvl >= 16;               // whole 16-row tiles are upper or lower: no masking
     const bool wide = !lvl && bdir >= 16;     // direct block made of whole tiles
     const int blk = lvl ? ((16 * I) & ~(2 * lvl - 1)) : ((16 * I) & ~(bdir - 1));
@@ -594,7 +592,7 @@ __device__ __forceinline__ void intra_bwd_item(const IntraBwdParams& p, const In
       if (lvl) epi_add<false>(dKt, dG, t, sFac, sY, -1.f, 16 * I + gq, 32 * cq + 2 * tq);
       else epi_add<true>(dKt, dG, t, sFac, sY, -1.f, 16 * I + gq, 32 * cq + 2 * tq);
     }
-    __syncthreads(); PKDA_PHASE(13);
+    __syncthreads();
   }
   // ungated diagonal of P
 #pragma unroll
@@ -645,7 +643,7 @@ __device__ __forceinline__ void intra_bwd_item(const IntraBwdParams& p, const In
         *reinterpret_cast<float2*>(sdG + i * kLdG + c) = make_float2(dG[0][nt][2 * half], dG[0][nt][2 * half + 1]);
       }
   }
-  __syncthreads(); PKDA_PHASE(14);
+  __syncthreads();
   if (out_tma) {
     // every warp is past its reads of q and kt: their tiles take dq and dk_read
     if (tid == 0) {
@@ -690,7 +688,7 @@ __device__ __forceinline__ void intra_bwd_item(const IntraBwdParams& p, const In
       sdG[r * kLdG + c] = run;
     }
   }
-  __syncthreads(); PKDA_PHASE(15);
+  __syncthreads();
   if (out_tma && tid == 0) {
     tc::tma_store_3d(&maps.dq, smem_u32(sQ), 0, h, tok0);
     tc::tma_store_3d(&maps.dk_read, smem_u32(smem + oA1), 0, h, tok0);
@@ -742,7 +740,7 @@ __device__ __forceinline__ void intra_bwd_item(const IntraBwdParams& p, const In
     for (int o = 16; o >= 1; o >>= 1) pa += __shfl_xor_sync(0xffffffffu, pa, o);
     if (lane == 0) sRed[warp] = pa;
   }
-  __syncthreads(); PKDA_PHASE(16);
+  __syncthreads();
   if (tid < kD) {
     float acc = 0.f;
 #pragma unroll 8
@@ -757,7 +755,6 @@ __device__ __forceinline__ void intra_bwd_item(const IntraBwdParams& p, const In
     if (out_tma) tc::bulk_wait_read();  // the tiles stay in place until the stores have read them
     if (by_tma) tc::mbar_inval(bar);    // a CTA that walks a work list sets the barrier up anew per item
   }
-  PKDA_PHASE(17);
 }
 
 // grid (chunks, heads): one item per CTA; or, with a work list, a few persistent CTAs that walk it.
@@ -1378,8 +1375,3 @@ int chunk_bwd(const pkda_chunk_bwd_args* a, cudaStream_t st) {
 
 }  // namespace pkda
 
-#ifdef PKDA_PHASE_PROFILE
-extern "C" int pkda_phase_prof_bwd(long long* out) {
-  return cudaMemcpyFromSymbol(out, g_phase_prof, sizeof(long long) * 64) == cudaSuccess ? 0 : 1;
-}
-#endif

@@ -167,7 +167,6 @@ template <bool kRecompute>
 __device__ __forceinline__ void intra_fwd_item(const IntraParams& p, int bx, int by) {
   using namespace intra;
   extern __shared__ __align__(128) unsigned char smem[];
-  PKDA_PHASE(0);
   bf16* sQ = reinterpret_cast<bf16*>(smem + oQ);
   bf16* sK = reinterpret_cast<bf16*>(smem + oK);
   bf16* sKt = reinterpret_cast<bf16*>(smem + oKt);
@@ -229,13 +228,13 @@ __device__ __forceinline__ void intra_fwd_item(const IntraParams& p, int bx, int
   }
   // zero the P staging tile (upper triangle must read as zero)
   for (int i = tid; i < kChunk * kLdC / 8; i += kThreads) reinterpret_cast<uint4*>(sTmb)[i] = make_uint4(0, 0, 0, 0);
-  __syncthreads(); PKDA_PHASE(1);
+  __syncthreads();
 
   // ---- 2. decay gate (elementwise, all threads; the q and k tiles are still landing), then
   // the two per-channel sequential passes side by side: cumulative sum | preconditioner recurrence A_t
   gate_apply(graw, sG, valid, sBias, __expf(a_log) * kLog2e, tid);
   cp_async_wait<0>();
-  __syncthreads(); PKDA_PHASE(2);
+  __syncthreads();
   if (tid < kD) {
     gate_cumsum(sG, tid);
     float dmax[6];
@@ -256,7 +255,7 @@ __device__ __forceinline__ void intra_fwd_item(const IntraParams& p, int bx, int
       sAt[r * kLdG + c] = A;
     }
   }
-  __syncthreads(); PKDA_PHASE(3);
+  __syncthreads();
   if (!kRecompute) {
     // write keys kt = k * exp(-ln(x) * dev / (1 + |dev|)), dev = log(A + eps) - centre
     for (int idx = tid; idx < kChunk * kD / 8; idx += kThreads) {
@@ -275,7 +274,7 @@ __device__ __forceinline__ void intra_fwd_item(const IntraParams& p, int bx, int
       *reinterpret_cast<uint4*>(sKt + r * kLdD + c8) = x;
       if (r < valid) *reinterpret_cast<uint4*>(p.kt + row0 + (size_t)r * gld + c8) = x;
     }
-    __syncthreads(); PKDA_PHASE(4);
+    __syncthreads();
   }
 
   // ---- 3. gated pair products, level by level.
@@ -300,7 +299,7 @@ __device__ __forceinline__ void intra_fwd_item(const IntraParams& p, int bx, int
     const int lvl = it ? (64 >> it) : 0;  // 0 (direct), 32, 16, 8, 4, 2, 1
     if (lvl && lvl < bdir) break;
     stage_level(sXq, sXk, sY, sQ, sK, sKt, sG, lvl, bdir, tid, kThreads);
-    __syncthreads(); PKDA_PHASE(5);
+    __syncthreads();
     const bf16* X = mat ? sXq : sXk;
     float tmp[1][2][4];
     if (!diagw) {
@@ -334,7 +333,7 @@ __device__ __forceinline__ void intra_fwd_item(const IntraParams& p, int bx, int
           if (pair_ok(i, j, lvl, bdir)) accA[nt][e] += tmp[0][nt][e];
         }
     }
-    __syncthreads(); PKDA_PHASE(6);
+    __syncthreads();
   }
   if (diagw && mat == 1) {  // diagonal of P: ungated q_i . kt_i
     float tmp[1][2][4];
@@ -352,7 +351,7 @@ __device__ __forceinline__ void intra_fwd_item(const IntraParams& p, int bx, int
 
   // ---- 4. P -> bf16 staging tile (scaled) ; L = tril(M,-1) diag(beta) -> smem fp32
   for (int i = tid; i < kChunk * kLdL; i += kThreads) sL[i] = 0.f;
-  __syncthreads(); PKDA_PHASE(7);
+  __syncthreads();
   {
     auto putP = [&](int i, int j, float v) { if (j <= i) sTmb[i * kLdC + j] = __float2bfloat16(v * p.scale); };
     auto putL = [&](int i, int j, float v) { if (j < i) sL[i * kLdL + j] = v * sBeta[j]; };
@@ -365,7 +364,7 @@ __device__ __forceinline__ void intra_fwd_item(const IntraParams& p, int bx, int
       }
     }
   }
-  __syncthreads(); PKDA_PHASE(8);
+  __syncthreads();
   if (!kRecompute) {
     for (int i = tid; i < kChunk * kChunk / 8; i += kThreads) {
       const int r = i >> 3, c8 = (i & 7) << 3;
@@ -384,7 +383,7 @@ __device__ __forceinline__ void intra_fwd_item(const IntraParams& p, int bx, int
     if (!kRecompute && r < valid)
       *reinterpret_cast<uint32_t*>(p.Akk + ((size_t)(tok0 + r) * H + h) * kChunk + c2) = pk;
   }
-  __syncthreads(); PKDA_PHASE(9);
+  __syncthreads();
 
   // ---- 6. decayed operands: Kd -> smem; qg, kg, gc -> global; V tile -> smem
   bf16* sKd = sXq;
@@ -424,7 +423,7 @@ __device__ __forceinline__ void intra_fwd_item(const IntraParams& p, int bx, int
     }
   }
   cp_async_wait<0>();
-  __syncthreads(); PKDA_PHASE(10);
+  __syncthreads();
 
   // ---- 7. W = Tm Kd, U = Tm V   (warp: matrix = warp>>3, rows 16*((warp>>1)&3), column half warp&1)
   {
@@ -443,7 +442,6 @@ __device__ __forceinline__ void intra_fwd_item(const IntraParams& p, int bx, int
               pack_bf16(acc2[0][nt][2 * half], acc2[0][nt][2 * half + 1]);
       }
   }
-  PKDA_PHASE(11);
 }
 
 // grid (chunks, heads): one item per CTA; or, with a work list, a few persistent CTAs that walk it.
@@ -559,7 +557,6 @@ pkda_scan_fwd_kernel(const ScanParams p) {
     const int valid = min(kChunk, sq.len - i * kChunk);
     const size_t chh = (size_t)(sq.chunk0 + i) * H + h;
 
-    PKDA_SCAN_PHASE(i, 0);
     // a. chunk-entry state -> bf16 operand tile (and the saved chunk states)
 #pragma unroll
     for (int mt = 0; mt < 2; ++mt)
@@ -571,7 +568,6 @@ pkda_scan_fwd_kernel(const ScanParams p) {
           *reinterpret_cast<uint32_t*>(sH + r * ldv + c) = pack_bf16(S[mt][nt][2 * half], S[mt][nt][2 * half + 1]);
         }
     __syncthreads();  // sH complete; stage i landed for every thread
-    PKDA_SCAN_PHASE(i, 1);
     {
       constexpr int cpr = VB / 8;
       for (int j = tid; j < kD * cpr; j += kT) {
@@ -600,7 +596,6 @@ pkda_scan_fwd_kernel(const ScanParams p) {
         }
     }
     __syncthreads();
-    PKDA_SCAN_PHASE(i, 2);
     // c. S <- Gam_last * S + kg^T F
 #pragma unroll
     for (int mt = 0; mt < 2; ++mt)
@@ -615,7 +610,6 @@ pkda_scan_fwd_kernel(const ScanParams p) {
       }
     warp_gemm<2, NT, true, true>(S, sKg, kLdD, 32 * wr, sF, ldv, c0, 0, kChunk);
     __syncthreads();  // everyone done with stage i and sF before they are refilled
-    PKDA_SCAN_PHASE(i, 3);
   }
   cp_async_wait<0>();
   if (!kRecompute && p.ST) {
@@ -914,8 +908,3 @@ int chunk_fwd(const pkda_chunk_fwd_args* a, cudaStream_t st) {
 
 }  // namespace pkda
 
-#ifdef PKDA_PHASE_PROFILE
-extern "C" int pkda_phase_prof_fwd(long long* out) {
-  return cudaMemcpyFromSymbol(out, g_phase_prof, sizeof(long long) * 64) == cudaSuccess ? 0 : 1;
-}
-#endif

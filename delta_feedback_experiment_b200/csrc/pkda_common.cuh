@@ -14,37 +14,6 @@
 
 #include "../../include/pkda_b200.h"
 
-// Optional phase timestamps (development builds only, -DPKDA_PHASE_PROFILE): one
-// CTA records clock64() at numbered points of a kernel.
-#ifdef PKDA_PHASE_PROFILE
-static __device__ long long g_phase_prof[64];
-#define PKDA_PHASE(k)                                                                   \
-  do {                                                                                  \
-    if (threadIdx.x == 0 && blockIdx.x == 300 && blockIdx.y == 3) g_phase_prof[k] = clock64(); \
-  } while (0)
-#define PKDA_SCAN_PHASE(i, k)                                                            \
-  do {                                                                                  \
-    if (threadIdx.x == 0 && blockIdx.x == 37 && (i) >= 10 && (i) < 12) g_phase_prof[32 + 4 * ((i) - 10) + (k)] = clock64(); \
-  } while (0)
-#define PKDA_SCANTC_PHASE(i, k)                                                          \
-  do {                                                                                  \
-    if (threadIdx.x == 0 && blockIdx.x == 37 && (i) >= 10 && (i) < 12) g_phase_prof[6 * ((i) - 10) + (k)] = clock64(); \
-  } while (0)
-#define PKDA_SCANTC_SUB(i, k)                                                            \
-  do {                                                                                  \
-    if (threadIdx.x == 0 && blockIdx.x == 37 && (i) >= 10 && (i) < 12) g_phase_prof[12 + 6 * ((i) - 10) + (k)] = clock64(); \
-  } while (0)
-#define PKDA_OUT_SUB(i, k)                                                               \
-  do {                                                                                  \
-    if (threadIdx.x == 288 && blockIdx.x == 37 && (i) >= 10 && (i) < 12) g_phase_prof[24 + 10 * ((i) - 10) + (k)] = clock64(); \
-  } while (0)
-#else
-#define PKDA_OUT_SUB(i, k)
-#define PKDA_SCANTC_SUB(i, k)
-#define PKDA_PHASE(k)
-#define PKDA_SCAN_PHASE(i, k)
-#define PKDA_SCANTC_PHASE(i, k)
-#endif
 
 namespace pkda {
 

@@ -40,13 +40,6 @@
 #include "pkda_chunk.cuh"
 #include "pkda_tc.cuh"
 
-#ifdef PKDA_PHASE_PROFILE
-#undef PKDA_PHASE
-#define PKDA_PHASE(k)                                                                             \
-  do {                                                                                            \
-    if (threadIdx.x == 0 && blockIdx.x == 37 && item == 37 + 10 * (int)gridDim.x) g_phase_prof[k] = clock64(); \
-  } while (0)
-#endif
 
 namespace pkda {
 
@@ -257,7 +250,6 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
 
 #pragma unroll 1
   for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
-  PKDA_PHASE(0);
   const int chh = chh_n;
   const int h = chh % H;
   int n, tok0, valid;
@@ -271,7 +263,6 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
   // stops the compiler from computing all sixty of them ahead of the loop and holding them in registers.
   uint32_t dbase = base;
   asm volatile("" : "+r"(dbase));
-  PKDA_PHASE(1);
 
   // ---- 1. T <- diag(beta) T (row j scaled by beta_j: the beta of dE = beta dF moves onto T), then dR^T
   ok = tc::mbar_wait(barB, ld_phase) && ok;
@@ -289,7 +280,7 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
     *piece = x;
   }
   tc::fence_proxy_async();
-  __syncthreads(); PKDA_PHASE(2);
+  __syncthreads();
   if (tid == 0) {
     tc::tc_fence_after();
     constexpr uint32_t idesc = tc::idesc_bf16(128, 64, true, true);
@@ -313,7 +304,7 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
     }
     sX1[sl * kD + c] = run;
   }
-  __syncthreads(); PKDA_PHASE(3);
+  __syncthreads();
   {
     float pre = 0.f;
 #pragma unroll
@@ -344,7 +335,6 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
   ok = tc::mbar_wait(barM, m_phase) && ok;
   m_phase ^= 1;
   tc::tc_fence_after();
-  PKDA_PHASE(4);
   {
     float acc[16];
     tc::tmem_ld16(tmem + lane_addr + cR + j0, acc);
@@ -354,7 +344,7 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
   }
   tc::fence_proxy_async();
   tc::tc_fence_before();
-  __syncthreads(); PKDA_PHASE(5);
+  __syncthreads();
   if (tid == 0) {
     tc::tc_fence_after();
     tc::tma_store_3d(&maps.dv, base + oStk, 0, h, tok0);
@@ -408,7 +398,6 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
   ok = tc::mbar_wait(barM, m_phase) && ok;
   m_phase ^= 1;
   tc::tc_fence_after();
-  PKDA_PHASE(6);
   {
     float acc[16];
     tc::tmem_ld16(tmem + lane_addr + cStk + j0, acc);
@@ -430,7 +419,7 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
   }
   tc::fence_proxy_async();  // also covers the gated operands written in step 2
   tc::tc_fence_before();
-  __syncthreads(); PKDA_PHASE(7);
+  __syncthreads();
   if (tid == 0) {
     tc::tc_fence_after();
     // the raw k tile comes back into the (dead) entry-state tile for the preconditioner's backward
@@ -457,7 +446,6 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
   ok = tc::mbar_wait(barM, m_phase) && ok;
   m_phase ^= 1;
   tc::tc_fence_after();
-  PKDA_PHASE(8);
 
   // ---- 5a. preconditioner state at the start of this thread's token slice: zero-start scan of the slice,
   // one exchange, then the slices before it folded in (a slice's decay product is the same for all channels)
@@ -576,7 +564,7 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
   tc::tc_fence_before();
   tc::fence_proxy_async();  // this item's last reads of the operand tiles come before the next item's copies
   if (tid == 0 && item + (int)gridDim.x < n_items) arm();
-  __syncthreads(); PKDA_PHASE(9);
+  __syncthreads();
   // every tile except the stack rows the dv store is reading is free: the next item's tiles start to
   // arrive while the gate's backward runs
   if (item + (int)gridDim.x < n_items) {
@@ -615,7 +603,7 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
   if (tid < kChunk)
     p.dbeta[(size_t)(tok0 + tid) * H + h] =
         __float2bfloat16(sDb[tid] + sDb[kChunk + tid] + sDb[2 * kChunk + tid] + sDb[3 * kChunk + tid]);
-  __syncthreads(); PKDA_PHASE(10);
+  __syncthreads();
   if (tid < kD) {
     p.partB[(size_t)chh * kD + tid] = sX5[tid] + sX5[kD + tid] + sX5[2 * kD + tid] + sX5[3 * kD + tid];
     p.c_loc[(size_t)chh * kD + tid] = sX6[tid] + sX6[kD + tid] + sX6[2 * kD + tid] + sX6[3 * kD + tid];
@@ -632,7 +620,6 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
     tc::bulk_wait_read();  // the dv store has read the stack rows the next item's dR overwrites
   }
   __syncthreads();  // the exchange arrays and beta are rewritten by the next item
-  PKDA_PHASE(11);
   }  // item loop
   if (__syncthreads_or(!ok) && tid == 0) atomicExch(p.status, 1);
   tc::tc_fence_before();
@@ -683,8 +670,3 @@ int launch_intra_bwd_tc(const IntraBwdParams& ip, cudaStream_t st) {
 
 }  // namespace pkda
 
-#ifdef PKDA_PHASE_PROFILE
-extern "C" int pkda_phase_prof_ibtc(long long* out) {
-  return cudaMemcpyFromSymbol(out, g_phase_prof, sizeof(long long) * 64) == cudaSuccess ? 0 : 1;
-}
-#endif

@@ -32,13 +32,6 @@
 #include "pkda_chunk.cuh"
 #include "pkda_tc.cuh"
 
-#ifdef PKDA_PHASE_PROFILE
-#undef PKDA_PHASE
-#define PKDA_PHASE(k)                                                                             \
-  do {                                                                                            \
-    if (threadIdx.x == 0 && item == 3000) g_phase_prof[k] = clock64();                               \
-  } while (0)
-#endif
 
 namespace pkda {
 
@@ -138,7 +131,6 @@ pkda_intra_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_
   int item = s_next;
 #pragma unroll 1
   while (item < n_items) {
-  PKDA_PHASE(0);
   const int h = item % H;
   int n, tok0, valid;
   if (!chunk_lookup(p.geo, item / H, n, tok0, valid)) break;  // past the last real chunk of a packed batch (items ascend)
@@ -193,7 +185,6 @@ pkda_intra_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_
     centre = p.log_atk_scale[h];
   }
   cp_async_wait<0>();
-  PKDA_PHASE(1);
 
   // ---- 1. decay gate, strip-local cumulative sum; strip-local preconditioner scan from zero
   float G[8][4];
@@ -227,7 +218,7 @@ pkda_intra_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_
   }
   *reinterpret_cast<float4*>(sTot + warp * kD + c4) = make_float4(G[7][0], G[7][1], G[7][2], G[7][3]);
   if (lane < 8) sBeta[r0 + lane] = sc_beta;
-  __syncthreads(); PKDA_PHASE(2);
+  __syncthreads();
 
   // ---- 2. prefixes over the strips: cumulative decay of every row, and of the chunk's last row
   float Glast[4];
@@ -337,7 +328,7 @@ pkda_intra_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_
   }
   tc::fence_proxy_async();
   tc::tc_fence_before();
-  __syncthreads(); PKDA_PHASE(3);  // (the strip exchange arrays are dead from here on: L takes their place)
+  __syncthreads();  // (the strip exchange arrays are dead from here on: L takes their place)
   if (!kRecompute) {
     if (tid == 0) {
       tc::tc_fence_after();
@@ -353,7 +344,6 @@ pkda_intra_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_
     ok = tc::mbar_wait(bar_mma, mma_phase) && ok;
     mma_phase ^= 1;
     tc::tc_fence_after();
-    PKDA_PHASE(4);
     {
       float acc[32];
       tc::tmem_ld32(tmem + ((uint32_t)(32 * (warp & 3)) << 16) + j0, acc);
@@ -378,7 +368,6 @@ pkda_intra_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_
       }
     }
     tc::tc_fence_before();
-    PKDA_PHASE(5);
   }
   ok = tc::mbar_wait(bar_tma, tma_phase) && ok;  // V (and T) landed long ago
   tma_phase ^= 1;
@@ -390,7 +379,7 @@ pkda_intra_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_
     }
   }
   tc::fence_proxy_async();
-  __syncthreads(); PKDA_PHASE(6);
+  __syncthreads();
 
   if (!kRecompute) {
     // ---- 5. scaled P -> Aqk;  T = (I + L)^-1 -> bf16 operand tile and Akk
@@ -409,7 +398,6 @@ pkda_intra_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_
     }
     float* sT = reinterpret_cast<float*>(tiles + oT);
     unit_lower_inverse_64(sL, sT, reinterpret_cast<float*>(tiles + oY2), kLdL, tid, kThreads);  // ends with a barrier
-    PKDA_PHASE(7);
     for (int idx = tid; idx < kChunk * 8; idx += kThreads) {
       const int r = idx >> 3, pc = idx & 7;
       const float* src = sT + r * kLdL + 8 * pc;
@@ -421,7 +409,7 @@ pkda_intra_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_
     }
     tc::fence_proxy_async();
     tc::tc_fence_before();
-    __syncthreads(); PKDA_PHASE(8);
+    __syncthreads();
   }
 
   // ---- 6. W^T = Kd^T T^T, U^T = V^T T^T
@@ -445,7 +433,6 @@ pkda_intra_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_
   ok = tc::mbar_wait(bar_mma, mma_phase) && ok;
   mma_phase ^= 1;
   tc::tc_fence_after();
-  PKDA_PHASE(9);
   {
     const int ch = 32 * (warp & 3) + lane, t0 = 32 * (warp >> 2);  // accumulator row = channel; this warp's tokens
 #pragma unroll
@@ -468,7 +455,7 @@ pkda_intra_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_
   }
   tc::fence_proxy_async();
   tc::tc_fence_before();
-  __syncthreads(); PKDA_PHASE(10);
+  __syncthreads();
   if (tid == 0) {
     if (full) {
       tc::tma_store_3d(&tm_w, base + oA, 0, h, tok0);
@@ -481,7 +468,6 @@ pkda_intra_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_
     s_next = atomicAdd(p.counts, 1);
   }
   __syncthreads();  // the next item's copies overwrite the tiles
-  PKDA_PHASE(11);
   item = s_next;
   }  // item loop
   if (__syncthreads_or(!ok) && tid == 0) atomicExch(p.status, 1);
@@ -530,8 +516,3 @@ int launch_intra_fwd_tc(const IntraParams& ip, bool recompute, cudaStream_t st) 
 
 }  // namespace pkda
 
-#ifdef PKDA_PHASE_PROFILE
-extern "C" int pkda_phase_prof_intratc(long long* out) {
-  return cudaMemcpyFromSymbol(out, g_phase_prof, sizeof(long long) * 64) == cudaSuccess ? 0 : 1;
-}
-#endif

@@ -174,7 +174,6 @@ pkda_scan_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_c
       unsigned char* qpp = tiles + oQP + (i & 1) * kQP;
       const int tok0 = sq.bos + i * kChunk;
       const int valid = min(kChunk, sq.len - i * kChunk);
-      PKDA_OUT_SUB(i, 0);
       // qg and P of this chunk were requested a chunk step ago: one poll each
       ok = tc::mbar_wait(bar_qp0 + 8 * (i & 1), (i >> 1) & 1) && ok;
       if (issuer_warp) {
@@ -182,7 +181,6 @@ pkda_scan_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_c
           // the other buffer was last read by the products of chunk i - 1, which this thread saw complete
           if (i + 1 < sq.nchunks) fetch(i + 1);
           ok = tc::mbar_wait(bar_hready, i & 1) && ok;  // h of this chunk stands in its tile
-          PKDA_OUT_SUB(i, 1);
           if (ok) {
             tc::tc_fence_after();  // (the accumulator is free: all four warps read it before the barrier after the read)
 #pragma unroll
@@ -191,7 +189,6 @@ pkda_scan_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_c
                             tc::desc_kmajor(qp + (kk >> 2) * 8192 + (kk & 3) * 32), idesc_o, kk > 0);
             tc::umma_commit(bar_o1);
           }
-          PKDA_OUT_SUB(i, 2);
         }
         __syncwarp();
       } else {
@@ -213,10 +210,8 @@ pkda_scan_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_c
         tc::fence_proxy_async();
       }
       if (out_sync_or(!ok)) { ok = false; break; }
-      PKDA_OUT_SUB(i, 3);
       if (issuer) {
         ok = tc::mbar_wait(bar_eready, i & 1) && ok;  // E of this chunk stands in its tile
-        PKDA_OUT_SUB(i, 4);
         if (ok) {
           tc::tc_fence_after();
 #pragma unroll
@@ -226,18 +221,15 @@ pkda_scan_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_c
           tc::umma_commit(bar_o);
           ok = tc::mbar_wait(bar_o, i & 1) && ok;
         }
-        PKDA_OUT_SUB(i, 5);
       }
       if (out_sync_or(!ok)) { ok = false; break; }
       tc::tc_fence_after();
-      PKDA_OUT_SUB(i, 6);
       float acc0[32], acc1[32];
       tc::tmem_ld32(tO, acc0);
       tc::tmem_ld32(tO + 32, acc1);
       tc::tmem_ld_wait();
       tc::tc_fence_before();
       out_sync_or(false);  // all four warps hold their part: the next chunk's first product may overwrite the accumulator
-      PKDA_OUT_SUB(i, 7);
       bf16* dst = p.o + ((size_t)tok0 * H + h) * kD + L;
       const size_t gld = (size_t)H * kD;
       if (valid == kChunk) {
@@ -262,7 +254,6 @@ pkda_scan_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_c
         for (int t = 0; t < 32; ++t)
           if (32 + t < valid) dst[(32 + t) * gld] = __float2bfloat16(acc1[t]);
       }
-      PKDA_OUT_SUB(i, 8);
     }
     if (!ok && issuer) atomicExch(p.status, 1);
   } else {
@@ -318,23 +309,18 @@ pkda_scan_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_c
     const int tok0 = sq.bos + i * kChunk;
     const int valid = min(kChunk, sq.len - i * kChunk);
     const size_t chh = (size_t)(sq.chunk0 + i) * H + h;
-    PKDA_SCANTC_PHASE(i, 0);
     if (lane == 0) {
       if (warp >= 1 && warp <= 4) tc::bulk_wait_read();  // this thread's store of the previous chunk has read its tile
       if (i + kStages - 1 < sq.nchunks) prefetch_piece(i + kStages - 1, warp);  // into the stage chunk i-1 used
     }
-    PKDA_SCANTC_SUB(i, 1);
     // (one warp polls each barrier; the others sleep in the named barrier that follows: a polling warp
     // takes issue slots and shared-memory bandwidth from whoever shares its scheduler)
     if (warp == 0) ok = tc::mbar_wait(bar_full0 + 8 * stg, (i / kStages) & 1) && ok;
-    PKDA_SCANTC_SUB(i, 2);
     // The h tile is rewritten below: the output's first product of the previous chunk, queued most of a
     // chunk step ago, must have read it.
     if (kOut && warp == 0 && i > 0) ok = tc::mbar_wait(bar_o1, (i - 1) & 1) && ok;
-    PKDA_SCANTC_SUB(i, 3);
     if (scan_sync_or(!ok)) { ok = false; break; }
     tc::tc_fence_after();
-    PKDA_SCANTC_PHASE(i, 1);
 
     // a. h = bf16(S) -> operand tile; S *= Gam_last
     {
@@ -362,7 +348,6 @@ pkda_scan_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_c
     tc::fence_proxy_async();
     tc::tc_fence_before();
     scan_sync();
-    PKDA_SCANTC_PHASE(i, 2);
     if (lane == 0 && (warp == 1 || warp == 2)) {  // the state tile out, one half each
       tc::tma_store_2d(&tm_h, base + oH + (warp - 1) * 16384, 64 * (warp - 1), (int)(chh * kD));
       tc::bulk_commit();
@@ -390,7 +375,6 @@ pkda_scan_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_c
     if (kOut && warp == 0 && i > 0) ok = tc::mbar_wait(bar_o, (i - 1) & 1) && ok;
     if (scan_sync_or(!ok)) { ok = false; break; }
     tc::tc_fence_after();
-    PKDA_SCANTC_PHASE(i, 3);
 
     // b. E^T sits in the accumulator (lane = value channel, column = token);  F = beta E
     {
@@ -436,7 +420,6 @@ pkda_scan_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_c
     tc::fence_proxy_async();
     tc::tc_fence_before();
     scan_sync();
-    PKDA_SCANTC_PHASE(i, 4);
     if (lane == 0 && (warp == 3 || warp == 4) && valid == kChunk) {
       tc::tma_store_3d(&tm_e, base + oE + (warp - 3) * 8192, 64 * (warp - 3), h, tok0);
       tc::bulk_commit();
@@ -454,7 +437,6 @@ pkda_scan_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_c
     }
     if (warp == 0) ok = tc::mbar_wait(bar_mma2, i & 1) && ok;
     tc::tc_fence_before();  // (the barrier at the top of the next step, or the one after the loop, follows)
-    PKDA_SCANTC_PHASE(i, 5);
   }
   if (scan_sync_or(!ok)) {
     if (tid == 0) atomicExch(p.status, 1);
@@ -538,8 +520,3 @@ int launch_scan_fwd_tc(const Geo& geo, int total_tokens, int units, const bf16* 
 
 }  // namespace pkda
 
-#ifdef PKDA_PHASE_PROFILE
-extern "C" int pkda_phase_prof_scantc(long long* out) {
-  return cudaMemcpyFromSymbol(out, g_phase_prof, sizeof(long long) * 64) == cudaSuccess ? 0 : 1;
-}
-#endif

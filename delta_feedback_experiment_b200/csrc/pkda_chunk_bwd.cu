@@ -1274,11 +1274,11 @@ int chunk_bwd(const pkda_chunk_bwd_args* a, cudaStream_t st) {
   sp.dS0 = a->d_initial_state;
   {
     const int units = p.n_seqs * p.heads;
-    const int vb = units >= 120 ? 128 : (units >= 60 ? 64 : 32);
-    // Full-width slices run on tcgen05 / TMEM / TMA unless the mma.sync kernel is pinned (pkda_set_variant).
-    const bool scan_mma = stage_variant(kStageScanBwd) != 0;
+    const int vb = units >= 120 ? 128 : (units >= 60 ? 64 : 32);  // value columns per CTA of the mma.sync kernel
+    // tcgen05 / TMEM / TMA at every size unless the mma.sync kernel is pinned (pkda_set_variant).
+    const bool scan_mma = stage_variant(kStageScanBwd) == 1;
     begin_stage(kStageScanBwd, st);
-    if (vb == 128 && !scan_mma)
+    if (!scan_mma)
       rc = launch_scan_bwd_tc(geo, p.total_tokens, units, kg, w, qg, sp.d_o, Aqk, ws.beta_c, gc, a->d_final_state,
                               ws.dh, ws.dF, a->d_initial_state, ws.status, st);
     else if (vb == 128) rc = launch_scan_bwd<128>(sp, units, st);

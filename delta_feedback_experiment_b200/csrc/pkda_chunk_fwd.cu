@@ -808,19 +808,21 @@ int run_forward_stages(const pkda_problem& p, const Geo& geo, const float* beta_
   ScanParams sp;
   sp.geo = geo; sp.w = w; sp.u = u_ws; sp.kg = kg; sp.beta_c = beta_c; sp.gc = gc;
   sp.S0 = p.initial_state; sp.h = h; sp.v_new = v_new; sp.ST = ST;
-  // Value columns per CTA: as wide as possible (no redundant reads of W and kg, all
-  // warps of an SM on one chain) while still leaving about one CTA per SM.
+  // The scan runs on tcgen05 / TMEM / TMA, one CTA per (sequence, head), unless the mma.sync kernel is
+  // pinned (pkda_set_variant).  That holds for few units too: a chunk step is a latency chain whose
+  // length does not depend on how many CTAs run (2 rows x 16 heads, T = 4096: 0.82 ms per
+  // forward+backward against 0.87 ms with the value-sliced mma.sync scans).  The mma.sync kernel
+  // slices the value columns when there are fewer units than SMs.
   const int units = p.n_seqs * p.heads;
   const int vb = units >= 120 ? 128 : (units >= 60 ? 64 : 32);
   int rc = PKDA_ERR_LAUNCH;
-  // Full-width slices run on tcgen05 / TMEM / TMA unless the mma.sync kernel is pinned (pkda_set_variant).
-  const bool scan_mma = stage_variant(kStageScanFwd) != 0;
+  const bool scan_mma = stage_variant(kStageScanFwd) == 1;
   // The tcgen05 scan also produces the output (it holds h and E of every chunk) unless a separate
   // output kernel is asked for (pkda_set_variant("out_fwd", 1: mma.sync, 2: tcgen05)).
   const bool fuse_out = o && !recompute && stage_variant(kStageOutFwd) == 0;
   if (o_done) *o_done = false;
   begin_stage(kStageScanFwd, st);
-  if (vb == 128 && status && !scan_mma) {
+  if (status && !scan_mma) {
     rc = launch_scan_fwd_tc(geo, p.total_tokens, units, w, kg, u_ws, beta_c, gc, p.initial_state, h, v_new, ST,
                             status, recompute, qg, Aqk, fuse_out ? o : nullptr, st);
     if (o_done) *o_done = fuse_out;

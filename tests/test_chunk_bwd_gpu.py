@@ -5,7 +5,7 @@ import pytest
 import torch
 
 from conftest import assert_close, load_golden, rel_rms
-from delta_feedback_experiment_b200 import chunk_precond_kda, pkda_recurrence
+from delta_feedback_experiment_b200 import _lib, chunk_precond_kda, pkda_recurrence
 from delta_feedback_experiment_b200.synthetic import INPUT_NAMES, make_inputs
 from oracle.pkda_oracle import pkda_oracle_with_grads
 
@@ -184,16 +184,18 @@ def test_direct_block_variants(cap, dist):
 
 @pytest.mark.parametrize("B", [4, 8])
 def test_wide_state_slices_match_narrow_ones(B):
-    """The state scans run as tcgen05 / tensor-memory kernels (one CTA per (row, head), all
-    128 value columns) when there are at least 120 (row, head) units -- B = 8 here -- and as
-    mma.sync kernels on 32- or 64-column slices below that.  Rows are independent, so a row of
-    the big batch must agree with the same row run alone through the other implementation.
+    """The state scans have two implementations: tcgen05 / tensor-memory kernels (one CTA per
+    (row, head), all 128 value columns; the default at every size) and mma.sync kernels that
+    cut the value columns into 32- or 64-wide slices when there are fewer than 120 (row, head)
+    units (`set_variant("scan_fwd" / "scan_bwd", 1)`).  Rows are independent, so a row of the
+    big batch must agree with the same row run alone through the other implementation.
     Both feed the same bf16 operands to the tensor cores in the same order; on this short input
     every result is equal bit for bit, which this test pins.  That is a property of the input,
     not a guarantee: the tcgen05 scan adds U inside the fp32 accumulator while the mma.sync
     scan subtracts in a register, and on long inputs a few outputs differ by one bf16 unit in
     the last place (T = 1024: max |delta o| = 3.8e-6 with every gradient and the final state
-    still equal), which is why the full-size tests compare within tolerance."""
+    still equal), which is why the full-size tests compare within tolerance.  A row run alone
+    through the default kernels must equal the batch in any case."""
     H, T = 16, 130
     d = make_inputs(B, T, H, 128, seed=97, dist="production", dtype=torch.bfloat16, with_state=True)
     dS = torch.randn(B, H, 128, 128, generator=torch.Generator().manual_seed(6)) * 0.1
@@ -201,6 +203,14 @@ def test_wide_state_slices_match_narrow_ones(B):
     for b in range(0, B, 3):
         one = {k: (v[b:b + 1] if torch.is_tensor(v) and v.dim() >= 3 and v.shape[0] == B else v)
                for k, v in d.items()}
-        part = run(one, dS=dS[b:b + 1])
+        same = run(one, dS=dS[b:b + 1])
+        _lib.set_variant("scan_fwd", 1)
+        _lib.set_variant("scan_bwd", 1)
+        try:
+            part = run(one, dS=dS[b:b + 1])
+        finally:
+            _lib.set_variant("scan_fwd", 0)
+            _lib.set_variant("scan_bwd", 0)
         for key in ("o", "dq", "dk", "dv", "dg", "dbeta", "dg_atk", "dbeta_atk", "dinitial_state"):
-            assert torch.equal(full[key][b:b + 1], part[key]), (b, key)
+            assert torch.equal(full[key][b:b + 1], same[key]), (b, key, "default kernels")
+            assert torch.equal(full[key][b:b + 1], part[key]), (b, key, "sliced mma.sync scans")

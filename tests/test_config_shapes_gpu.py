@@ -1,7 +1,7 @@
 """The two timed chunked configurations at their real shapes against the CPU oracle:
 B=8, T=4096, H=16 (one GPU) and B=16, T=8192, H=16 (the per-GPU shape of the eight-GPU
-run).  The whole problem runs on the GPU -- with 128 or 256 (row, head) units the state
-scans take their tcgen05 / tensor-memory kernels, which is the point -- and one (row, head)
+run).  The whole problem runs on the GPU, through the tcgen05 / tensor-memory kernels that
+the benchmark times, and one (row, head)
 slice is compared with the float64 oracle: output, both final states, the seven per-token
 gradients and both initial-state gradients.  The three per-head parameter gradients are sums
 over all rows, so they are checked on a GPU run of the slice alone."""

@@ -1,5 +1,7 @@
 // extern "C" surface of libpkda_b200.so (declared in include/pkda_b200.h).
 #include <cstring>
+#include <mutex>
+#include <unordered_map>
 #include <vector>
 
 #include "pkda_launch.h"
@@ -13,6 +15,24 @@ static int g_direct_cap = 64;
 int direct_block_cap() { return g_direct_cap; }
 
 static int g_variant[kStageCount] = {};
+
+bool dynamic_smem_once(const void* kernel, int bytes, int carveout) {
+  static std::mutex mu;
+  static std::unordered_map<const void*, unsigned long long> seen;  // kernel -> one bit per device
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return false;
+  const unsigned long long bit = dev < 64 ? 1ull << dev : 0ull;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = seen.find(kernel);
+    if (it != seen.end() && (it->second & bit)) return true;
+  }
+  if (carveout >= 0) cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, carveout);
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return false;
+  std::lock_guard<std::mutex> lock(mu);
+  seen[kernel] |= bit;
+  return true;
+}
 int stage_variant(int stage) { return (stage >= 0 && stage < kStageCount) ? g_variant[stage] : 0; }
 
 __global__ void pkda_status_guard_kernel(const int* status, bf16* out0, bf16* out1, bf16* out2, size_t n) {

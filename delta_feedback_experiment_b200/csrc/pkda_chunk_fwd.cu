@@ -733,7 +733,7 @@ size_t chunk_fwd_status_offset(const pkda_problem& p) {
 
 template <typename K>
 static bool set_smem(K kernel, int bytes) {
-  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess;
+  return ensure_dynamic_smem(kernel, bytes);
 }
 
 #define PKDA_CHECK_LAUNCH()                                        \

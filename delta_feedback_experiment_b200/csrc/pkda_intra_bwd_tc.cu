@@ -651,8 +651,7 @@ int launch_intra_bwd_tc(const IntraBwdParams& ip, cudaStream_t st) {
     if (!encode_bf16_map(&maps.h, ip.h, 2, dims, str, box) || !encode_bf16_map(&maps.dh, ip.dh, 2, dims, str, box))
       return PKDA_ERR_LAUNCH;
   }
-  if (cudaFuncSetAttribute(pkda_intra_bwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ibtc::kSmem) !=
-      cudaSuccess)
+  if (!ensure_dynamic_smem(pkda_intra_bwd_tc_kernel, ibtc::kSmem))
     return PKDA_ERR_LAUNCH;
   const int items = ip.geo.total_chunks * ip.geo.heads;
   begin_stage(kStageBwdClassify, st);

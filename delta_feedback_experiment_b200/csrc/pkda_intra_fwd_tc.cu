@@ -498,16 +498,12 @@ int launch_intra_fwd_tc(const IntraParams& ip, bool recompute, cudaStream_t st) 
   const int items = ip.geo.total_chunks * ip.geo.heads;
   const int grid = items < 2 * sms ? items : 2 * sms;  // persistent: two CTAs per SM
   // two CTAs per SM need the largest shared-memory carve-out
-  cudaFuncSetAttribute(pkda_intra_fwd_tc_kernel<true>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-  cudaFuncSetAttribute(pkda_intra_fwd_tc_kernel<false>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
   if (recompute) {
-    if (cudaFuncSetAttribute(pkda_intra_fwd_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             intratc::kSmem) != cudaSuccess)
+    if (!ensure_dynamic_smem(pkda_intra_fwd_tc_kernel<true>, intratc::kSmem, 100))
       return PKDA_ERR_LAUNCH;
     pkda_intra_fwd_tc_kernel<true><<<grid, intratc::kThreads, intratc::kSmem, st>>>(tm_v, tm_akk, tm_aqk, tm_w, tm_u, ip);
   } else {
-    if (cudaFuncSetAttribute(pkda_intra_fwd_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             intratc::kSmem) != cudaSuccess)
+    if (!ensure_dynamic_smem(pkda_intra_fwd_tc_kernel<false>, intratc::kSmem, 100))
       return PKDA_ERR_LAUNCH;
     pkda_intra_fwd_tc_kernel<false><<<grid, intratc::kThreads, intratc::kSmem, st>>>(tm_v, tm_akk, tm_aqk, tm_w, tm_u, ip);
   }

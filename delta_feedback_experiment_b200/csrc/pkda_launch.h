@@ -31,6 +31,15 @@ int stage_variant(int stage);
 // overwritten with NaN so that the failure reaches the caller's non-finite check.
 int launch_status_guard(const int* status, void* out0, void* out1, void* out2, size_t n, cudaStream_t st);
 
+// Raises a kernel's dynamic shared-memory limit, once per kernel and device (the attribute
+// sticks to the function; asking again on every launch costs host time in eager mode).
+// carveout >= 0 also sets the preferred shared-memory carve-out (percent).
+bool dynamic_smem_once(const void* kernel, int bytes, int carveout);
+template <typename K>
+inline bool ensure_dynamic_smem(K kernel, int bytes, int carveout = -1) {
+  return dynamic_smem_once(reinterpret_cast<const void*>(kernel), bytes, carveout);
+}
+
 // Upper limit for the kernels' direct block size (64 unless lowered through
 // pkda_set_direct_block_cap, a testing aid).
 int direct_block_cap();

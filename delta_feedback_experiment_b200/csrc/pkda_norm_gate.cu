@@ -274,7 +274,7 @@ template <typename K> static int ng_grid(const pkda_norm_gate_args& a, K kernel,
 }
 
 template <typename K> static bool ng_allow_smem(K kernel, int bytes) {
-  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess;
+  return ensure_dynamic_smem(kernel, bytes);
 }
 
 static int ng_check(const pkda_norm_gate_args& a, NormGateParams& p) {

@@ -219,8 +219,7 @@ int launch_out_fwd_tc(const Geo& geo, int total_tokens, const bf16* qg, const bf
   }
   OutTcParams op;
   op.geo = geo; op.beta_c = beta_c; op.o = o; op.status = status;
-  if (cudaFuncSetAttribute(pkda_out_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, outtc::kSmem) !=
-      cudaSuccess)
+  if (!ensure_dynamic_smem(pkda_out_fwd_tc_kernel, outtc::kSmem))
     return PKDA_ERR_LAUNCH;
   begin_stage(kStageOutFwd, st);
   pkda_out_fwd_tc_kernel<<<dim3(geo.total_chunks, geo.heads), outtc::kThreads, outtc::kSmem, st>>>(tm_h, tm_qg, tm_e,

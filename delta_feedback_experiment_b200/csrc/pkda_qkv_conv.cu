@@ -469,7 +469,7 @@ static dim3 conv_grid(ConvParams& p, int tokens) {
 static bool aligned16(const void* x) { return (reinterpret_cast<uintptr_t>(x) & 15) == 0; }
 
 template <typename K> static bool allow_smem(K kernel, int bytes) {
-  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess;
+  return ensure_dynamic_smem(kernel, bytes);
 }
 
 template <typename T, int kHeadLanes>

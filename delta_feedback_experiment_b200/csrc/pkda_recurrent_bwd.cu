@@ -320,8 +320,7 @@ size_t recurrent_bwd_workspace(const pkda_problem& p) { return carve_rec_bwd(p, 
 template <int D, typename T>
 static int launch_rec_bwd(const RecBwdParams& bp, cudaStream_t st) {
   const int smem = rec_bwd_smem_floats<D>() * 4 + 3 * RecCfg<D>::kThreads * 4;
-  if (cudaFuncSetAttribute(pkda_recurrent_bwd_kernel<D, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
-      cudaSuccess)
+  if (!ensure_dynamic_smem(pkda_recurrent_bwd_kernel<D, T>, smem))
     return PKDA_ERR_LAUNCH;
   begin_stage(kStageRecurrent, st);
   pkda_recurrent_bwd_kernel<D, T><<<bp.geo.n_seqs * bp.geo.heads, RecCfg<D>::kThreads, smem, st>>>(bp);

@@ -324,8 +324,7 @@ int launch_scan_bwd_tc(const Geo& geo, int total_tokens, int units, const bf16* 
   }
   ScanBwdTcParams sp;
   sp.geo = geo; sp.beta_c = beta_c; sp.gc = gc; sp.dST = dST; sp.dF = dF; sp.dS0 = dS0; sp.status = status;
-  if (cudaFuncSetAttribute(pkda_scan_bwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, scanbtc::kSmem) !=
-      cudaSuccess)
+  if (!ensure_dynamic_smem(pkda_scan_bwd_tc_kernel, scanbtc::kSmem))
     return PKDA_ERR_LAUNCH;
   pkda_scan_bwd_tc_kernel<<<units, scanbtc::kThreads, scanbtc::kSmem, st>>>(tm_kg, tm_w, tm_qg, tm_do, tm_p, tm_dh,
                                                                              tm_df, sp);

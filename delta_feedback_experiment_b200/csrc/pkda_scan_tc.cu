@@ -497,20 +497,17 @@ int launch_scan_fwd_tc(const Geo& geo, int total_tokens, int units, const bf16* 
   ScanTcParams sp;
   sp.geo = geo; sp.beta_c = beta_c; sp.gc = gc; sp.S0 = S0; sp.v_new = v_new; sp.ST = ST; sp.o = o; sp.status = status;
   if (recompute) {
-    if (cudaFuncSetAttribute(pkda_scan_fwd_tc_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             scantc::kSmem) != cudaSuccess)
+    if (!ensure_dynamic_smem(pkda_scan_fwd_tc_kernel<true, false>, scantc::kSmem))
       return PKDA_ERR_LAUNCH;
     pkda_scan_fwd_tc_kernel<true, false><<<units, scantc::kThreads, scantc::kSmem, st>>>(tm_w, tm_kg, tm_u, tm_h, tm_e,
                                                                                         tm_qg, tm_p, sp);
   } else if (with_out) {
-    if (cudaFuncSetAttribute(pkda_scan_fwd_tc_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             scantc::kSmemOut) != cudaSuccess)
+    if (!ensure_dynamic_smem(pkda_scan_fwd_tc_kernel<false, true>, scantc::kSmemOut))
       return PKDA_ERR_LAUNCH;
     pkda_scan_fwd_tc_kernel<false, true><<<units, scantc::kThreads + scantc::kOutThreads, scantc::kSmemOut, st>>>(
         tm_w, tm_kg, tm_u, tm_h, tm_e, tm_qg, tm_p, sp);
   } else {
-    if (cudaFuncSetAttribute(pkda_scan_fwd_tc_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             scantc::kSmem) != cudaSuccess)
+    if (!ensure_dynamic_smem(pkda_scan_fwd_tc_kernel<false, false>, scantc::kSmem))
       return PKDA_ERR_LAUNCH;
     pkda_scan_fwd_tc_kernel<false, false><<<units, scantc::kThreads, scantc::kSmem, st>>>(tm_w, tm_kg, tm_u, tm_h, tm_e,
                                                                                          tm_qg, tm_p, sp);

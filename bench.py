@@ -74,6 +74,15 @@ STAGE_FLOPS = {
 # in proportion to the units, so a launch of any size moves this many bytes per unit.
 STAGE_TRAFFIC_PER_UNIT = {"intra_fwd": 2158, "scan_fwd": 1245, "out_fwd": 1280, "scan_bwd": 1661,
                           "intra_bwd": 4496}
+# Bytes per (token, head) that each kernel must read and write by its own interface (its input and
+# output tensors, each touched once): the HBM view of the same kernels.
+STAGE_IO_BYTES = {
+    "intra_fwd": 4 * 256 + (128 + 128 + 5 * 256),             # q,k,v,g -> Aqk, Akk, k_precond, w, u, kg, qg
+    "scan_fwd": 3 * 256 + (512 + 256),                          # w,u,kg -> h, v_new
+    "out_fwd": 512 + 256 + 256 + 128 + 256,                     # h, qg, v_new, Aqk -> o
+    "scan_bwd": 4 * 256 + 128 + (512 + 256),                    # kg,w,qg,dO,Aqk -> dh, dF
+    "intra_bwd": 7 * 256 + 2 * 128 + 2 * 512 + (3 * 256 + 2 * 512 + 256),  # dO,dF,E,q,k,kt,g,Akk,Aqk,h,dh -> dq,dv,dg,dk_read,dkt(+k again)
+}
 # The kernel behind each stage name (tcgen05 / tensor-memory build; --legacy runs the mma.sync ones).
 STAGE_KERNEL = {"intra_fwd": "pkda_intra_fwd_tc_kernel", "scan_fwd": "pkda_scan_fwd_tc_kernel",
                 "out_fwd": "pkda_out_fwd_tc_kernel", "scan_bwd": "pkda_scan_bwd_tc_kernel",
@@ -689,6 +698,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     if "out_fwd" not in stages:  # the state scan formed the output too: its products belong to that launch
         STAGE_FLOPS["scan_fwd"] += STAGE_FLOPS["out_fwd"]
         STAGE_TRAFFIC_PER_UNIT["scan_fwd"] = 1898  # (ncu, same capture: 161.0 MB read + 87.8 MB written per 131,072 units)
+        STAGE_IO_BYTES["scan_fwd"] += 256 + 128 + 256  # qg, Aqk -> o
     top = max((n for n in stages if n in STAGE_FLOPS), key=lambda n: stages[n][0])
     top_ms = per_launch[top]
     achieved_tf = STAGE_FLOPS[top] * units / (top_ms * 1e-3) / 1e12
@@ -702,6 +712,10 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         "launch_ms": top_ms, "algorithmic_flops_per_launch": STAGE_FLOPS[top] * units,
         "peak_source": pk["source"] + " (sustained bf16 GEMM; kernel timed inside a long step)",
         "share_of_step": stages[top][0] / sum(ms for ms, _ in stages.values()),
+        # the same kernel against the HBM roof: its own inputs and outputs, each touched once
+        "hbm_view": {"io_bytes_per_launch": STAGE_IO_BYTES[top] * units,
+                     "achieved_gbs": STAGE_IO_BYTES[top] * units / (top_ms * 1e-3) / 1e9,
+                     "frac": STAGE_IO_BYTES[top] * units / (top_ms * 1e-3) / 1e9 / pk["hbm_gbs"]},
         "whole_step": {
             "tensor_frac": FWD_BWD_FLOPS * units / (ms_per_step * 1e-3) / 1e12 / peak_tf,
             "hbm_frac": (FWD_BYTES + BWD_BYTES) * units / (ms_per_step * 1e-3) / 1e9 / pk["hbm_gbs"],

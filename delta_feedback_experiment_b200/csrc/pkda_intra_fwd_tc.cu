@@ -255,8 +255,11 @@ pkda_intra_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_
     }
   }
 
-  // ---- 3. preconditioner states of this strip's rows -> write keys kt = k * B(A_t) (into the slots g
-  // has left, and to global memory), kg = kt * decay to the chunk end; diagonal q_i . kt_i
+  // ---- 3. one pass over the strip: preconditioner states of its rows -> write keys kt = k * B(A_t)
+  // (to global memory), kg = kt * decay to the chunk end, the diagonal q_i . kt_i, and the gated operands
+  // in place: Kd = k 2^G (rows 0..63 of the stacked operand, later the operand of W^T), q 2^G (rows
+  // 64..127), kt 2^-G (into the slots g has left); qg goes to global memory.  The decay to the chunk
+  // end is 2^G_last times the 2^-G the operand needs anyway.  Nothing of the strip is needed afterwards.
   {
     float A[4] = {a_first.x, a_first.y, a_first.z, a_first.w};
     if (!kRecompute) {
@@ -266,13 +269,15 @@ pkda_intra_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_
         A[0] = d * A[0] + e4.x; A[1] = d * A[1] + e4.y; A[2] = d * A[2] + e4.z; A[3] = d * A[3] + e4.w;
       }
     }
+    const float glE[4] = {ex2(Glast[0]), ex2(Glast[1]), ex2(Glast[2]), ex2(Glast[3])};
     float dg[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
+      const int off = slot_off(i);
+      const uint2 kr = ld_k(i), qr = ld_q(i);
       uint2 kt = ktraw[i];
       if (!kRecompute) {
         const float pd = __shfl_sync(0xffffffffu, sc_pd, i), bp = __shfl_sync(0xffffffffu, sc_bp, i);
-        const uint2 kr = ld_k(i);
         float kc[4], f[4];
         unpack4(kr, kc);
 #pragma unroll
@@ -282,48 +287,35 @@ pkda_intra_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_
           f[e] = __expf(-p.ln_x * __fdividef(dev, 1.f + fabsf(dev)));
         }
         kt = scale4(kr, f);
-        *reinterpret_cast<uint2*>(yBase + slot_off(i)) = kt;
         if (r0 + i < valid) *reinterpret_cast<uint2*>(p.kt + row0 + (size_t)(r0 + i) * gld + c4) = kt;
         float kc2[4], qc[4];
         unpack4(kt, kc2);
-        unpack4(ld_q(i), qc);
+        unpack4(qr, qc);
         dg[i] = qc[0] * kc2[0] + qc[1] * kc2[1] + qc[2] * kc2[2] + qc[3] * kc2[3];
       }
-      float tl[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e) tl[e] = ex2(Glast[e] - G[i][e]);
-      if (r0 + i < valid) *reinterpret_cast<uint2*>(p.kg + row0 + (size_t)(r0 + i) * gld + c4) = scale4(kt, tl);
-    }
-    if (!kRecompute) {
-      row_sums8(dg, lane);
-      if ((lane & 3) == 0) sDiag[r0 + ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1)] = dg[0];
-      if (warp == 0)
-        *reinterpret_cast<float4*>(p.gc + chh * kD + c4) =
-            make_float4(ex2(Glast[0]), ex2(Glast[1]), ex2(Glast[2]), ex2(Glast[3]));
-    }
-  }
-
-  // ---- 4. one pass gates the operands in place: Kd = k 2^G (rows 0..63 of the stacked operand, and
-  // later the operand of W^T), q 2^G (rows 64..127), the write keys times 2^-G; qg goes to global
-  // memory.  Nothing of the strip is needed afterwards.
-  {
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      float e[4], es[4], fi[4];
+      float e[4], es[4], fi[4], tl[4];
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         e[c] = ex2(G[i][c]);
         es[c] = e[c] * p.scale;
         fi[c] = __fdividef(1.f, e[c]);
+        tl[c] = glE[c] * fi[c];
       }
-      const int off = slot_off(i);
-      const uint2 qr = ld_q(i);
-      *reinterpret_cast<uint2*>(aBase + off) = scale4(ld_k(i), e);
+      *reinterpret_cast<uint2*>(aBase + off) = scale4(kr, e);
       if (!kRecompute) {
         *reinterpret_cast<uint2*>(aBase + 8192 + off) = scale4(qr, e);
-        *reinterpret_cast<uint2*>(yBase + off) = scale4(ld_y(i), fi);
+        *reinterpret_cast<uint2*>(yBase + off) = scale4(kt, fi);
       }
-      if (r0 + i < valid) *reinterpret_cast<uint2*>(p.qg + row0 + (size_t)(r0 + i) * gld + c4) = scale4(qr, es);
+      if (r0 + i < valid) {
+        *reinterpret_cast<uint2*>(p.kg + row0 + (size_t)(r0 + i) * gld + c4) = scale4(kt, tl);
+        *reinterpret_cast<uint2*>(p.qg + row0 + (size_t)(r0 + i) * gld + c4) = scale4(qr, es);
+      }
+    }
+    if (!kRecompute) {
+      row_sums8(dg, lane);
+      if ((lane & 3) == 0) sDiag[r0 + ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1)] = dg[0];
+      if (warp == 0)
+        *reinterpret_cast<float4*>(p.gc + chh * kD + c4) = make_float4(glE[0], glE[1], glE[2], glE[3]);
     }
   }
   tc::fence_proxy_async();

@@ -418,6 +418,18 @@ struct IntraParams {
   // counts[1] is its length, counts[0] and counts[2] the cursors the CTAs of the two kernels draw their
   // items with (all zeroed before every call).  slow_list == NULL: the mma.sync kernel takes every chunk, one CTA per item.
   int *slow_list, *counts;
+  // Preconditioner state across chunks inside the tensor-memory kernel (dense batches; chain != 0):
+  // every item computes its chunk's local scan anyway, so it takes its chunk-entry state from the item
+  // of the chunk before (a_chain, which is the saved "state at chunk starts" tensor; chain_flags counts
+  // the four warps that have published an entry), and publishes the next chunk's.  The items are
+  // then drawn chunk level by chunk level across all (row, head) units, so that an item's predecessor
+  // started long before it.  beta (raw) is packed to beta_c_w on the way; sa takes the chunk's summed
+  // preconditioner log-decay, A0 / AT are the initial / final preconditioner states (may be NULL).
+  int chain;
+  const bf16* beta;
+  float *beta_c_w, *a_chain, *sa, *AT;
+  const float* A0;
+  int* chain_flags;
 };
 
 // tcgen05 / tensor-memory intra-chunk forward stage (pkda_intra_fwd_tc.cu).
@@ -477,9 +489,17 @@ int check_chunk_problem(const pkda_problem& p);
 int run_prologue(const pkda_problem& p, int* chunk_offsets, float* beta_c, Geo* geo, cudaStream_t st);
 // lists: room for chunks * heads ints (the forward's work list); counts: three zeroed ints.
 // o / o_done: the forward's output tensor; *o_done says whether the state scan has already written it.
+// What the tensor-memory intra kernel needs to carry the preconditioner state across chunks itself
+// (dense batches): see IntraParams::chain.
+struct ChainArgs {
+  float *beta_c_w, *a_chain, *sa, *AT;
+  int* flags;
+};
+// True when the forward can run in chained mode (no preconditioner kernels in front of the intra stage).
+bool forward_chain_possible(const pkda_problem& p);
 int run_forward_stages(const pkda_problem& p, const Geo& geo, const float* beta_c, bf16* u_ws, bf16* Aqk,
                        bf16* Akk, bf16* kt, float* gc, const float* a_start, bf16* w, bf16* kg, bf16* v_new,
                        bf16* h, bf16* qg, float* ST, bool recompute, int* status, int* lists, int* counts,
-                       cudaStream_t st, bf16* o = nullptr, bool* o_done = nullptr);
+                       cudaStream_t st, bf16* o = nullptr, bool* o_done = nullptr, const ChainArgs* chain = nullptr);
 
 }  // namespace pkda

@@ -699,6 +699,7 @@ pkda_out_fwd_kernel(const OutParams p) {
 
 // ------------------------------------------------------------------ host side
 struct FwdWorkspace {
+  int* chain_flags;  // one counter per (chunk, head) item, right behind the status slot (zeroed with it)
   int* chunk_offsets;
   float* beta_c;
   bf16* u;
@@ -721,12 +722,18 @@ static FwdWorkspace carve_fwd(const pkda_problem& p, void* base) {
   w.lists = reinterpret_cast<int*>(b + off);
   off += align_up(chunks * p.heads * sizeof(int));
   w.status = reinterpret_cast<int*>(b + off);
-  off += align_up(8 * sizeof(int));
+  off += 8 * sizeof(int);
+  w.chain_flags = reinterpret_cast<int*>(b + off);
+  off += align_up(chunks * p.heads * sizeof(int));
   w.bytes = off;
   return w;
 }
 
 size_t chunk_fwd_workspace(const pkda_problem& p) { return carve_fwd(p, nullptr).bytes; }
+
+bool forward_chain_possible(const pkda_problem& p) {
+  return !p.cu_seqlens && stage_variant(kStageIntraFwd) == 0 && direct_block_cap() >= 64;
+}
 size_t chunk_fwd_status_offset(const pkda_problem& p) {
   return (size_t)(reinterpret_cast<unsigned char*>(carve_fwd(p, nullptr).status) - static_cast<unsigned char*>(nullptr));
 }
@@ -762,7 +769,7 @@ int run_forward_stages(const pkda_problem& p, const Geo& geo, const float* beta_
                        bf16* Aqk, bf16* Akk, bf16* kt, float* gc, const float* a_start,
                        bf16* w, bf16* kg, bf16* v_new, bf16* h, bf16* qg, float* ST,
                        bool recompute, int* status, int* lists, int* counts, cudaStream_t st, bf16* o,
-                       bool* o_done) {
+                       bool* o_done, const ChainArgs* chain) {
   const int chunks = geo.total_chunks;
   IntraParams ip;
   ip.geo = geo;
@@ -777,6 +784,15 @@ int run_forward_stages(const pkda_problem& p, const Geo& geo, const float* beta_
   ip.direct_cap = direct_block_cap();
   ip.status = status;
   ip.slow_list = ip.counts = nullptr;
+  ip.chain = 0;
+  ip.beta = static_cast<const bf16*>(p.beta); ip.A0 = p.initial_A_state;
+  ip.beta_c_w = ip.a_chain = ip.sa = ip.AT = nullptr;
+  ip.chain_flags = nullptr;
+  if (chain && !recompute && status && lists && forward_chain_possible(p)) {
+    ip.chain = 1;
+    ip.beta_c_w = chain->beta_c_w; ip.a_chain = chain->a_chain; ip.sa = chain->sa; ip.AT = chain->AT;
+    ip.chain_flags = chain->flags;
+  }
   dim3 gridc(chunks, p.heads);
   // Chunks that are one direct block run on tcgen05 / tensor memory; that kernel lists the others and
   // the mma.sync kernel works the list off (it takes every chunk, one CTA each, when it is pinned or the
@@ -865,24 +881,33 @@ int chunk_fwd(const pkda_chunk_fwd_args* a, cudaStream_t st) {
   rc = run_prologue(p, ws.chunk_offsets, nullptr, &geo, st);
   if (rc != PKDA_OK) return rc;
 
-  dim3 gridc(geo.total_chunks, p.heads);
-  begin_stage(kStageAtkLocal, st);
-  pkda_atk_local_kernel<<<gridc, 256, 0, st>>>(geo, static_cast<const bf16*>(p.k), p.g_atk,
-                                               static_cast<const bf16*>(p.beta_atk), static_cast<const bf16*>(p.beta),
-                                               a->ac_atk, a->sa_atk, ws.beta_c);
-  PKDA_CHECK_LAUNCH();
-  begin_stage(kStageAtkCarry, st);
-  pkda_atk_carry_kernel<<<dim3(p.n_seqs, p.heads), kD, 0, st>>>(geo, a->ac_atk, a->sa_atk, p.initial_A_state,
-                                                               a->a_atk, a->final_A_state);
-  PKDA_CHECK_LAUNCH();
+  // Dense batches on the default kernels: the intra stage carries the preconditioner state across
+  // chunks itself (and packs beta).  Otherwise two small kernels in front do.
+  const bool chained = forward_chain_possible(p);
+  if (!chained) {
+    dim3 gridc(geo.total_chunks, p.heads);
+    begin_stage(kStageAtkLocal, st);
+    pkda_atk_local_kernel<<<gridc, 256, 0, st>>>(geo, static_cast<const bf16*>(p.k), p.g_atk,
+                                                 static_cast<const bf16*>(p.beta_atk), static_cast<const bf16*>(p.beta),
+                                                 a->ac_atk, a->sa_atk, ws.beta_c);
+    PKDA_CHECK_LAUNCH();
+    begin_stage(kStageAtkCarry, st);
+    pkda_atk_carry_kernel<<<dim3(p.n_seqs, p.heads), kD, 0, st>>>(geo, a->ac_atk, a->sa_atk, p.initial_A_state,
+                                                                 a->a_atk, a->final_A_state);
+    PKDA_CHECK_LAUNCH();
+  }
 
-  if (cudaMemsetAsync(ws.status, 0, 8 * sizeof(int), st) != cudaSuccess) return PKDA_ERR_LAUNCH;
+  const size_t zero_ints = 8 + (chained ? (size_t)geo.total_chunks * p.heads : 0);  // status, cursors, chain counters
+  if (cudaMemsetAsync(ws.status, 0, zero_ints * sizeof(int), st) != cudaSuccess) return PKDA_ERR_LAUNCH;
+  ChainArgs chain_args;
+  chain_args.beta_c_w = ws.beta_c; chain_args.a_chain = a->a_atk; chain_args.sa = a->sa_atk;
+  chain_args.AT = a->final_A_state; chain_args.flags = ws.chain_flags;
   bool o_done = false;
   rc = run_forward_stages(p, geo, ws.beta_c, ws.u, static_cast<bf16*>(a->Aqk), static_cast<bf16*>(a->Akk),
                           static_cast<bf16*>(a->k_precond), a->ac_atk, a->a_atk, static_cast<bf16*>(a->w),
                           static_cast<bf16*>(a->kg), static_cast<bf16*>(a->v_new), static_cast<bf16*>(a->h),
                           static_cast<bf16*>(a->qg), a->final_state, false, ws.status, ws.lists, ws.status + 1, st,
-                          static_cast<bf16*>(a->o), &o_done);
+                          static_cast<bf16*>(a->o), &o_done, chained ? &chain_args : nullptr);
   if (rc != PKDA_OK) return rc;
 
   // Output stage, when the scan has not produced o already: tcgen05 + TMA unless the mma.sync kernel is
@@ -903,7 +928,7 @@ int chunk_fwd(const pkda_chunk_fwd_args* a, cudaStream_t st) {
   op.beta_c = ws.beta_c; op.o = static_cast<bf16*>(a->o);
   if (!set_smem(pkda_out_fwd_kernel, outk::kSmem)) return PKDA_ERR_LAUNCH;
   begin_stage(kStageOutFwd, st);
-  pkda_out_fwd_kernel<<<gridc, outk::kThreads, outk::kSmem, st>>>(op);
+  pkda_out_fwd_kernel<<<dim3(geo.total_chunks, p.heads), outk::kThreads, outk::kSmem, st>>>(op);
   PKDA_CHECK_LAUNCH();
   return launch_status_guard(ws.status, a->o, nullptr, nullptr, guard_n, st);
 }

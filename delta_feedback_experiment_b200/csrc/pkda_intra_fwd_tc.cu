@@ -53,10 +53,12 @@ constexpr int kSmem = oBar + 64 + 1024;     // + slack to align the tiles to 102
 constexpr int oTot = oL;                    // f32 [8][128] per-strip decay totals
 constexpr int oEnd = oL + 4096;             // f32 [8][128] per-strip end value of the zero-start A scan
 constexpr int oDec = oL + 8192;             // f32 [8] per-strip product of preconditioner decays
+constexpr int oSum = oDec + 32;             // f32 [8] per-strip sum of the preconditioner's log-decays
+constexpr int oA0 = oSum + 32;              // f32 [128] the chunk-entry preconditioner state (chained mode)
 // while the inverse runs: T in the (dead) write-key operand, its scratch in the (dead) q rows of block 0
 constexpr int oT = oY;                      // f32 [64][65]
 constexpr int oY2 = oA + 8192;              // f32 [1024]
-static_assert(oDec + 32 <= oBeta && oT + 64 * kLdL * 4 <= oV && oY2 + 4096 <= oA + 16384, "aliases must fit");
+static_assert(oA0 + 512 <= oBeta && oT + 64 * kLdL * 4 <= oV && oY2 + 4096 <= oA + 16384, "aliases must fit");
 constexpr uint32_t kCols = 256;             // pair accumulator 0..63, W^T 64..127, U^T 128..191
 }  // namespace intratc
 
@@ -68,6 +70,16 @@ __device__ __forceinline__ uint2 scale4(uint2 r, const float (&f)[4]) {
   float x[4];
   unpack4(r, x);
   return make_uint2(pack_bf16(x[0] * f[0], x[1] * f[1]), pack_bf16(x[2] * f[2], x[3] * f[3]));
+}
+
+// Acquire load / release add at device scope: the hand-over of the preconditioner state between items.
+__device__ __forceinline__ int ld_acquire(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_add(int* p, int v) {
+  asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
 template <bool kRecompute>
@@ -91,6 +103,10 @@ pkda_intra_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_
   float* sTot = reinterpret_cast<float*>(tiles + oTot);
   float* sEnd = reinterpret_cast<float*>(tiles + oEnd);
   float* sDec = reinterpret_cast<float*>(tiles + oDec);
+  float* sSum = reinterpret_cast<float*>(tiles + oSum);
+  float* sA0 = reinterpret_cast<float*>(tiles + oA0);
+  const bool chain = !kRecompute && p.chain;
+  const int units = p.geo.n_seqs * H;  // (chained mode: items are drawn level by level over all units)
 
   // strip layout: this thread's rows r0..r0+7, channels c4..c4+3
   const int r0 = warp * 8, c4 = lane << 2;
@@ -128,9 +144,12 @@ pkda_intra_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_
   __shared__ int s_next;
   if (tid == 0) s_next = atomicAdd(p.counts, 1);
   __syncthreads();
-  int item = s_next;
+  int draw = s_next;
 #pragma unroll 1
-  while (item < n_items) {
+  while (draw < n_items) {
+  // the draw-th item: in chained mode chunk level draw / units of unit draw % units (a dense batch)
+  const int level = chain ? draw / units : 0;
+  const int item = chain ? ((draw % units) / H * p.geo.chunks_per_seq + level) * H + (draw % units) % H : draw;
   const int h = item % H;
   int n, tok0, valid;
   if (!chunk_lookup(p.geo, item / H, n, tok0, valid)) break;  // past the last real chunk of a packed batch (items ascend)
@@ -169,7 +188,12 @@ pkda_intra_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_
   float sc_beta = 0.f, sc_pd = 0.f, sc_bp = 0.f;  // lane i < 8: scalars of row r0 + i
   if (lane < 8) {
     const int r = r0 + lane;
-    sc_beta = p.beta_c[chh * kChunk + r];
+    if (chain) {  // beta is packed chunk-major on the way (the later stages read that copy)
+      sc_beta = r < valid ? to_f(p.beta[(size_t)(tok0 + r) * H + h]) : 0.f;
+      p.beta_c_w[chh * kChunk + r] = sc_beta;
+    } else {
+      sc_beta = p.beta_c[chh * kChunk + r];
+    }
     if (!kRecompute && r < valid) {
       const size_t s = (size_t)(tok0 + r) * H + h;
       sc_pd = p.g_atk[s];
@@ -180,8 +204,22 @@ pkda_intra_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_
   const float ea2 = __expf(p.A_log[h]) * kLog2e;
   float4 a_first = make_float4(0.f, 0.f, 0.f, 0.f);
   float centre = 0.f;
+  // Chained mode: the chunk-entry state of the preconditioner was normally published long ago by the
+  // item of the chunk before; it is asked for now, so that the two dependent loads (counter, then
+  // value) are back when the strips are.
+  int chain_seen = 4;
+  float chain_a0 = 0.f;
   if (!kRecompute) {
-    a_first = *reinterpret_cast<const float4*>(p.a_start + chh * kD + c4);
+    if (!chain) {
+      a_first = *reinterpret_cast<const float4*>(p.a_start + chh * kD + c4);
+    } else if (tid < kD) {
+      if (level == 0) {
+        if (p.A0) chain_a0 = p.A0[((size_t)n * H + h) * kD + tid];
+      } else {
+        chain_seen = ld_acquire(p.chain_flags + item);
+        if (chain_seen >= 4) chain_a0 = __ldcg(p.a_chain + chh * kD + tid);
+      }
+    }
     centre = p.log_atk_scale[h];
   }
   cp_async_wait<0>();
@@ -202,6 +240,12 @@ pkda_intra_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_
     }
   }
   if (!kRecompute) {
+    if (chain) {  // the strip's summed log-decay, added in row order
+      float gsum = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) gsum += __shfl_sync(0xffffffffu, sc_pd, i);
+      if (lane == 0) sSum[warp] = gsum;
+    }
     sc_pd = __expf(sc_pd);  // rows past the end: exp(0) = 1, beta 0
     float a[4] = {0.f, 0.f, 0.f, 0.f}, dblk = 1.f;
 #pragma unroll
@@ -240,6 +284,37 @@ pkda_intra_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_
 #pragma unroll
       for (int e = 0; e < 4; ++e) G[i][e] += pre[e];
   }
+  // Chained mode: this chunk's entry state of the preconditioner comes from the item of the chunk
+  // before it (or the initial state), the next chunk's goes out.  Four warps, one channel per thread;
+  // a warp publishes with a fence and one count on the successor's flag, which the successor's four
+  // warps poll (bounded) until all four counts are in.
+  if (chain && tid < kD) {
+    float loc = 0.f, gs = 0.f;
+#pragma unroll
+    for (int b = 0; b < 8; ++b) {
+      loc = sDec[b] * loc + sEnd[b * kD + tid];
+      gs += sSum[b];
+    }
+    float a0 = chain_a0;
+    if (level == 0) {
+      p.a_chain[chh * kD + tid] = a0;
+    } else if (chain_seen < 4) {  // not there yet when the item began: poll (bounded)
+      uint32_t it = 0;
+      while ((chain_seen = ld_acquire(p.chain_flags + item)) < 4 && ++it < tc::kSpinLimit) {}
+      ok = ok && chain_seen >= 4;
+      a0 = __ldcg(p.a_chain + chh * kD + tid);
+    }
+    sA0[tid] = a0;
+    const float an = __expf(gs) * a0 + loc;
+    if (level + 1 < p.geo.chunks_per_seq) {
+      p.a_chain[(chh + H) * kD + tid] = an;
+      __syncwarp();
+      if (lane == 0) red_release_add(p.chain_flags + item + H, 1);  // (orders the warp's stores before the count)
+    } else if (p.AT) {
+      p.AT[((size_t)n * H + h) * kD + tid] = an;
+    }
+    if (tid == 0) p.sa[chh] = gs;
+  }
   // A chunk that decays too much for one direct block goes to the mma.sync kernel (the decision is
   // the same for all threads: every thread holds the totals of its four channels, the CTA all 128).
   {
@@ -250,7 +325,7 @@ pkda_intra_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_
       tma_phase ^= 1;
       if (tid == 0) s_next = atomicAdd(p.counts, 1);
       __syncthreads();
-      item = s_next;
+      draw = s_next;
       continue;
     }
   }
@@ -261,6 +336,7 @@ pkda_intra_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_
   // 64..127), kt 2^-G (into the slots g has left); qg goes to global memory.  The decay to the chunk
   // end is 2^G_last times the 2^-G the operand needs anyway.  Nothing of the strip is needed afterwards.
   {
+    if (chain) a_first = *reinterpret_cast<const float4*>(sA0 + c4);  // (written before the barrier of the decision)
     float A[4] = {a_first.x, a_first.y, a_first.z, a_first.w};
     if (!kRecompute) {
       for (int b = 0; b < warp; ++b) {
@@ -460,7 +536,7 @@ pkda_intra_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_
     s_next = atomicAdd(p.counts, 1);
   }
   __syncthreads();  // the next item's copies overwrite the tiles
-  item = s_next;
+  draw = s_next;
   }  // item loop
   if (__syncthreads_or(!ok) && tid == 0) atomicExch(p.status, 1);
   tc::tc_fence_before();

@@ -469,6 +469,10 @@ struct IntraBwdParams {
 
 // tcgen05 / tensor-memory chunk-parallel backward stage (pkda_intra_bwd_tc.cu).
 int launch_intra_bwd_tc(const IntraBwdParams& ip, cudaStream_t st);
+// The backward's first kernel on the default path: sorts the items into the two work lists (counts zeroed
+// before) and packs beta chunk-major.
+int launch_bwd_classify(const Geo& geo, const float* gc, int direct_cap, int* fast_list, int* slow_list, int* counts,
+                        const bf16* beta, float* beta_c, cudaStream_t st);
 
 // tcgen05 / TMA output stage (pkda_out_tc.cu).
 int launch_out_fwd_tc(const Geo& geo, int total_tokens, const bf16* qg, const bf16* h, const bf16* Aqk,

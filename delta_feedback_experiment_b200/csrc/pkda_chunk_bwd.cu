@@ -1247,7 +1247,9 @@ int chunk_bwd(const pkda_chunk_bwd_args* a, cudaStream_t st) {
   if (!a->workspace || a->workspace_bytes < chunk_bwd_workspace(p)) return PKDA_ERR_WORKSPACE;
   BwdWorkspace ws = carve_bwd(p, a->workspace);
   Geo geo;
-  rc = run_prologue(p, ws.chunk_offsets, ws.beta_c, &geo, st);
+  // On the default path the classifier of the intra stage runs first and packs beta on the way.
+  const bool tc_intra = stage_variant(kStageIntraBwd) == 0;
+  rc = run_prologue(p, ws.chunk_offsets, tc_intra ? nullptr : ws.beta_c, &geo, st);
   if (rc != PKDA_OK) return rc;
 
   const bf16* Aqk = static_cast<const bf16*>(a->Aqk);
@@ -1260,6 +1262,11 @@ int chunk_bwd(const pkda_chunk_bwd_args* a, cudaStream_t st) {
   bf16* h = static_cast<bf16*>(a->h);
   bf16* qg = static_cast<bf16*>(a->qg);
   if (cudaMemsetAsync(ws.status, 0, 16 * sizeof(int), st) != cudaSuccess) return PKDA_ERR_LAUNCH;
+  if (tc_intra) {
+    rc = launch_bwd_classify(geo, gc, direct_block_cap(), ws.fast_list, ws.slow_list, ws.counts,
+                             static_cast<const bf16*>(p.beta), ws.beta_c, st);
+    if (rc != PKDA_OK) return rc;
+  }
   if (a->recompute) {
     // The recompute kernels only read the products, write keys and decay totals.
     rc = run_forward_stages(p, geo, ws.beta_c, ws.u, const_cast<bf16*>(Aqk), const_cast<bf16*>(Akk),
@@ -1330,7 +1337,7 @@ int chunk_bwd(const pkda_chunk_bwd_args* a, cudaStream_t st) {
   ip.fast_list = ip.slow_list = ip.fast_count = nullptr;
   int sms = 148, dev = 0;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  if (stage_variant(kStageIntraBwd) == 0) {
+  if (tc_intra) {
     ip.fast_list = ws.fast_list; ip.slow_list = ws.slow_list; ip.fast_count = ws.counts;
     rc = launch_intra_bwd_tc(ip, st);
     if (rc != PKDA_OK) return rc;

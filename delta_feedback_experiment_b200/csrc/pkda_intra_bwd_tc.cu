@@ -114,8 +114,10 @@ struct IntraBwdTcMaps {
 
 // Sorts the (chunk, head) items of a backward call into the two work lists.  One warp per item
 // reads the chunk's decay totals (128 floats); a CTA appends its items with one atomic per list.
+// It is the backward's first kernel and also packs beta chunk-major.
 __global__ void __launch_bounds__(256)
-pkda_bwd_classify_kernel(Geo geo, const float* gc, int direct_cap, int* fast_list, int* slow_list, int* counts) {
+pkda_bwd_classify_kernel(Geo geo, const float* gc, int direct_cap, int* fast_list, int* slow_list, int* counts,
+                         const bf16* beta, float* beta_c) {
   __shared__ int sKind[64];
   __shared__ int sBase[2];
   const int H = geo.heads, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -132,6 +134,10 @@ pkda_bwd_classify_kernel(Geo geo, const float* gc, int direct_cap, int* fast_lis
         for (int o = 16; o >= 1; o >>= 1) m = fminf(m, __shfl_xor_sync(0xffffffffu, m, o));
         const bool fast = valid == kChunk && direct_cap >= 64 && m > 0.f && -__log2f(m) <= kDirectLimit;
         kind = fast ? 0 : 1;
+        // the chunk-major fp32 copy of beta that every later stage reads (saves the packing launch)
+        const int h = chh % H;
+        for (int r = lane; r < kChunk; r += 32)
+          beta_c[(size_t)chh * kChunk + r] = r < valid ? to_f(beta[(size_t)(tok0 + r) * H + h]) : 0.f;
       }
     }
     if (lane == 0) sKind[local] = kind;
@@ -628,6 +634,16 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
 }
 
 // ------------------------------------------------------------------ host side
+int launch_bwd_classify(const Geo& geo, const float* gc, int direct_cap, int* fast_list, int* slow_list, int* counts,
+                        const bf16* beta, float* beta_c, cudaStream_t st) {
+  const int items = geo.total_chunks * geo.heads;
+  begin_stage(kStageBwdClassify, st);
+  pkda_bwd_classify_kernel<<<(items + 63) / 64, 256, 0, st>>>(geo, gc, direct_cap, fast_list, slow_list, counts, beta,
+                                                             beta_c);
+  end_stage(st);
+  return cudaGetLastError() == cudaSuccess ? PKDA_OK : PKDA_ERR_LAUNCH;
+}
+
 int launch_intra_bwd_tc(const IntraBwdParams& ip, cudaStream_t st) {
   const uint64_t H = ip.geo.heads, tok = ip.geo.total_tokens, rows = (uint64_t)ip.geo.total_chunks * H * kD;
   IntraBwdTcMaps maps;
@@ -654,11 +670,6 @@ int launch_intra_bwd_tc(const IntraBwdParams& ip, cudaStream_t st) {
   if (!ensure_dynamic_smem(pkda_intra_bwd_tc_kernel, ibtc::kSmem))
     return PKDA_ERR_LAUNCH;
   const int items = ip.geo.total_chunks * ip.geo.heads;
-  begin_stage(kStageBwdClassify, st);
-  pkda_bwd_classify_kernel<<<(items + 63) / 64, 256, 0, st>>>(ip.geo, ip.gc, ip.direct_cap, ip.fast_list, ip.slow_list,
-                                                             ip.fast_count);
-  end_stage(st);
-  if (cudaGetLastError() != cudaSuccess) return PKDA_ERR_LAUNCH;
   begin_stage(kStageIntraBwd, st);
   int sms = 148, dev = 0;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);

@@ -732,7 +732,11 @@ static FwdWorkspace carve_fwd(const pkda_problem& p, void* base) {
 size_t chunk_fwd_workspace(const pkda_problem& p) { return carve_fwd(p, nullptr).bytes; }
 
 bool forward_chain_possible(const pkda_problem& p) {
-  return !p.cu_seqlens && stage_variant(kStageIntraFwd) == 0 && direct_block_cap() >= 64;
+  // With few (row, head) units the chains are few and long compared with the number of items in
+  // flight, and an item waits for many hand-overs: measured break-even near 32 units (the state it
+  // yields is the same bit for bit either way).
+  return !p.cu_seqlens && stage_variant(kStageIntraFwd) == 0 && direct_block_cap() >= 64 &&
+         (long)p.n_seqs * p.heads >= 32;
 }
 size_t chunk_fwd_status_offset(const pkda_problem& p) {
   return (size_t)(reinterpret_cast<unsigned char*>(carve_fwd(p, nullptr).status) - static_cast<unsigned char*>(nullptr));

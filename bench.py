@@ -742,7 +742,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
                 "steps": e2e_steps, "finite": e2e_finite, "copy_floor_ms": floor,
                 "call": f"host_pipeline.HostStep(slices={args.e2e_slices}): pinned host inputs -> forward+backward -> "
                         "pinned host outputs, copies overlapped with the kernels by row slice; the kernels of a "
-                        "slice replay from a CUDA graph on fixed device buffers"},
+                        "slice replay from two CUDA graphs (forward, backward) on fixed device buffers"},
         "gpu_launches": launches,
         "clocks": clocks.summary(),
         "stages_ms_per_step": {n: ms / args.steps for n, (ms, _) in stages.items()},

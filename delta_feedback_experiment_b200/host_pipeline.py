@@ -19,7 +19,10 @@ the bottleneck.  When the batch divides evenly into the slices, ``HostStep``
 therefore captures the forward+backward of one slice into a CUDA graph on fixed
 device buffers (three sets, used in turn, so that copy-in, kernels and copy-out of
 neighbouring slices overlap) and replays it per slice; the host then only enqueues
-the copies and one replay.
+the copies and the replays.  Forward and backward are two graphs: the forward does
+not need the output cotangent, so it starts while that tensor is still on its way in,
+and the output leaves for the host while the backward runs; this shortens the two ends
+of the pipeline, where nothing else overlaps.
 """
 
 from __future__ import annotations
@@ -82,8 +85,8 @@ class HostStep:
         return out
 
     # ------------------------------------------------------------------ graph mode
-    def _step(self, rows, params, with_state):
-        """Forward + backward of one slice on device tensors; returns (o, grads)."""
+    def _forward(self, rows, params, with_state):
+        """Forward of one slice on device tensors; returns (o, the tensors to differentiate)."""
         # (detached views: the fixed buffers themselves stay plain tensors the copies can write into)
         leaves = [rows[n].detach().requires_grad_(True) for n in ROW_INPUTS]
         heads = [params[n].detach().requires_grad_(True) for n in HEAD_PARAMS]
@@ -98,6 +101,11 @@ class HostStep:
         o, _, _ = chunk_precond_kda(**kw, initial_state=S0, initial_A_state=A0,
                                     output_final_state=False, log_atk_scale=centre,
                                     disable_recompute=not self.lean)
+        return o, wrt
+
+    def _step(self, rows, params, with_state):
+        """Forward + backward of one slice on device tensors; returns (o, grads)."""
+        o, wrt = self._forward(rows, params, with_state)
         grads = torch.autograd.grad(o, wrt, rows["do"])
         return o.detach(), [g.detach() for g in grads]
 
@@ -120,12 +128,16 @@ class HostStep:
                         rows[n].copy_(src[n][:rows_per], non_blocking=True)
                     self._step(rows, self._params, with_state)
             self.s_comp.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=self.s_comp):
-                o, grads = self._step(rows, self._params, with_state)
-            slots.append({"rows": rows, "graph": graph, "o": o, "grads": grads,
+            # two graphs on one private pool (they replay in capture order): forward, then backward
+            graph_f, graph_b = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph_f, stream=self.s_comp):
+                o_live, wrt = self._forward(rows, self._params, with_state)
+            with torch.cuda.graph(graph_b, pool=graph_f.pool(), stream=self.s_comp):
+                grads = [g.detach() for g in torch.autograd.grad(o_live, wrt, rows["do"])]
+            slots.append({"rows": rows, "graph_f": graph_f, "graph_b": graph_b, "o": o_live.detach(), "grads": grads,
                           "in_free": torch.cuda.Event(), "out_free": torch.cuda.Event(),
-                          "ready": torch.cuda.Event(), "done": torch.cuda.Event()})
+                          "ready_f": torch.cuda.Event(), "ready": torch.cuda.Event(),
+                          "done_f": torch.cuda.Event(), "done": torch.cuda.Event()})
         for sl in slots:  # nothing pending on a fresh slot
             sl["in_free"].record(self.s_comp)
             sl["out_free"].record(self.s_out)
@@ -172,18 +184,25 @@ class HostStep:
             with torch.cuda.stream(self.s_in):
                 self.s_in.wait_event(sl["in_free"])       # the replay that last read these inputs is over
                 m0 = mark(self.s_in)
-                for n in self._names:
-                    sl["rows"][n].copy_(src[n][b0:b1], non_blocking=True)
-                    self.h2d_bytes += nbytes(sl["rows"][n])
+                for n in self._names:  # the output cotangent last: only the backward waits for it
+                    if n != "do":
+                        sl["rows"][n].copy_(src[n][b0:b1], non_blocking=True)
+                        self.h2d_bytes += nbytes(sl["rows"][n])
+                sl["ready_f"].record(self.s_in)
+                sl["rows"]["do"].copy_(src["do"][b0:b1], non_blocking=True)
+                self.h2d_bytes += nbytes(sl["rows"]["do"])
                 sl["ready"].record(self.s_in)
                 m1 = mark(self.s_in)
             with torch.cuda.stream(self.s_comp):
                 if i == 0:
                     self.s_comp.wait_event(params_ready)
-                self.s_comp.wait_event(sl["ready"])
+                self.s_comp.wait_event(sl["ready_f"])
                 self.s_comp.wait_event(sl["out_free"])    # the copies that last read these outputs are over
                 m2 = mark(self.s_comp)
-                sl["graph"].replay()
+                sl["graph_f"].replay()
+                sl["done_f"].record(self.s_comp)
+                self.s_comp.wait_event(sl["ready"])
+                sl["graph_b"].replay()
                 head = sl["grads"][7:10]
                 if acc is None:
                     acc = [g.float().clone() for g in head]
@@ -194,10 +213,12 @@ class HostStep:
                 sl["done"].record(self.s_comp)
                 m3 = mark(self.s_comp)
             with torch.cuda.stream(self.s_out):
-                self.s_out.wait_event(sl["done"])
+                self.s_out.wait_event(sl["done_f"])       # the output goes home while the backward runs
                 m4 = mark(self.s_out)
-                pairs = [(out["o"][b0:b1], sl["o"])]
-                pairs += [(out["d" + n][b0:b1], g) for n, g in zip(ROW_INPUTS, sl["grads"][:7])]
+                out["o"][b0:b1].copy_(sl["o"], non_blocking=True)
+                self.d2h_bytes += nbytes(sl["o"])
+                self.s_out.wait_event(sl["done"])
+                pairs = [(out["d" + n][b0:b1], g) for n, g in zip(ROW_INPUTS, sl["grads"][:7])]
                 if with_state:
                     pairs += [(out["dinitial_state"][b0:b1], sl["grads"][10]),
                               (out["dinitial_A_state"][b0:b1], sl["grads"][11])]

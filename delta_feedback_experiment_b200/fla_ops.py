@@ -48,6 +48,23 @@ def _intermediate_meta(q: Tensor, v: Tensor, lean: bool):
     return ops.intermediate_meta(q, v, lean)
 
 
+def _check_intermediates(tensors, q: Tensor, v: Tensor, lean: bool) -> None:
+    """The list the forward hands back must be exactly what the fake implementation
+    promises to the compiler (count, and per entry shape, dtype, device, contiguity):
+    a mismatch would surface far away, as a stride or shape error inside a compiled
+    graph.  Same contract as the reference's check (``fla_ops.py:100-128``)."""
+    names = PKDA_INTERMEDIATES + (() if lean else PKDA_RETAINED)
+    promised = _intermediate_meta(q, v, lean)
+    if len(tensors) != len(promised):
+        raise RuntimeError(f"the PKDA forward produced {len(tensors)} intermediates where "
+                           f"{len(promised)} are promised")
+    for name, t, (shape, dtype) in zip(names, tensors, promised):
+        found = None if t is None else (tuple(t.shape), t.dtype, t.device, t.is_contiguous())
+        if found != (tuple(shape), dtype, q.device, True):
+            raise RuntimeError(f"PKDA intermediate {name}: forward produced {found}, the fake "
+                               f"implementation promises {(tuple(shape), dtype, q.device, True)}")
+
+
 def _chunk_capable(q: Tensor) -> bool:
     return q.dtype == torch.bfloat16 and q.shape[-1] == 128
 
@@ -66,7 +83,9 @@ def pkda_recurrence(
         o, _, _, saved = ops.chunk_forward(
             q, k, v, g, g_atk, beta_atk, beta, A_log, dt_bias, log_atk_scale,
             scale, squash_x, squash_eps)
-        return o, (saved[:6] if lean else saved)
+        saved = saved[:6] if lean else saved
+        _check_intermediates(saved, q, v, lean)
+        return o, saved
     # fp32 activations or another head width: exact token-by-token kernel.
     o, _, _ = ops.recurrent_forward(
         q, k, v, g, g_atk, beta_atk, beta, A_log, dt_bias, log_atk_scale,
@@ -75,6 +94,7 @@ def pkda_recurrence(
     # operator's output contract (names, shapes, dtypes), so it is left unwritten.
     saved = [torch.empty(shape, device=q.device, dtype=dt)
              for shape, dt in _intermediate_meta(q, v, lean)]
+    _check_intermediates(saved, q, v, lean)
     return o, saved
 
 

@@ -107,3 +107,29 @@ def test_arguments_on_different_devices_are_rejected_before_any_launch():
     with pytest.raises(RuntimeError, match="no CPU path"):
         guarded(_FakeTensor(None))
     assert not calls
+
+
+def test_intermediate_contract_check_names_the_offender():
+    """`fla_ops._check_intermediates` compares what a forward returns with what the fake
+    implementation promises (reference: fla_ops.py:100-128): count, shape, dtype, contiguity."""
+    import pytest
+    import torch
+    from delta_feedback_experiment_b200 import fla_ops
+
+    q = torch.empty(2, 130, 3, 128, dtype=torch.bfloat16)
+    v = torch.empty(2, 130, 3, 128, dtype=torch.bfloat16)
+    for lean in (True, False):
+        good = [torch.empty(s, dtype=d) for s, d in fla_ops._intermediate_meta(q, v, lean)]
+        fla_ops._check_intermediates(good, q, v, lean)                       # passes
+        with pytest.raises(RuntimeError, match="intermediates where"):
+            fla_ops._check_intermediates(good[:-1], q, v, lean)
+        bad = list(good)
+        bad[2] = bad[2].float()                                               # wrong dtype
+        with pytest.raises(RuntimeError, match="k_precond"):
+            fla_ops._check_intermediates(bad, q, v, lean)
+        bad = list(good)
+        bad[0] = good[0].transpose(1, 2).contiguous().transpose(1, 2)         # right shape, not contiguous
+        with pytest.raises(RuntimeError, match="Aqk"):
+            fla_ops._check_intermediates(bad, q, v, lean)
+    assert len(fla_ops._intermediate_meta(q, v, True)) == len(fla_ops.PKDA_INTERMEDIATES)
+    assert fla_ops._intermediate_meta(q, v, False)[9][0] == (2, 3, 3, 128, 128)   # h: three chunks of 64

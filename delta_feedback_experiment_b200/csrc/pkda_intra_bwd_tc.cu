@@ -490,56 +490,44 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
     float* pk = p.dk_read + out0;
     float* pkt = p.dkt + out0;
     float A = A_in, w = w_in;
+    float dbv[8];
 #pragma unroll
-    for (int hh = 0; hh < 2; ++hh) {
-      const uint32_t ta = tmem + lane_addr + j0 + 8 * hh;
-      float a[8], b[8], dkr[8], e8[8];
-      tc::tmem_ld8(ta + cQs, a);
-      tc::tmem_ld8(ta + cR, b);
+    for (int qq = 0; qq < 4; ++qq) {  // four tokens at a time: all seven accumulator pieces of a token in one pass
+      const uint32_t ta = tmem + lane_addr + j0 + 4 * qq;
+      float aQ[4], bR[4], aK[4], bS[4], m[4], bP[4], aT[4];
+      tc::tmem_ld4(ta + cQs, aQ);
+      tc::tmem_ld4(ta + cR, bR);
+      tc::tmem_ld4(ta + cKs, aK);
+      tc::tmem_ld4(ta + cStk, bS);
+      tc::tmem_ld4(ta + cKtM, m);
+      tc::tmem_ld4(ta + cKtP, bP);
+      tc::tmem_ld4(ta + cKts, aT);
       tc::tmem_ld_wait();
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const int t = 8 * hh + u;
-        const float tot = p.scale * a[u] + b[u];
-        const float xq = lds_bf16(sa[t & 7] + oQ + 128 * t);
-        e8[u] = ex2(G[t]);
-        *pq = __float2bfloat16(e8[u] * tot);
+      for (int u = 0; u < 4; ++u) {
+        const int t = 4 * qq + u;
+        const uint32_t a0 = sa[t & 7] + 128 * t;
+        const float e = ex2(G[t]);
+        const float totq = p.scale * aQ[u] + bR[u];
+        const float xq = lds_bf16(a0 + oQ);
+        *pq = __float2bfloat16(e * totq);
         pq += gld;
-        dGv[t] = xq * tot;
-      }
-      tc::tmem_ld8(ta + cKs, a);
-      tc::tmem_ld8(ta + cStk, b);
-      tc::tmem_ld_wait();
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const int t = 8 * hh + u;
-        const float tot = a[u] + b[u];
-        const float xk = lds_bf16(sa[t & 7] + oK + 128 * t);
-        dkr[u] = e8[u] * tot;
-        dGv[t] += xk * tot;
-      }
-      // write-key gradient; the part of dbeta that flows through M (rows of KtM against Y)
-      float m[8];
-      tc::tmem_ld8(ta + cKtM, m);
-      tc::tmem_ld8(ta + cKtP, b);
-      tc::tmem_ld8(ta + cKts, a);
-      tc::tmem_ld_wait();
-      float dbv[8];
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const int t = 8 * hh + u;
+        const float totk = aK[u] + bS[u];
+        const float xk = lds_bf16(a0 + oK);
+        const float dkr = e * totk;
+        // write-key gradient; the part of dbeta that flows through M (rows of KtM against Y)
         const float bj = sBeta[j0 + t];
-        const float y = lds_bf16(sa[t & 7] + oKt + 128 * t);
-        const float df = lds_bf16(sa[t & 7] + oDF + 128 * t);
-        const float ev = lds_bf16(sa[t & 7] + oE + 128 * t);
-        dbv[u] = df * ev + y * m[u] * sBinv[j0 + t];
-        const float st = gl * bj * a[u], pr = m[u] + b[u];
-        const float dkt = __fdividef(st + pr, e8[u]);
+        const float y = lds_bf16(a0 + oKt);
+        const float df = lds_bf16(a0 + oDF);
+        const float ev = lds_bf16(a0 + oE);
+        dbv[4 * (qq & 1) + u] = df * ev + y * m[u] * sBinv[j0 + t];
+        const float st = gl * bj * aT[u], pr = m[u] + bP[u];
+        const float dkt = __fdividef(st + pr, e);
         const float kd = y * st;
-        dGv[t] -= y * pr + kd;
+        dGv[t] = xq * totq + xk * totk - (y * pr + kd);
         kdsum += kd;
         // the preconditioner: A_t, the factor B(A_t) and its derivative (pkda_atk_bwd_kernel has the same math)
-        const float kc = lds_bf16(sa[t & 7] + oS0 + 128 * t);
+        const float kc = lds_bf16(a0 + oS0);
         const float pd = sPd[j0 + t];
         A = pd * A + sBp[j0 + t] * kc * kc;
         w *= pd;
@@ -550,14 +538,16 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
         const float dA = __fdividef(ddev, A + p.eps);
         *pkt = dA;
         pkt += gld;
-        *pk = dkr[u] + dkt * Bf;
+        *pk = dkr + dkt * Bf;
         pk += gld;
         dcen -= ddev;
         cloc += w * dA;
       }
-      row_sums8(dbv, lane);
-      if ((lane & 3) == 0)
-        sDb[q4 * kChunk + j0 + 8 * hh + ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1)] = dbv[0];
+      if (qq & 1) {
+        row_sums8(dbv, lane);
+        if ((lane & 3) == 0)
+          sDb[q4 * kChunk + j0 + 8 * (qq >> 1) + ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1)] = dbv[0];
+      }
     }
     float tot = 0.f;
 #pragma unroll

@@ -239,28 +239,29 @@ __device__ __forceinline__ void warp_gemm_lvl(float (&acc)[1][kNT][4], const bf1
 // blocks T11, T22 of size N and their coupling block L21, T21 = -T22 (L21 T11).
 // Loops run over full N (the blocks' upper triangles are zero) so they unroll.
 template <int N>
-__device__ __forceinline__ void inverse_merge(const float* sL, float* sT, float* sY2, int ld, int tid, int nthreads) {
+__device__ __forceinline__ void inverse_merge(const float* sL, float* sT, float* sY2, int ldl, int ldt, int tid,
+                                              int nthreads) {
   constexpr int SH = N == 4 ? 2 : (N == 8 ? 3 : (N == 16 ? 4 : 5));
   for (int o = tid; o < 32 * N; o += nthreads) {
     const int pr = o >> (2 * SH), r = (o >> SH) & (N - 1), c = o & (N - 1);
     const int base = pr * 2 * N;
-    const float* Lrow = sL + (base + N + r) * ld + base;
-    const float* Tcol = sT + base * ld + base + c;
+    const float* Lrow = sL + (base + N + r) * ldl + base;
+    const float* Tcol = sT + base * ldt + base + c;
     float s = 0.f;
 #pragma unroll
-    for (int m = 0; m < N; ++m) s += Lrow[m] * Tcol[m * ld];
+    for (int m = 0; m < N; ++m) s += Lrow[m] * Tcol[m * ldt];
     sY2[o] = s;
   }
   __syncthreads();
   for (int o = tid; o < 32 * N; o += nthreads) {
     const int pr = o >> (2 * SH), r = (o >> SH) & (N - 1), c = o & (N - 1);
     const int base = pr * 2 * N;
-    const float* Trow = sT + (base + N + r) * ld + base + N;
+    const float* Trow = sT + (base + N + r) * ldt + base + N;
     const float* Ycol = sY2 + (pr << (2 * SH)) + c;
     float t = 0.f;
 #pragma unroll
     for (int m = 0; m < N; ++m) t -= Trow[m] * Ycol[m << SH];
-    sT[(base + N + r) * ld + base + c] = t;
+    sT[(base + N + r) * ldt + base + c] = t;
   }
   __syncthreads();
 }
@@ -270,10 +271,15 @@ __device__ __forceinline__ void inverse_merge(const float* sL, float* sT, float*
 // part (three MMAs per step: lo*hi + hi*lo + hi*hi), which keeps fp32-level
 // accuracy (the dropped lo*lo term is 2^-22 relative).  One warp per 16 x 8
 // output tile; operands come straight from the fp32 arrays in shared memory.
+//
+// Rounding to TF32 (nearest, ties away from zero: what cvt.rna.tf32.f32 returns for
+// finite values and infinities) is an integer add and a mask on the bit pattern; both
+// run at full rate, the conversion instruction does not.
+__device__ __forceinline__ uint32_t tf32_rna(float x) { return (__float_as_uint(x) + 0x1000u) & 0xffffe000u; }
+
 __device__ __forceinline__ void tf32_split(float x, uint32_t& hi, uint32_t& lo) {
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(x));
-  const float rest = x - __uint_as_float(hi);
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(rest));
+  hi = tf32_rna(x);
+  lo = tf32_rna(x - __uint_as_float(hi));
 }
 
 __device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
@@ -283,13 +289,17 @@ __device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], 
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
-// d[16 x 8] += A[16 x K] B[K x 8],  A(r, m) = Ap[r * lda + m],  B(m, c) = Bp[m * ldb + c].
+// d[16 x 8] += A[16 x K] B[K x 8] over the k range [kbeg, kend) (multiples of 8),
+// A(r, m) = Ap[r * lda + m],  B(m, c) = Bp[m * ldb + c].  The fragment loads of A are
+// free of bank conflicts when lda = 4 (mod 8), those of B when ldb = 8 (mod 16); with an
+// odd stride (65) every one of them is a 4-way conflict, and the merge is bound by them.
 template <int K>
 __device__ __forceinline__ void tile_mma_3xtf32(float (&d)[4], const float* Ap, int lda, const float* Bp, int ldb,
-                                                int lane) {
+                                                int lane, int kbeg = 0, int kend = K) {
   const int g = lane >> 2, t = lane & 3;
 #pragma unroll
   for (int k0 = 0; k0 < K; k0 += 8) {
+    if (k0 < kbeg || k0 >= kend) continue;
     const float a[4] = {Ap[g * lda + k0 + t], Ap[(g + 8) * lda + k0 + t], Ap[g * lda + k0 + t + 4],
                         Ap[(g + 8) * lda + k0 + t + 4]};
     const float b[2] = {Bp[(k0 + t) * ldb + g], Bp[(k0 + t + 4) * ldb + g]};
@@ -304,38 +314,49 @@ __device__ __forceinline__ void tile_mma_3xtf32(float (&d)[4], const float* Ap, 
   }
 }
 
-template <int N>
-__device__ __forceinline__ void inverse_merge_tc(const float* sL, float* sT, float* sY2, int ld, int tid) {
+// kYPad widens the rows of the scratch Y to N + kYPad floats (8 makes the second
+// product's B loads conflict-free; the scratch then holds 2 * 16 * 24 or 32 * 40 floats).
+// kSkip leaves out the k-steps in which a triangular factor is all zero (the rows of
+// T11 above the output tile's columns, the columns of T22 right of the output tile's
+// rows): the sums lose only exact zeros.
+template <int N, int kYPad, bool kSkip>
+__device__ __forceinline__ void inverse_merge_tc(const float* sL, float* sT, float* sY2, int ldl, int ldt, int tid) {
   constexpr int kMT = N / 16, kNT = N / 8, kTiles = (32 / N) * kMT * kNT;  // N = 32: 8 tiles, N = 16: 4 tiles
+  constexpr int ldy = N + kYPad;
   const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int pr = warp / (kMT * kNT), mt = (warp / kNT) % kMT, nt = warp % kNT;
   const int base = pr * 2 * N;
   if (warp < kTiles) {  // Y = L21 T11
     float d[4] = {0.f, 0.f, 0.f, 0.f};
-    tile_mma_3xtf32<N>(d, sL + (base + N + 16 * mt) * ld + base, ld, sT + base * ld + base + 8 * nt, ld, lane);
-    float* y = sY2 + pr * N * N + (16 * mt + g) * N + 8 * nt + 2 * t;
+    tile_mma_3xtf32<N>(d, sL + (base + N + 16 * mt) * ldl + base, ldl, sT + base * ldt + base + 8 * nt, ldt, lane,
+                       kSkip ? 8 * nt : 0, N);
+    float* y = sY2 + pr * N * ldy + (16 * mt + g) * ldy + 8 * nt + 2 * t;
     *reinterpret_cast<float2*>(y) = make_float2(d[0], d[1]);
-    *reinterpret_cast<float2*>(y + 8 * N) = make_float2(d[2], d[3]);
+    *reinterpret_cast<float2*>(y + 8 * ldy) = make_float2(d[2], d[3]);
   }
   __syncthreads();
   if (warp < kTiles) {  // T21 = -T22 Y
     float d[4] = {0.f, 0.f, 0.f, 0.f};
-    tile_mma_3xtf32<N>(d, sT + (base + N + 16 * mt) * ld + base + N, ld, sY2 + pr * N * N + 8 * nt, N, lane);
-    float* o = sT + (base + N + 16 * mt + g) * ld + base + 8 * nt + 2 * t;
+    tile_mma_3xtf32<N>(d, sT + (base + N + 16 * mt) * ldt + base + N, ldt, sY2 + pr * N * ldy + 8 * nt, ldy, lane, 0,
+                       kSkip ? 16 * mt + 16 : N);
+    float* o = sT + (base + N + 16 * mt + g) * ldt + base + 8 * nt + 2 * t;
     o[0] = -d[0];
     o[1] = -d[1];
-    o[8 * ld] = -d[2];
-    o[8 * ld + 1] = -d[3];
+    o[8 * ldt] = -d[2];
+    o[8 * ldt + 1] = -d[3];
   }
   __syncthreads();
 }
 
-// T = (I + L)^-1 for a 64 x 64 strictly lower triangular L (fp32, row stride ld),
-// all nthreads threads of the CTA: 4 x 4 diagonal blocks by forward substitution,
-// then four doubling steps (the last two on the tensor cores; at least 256 threads).  sY2 is a 1024-float scratch.  Ends with a __syncthreads().
-__device__ __forceinline__ void unit_lower_inverse_64(const float* sL, float* sT, float* sY2, int ld, int tid,
+// T = (I + L)^-1 for a 64 x 64 strictly lower triangular L (fp32; row strides ldl of L
+// and ldt of T), all nthreads threads of the CTA (at least 256): 4 x 4 diagonal blocks by
+// forward substitution, then four doubling steps, the last two on the tensor cores.  sY2 is
+// a scratch of 1024 floats (kYPad = 0) or 1280 (kYPad = 8).  The result does not depend on
+// the strides or on kYPad.  Ends with a __syncthreads().
+template <int kYPad = 0>
+__device__ __forceinline__ void unit_lower_inverse_64(const float* sL, float* sT, float* sY2, int ldl, int ldt, int tid,
                                                       int nthreads) {
-  for (int i = tid; i < kChunk * kChunk; i += nthreads) sT[(i >> 6) * ld + (i & 63)] = 0.f;
+  for (int i = tid; i < kChunk * kChunk; i += nthreads) sT[(i >> 6) * ldt + (i & 63)] = 0.f;
   __syncthreads();
   if (tid < 64) {
     const int base = (tid >> 2) << 2, col = tid & 3;
@@ -344,17 +365,17 @@ __device__ __forceinline__ void unit_lower_inverse_64(const float* sL, float* sT
     for (int i = 0; i < 4; ++i) {
       float s = (i == col) ? 1.f : 0.f;
 #pragma unroll
-      for (int m = 0; m < i; ++m) s -= sL[(base + i) * ld + base + m] * x[m];
+      for (int m = 0; m < i; ++m) s -= sL[(base + i) * ldl + base + m] * x[m];
       x[i] = s;
     }
 #pragma unroll
-    for (int i = 0; i < 4; ++i) sT[(base + i) * ld + base + col] = x[i];
+    for (int i = 0; i < 4; ++i) sT[(base + i) * ldt + base + col] = x[i];
   }
   __syncthreads();
-  inverse_merge<4>(sL, sT, sY2, ld, tid, nthreads);
-  inverse_merge<8>(sL, sT, sY2, ld, tid, nthreads);
-  inverse_merge_tc<16>(sL, sT, sY2, ld, tid);
-  inverse_merge_tc<32>(sL, sT, sY2, ld, tid);
+  inverse_merge<4>(sL, sT, sY2, ldl, ldt, tid, nthreads);
+  inverse_merge<8>(sL, sT, sY2, ldl, ldt, tid, nthreads);
+  inverse_merge_tc<16, kYPad, true>(sL, sT, sY2, ldl, ldt, tid);
+  inverse_merge_tc<32, kYPad, true>(sL, sT, sY2, ldl, ldt, tid);
 }
 
 // Sums each of v[0..7] over the 32 lanes.  On return lane l holds in v[0] the

@@ -375,7 +375,7 @@ __device__ __forceinline__ void intra_fwd_item(const IntraParams& p, int bx, int
   }
 
   // ---- 5. T = (I + L)^-1 in fp32
-  unit_lower_inverse_64(sL, sT, sY2, kLdL, tid, kThreads);  // ends with a __syncthreads()
+  unit_lower_inverse_64(sL, sT, sY2, kLdL, kLdL, tid, kThreads);  // ends with a __syncthreads()
   for (int i = tid; i < kChunk * kChunk / 2; i += kThreads) {
     const int r = i >> 5, c2 = (i & 31) << 1;
     const uint32_t pk = pack_bf16(sT[r * kLdL + c2], sT[r * kLdL + c2 + 1]);

@@ -37,14 +37,14 @@ namespace pkda {
 
 namespace intratc {
 constexpr int kThreads = 256;
-constexpr int kLdL = 65;
+constexpr int kLdL = 68;                    // row stride of L and T: float4 rows, and conflict-free MMA fragments
 constexpr int oA = 0;                       // 2 blocks [128 rows][64 ch]: rows 0..63 k 2^G (= Kd, the MN-major A of
                                             // W^T), rows 64..127 q 2^G (together the K-major A of the pair products)
 constexpr int oY = oA + 32768;              // 2 blocks [64 rows][64 ch]: kt 2^-G (K-major B); + 1 KB so that T fits
 constexpr int oV = oY + 16384 + 1024;       // 2 blocks [64 tok][64 ch]: V (MN-major A of U^T)
 constexpr int oTm = oV + 16384;             // [64 i][64 j] bf16 T (K-major B)
 constexpr int oP = oTm + 8192;              // [64 i][64 j] bf16 scale * P
-constexpr int oL = oP + 8192;               // f32 [64][65] L; before the products: the scan exchange arrays
+constexpr int oL = oP + 8192;               // f32 [64][68] L; before the products: the scan exchange arrays
 constexpr int oBeta = oL + 64 * kLdL * 4;   // f32 [64]
 constexpr int oDiag = oBeta + 256;          // f32 [64] q_i . kt_i
 constexpr int oBar = oDiag + 256;           // TMA barrier, MMA barrier, tensor-memory base address
@@ -56,9 +56,9 @@ constexpr int oDec = oL + 8192;             // f32 [8] per-strip product of prec
 constexpr int oSum = oDec + 32;             // f32 [8] per-strip sum of the preconditioner's log-decays
 constexpr int oA0 = oSum + 32;              // f32 [128] the chunk-entry preconditioner state (chained mode)
 // while the inverse runs: T in the (dead) write-key operand, its scratch in the (dead) q rows of block 0
-constexpr int oT = oY;                      // f32 [64][65]
-constexpr int oY2 = oA + 8192;              // f32 [1024]
-static_assert(oA0 + 512 <= oBeta && oT + 64 * kLdL * 4 <= oV && oY2 + 4096 <= oA + 16384, "aliases must fit");
+constexpr int oT = oY;                      // f32 [64][68]
+constexpr int oY2 = oA + 8192;              // f32 [1280]
+static_assert(oA0 + 512 <= oBeta && oT + 64 * kLdL * 4 <= oV && oY2 + 5120 <= oA + 16384, "aliases must fit");
 constexpr uint32_t kCols = 256;             // pair accumulator 0..63, W^T 64..127, U^T 128..191
 }  // namespace intratc
 
@@ -418,7 +418,14 @@ pkda_intra_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_
       tc::tmem_ld_wait();
       if (!isP) {  // L = tril(M, -1) diag(beta)
 #pragma unroll
-        for (int t = 0; t < 32; ++t) sL[ei * kLdL + j0 + t] = (j0 + t < ei) ? acc[t] * sBeta[j0 + t] : 0.f;
+        for (int t = 0; t < 32; t += 4) {
+          float4 x;
+          x.x = (j0 + t < ei) ? acc[t] * sBeta[j0 + t] : 0.f;
+          x.y = (j0 + t + 1 < ei) ? acc[t + 1] * sBeta[j0 + t + 1] : 0.f;
+          x.z = (j0 + t + 2 < ei) ? acc[t + 2] * sBeta[j0 + t + 2] : 0.f;
+          x.w = (j0 + t + 3 < ei) ? acc[t + 3] * sBeta[j0 + t + 3] : 0.f;
+          *reinterpret_cast<float4*>(sL + ei * kLdL + j0 + t) = x;
+        }
       } else {     // scale * tril(P) with the ungated diagonal
         unsigned char* prow = tiles + oP + ei * 128;
         const float dv = sDiag[ei];
@@ -465,12 +472,13 @@ pkda_intra_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_
       }
     }
     float* sT = reinterpret_cast<float*>(tiles + oT);
-    unit_lower_inverse_64(sL, sT, reinterpret_cast<float*>(tiles + oY2), kLdL, tid, kThreads);  // ends with a barrier
+    unit_lower_inverse_64<8>(sL, sT, reinterpret_cast<float*>(tiles + oY2), kLdL, kLdL, tid, kThreads);  // ends with a barrier
     for (int idx = tid; idx < kChunk * 8; idx += kThreads) {
       const int r = idx >> 3, pc = idx & 7;
-      const float* src = sT + r * kLdL + 8 * pc;
-      const uint4 pk = make_uint4(pack_bf16(src[0], src[1]), pack_bf16(src[2], src[3]), pack_bf16(src[4], src[5]),
-                                  pack_bf16(src[6], src[7]));
+      const float4 s0 = *reinterpret_cast<const float4*>(sT + r * kLdL + 8 * pc);
+      const float4 s1 = *reinterpret_cast<const float4*>(sT + r * kLdL + 8 * pc + 4);
+      const uint4 pk = make_uint4(pack_bf16(s0.x, s0.y), pack_bf16(s0.z, s0.w), pack_bf16(s1.x, s1.y),
+                                  pack_bf16(s1.z, s1.w));
       *reinterpret_cast<uint4*>(tiles + oTm + r * 128 + ((pc ^ (r & 7)) << 4)) = pk;
       if (!full && r < valid)
         *reinterpret_cast<uint4*>(p.Akk + ((size_t)(tok0 + r) * H + h) * kChunk + 8 * pc) = pk;

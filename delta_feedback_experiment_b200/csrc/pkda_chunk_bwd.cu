@@ -824,11 +824,10 @@ constexpr int kRows = 8;  // rows per warp
 
 // Thread-private prefetch slots in dynamic shared memory (a thread only reads back
 // what it copied itself, so they need no barrier): per row k (8 B), dkt (16 B),
-// dk_read (16 B, final pass only), the row's log-decay (4 B); per tile the chunk's
-// entry state and incoming carry (16 B each).
+// dk_read (16 B); per tile the chunk's entry state and incoming carry (16 B each).
 namespace atkb {
 template <bool kFinal> __host__ __device__ constexpr int slot_bytes() {
-  return kRows * (8 + 16 + 16 + 4) + 16 + (kFinal ? 16 : 0);
+  return kRows * (8 + 16 + 16) + 16 + (kFinal ? 16 : 0);
 }
 template <bool kFinal> __host__ __device__ constexpr int smem_bytes() { return kThreads * slot_bytes<kFinal>(); }
 }  // namespace atkb
@@ -848,18 +847,17 @@ pkda_atk_bwd_kernel(const AtkBwdParams p, int n_tiles) {
   uint2* sK = reinterpret_cast<uint2*>(slots);
   float4* sDkt = reinterpret_cast<float4*>(slots + kThreads * kRows * 8);
   float4* sDkr = sDkt + kThreads * kRows;
-  float* sLg = reinterpret_cast<float*>(sDkr + kThreads * kRows);
-  float4* sA0 = reinterpret_cast<float4*>(sLg + kThreads * kRows);
+  float4* sA0 = sDkr + kThreads * kRows;
   float4* sLin = sA0 + kThreads;
 
   // A persistent CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...; a tile is one (chunk, head).
   // The next tile's data is requested before the current tile is computed.
   int tok0_n = 0, valid_n = 0;
   bool live_n = false;
-  // The next tile's beta_atk (lane i of a warp holds the bf16 bits of the warp's row i) and centre,
+  // The next tile's beta_atk and log-decay (lane i of a warp holds the values of the warp's row i) and centre,
   // by plain loads that nothing consumes before the next iteration.
   uint32_t bpraw_n = 0;
-  float centre_n = 0.f;
+  float centre_n = 0.f, lg_n = 0.f;  // lg_n: the same for the row's log-decay
   static_assert(kRows <= 32 && (kRows & (kRows - 1)) == 0, "one lane per row");
   if (!kFinal && p.tile_list) n_tiles = *p.tile_count;
   int tile_n = 0;  // the (chunk * heads + head) item behind the next position of the walk
@@ -880,19 +878,20 @@ pkda_atk_bwd_kernel(const AtkBwdParams p, int n_tiles) {
         const int r = r0 + i;
         const bool ok = r < valid_n;
         const size_t off = ok ? col0 + (size_t)r * gld : 0;
-        const size_t s = ok ? (size_t)(tok0_n + r) * H + hh : 0;
         // 8-byte copy as two 4-byte pieces (cp.async sizes are 4, 8 or 16)
         asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;\n" ::"r"(smem_u32(sK + i * kThreads + tid)),
                      "l"(p.k + off), "r"(ok ? 8 : 0));
         cp_async16(sDkt + i * kThreads + tid, p.dkt + off, ok);
         cp_async16(sDkr + i * kThreads + tid, p.dk_read + off, ok);
-        cp_async4(sLg + i * kThreads + tid, p.g_atk + s, ok);
       }
       {
         const int r = r0 + (lane & (kRows - 1));
         bpraw_n = 0;
-        if (r < valid_n)
+        lg_n = 0.f;  // rows past the end: decay 1
+        if (r < valid_n) {
           bpraw_n = *reinterpret_cast<const unsigned short*>(p.beta_atk + (size_t)(tok0_n + r) * H + hh);
+          lg_n = p.g_atk[(size_t)(tok0_n + r) * H + hh];
+        }
         centre_n = p.log_atk_scale[hh];
       }
       cp_async16(sA0 + tid, p.a_start + (size_t)tile * kD + c4, true);
@@ -919,7 +918,7 @@ pkda_atk_bwd_kernel(const AtkBwdParams p, int n_tiles) {
       dkt[i] = sDkt[i * kThreads + tid];
       dkr[i] = sDkr[i * kThreads + tid];
     }
-    pd[i] = sLg[i * kThreads + tid];  // the log-decay for now (zero fill past the end: decay 1)
+    pd[i] = __shfl_sync(0xffffffffu, lg_n, i);  // the log-decay for now
     bp[i] = __uint_as_float(__shfl_sync(0xffffffffu, bpraw_n, i) << 16);
   }
   const float4 a0 = sA0[tid];

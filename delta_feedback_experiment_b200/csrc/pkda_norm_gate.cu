@@ -23,10 +23,10 @@ constexpr int kVec = 8;
 constexpr int kStages = 4;
 constexpr int kUnits = 2;  // units (rows) per thread and stage
 template <typename T> __host__ __device__ constexpr int unit_bytes() { return kVec * (int)sizeof(T); }
-// ring: [stage][tensor][unit][thread] unit_bytes, then (backward) [stage][unit][thread] floats for rstd
+// ring: [stage][tensor][unit][thread] unit_bytes
 template <typename T> __host__ __device__ constexpr int fwd_smem() { return kStages * 2 * kUnits * kThreads * unit_bytes<T>(); }
 template <typename T> __host__ __device__ constexpr int bwd_smem() {
-  return kStages * 3 * kUnits * kThreads * unit_bytes<T>() + kStages * kUnits * kThreads * 4;
+  return kStages * 3 * kUnits * kThreads * unit_bytes<T>();
 }
 }  // namespace ng
 
@@ -155,7 +155,6 @@ pkda_norm_gate_bwd_kernel(const NormGateParams p) {
   using namespace ng;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   T* ring = reinterpret_cast<T*>(smem_raw);
-  float* ring_r = reinterpret_cast<float*>(smem_raw + (size_t)kStages * 3 * kUnits * kThreads * unit_bytes<T>());
   const int tid = threadIdx.x;
   const int lane_in_row = tid % p.lanes, slot = tid / p.lanes, slots = kThreads / p.lanes;
   const int c0 = lane_in_row * kVec;
@@ -183,15 +182,30 @@ pkda_norm_gate_bwd_kernel(const NormGateParams p) {
         copy_unit(slot_ptr(stage, 0, u), static_cast<const T*>(p.x) + off, ok);
         copy_unit(slot_ptr(stage, 1, u), static_cast<const T*>(p.gate) + off, ok);
         copy_unit(slot_ptr(stage, 2, u), static_cast<const T*>(p.dy) + off, ok);
-        cp_async4(ring_r + (stage * kUnits + u) * kThreads + tid, p.rstd + (ok ? r : 0), ok);
       }
     }
     cp_async_commit();
   };
+  // The rows' reciprocal deviations come by plain loads one iteration ahead (the lanes of a row read the
+  // same word: one broadcast transaction), not through the ring: a 4-byte asynchronous copy per thread
+  // costs as much of the shared-memory pipe as a 16-byte one.
+  float rs_next[kUnits];
+  auto load_rstd = [&](int it) {
+#pragma unroll
+    for (int u = 0; u < kUnits; ++u) {
+      const long long r = row_of(it, u);
+      rs_next[u] = (it < n_iter && r < p.rows) ? p.rstd[r] : 0.f;
+    }
+  };
 #pragma unroll
   for (int s = 0; s < kStages - 1; ++s) issue(s);
+  load_rstd(0);
   for (int it = 0; it < n_iter; ++it) {
     issue(it + kStages - 1);
+    float rs_cur[kUnits];
+#pragma unroll
+    for (int u = 0; u < kUnits; ++u) rs_cur[u] = rs_next[u];
+    load_rstd(it + 1);
     cp_async_wait<kStages - 1>();
     const int stage = it % kStages;
 #pragma unroll
@@ -201,7 +215,7 @@ pkda_norm_gate_bwd_kernel(const NormGateParams p) {
       Vec8<T>::load(slot_ptr(stage, 0, u), x);
       Vec8<T>::load(slot_ptr(stage, 1, u), g);
       Vec8<T>::load(slot_ptr(stage, 2, u), dy);
-      const float rs = ring_r[(stage * kUnits + u) * kThreads + tid];
+      const float rs = rs_cur[u];
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const float sg = Vec8<T>::sigmoid(g[j]);

@@ -143,11 +143,11 @@ constexpr int oSmall = oTmb + kChunk * kLdC * 2;  // beta[64] pd[64] bp[64] bias
 constexpr int kSmem = oSmall + (3 * kChunk + kD + 24) * 4;  // + per-warp block-decay maxima
 // aliases inside the staging area
 constexpr int oAt = oStage;                       // fp32 [64][kLdG] preconditioner states (before the levels)
-constexpr int kLdL = 65;
+constexpr int kLdL = 68;                          // = 4 (mod 8): the inverse's MMA fragments load without bank conflicts
 constexpr int oL = oStage;                        // after the levels: L, T, Y2
 constexpr int oT = oL + kChunk * kLdL * 4;
-constexpr int oY2 = oT + kChunk * kLdL * 4;       // fp32 [16][64]
-static_assert(oY2 + 16 * 64 * 4 <= oTmb, "inverse scratch must fit in the staging area");
+constexpr int oY2 = oT + kChunk * kLdL * 4;       // fp32 [1280]
+static_assert(oY2 + 1280 * 4 <= oTmb, "inverse scratch must fit in the staging area");
 static_assert(kChunk * kLdG * 4 <= 3 * kTileBytes, "A_t array must fit in the staging area");
 }  // namespace intra
 
@@ -375,7 +375,7 @@ __device__ __forceinline__ void intra_fwd_item(const IntraParams& p, int bx, int
   }
 
   // ---- 5. T = (I + L)^-1 in fp32
-  unit_lower_inverse_64(sL, sT, sY2, kLdL, kLdL, tid, kThreads);  // ends with a __syncthreads()
+  unit_lower_inverse_64<8>(sL, sT, sY2, kLdL, kLdL, tid, kThreads);  // ends with a __syncthreads()
   for (int i = tid; i < kChunk * kChunk / 2; i += kThreads) {
     const int r = i >> 5, c2 = (i & 31) << 1;
     const uint32_t pk = pack_bf16(sT[r * kLdL + c2], sT[r * kLdL + c2 + 1]);

@@ -72,8 +72,8 @@ STAGE_FLOPS = {
 # DRAM traffic per (token, head) of each kernel: dram__bytes_read.sum + dram__bytes_write.sum of one
 # ncu capture on the quarter-size workload (131,072 units), divided by its units; the traffic grows
 # in proportion to the units, so a launch of any size moves this many bytes per unit.
-STAGE_TRAFFIC_PER_UNIT = {"intra_fwd": 2158, "scan_fwd": 1245, "out_fwd": 1280, "scan_bwd": 1661,
-                          "intra_bwd": 4496}
+STAGE_TRAFFIC_PER_UNIT = {"intra_fwd": 2188, "scan_fwd": 1245, "out_fwd": 1280, "scan_bwd": 1655,
+                          "intra_bwd": 4506}
 # Bytes per (token, head) that each kernel must read and write by its own interface (its input and
 # output tensors, each touched once): the HBM view of the same kernels.
 STAGE_IO_BYTES = {
@@ -697,7 +697,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     step_kernel_ms = sum(ms for ms, _ in stages.values()) / args.steps
     if "out_fwd" not in stages:  # the state scan formed the output too: its products belong to that launch
         STAGE_FLOPS["scan_fwd"] += STAGE_FLOPS["out_fwd"]
-        STAGE_TRAFFIC_PER_UNIT["scan_fwd"] = 1898  # (ncu, same capture: 161.0 MB read + 87.8 MB written per 131,072 units)
+        STAGE_TRAFFIC_PER_UNIT["scan_fwd"] = 1894  # (ncu, same capture: 161.0 MB read + 87.2 MB written per 131,072 units)
         STAGE_IO_BYTES["scan_fwd"] += 256 + 128 + 256  # qg, Aqk -> o
     top = max((n for n in stages if n in STAGE_FLOPS), key=lambda n: stages[n][0])
     top_ms = per_launch[top]

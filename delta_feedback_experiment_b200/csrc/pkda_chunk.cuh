@@ -352,7 +352,8 @@ __device__ __forceinline__ void inverse_merge_tc(const float* sL, float* sT, flo
 // and ldt of T), all nthreads threads of the CTA (at least 256): 4 x 4 diagonal blocks by
 // forward substitution, then four doubling steps, the last two on the tensor cores.  sY2 is
 // a scratch of 1024 floats (kYPad = 0) or 1280 (kYPad = 8).  The result does not depend on
-// the strides or on kYPad.  Ends with a __syncthreads().
+// the strides or on kYPad.  L must be visible to every thread on entry (a barrier after its
+// last write); ends with a __syncthreads().
 template <int kYPad = 0>
 __device__ __forceinline__ void unit_lower_inverse_64(const float* sL, float* sT, float* sY2, int ldl, int ldt, int tid,
                                                       int nthreads) {

@@ -122,23 +122,41 @@ pkda_bwd_classify_kernel(Geo geo, const float* gc, int direct_cap, int* fast_lis
   __shared__ int sBase[2];
   const int H = geo.heads, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int items = geo.total_chunks * H;
+  // a warp's eight items: every load of all eight is issued before the first is used
+  float4 x[8];
+  float bv[8][2];
+  int tok0s[8], valids[8];
+  bool live[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const int chh = blockIdx.x * 64 + warp * 8 + k;
+    int n;
+    live[k] = chh < items && chunk_lookup(geo, chh / H, n, tok0s[k], valids[k]);
+    x[k] = make_float4(1.f, 1.f, 1.f, 1.f);
+    bv[k][0] = bv[k][1] = 0.f;
+    if (live[k]) {
+      x[k] = *reinterpret_cast<const float4*>(gc + (size_t)chh * kD + 4 * lane);
+      const int h = chh % H;
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int r = lane + 32 * j;
+        if (r < valids[k]) bv[k][j] = to_f(beta[(size_t)(tok0s[k] + r) * H + h]);
+      }
+    }
+  }
+#pragma unroll
   for (int k = 0; k < 8; ++k) {
     const int local = warp * 8 + k, chh = blockIdx.x * 64 + local;
     int kind = -1;  // -1: not an item, 0: tensor-memory kernel, 1: mma.sync kernel
-    if (chh < items) {
-      int n, tok0, valid;
-      if (chunk_lookup(geo, chh / H, n, tok0, valid)) {
-        const float4 x = *reinterpret_cast<const float4*>(gc + (size_t)chh * kD + 4 * lane);
-        float m = fminf(fminf(x.x, x.y), fminf(x.z, x.w));
+    if (live[k]) {
+      float m = fminf(fminf(x[k].x, x[k].y), fminf(x[k].z, x[k].w));
 #pragma unroll
-        for (int o = 16; o >= 1; o >>= 1) m = fminf(m, __shfl_xor_sync(0xffffffffu, m, o));
-        const bool fast = valid == kChunk && direct_cap >= 64 && m > 0.f && -__log2f(m) <= kDirectLimit;
-        kind = fast ? 0 : 1;
-        // the chunk-major fp32 copy of beta that every later stage reads (saves the packing launch)
-        const int h = chh % H;
-        for (int r = lane; r < kChunk; r += 32)
-          beta_c[(size_t)chh * kChunk + r] = r < valid ? to_f(beta[(size_t)(tok0 + r) * H + h]) : 0.f;
-      }
+      for (int o = 16; o >= 1; o >>= 1) m = fminf(m, __shfl_xor_sync(0xffffffffu, m, o));
+      const bool fast = valids[k] == kChunk && direct_cap >= 64 && m > 0.f && -__log2f(m) <= kDirectLimit;
+      kind = fast ? 0 : 1;
+      // the chunk-major fp32 copy of beta that every later stage reads (saves the packing launch)
+      beta_c[(size_t)chh * kChunk + lane] = bv[k][0];
+      beta_c[(size_t)chh * kChunk + lane + 32] = bv[k][1];
     }
     if (lane == 0) sKind[local] = kind;
   }

@@ -469,9 +469,6 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
     }
     tc::umma_commit(barM);
   }
-  ok = tc::mbar_wait(barM, m_phase) && ok;
-  m_phase ^= 1;
-  tc::tc_fence_after();
 
   // ---- 5a. preconditioner state at the start of this thread's token slice: zero-start scan of the slice,
   // one exchange, then the slices before it folded in (a slice's decay product is the same for all channels)
@@ -499,7 +496,12 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
     }
   }
 
-  // ---- 5b. gradients of this thread's channel and 16 tokens, eight tokens at a time (the accumulator
+  // the four pair products ran while the slice states were formed
+  ok = tc::mbar_wait(barM, m_phase) && ok;
+  m_phase ^= 1;
+  tc::tc_fence_after();
+
+  // ---- 5b. gradients of this thread's channel and 16 tokens, four tokens at a time (the accumulator
   // pieces stay small next to the per-token state)
   const size_t out0 = ((size_t)(tok0 + j0) * H + h) * kD + c;  // element (first token of the slice, h, c)
   float dGv[16], kdsum = 0.f, cloc = 0.f, dcen = 0.f;

@@ -57,8 +57,8 @@ constexpr int oG = oKt + 16384;         // [64][128 c] raw gate
 constexpr int oTm = oG + 16384;         // [64 j][64 i] T, then diag(beta) T           (MN-major B)
 constexpr int oDM = oTm + 8192;         // [64 i][64 j] dM                             (K-major / MN-major B)
 constexpr int oDP = oDM + 8192;         // [64 i][64 j] dP
-constexpr int oSmall = oDP + 8192;      // f32: beta[64] | x1[4][128] | x2[4][128] | red[32] | pd[64] | bp[64] | 1/beta[64]
-constexpr int oBar = oSmall + 256 + 2048 + 2048 + 128 + 512 + 256;  // barriers A, B, C, M, K and the tensor-memory address
+constexpr int oSmall = oDP + 8192;      // f32: beta[64] | x1[4][128] | x2[4][128] | red[32] | pd[64] | bp[64] | 1/beta[64] | slice decays[4]
+constexpr int oBar = oSmall + 256 + 2048 + 2048 + 128 + 512 + 256 + 64;  // barriers A, B, C, M, K and the tensor-memory address
 constexpr int kSmem = oBar + 64 + 1024;
 static_assert(kSmem <= 232448, "shared memory of one SM");
 // after the last product: exchange arrays in the (dead) pair-gradient tiles
@@ -193,6 +193,7 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
   float* sPd = sRed + 32;      // [64] preconditioner decay exp(g_atk) per token
   float* sBp = sPd + 64;       // [64] preconditioner gain beta_atk per token
   float* sBinv = sBp + 64;     // [64] 1 / beta (0 where beta is 0)
+  float* sDsl = sBinv + 64;    // [4] product of the preconditioner decays of each 16-token slice
   float* sX3 = reinterpret_cast<float*>(tiles + oX3);
   float* sX4 = reinterpret_cast<float*>(tiles + oX4);
   float* sX5 = reinterpret_cast<float*>(tiles + oX5);
@@ -313,6 +314,12 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
       tc::umma_bf16(tmem + cR, tc::desc_mnmajor(dbase + oDF + kk * 2048, 8192), tc::desc_mnmajor(dbase + oTm + kk * 2048, 8192),
                     idesc, kk > 0);
     tc::umma_commit(barM);
+  }
+  if (warp == 15 && lane < 4) {  // (multiplied in token order, once, instead of by every thread)
+    float d = 1.f;
+#pragma unroll
+    for (int t = 0; t < 16; ++t) d *= sPd[16 * lane + t];
+    sDsl[lane] = d;
   }
 
   // ---- 2. while that runs: the gate, its cumulative sum over the tokens, the operands gated in place
@@ -486,9 +493,7 @@ pkda_intra_bwd_tc_kernel(const IntraBwdParams p, const __grid_constant__ IntraBw
     A_in = a_start;
 #pragma unroll
     for (int s = 0; s < 3; ++s) {
-      float d = 1.f;
-#pragma unroll
-      for (int t = 0; t < 16; ++t) d *= sPd[16 * s + t];
+      const float d = sDsl[s];
       if (s < sl) {
         A_in = d * A_in + sX1[s * kD + c];
         w_in *= d;
